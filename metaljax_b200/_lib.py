@@ -1,0 +1,127 @@
+"""ctypes binding of libqmm.so: DLPack views in, status codes out.
+
+Every tensor crosses as a DLPack `DLTensor` (taken from the tensor's own `__dlpack__`
+capsule), which is the `qmm_tensor` of include/qmm.h. The library is looked up next to
+this file; it is never built implicitly and there is no fallback when it is missing.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libqmm.so")
+
+MODE = {"affine": 0, "mxfp4": 1}
+ROUTES = {0: "none", 1: "gemv", 2: "gemm_tc", 3: "simt"}
+ELEM = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2, torch.uint8: 3,
+        torch.uint32: 4, torch.int32: 5}
+
+
+class QmmError(RuntimeError):
+    """A non-zero status from libqmm (`.status` holds the qmm_status value)."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"libqmm status {status}: {message}")
+        self.status = status
+
+
+class Problem(ctypes.Structure):
+    """`qmm_problem` of include/qmm.h."""
+
+    _fields_ = [
+        ("struct_size", ctypes.c_uint32), ("mode", ctypes.c_int32), ("bits", ctypes.c_int32),
+        ("group_size", ctypes.c_int32), ("x_dtype", ctypes.c_int32),
+        ("table_dtype", ctypes.c_int32), ("y_dtype", ctypes.c_int32),
+        ("reserved0", ctypes.c_int32),
+        ("batch", ctypes.c_int64), ("M", ctypes.c_int64), ("K", ctypes.c_int64),
+        ("N", ctypes.c_int64),
+        ("x", ctypes.c_void_p), ("w", ctypes.c_void_p), ("scales", ctypes.c_void_p),
+        ("biases", ctypes.c_void_p), ("y", ctypes.c_void_p),
+        ("x_batch_stride", ctypes.c_int64), ("w_batch_stride", ctypes.c_int64),
+        ("y_batch_stride", ctypes.c_int64),
+        ("lhs_idx", ctypes.c_void_p), ("rhs_idx", ctypes.c_void_p),
+        ("group_sizes", ctypes.c_void_p),
+    ]
+
+
+_lib = None
+
+ctypes.pythonapi.PyCapsule_GetPointer.restype = ctypes.c_void_p
+ctypes.pythonapi.PyCapsule_GetPointer.argtypes = [ctypes.py_object, ctypes.c_char_p]
+
+_T = ctypes.c_void_p  # const qmm_tensor*
+_SIGNATURES = {
+    "qmm_version": (ctypes.c_int, []),
+    "qmm_last_error": (ctypes.c_char_p, []),
+    "qmm_launch_count": (ctypes.c_uint64, []),
+    "qmm_quantized_matmul": (ctypes.c_int, [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
+                                            ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "qmm_check_quantized_matmul": (ctypes.c_int, [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
+                                                  ctypes.c_int, ctypes.c_int]),
+    "qmm_gather_qmm": (ctypes.c_int, [_T, _T, _T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "qmm_ragged_dot": (ctypes.c_int, [_T, _T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_int, ctypes.c_void_p]),
+    "qmm_dequantize": (ctypes.c_int, [_T, _T, _T, _T, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_void_p]),
+    "qmm_pack_codes": (ctypes.c_int, [_T, _T, ctypes.c_int, ctypes.c_void_p]),
+    "qmm_launch": (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.c_void_p]),
+    "qmm_route": (ctypes.c_int, [ctypes.POINTER(Problem)]),
+}
+
+
+def exported_symbols() -> list[str]:
+    """Every entry point include/qmm.h declares (and this binding expects)."""
+    return sorted(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m metaljax_b200.build`. "
+                "There is no fallback path for the fused quantized matmul.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        if handle.qmm_version() != 1:
+            raise RuntimeError(f"libqmm ABI version {handle.qmm_version()} != 1")
+        _lib = handle
+    return _lib
+
+
+def check(status: int) -> None:
+    if status:
+        raise QmmError(status, lib().qmm_last_error().decode(errors="replace"))
+
+
+class Views:
+    """DLPack views of a call's tensors, kept alive until the call returns."""
+
+    def __init__(self):
+        self._caps = []
+
+    def __call__(self, t):
+        if t is None:
+            return None
+        cap = t.__dlpack__()
+        self._caps.append(cap)
+        # DLManagedTensor begins with its DLTensor, so the capsule pointer is the view.
+        return ctypes.pythonapi.PyCapsule_GetPointer(cap, b"dltensor")
+
+
+def stream_ptr(t) -> int:
+    """The current CUDA stream of `t`'s device (work is enqueued there, unsynchronized)."""
+    if t.is_cuda:
+        return torch.cuda.current_stream(t.device).cuda_stream
+    return 0
+
+
+def launch_count() -> int:
+    return int(lib().qmm_launch_count())

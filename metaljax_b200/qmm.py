@@ -1,0 +1,603 @@
+"""Host side of the fused quantized matmul, with the reference recognizer's interface.
+
+Mirrors `metaljax.qmm` of eterevsky/metaljax 0.11.3 for the part of it that sits on the
+hot path -- same names, argument meaning and error behaviour -- with torch tensors in
+place of MLX arrays and `libqmm.so` (CUDA, sm_100a) in place of `mx.quantized_matmul`:
+
+  pack primitives   pack_codes (src/metaljax/qmm.py:206-232), pack_exact / _scale_bias /
+                    _lossless (:235-286), mxfp4_codes (:300-332), mxfp4_scale_bytes
+                    (:335-357), _group_const / _group_heads / _pick_group /
+                    _pick_group_heads (:1204-1247), _regroup / _column_keys / _take_k
+                    (:390-464)
+  metadata          Match, _Pack, State (:588-699), STATS / stats / reset_stats (:176-187)
+  runtime           values / push / pop / pack_arrays (:2395-2421), emit_reads (:2424-2442),
+                    emit_bytes (:2445-2466), emit (:2469-2501)
+  the op itself     quantized_matmul / dequantize stand where the reference calls
+                    mx.quantized_matmul (:2491) and mx.dequantize (tests/test_qmm.py:121)
+
+The structural matcher (`analyze`) needs an MLIR front end and is outside this module.
+There is no literal-chain fallback: a pack that cannot be built raises `_Reject`, and the
+fused ops raise when libqmm or a CUDA device is missing.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+import weakref
+
+import numpy as np
+import torch
+
+from . import _lib
+
+QMM_ENABLED = os.environ.get("METALJAX_QMM", "1") != "0"
+ENABLED = QMM_ENABLED or os.environ.get("METALJAX_MOE", "1") != "0"
+_DEBUG = os.environ.get("METALJAX_DEBUG", "") == "1"
+
+_GROUP_SIZES = (128, 64, 32)
+_MAX_PACKS = int(os.environ.get("METALJAX_QMM_CACHE", "2"))
+_MAX_REPACKS = int(os.environ.get("METALJAX_QMM_REPACKS", "8"))
+_SCALE_WIDTH = os.environ.get("METALJAX_QMM_SCALES", "auto")
+_BATCH = os.environ.get("METALJAX_QMM_BATCH", "1") != "0"
+
+_E2M1_MAGS = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+_MXFP4_GROUP = 32
+
+STATS = {"recognized": 0, "packs": 0, "fallbacks": 0, "perms": 0, "mxfp4": 0,
+         "batched": 0, "shared": 0, "blocked": 0, "build_hits": 0, "build_declines": 0}
+
+_FLOATS = (torch.float32, torch.float16, torch.bfloat16)
+
+
+def stats() -> dict:
+    return dict(STATS)
+
+
+def reset_stats():
+    for k in STATS:
+        STATS[k] = 0
+
+
+class _Reject(Exception):
+    """A candidate cannot be represented (or trusted). The reference then runs the chain
+    literally; this build has no literal chain, so callers surface the rejection."""
+
+
+# --------------------------------------------------------------------------------------
+# packing
+# --------------------------------------------------------------------------------------
+
+
+def _as_u32(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.uint32 else t.view(torch.uint32)
+
+
+def pack_codes(codes: torch.Tensor, bits: int) -> torch.Tensor:
+    """Unsigned codes `[..., K]` -> uint32 words `[..., K*bits//32]`.
+
+    Each row is one little-endian bit stream, LSB first: element i occupies bits
+    [i*bits, (i+1)*bits). Codes are masked to `bits` so an out-of-range value cannot
+    spill into its neighbour. Device tensors are packed by libqmm's kernel; host tensors
+    by integer arithmetic here (the pack prologue may run before weights are moved).
+    """
+    if 32 % bits:
+        raise ValueError(f"pack_codes: bits={bits} does not divide 32")
+    per = 32 // bits
+    k = codes.shape[-1]
+    if k % per:
+        raise ValueError(f"pack_codes: K={k} not a multiple of {per}")
+    lead = list(codes.shape[:-1])
+    if codes.is_cuda and bits in (4, 8):
+        c8 = codes.contiguous() if codes.dtype == torch.uint8 else \
+            (codes.contiguous().to(torch.int64) & ((1 << bits) - 1)).to(torch.uint8)
+        out = torch.empty(lead + [k // per], dtype=torch.uint32, device=codes.device)
+        if out.numel():
+            v = _lib.Views()
+            _lib.check(_lib.lib().qmm_pack_codes(v(c8), v(out), bits, _lib.stream_ptr(out)))
+        return out
+    c = codes.contiguous().to(torch.int64).reshape(lead + [k // per, per]) & ((1 << bits) - 1)
+    shifts = torch.arange(per, dtype=torch.int64, device=codes.device) * bits
+    words = (c << shifts).sum(dim=-1)                       # < 2**32, exact in int64
+    words = torch.where(words >= (1 << 31), words - (1 << 32), words)
+    return words.to(torch.int32).view(torch.uint32)
+
+
+def _lossless(x: torch.Tensor, dtype) -> bool:
+    return bool(torch.all(x.to(dtype).to(torch.float32) == x).item())
+
+
+def _scale_bias(scales, zeros, offset, scale_dtype):
+    """`biases = -scale * (offset + zero)` in float32, narrowed to the source dtype only
+    when nothing is lost ("auto"), always ("source") or never ("f32")."""
+    s32 = scales.contiguous().to(torch.float32)
+    z32 = zeros.contiguous().to(torch.float32) if zeros is not None else 0.0
+    b32 = -(s32 * (z32 + float(offset)))
+    if scale_dtype is not None and scale_dtype != torch.float32 and _SCALE_WIDTH != "f32":
+        if _SCALE_WIDTH == "source" or (_lossless(s32, scale_dtype)
+                                        and _lossless(b32, scale_dtype)):
+            return s32.to(scale_dtype), b32.to(scale_dtype)
+    return s32, b32
+
+
+def pack_exact(codes, scales, zeros, bits: int, scale_dtype=None, offset=None):
+    """Repack `w = scale * (code - zero)` (signed codes `[N, K]`, per-group tables
+    `[N, K/group_size]`) into `(packed_u32, scales, biases)` for `quantized_matmul`:
+    `q_hat = code + offset` (unsigned, must fit `bits`), `biases = -scale*(offset+zero)`;
+    `offset` defaults to `2**(bits-1)`."""
+    off = (1 << (bits - 1)) if offset is None else int(offset)
+    packed = pack_codes(codes.contiguous().to(torch.int32) + off, bits)
+    s, b = _scale_bias(scales, zeros, off, scale_dtype)
+    return packed, s, b
+
+
+# --------------------------------------------------------------------------------------
+# MXFP4
+# --------------------------------------------------------------------------------------
+
+
+def _int_view(dtype):
+    return {torch.float32: (torch.int32, 32), torch.bfloat16: (torch.int16, 16),
+            torch.float16: (torch.int16, 16)}.get(dtype)
+
+
+def mxfp4_codes(values: torch.Tensor) -> torch.Tensor:
+    """4-bit MXFP4 codes (uint8) for values lying EXACTLY on the E2M1 grid; `_Reject`
+    otherwise. Bit patterns are compared, so -0.0 is code 8 and +0.0 is code 0."""
+    iv = _int_view(values.dtype)
+    if iv is None:
+        raise _Reject(f"MXFP4 values in {values.dtype}")
+    itype, width = iv
+    bits = values.contiguous().view(itype).to(torch.int64) & ((1 << width) - 1)
+    sign = bits >> (width - 1)
+    mag = bits & ((1 << (width - 1)) - 1)
+    grid = (torch.tensor(_E2M1_MAGS, dtype=values.dtype).view(itype).to(torch.int64)
+            & ((1 << width) - 1)).tolist()
+    if len(set(grid)) != len(_E2M1_MAGS):
+        raise _Reject(f"the E2M1 grid is not distinct in {values.dtype}")
+    codes = torch.zeros(mag.shape, dtype=torch.int64, device=values.device)
+    ok = torch.zeros(mag.shape, dtype=torch.bool, device=values.device)
+    for i, g in enumerate(grid):
+        hit = mag == g
+        codes = torch.where(hit, i, codes)
+        ok |= hit
+    if not bool(ok.all().item()):
+        raise _Reject("weight values are not on the MXFP4 (E2M1) grid")
+    return (codes | (sign << 3)).to(torch.uint8)
+
+
+def mxfp4_scale_bytes(scales: torch.Tensor) -> torch.Tensor:
+    """E8M0 bytes for scales that are exact positive normal powers of two: the byte is
+    the float32 exponent field; a set sign or mantissa bit, or field 0 / 255, rejects."""
+    bits = scales.to(torch.float32).contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    exp = (bits >> 23) & 0xFF
+    bad = ((bits & 0x807FFFFF) != 0) | (exp == 0) | (exp == 0xFF)
+    if bool(bad.any().item()):
+        raise _Reject("MXFP4 group scales are not exact positive powers of two")
+    return exp.to(torch.uint8)
+
+
+# --------------------------------------------------------------------------------------
+# group detection and regrouping of an interleaved contraction axis
+# --------------------------------------------------------------------------------------
+
+
+def _group_const(x: torch.Tensor, gs: int) -> bool:
+    k = x.shape[-1]
+    v = x.reshape(-1, k // gs, gs)
+    return bool(torch.all(v == v[:, :, :1]).item())
+
+
+def _group_heads(x: torch.Tensor, gs: int) -> torch.Tensor:
+    """The first element of each group: `[..., K] -> [..., K/gs]`."""
+    k = x.shape[-1]
+    return x.reshape(list(x.shape[:-1]) + [k // gs, gs])[..., 0].contiguous()
+
+
+def _pick_group_heads(k, scale_heads, zero_heads):
+    g0 = _GROUP_SIZES[-1]
+    for g in _GROUP_SIZES:
+        if g < g0 or k % g:
+            continue
+        r = g // g0
+        if r == 1 or (_group_const(scale_heads, r)
+                      and (zero_heads is None or _group_const(zero_heads, r))):
+            return g
+    return None
+
+
+def _pick_group(k, scale_map, zero_map):
+    """The largest legal group size (128, 64, 32) these full-size maps are constant in."""
+    g0 = _GROUP_SIZES[-1]
+    if k % g0 or not _group_const(scale_map, g0):
+        return None
+    if zero_map is not None and not _group_const(zero_map, g0):
+        return None
+    return _pick_group_heads(k, _group_heads(scale_map, g0),
+                             None if zero_map is None else _group_heads(zero_map, g0))
+
+
+_MIX = 2246822519
+
+
+def _mix(u: np.ndarray) -> np.ndarray:
+    u = (u * np.uint32(_MIX)).astype(np.uint32)
+    return u ^ (u >> np.uint32(15))
+
+
+def _bits_u32(x: torch.Tensor) -> np.ndarray:
+    if x.dtype in _FLOATS:
+        return x.to(torch.float32).cpu().numpy().view(np.uint32)
+    return x.to(torch.int64).cpu().numpy().astype(np.uint32)
+
+
+def _column_keys(x: torch.Tensor) -> np.ndarray:
+    """Per-column digest `[K, 2]` (uint32): equal columns digest equally; a collision can
+    only merge two groups, which the exact constancy check afterwards rejects."""
+    k = x.shape[-1]
+    u = _bits_u32(x.reshape(-1, k))
+    rows = np.arange(u.shape[0], dtype=np.uint32).reshape(-1, 1)
+    with np.errstate(over="ignore"):
+        r = _mix(rows * np.uint32(0x9E3779B9) + np.uint32(1))
+        v = _mix(u)
+        h1 = (v * (r | np.uint32(1))).sum(axis=0, dtype=np.uint32)
+        h2 = _mix(v ^ r).sum(axis=0, dtype=np.uint32)
+    return np.stack([h1, h2], axis=1)
+
+
+def _regroup(k: int, maps):
+    """A permutation of K that un-interleaves the quantization groups, or None when the
+    columns are already grouped or no legal group size divides every run."""
+    keys = np.concatenate([_column_keys(x) for x in maps if x is not None], axis=1)
+    _, first, inv = np.unique(keys, axis=0, return_index=True, return_inverse=True)
+    inv = np.asarray(inv).reshape(-1)
+    order = np.argsort(first)
+    rank = np.empty(len(order), np.int64)
+    rank[order] = np.arange(len(order))
+    ids = rank[inv]
+    g = 0
+    for length in np.bincount(ids):
+        g = math.gcd(g, int(length))
+    if not any(g and g % s == 0 for s in _GROUP_SIZES):
+        return None
+    perm = np.argsort(ids, kind="stable").astype(np.int32)
+    if np.array_equal(perm, np.arange(k, dtype=np.int32)):
+        return None
+    return perm
+
+
+def _take_k(x: torch.Tensor, perm) -> torch.Tensor:
+    idx = torch.as_tensor(np.asarray(perm), dtype=torch.int64, device=x.device)
+    return x.index_select(-1, idx).contiguous()
+
+
+# --------------------------------------------------------------------------------------
+# the fused op (the kernel boundary)
+# --------------------------------------------------------------------------------------
+
+
+def _mode_id(mode: str) -> int:
+    try:
+        return _lib.MODE[mode]
+    except KeyError:
+        raise ValueError(f"unknown quantization mode {mode!r}") from None
+
+
+def quantized_matmul(x, w, scales, biases=None, transpose=True, group_size=64, bits=4,
+                     mode="affine", out=None, out_dtype=None):
+    """`y[.., m, n] = sum_k x[.., m, k] * deq(w)[.., n, k]` on the GPU.
+
+    Argument meaning follows `mx.quantized_matmul` as the reference calls it
+    (src/metaljax/qmm.py:2491): `w` uint32 `[(B,) N, K*bits/32]`, `scales`/`biases`
+    `[(B,) N, K/group_size]` (`biases=None` and uint8 E8M0 scales for mode="mxfp4"),
+    float32 accumulation. The result has `x`'s dtype unless `out_dtype` / `out` says
+    otherwise (the reference casts to the dot's result type right after the call).
+    """
+    lead = list(x.shape[:-2])
+    m, k = x.shape[-2], x.shape[-1]
+    n = w.shape[-2]
+    if out is None:
+        out = torch.empty(lead + [m, n], dtype=out_dtype or x.dtype, device=x.device)
+    elif not out.is_contiguous() or list(out.shape) != lead + [m, n]:
+        raise ValueError("quantized_matmul: `out` must be contiguous [.., M, N]")
+    xc = x.contiguous()
+    if not lead:
+        x3, y3 = xc, out
+    elif w.dim() == 3:                       # one weight per batch
+        x3, y3 = xc.reshape(-1, m, k), out.reshape(-1, m, n)
+    else:                                    # shared weight: batches are more rows
+        x3, y3 = xc.reshape(-1, k), out.reshape(-1, n)
+    v = _lib.Views()
+    _lib.check(_lib.lib().qmm_quantized_matmul(
+        v(x3), v(_as_u32(w)), v(scales), v(biases), v(y3), 1 if transpose else 0,
+        int(group_size), int(bits), _mode_id(mode), _lib.stream_ptr(x)))
+    return out
+
+
+def dequantize(w, scales, biases=None, group_size=64, bits=4, mode="affine",
+               dtype=torch.float32):
+    """The dequantized weight `[.., N, K]` (stands where the reference's tests call
+    `mx.dequantize`, tests/test_qmm.py:121 and tests/test_qmm_mxfp4.py:192)."""
+    k = w.shape[-1] * 32 // bits
+    out = torch.empty(list(w.shape[:-1]) + [k], dtype=dtype, device=w.device)
+    v = _lib.Views()
+    _lib.check(_lib.lib().qmm_dequantize(v(_as_u32(w)), v(scales), v(biases), v(out),
+                                         int(group_size), int(bits), _mode_id(mode),
+                                         _lib.stream_ptr(w)))
+    return out
+
+
+def route(M, K, N, group_size=64, bits=4, mode="affine", x_dtype=torch.bfloat16,
+          table_dtype=None, y_dtype=None, batch=1, gather=False, ragged=False) -> str:
+    """Name of the kernel family libqmm picks for a problem of this shape (no device
+    work): "gemv", "gemm_tc", "simt" or "none"."""
+    p = _lib.Problem()
+    p.struct_size = _lib.ctypes.sizeof(_lib.Problem)
+    p.mode, p.bits, p.group_size = _mode_id(mode), bits, group_size
+    p.x_dtype = _lib.ELEM[x_dtype]
+    p.table_dtype = _lib.ELEM[table_dtype or (torch.uint8 if mode == "mxfp4" else x_dtype)]
+    p.y_dtype = _lib.ELEM[y_dtype or x_dtype]
+    p.batch, p.M, p.K, p.N = batch, M, K, N
+    p.w_batch_stride = N if (batch > 1 or gather or ragged) else 0
+    if gather:
+        p.lhs_idx = p.rhs_idx = 16
+    if ragged:
+        p.group_sizes = 16
+    r = _lib.lib().qmm_route(_lib.ctypes.byref(p))
+    if r < 0:
+        _lib.check(-r)
+    return _lib.ROUTES[r]
+
+
+# --------------------------------------------------------------------------------------
+# recognizer metadata
+# --------------------------------------------------------------------------------------
+
+
+class Match:
+    """One recognized quantized matmul (same slots as the reference's `Match`)."""
+
+    __slots__ = ("root", "key", "lhs", "codes", "zero", "scale", "recip", "post",
+                 "bcast_dims", "ops", "arg_indices", "required", "lperm", "rperm", "rshape",
+                 "bshape", "mshape", "nshape", "B", "M", "K", "N", "out_dtype", "disabled",
+                 "slot", "gs", "bits", "packs", "repacks", "name", "sub_range", "has_perm",
+                 "mode", "nvals", "swapped", "absorbed", "fp")
+
+    def __init__(self):
+        self.recip = False
+        self.fp = None
+        self.absorbed = False
+        self.mode = "affine"
+        self.zero = None
+        self.sub_range = None
+        self.post = []
+        self.bcast_dims = None
+        self.ops = {}
+        self.required = []
+        self.arg_indices = ()
+        self.disabled = False
+        self.slot = -1
+        self.nvals = 0
+        self.gs = 0
+        self.bits = 0
+        self.has_perm = False
+        self.packs = []
+        self.repacks = 0
+        self.name = "?"
+        self.bshape = []
+        self.mshape = []
+        self.nshape = []
+        self.lperm = None
+        self.B = 1
+        self.swapped = False
+
+
+class _Pack:
+    """The packed arrays of one weight, keyed by the identity of the buffers they were
+    built from (weak references: a pack never keeps its source alive)."""
+
+    __slots__ = ("refs", "w", "scales", "biases", "perm", "gs", "bits", "mode", "blocked")
+
+    def __init__(self, leaves, w, scales, biases, perm, gs, bits, mode="affine"):
+        self.refs = [weakref.ref(a) for a in leaves]
+        self.w, self.scales, self.biases = w, scales, biases
+        self.perm = perm
+        self.gs, self.bits = gs, bits
+        self.mode = mode
+        self.blocked = False
+
+    def arrays(self):
+        out = [self.w, self.scales]
+        if self.biases is not None:
+            out.append(self.biases)
+        if self.perm is not None:
+            out.append(self.perm)
+        return out
+
+    def matches(self, leaves) -> bool:
+        if len(leaves) != len(self.refs):
+            return False
+        return all(r() is a for r, a in zip(self.refs, leaves))
+
+
+class State:
+    """Per-program recognizer state: matches, the skip set, root dispatch and the flat
+    list of packed arrays `emit` reads by slot."""
+
+    __slots__ = ("matches", "skip", "roots", "values", "active", "moe")
+
+    def __init__(self):
+        self.matches = []
+        self.moe = []
+        self.skip = frozenset()
+        self.roots = {}
+        self.values = []
+        self.active = False
+
+    def rebuild(self):
+        live = [m for m in self.matches if not m.disabled]
+        self.roots = {m.key: m for m in live if not m.absorbed}
+        skip = set()
+        for m in live:
+            skip.update(m.ops)
+        for g in self.moe:
+            if g.disabled:
+                continue
+            self.roots[g.key] = g
+            skip.update(g.skip_keys)
+        self.skip = frozenset(skip)
+        self.active = bool(self.roots)
+
+
+def build_pack(m: Match, codes, scale_map, zero_map=None, leaves=()) -> _Pack:
+    """The value-level half of the reference's pack prologue for one match
+    (`_build_affine_pack`, src/metaljax/qmm.py:1773-1915; `_build_mxfp4_pack`,
+    :1723-1770) on already-materialized operands laid out `[.., N, K]`:
+
+    affine  integral codes -> 4 bits if their span is < 16, 8 if < 256; offset
+            `2**(bits-1)` unless the codes do not fit it, then `-lo`; scale / zero maps
+            constant within groups -> largest legal group; integer zero points;
+            interleaved groups -> a K permutation applied to codes, maps and (at run
+            time) activations.
+    mxfp4   (`m.mode == "mxfp4"`) values on the E2M1 grid, scales exact powers of two
+            constant within groups of 32.
+    Fills `m.gs / m.bits / m.has_perm`, appends the pack to `m.packs` (LRU of
+    `_MAX_PACKS`) and returns it. Raises `_Reject` when a check fails.
+    """
+    k = codes.shape[-1]
+    if m.mode == "mxfp4":
+        if k % _MXFP4_GROUP:
+            raise _Reject(f"K={k} is not a multiple of 32")
+        if not _group_const(scale_map, _MXFP4_GROUP):
+            raise _Reject("MXFP4 scales are not constant within groups of 32")
+        q = mxfp4_codes(codes)
+        sb = mxfp4_scale_bytes(_group_heads(scale_map, _MXFP4_GROUP))
+        pack = _Pack(leaves, pack_codes(q, 4), sb, None, None, _MXFP4_GROUP, 4, "mxfp4")
+        STATS["mxfp4"] += 1
+    else:
+        c = codes
+        if c.dtype in _FLOATS:
+            if not bool(torch.all(c == torch.round(c)).item()):
+                raise _Reject("codes are not integers")
+        c = c.to(torch.int64)
+        lo, hi = int(c.min().item()), int(c.max().item())
+        span = hi - lo + 1
+        bits = 4 if span <= 16 else (8 if span <= 256 else 0)
+        if not bits:
+            raise _Reject(f"codes span {span} values: more than 8 bits")
+        half = 1 << (bits - 1)
+        off = half if (lo >= -half and hi < half) else -lo
+        perm = None
+        gs = _pick_group(k, scale_map, zero_map)
+        if gs is None:
+            perm = _regroup(k, [scale_map, zero_map])
+            if perm is None:
+                raise _Reject("scale/zero maps are not constant within legal groups")
+            c, scale_map = _take_k(c, perm), _take_k(scale_map, perm)
+            zero_map = None if zero_map is None else _take_k(zero_map, perm)
+            gs = _pick_group(k, scale_map, zero_map)
+            if gs is None:
+                raise _Reject("regrouped maps are still not group-constant")
+            STATS["perms"] += 1
+        zh = None
+        if zero_map is not None:
+            zh = _group_heads(zero_map, gs).to(torch.float32)
+            if not bool(torch.all(zh == torch.round(zh)).item()):
+                raise _Reject("zero points are not integers")
+            if float(zh.abs().max().item()) > 32768:
+                raise _Reject("zero points out of range")
+            if m.sub_range is not None:
+                # the graph subtracts in integer arithmetic, which wraps; only fuse when
+                # nothing can wrap (src/metaljax/qmm.py:1889-1897)
+                zlo, zhi = int(zh.min().item()), int(zh.max().item())
+                if (lo - zhi) < m.sub_range[0] or (hi - zlo) > m.sub_range[1]:
+                    raise _Reject("integer zero-point subtraction can wrap")
+        sdt = scale_map.dtype if scale_map.dtype in _FLOATS else torch.float32
+        w, s, b = pack_exact(c, _group_heads(scale_map, gs), zh, bits, scale_dtype=sdt,
+                             offset=off)
+        pack = _Pack(leaves, w, s, b,
+                     None if perm is None else torch.as_tensor(perm, device=codes.device),
+                     gs, bits, "affine")
+    m.gs, m.bits, m.has_perm = pack.gs, pack.bits, pack.perm is not None
+    m.nvals = len(pack.arrays())
+    m.packs.insert(0, pack)
+    del m.packs[_MAX_PACKS:]
+    STATS["packs"] += 1
+    return pack
+
+
+# --------------------------------------------------------------------------------------
+# runtime
+# --------------------------------------------------------------------------------------
+
+
+def values(interp):
+    """Packed arrays for the current context."""
+    st = getattr(interp, "_qmm", None)
+    return st.values if st is not None else ()
+
+
+def push(interp, vals):
+    """Rebind the packed arrays (a traced function's own inputs in the reference; a
+    captured CUDA graph's static buffers here)."""
+    st = getattr(interp, "_qmm", None)
+    if st is None or not st.values:
+        return None
+    prev = st.values
+    st.values = list(vals)
+    return (prev,)
+
+
+def pop(interp, token):
+    if token is not None:
+        interp._qmm.values = token[0]
+
+
+def pack_arrays(interp, m):
+    st = interp._qmm
+    return st.values[m.slot:m.slot + m.nvals]
+
+
+def emit_reads(m):
+    """The `env` values `emit` reads: exactly the activation operand."""
+    if not isinstance(m, Match):
+        from . import moe as _moe
+        return _moe.emit_reads(m)
+    return (m.lhs,)
+
+
+def emit_bytes(m) -> int:
+    """Device bytes `emit` materializes beyond the root's result: one copy of the
+    activation at most (transpose / cast / group permutation)."""
+    if not isinstance(m, Match):
+        from . import moe as _moe
+        return _moe.emit_bytes(m)
+    esize = torch.empty((), dtype=m.out_dtype).element_size() if m.out_dtype else 2
+    return int(m.B * m.M * m.K * esize)
+
+
+def emit(interp, m, env):
+    """One fused `quantized_matmul` in place of the whole dequantize-and-dot."""
+    if not isinstance(m, Match):
+        from . import moe as _moe
+        return _moe.emit(interp, m, env)
+    st = interp._qmm
+    vals = st.values[m.slot:m.slot + m.nvals]
+    w, scales = vals[0], vals[1]
+    biases = vals[2] if m.mode == "affine" else None
+    x = env[m.lhs]
+    if m.lperm is not None and list(m.lperm) != list(range(x.dim())):
+        x = x.permute(*m.lperm)
+    x = x.reshape([m.B, m.M, m.K] if m.bshape else [m.M, m.K])
+    if x.dtype not in _FLOATS:
+        x = x.to(m.out_dtype)
+    if m.has_perm:
+        x = x.index_select(-1, vals[-1].to(torch.int64))
+    # The cast to the dot's result type happens in the kernel's epilogue.
+    y = quantized_matmul(x, w, scales, biases, transpose=True, group_size=m.gs,
+                         bits=m.bits, mode=m.mode, out_dtype=m.out_dtype)
+    if m.swapped:
+        y = y.transpose(-1, -2).reshape(list(m.bshape) + list(m.nshape) + list(m.mshape))
+    else:
+        y = y.reshape(list(m.bshape) + list(m.mshape) + list(m.nshape))
+    return [y]
