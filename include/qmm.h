@@ -207,6 +207,18 @@ int qmm_check_quantized_matmul(const qmm_tensor* x, const qmm_tensor* w,
                                const qmm_tensor* y, int transpose, int group_size, int bits,
                                int mode);
 
+/* Test hook: force every later launch of this process onto one kernel family
+ * (a qmm_route_id; QMM_ROUTE_NONE restores the automatic choice). A family that does
+ * not support the problem makes the call fail with QMM_ERR_UNSUPPORTED instead of
+ * silently taking another route. No counterpart in the reference. */
+int qmm_set_route_override(int route);
+
+/* Waits for the device and reports whether a kernel of this library gave up on a bounded
+ * device-side wait since the last poll: *status_out is 0, or the code of the wait that
+ * ran out (the call then returns QMM_ERR_TIMEOUT). Clears the word. No counterpart in the
+ * reference, whose MLX calls are synchronous from Python's point of view. */
+int qmm_poll_status(int* status_out);
+
 /* Number of kernels this library has launched on the calling process since load
  * (monotonic; used by benchmarks to report their launch count). */
 uint64_t qmm_launch_count(void);

@@ -58,6 +58,8 @@ _SIGNATURES = {
     "qmm_version": (ctypes.c_int, []),
     "qmm_last_error": (ctypes.c_char_p, []),
     "qmm_launch_count": (ctypes.c_uint64, []),
+    "qmm_poll_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "qmm_set_route_override": (ctypes.c_int, [ctypes.c_int]),
     "qmm_quantized_matmul": (ctypes.c_int, [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
                                             ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "qmm_check_quantized_matmul": (ctypes.c_int, [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
@@ -110,7 +112,9 @@ class Views:
     def __call__(self, t):
         if t is None:
             return None
-        cap = t.__dlpack__()
+        # stream=-1: the producer inserts no synchronization; libqmm enqueues on the
+        # caller's current stream, which is where the tensor's pending work already is.
+        cap = t.__dlpack__(stream=-1)
         self._caps.append(cap)
         # DLManagedTensor begins with its DLTensor, so the capsule pointer is the view.
         return ctypes.pythonapi.PyCapsule_GetPointer(cap, b"dltensor")
@@ -121,6 +125,29 @@ def stream_ptr(t) -> int:
     if t.is_cuda:
         return torch.cuda.current_stream(t.device).cuda_stream
     return 0
+
+
+class force_route:
+    """Context manager for tests: every launch inside goes to one kernel family
+    ("gemv", "gemm_tc", "simt") or fails with status 7 if that family declines it."""
+
+    def __init__(self, name: str):
+        self.route = {v: k for k, v in ROUTES.items()}[name]
+
+    def __enter__(self):
+        check(lib().qmm_set_route_override(self.route))
+        return self
+
+    def __exit__(self, *exc):
+        lib().qmm_set_route_override(0)
+        return False
+
+
+def poll_status() -> int:
+    """Synchronizes the device; raises QmmError(9) if a kernel gave up on a bounded wait."""
+    st = ctypes.c_int(0)
+    check(lib().qmm_poll_status(ctypes.byref(st)))
+    return int(st.value)
 
 
 def launch_count() -> int:

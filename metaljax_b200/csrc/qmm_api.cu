@@ -12,6 +12,7 @@ namespace qmm {
 namespace {
 thread_local char g_error[512] = "";
 std::atomic<uint64_t> g_launches{0};
+std::atomic<int> g_route_override{QMM_ROUTE_NONE};
 }  // namespace
 
 int fail(int code, const char* fmt, ...) {
@@ -175,6 +176,10 @@ int validate_problem(const qmm_problem& p, bool pointers) {
 
 int route_of(const qmm_problem& p) {
   if (p.batch == 0 || p.M == 0 || p.N == 0) return QMM_ROUTE_NONE;
+  const int forced = g_route_override.load(std::memory_order_relaxed);
+  if (forced == QMM_ROUTE_GEMV) return gemv_supports(p) ? forced : -QMM_ERR_UNSUPPORTED;
+  if (forced == QMM_ROUTE_GEMM_TC) return gemm_tc_supports(p) ? forced : -QMM_ERR_UNSUPPORTED;
+  if (forced == QMM_ROUTE_SIMT) return forced;
   if (gemv_supports(p)) return QMM_ROUTE_GEMV;
   if (gemm_tc_supports(p)) return QMM_ROUTE_GEMM_TC;
   return QMM_ROUTE_SIMT;
@@ -192,7 +197,9 @@ int launch_problem(const qmm_problem& p, cudaStream_t stream) {
     const int64_t rows = p.group_sizes ? p.M : p.batch * p.M;
     return zero_fill(p.y, rows * p.N * elem_size(p.y_dtype), stream);
   }
-  switch (route_of(p)) {
+  const int route = route_of(p);
+  if (route < 0) return fail(-route, "the forced kernel family does not support this problem");
+  switch (route) {
     case QMM_ROUTE_NONE: return QMM_OK;
     case QMM_ROUTE_GEMV: return launch_gemv(p, stream);
     case QMM_ROUTE_GEMM_TC: return launch_gemm_tc(p, stream);
@@ -264,6 +271,23 @@ int qmm_version(void) { return QMM_VERSION; }
 
 const char* qmm_last_error(void) { return g_error; }
 
+int qmm_set_route_override(int route) {
+  if (route < QMM_ROUTE_NONE || route > QMM_ROUTE_SIMT) return fail(QMM_ERR_UNSUPPORTED, "unknown route %d", route);
+  g_route_override.store(route, std::memory_order_relaxed);
+  return QMM_OK;
+}
+
+int qmm_poll_status(int* status_out) {
+  int st = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+  int rc = gemm_tc_status(&st);
+  if (rc) return rc;
+  if (status_out) *status_out = st;
+  if (st) return fail(QMM_ERR_TIMEOUT, "a device-side wait ran out (code %d)", st);
+  return QMM_OK;
+}
+
 uint64_t qmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int qmm_launch(const qmm_problem* problem, void* stream) {
@@ -277,7 +301,9 @@ int qmm_route(const qmm_problem* problem) {
   if (!problem) return -fail(QMM_ERR_NULL, "problem is NULL");
   int rc = validate_problem(*problem, false);
   if (rc) return -rc;
-  return route_of(*problem);
+  const int route = route_of(*problem);
+  if (route < 0) fail(-route, "the forced kernel family does not support this problem");
+  return route;
 }
 
 int qmm_check_quantized_matmul(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* scales,

@@ -1,5 +1,721 @@
+// Prefill kernel of the fused dequantize-and-matmul on the 5th-generation tensor cores.
+//
+//   y[t, f] = sum_k x[t, k] * deq(w)[f, k]          (transpose=True of the reference's call,
+//                                                    src/metaljax/qmm.py:2491)
+//
+// The WEIGHT is the MMA's A operand and lives in tensor memory: a tile is 128 output
+// features (= 128 TMEM lanes) x 64 K-elements, so one dequantizing thread owns one weight
+// row, reads its 32 packed bytes (64 for 8-bit) from shared memory, applies its own
+// per-group scale and bias in registers, and writes the bf16/f16 result straight to TMEM
+// with tcgen05.st -- the dequantized weight never exists in shared or global memory. The
+// ACTIVATIONS are the B operand: TMA brings [BT tokens x 64 K] tiles into shared memory in
+// the 128-byte-swizzled K-major layout tcgen05.mma reads. The accumulator D[feature, token]
+// (float32) sits in TMEM; the epilogue reads it back with tcgen05.ld, casts and stores
+// y[token, feature].
+//
+// Warp roles (10 warps): 0 = TMA producer, 1 = MMA issuer (+ TMEM allocation),
+// 2..9 = eight dequant/epilogue warps in two teams of four (one warp per TMEM lane
+// quarter); the teams take alternate K blocks.
+//
+// One persistent CTA per SM walks a list of tiles (segment, token tile, feature tile).
+// A segment is a run of x rows that meets one weight matrix: the whole of x for the plain
+// op, one batch of a batched weight, or one expert's rows of a ragged (grouped) product,
+// in which case the per-expert row offsets are prefix sums of `group_sizes` computed here.
+//
+// Every wait is bounded: when a barrier does not flip within ~2 s of SM clock the kernel
+// records the place in a status word, stops issuing work and drains.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <type_traits>
+
 #include "qmm_internal.h"
+
 namespace qmm {
-bool gemm_tc_supports(const qmm_problem&) { return false; }
-int launch_gemm_tc(const qmm_problem&, cudaStream_t) { return fail(QMM_ERR_UNSUPPORTED, "gemm_tc"); }
+namespace {
+
+constexpr int kBF = 128;        // features per tile (MMA M, TMEM lanes)
+constexpr int kBK = 64;         // K elements per pipeline stage
+constexpr int kAStages = 8;     // dequantized-A ring in TMEM (32 columns each)
+constexpr int kThreads = 320;   // 10 warps
+constexpr int kMaxSegments = 256;
+constexpr long long kSpinLimit = 4000000000LL;  // SM clocks (~2 s)
+
+enum { kAff4 = 0, kAff8 = 1, kMx4 = 2 };
+
+struct TcParams {
+  const void* scales;
+  const void* biases;
+  void* y;
+  const int32_t* group_sizes;  // ragged: [segments]; else NULL
+  int* status;                 // device status word (0 = ok)
+  int64_t M;                   // rows of x per segment (dense) or total rows (ragged)
+  int64_t K, N;
+  int64_t segments;            // weight matrices
+  int64_t w_seg_rows;          // rows of the packed weight between segments (N, or 0 = shared)
+  int group_size, table_dtype, y_dtype;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. Returns false (and records `where`) when the barrier never flips or another
+// role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int where) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++spins & 1023) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kSpinLimit) {
+        *abort_flag = where;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, void* dst, uint64_t* bar, int c0,
+                                            int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+// D[tmem_d] (+)= A[tmem_a] * B[desc_b]; A from tensor memory, B from shared memory.
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0;"
+      "  tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+#define QMM_R32(a, o) a[o + 0], a[o + 1], a[o + 2], a[o + 3], a[o + 4], a[o + 5], a[o + 6], a[o + 7]
+#define QMM_ASM_R(o) "r"(r[o]), "r"(r[o + 1]), "r"(r[o + 2]), "r"(r[o + 3]), "r"(r[o + 4]), "r"(r[o + 5]), "r"(r[o + 6]), "r"(r[o + 7])
+#define QMM_ASM_W(o) "=r"(r[o]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]), "=r"(r[o + 6]), "=r"(r[o + 7])
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp owns lane (base + i).
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      QMM_ASM_R(0), QMM_ASM_R(8), QMM_ASM_R(16), QMM_ASM_R(24)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : QMM_ASM_W(0), QMM_ASM_W(8), QMM_ASM_W(16), QMM_ASM_W(24)
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- dequantization of one weight row's K block into 32 packed 16-bit pairs ---------------
+
+template <typename XT>
+struct Half2Ops;
+
+template <>
+struct Half2Ops<__nv_bfloat16> {
+  static constexpr uint32_t kMagic = 0x43004300u;  // (128, 128): 7 mantissa bits hold the code
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+    __nv_bfloat162 r = __hfma2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b),
+                               *reinterpret_cast<__nv_bfloat162*>(&c));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+};
+
+template <>
+struct Half2Ops<__half> {
+  static constexpr uint32_t kMagic = 0x64006400u;  // (1024, 1024)
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+    __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+    __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b),
+                        *reinterpret_cast<__half2*>(&c));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+};
+
+__device__ __forceinline__ float table_f32(const void* p, int dtype, int64_t i) {
+  if (dtype == QMM_BF16) return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p) + i));
+  if (dtype == QMM_F16) return __half2float(__ldg(reinterpret_cast<const __half*>(p) + i));
+  return __ldg(reinterpret_cast<const float*>(p) + i);
+}
+
+// 4-bit affine, one 32-element half of the K block (4 words -> 16 pairs). A byte holds
+// elements (2i, 2i+1): PRMT takes it from the word (even element in its low nibble) into
+// byte 0 and from the word shifted right by four (odd element) into byte 2, one LOP3 keeps
+// the two nibbles under the magic exponent (128 + q, or 1024 + q for f16, both exact), an
+// exact subtraction removes the magic, and one FMA with (s, s), (b, b) rounds once.
+template <typename XT>
+__device__ __forceinline__ void dequant_aff4(const uint32_t (&w)[4], float s, float b, uint32_t* out) {
+  using H = Half2Ops<XT>;
+  const uint32_t s2 = H::pack(s, s);
+  const uint32_t b2 = H::pack(b, b);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t hi = w[j] >> 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t t = __byte_perm(w[j], hi, i | ((4 + i) << 8));
+      const uint32_t v = (t & 0x000F000Fu) | H::kMagic;
+      out[j * 4 + i] = H::fma(H::sub(v, H::kMagic), s2, b2);
+    }
+  }
+}
+
+// 8-bit affine, one 32-element half of the K block (8 words): float32 FMA per element,
+// rounded to the 16-bit type in pairs.
+template <typename XT>
+__device__ __forceinline__ void dequant_aff8(const uint32_t (&w)[8], float s, float b, uint32_t* out) {
+  using H = Half2Ops<XT>;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float q[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      q[e] = __uint_as_float(__byte_perm(w[j], 0x4B000000u, 0x7540u + e)) - 8388608.0f;
+    out[j * 2] = H::pack(fmaf(s, q[0], b), fmaf(s, q[1], b));
+    out[j * 2 + 1] = H::pack(fmaf(s, q[2], b), fmaf(s, q[3], b));
+  }
+}
+
+// MXFP4, one 32-element group (4 words -> 16 pairs). The three magnitude bits of a code,
+// placed at the 16-bit type's exponent/mantissa boundary, are the E2M1 value scaled by
+// 2^-126 (bf16) or 2^-14 (f16), including the subnormal code 1 = 0.5; two exact power-of-two
+// multiplies undo that and apply the group's E8M0 scale.
+template <typename XT>
+__device__ __forceinline__ void dequant_mx4(const uint32_t (&w)[4], uint32_t e8, uint32_t* out) {
+  using H = Half2Ops<XT>;
+  constexpr bool kBf = std::is_same<XT, __nv_bfloat16>::value;
+  constexpr int kShift = kBf ? 6 : 9;  // magnitude bit 0 -> top mantissa bit
+  const float unbias = kBf ? 8.507059173023462e37f /* 2^126 */ : 16384.0f /* 2^14 */;
+  const uint32_t u2 = H::pack(unbias, unbias);
+  const float sc = __uint_as_float(e8 ? (e8 << 23) : 0x00400000u);
+  const uint32_t s2 = H::pack(sc, sc);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t hi = w[j] >> 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // byte 0 <- byte i of w (even element in its low nibble), byte 2 <- byte i of w>>4
+      const uint32_t t = __byte_perm(w[j], hi, 0x0000u | i | ((4 + i) << 8)) & 0x000F000Fu;
+      const uint32_t bits = ((t & 0x00070007u) << kShift) | ((t & 0x00080008u) << 12);
+      out[j * 4 + i] = H::mul(H::mul(bits, u2), s2);
+    }
+  }
+}
+
+// ---- UMMA descriptors ------------------------------------------------------------------
+
+// K-major operand in the 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);        // start address
+  d |= static_cast<uint64_t>(1) << 16;                        // leading byte offset (unused)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                        // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                        // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16, float32 accumulate, both operands K-major.
+__host__ __device__ constexpr uint32_t instr_desc(int fmt /*0 f16, 1 bf16*/, int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// ---- shared-memory plan -----------------------------------------------------------------
+
+template <int QK, int BT>
+struct Plan {
+  static constexpr int kBits = (QK == kAff8) ? 8 : 4;
+  static constexpr int kWRowBytes = kBK * kBits / 8;          // 32 or 64
+  static constexpr int kXBytes = BT * kBK * 2;                // one activation stage
+  static constexpr int kWBytes = kBF * kWRowBytes;            // one packed-weight stage
+  static constexpr int kStageBytes = kXBytes + kWBytes;
+  static constexpr int kStages = (BT >= 256) ? 5 : 6;
+  static constexpr int kBarBytes = 1024;
+  static constexpr int kSmem = kStages * kStageBytes + kBarBytes + 1024 /* alignment slack */;
+  static constexpr int kDCols = BT;                           // accumulator columns
+  static constexpr int kACol0 = 256;                          // A ring starts here
+  static constexpr int kTmemCols = 512;
+};
+
+struct TileInfo {
+  int seg;
+  int64_t row0;      // first x / y row of this tile
+  int rows;          // valid rows in the tile (<= BT)
+  int64_t f0;        // first feature
+};
+
+// Tile t of the persistent walk -> (segment, token tile, feature tile); feature tiles vary
+// fastest inside a token tile so that concurrently running CTAs share the activation tile
+// and stream disjoint weight rows.
+template <int BT>
+__device__ __forceinline__ bool tile_at(int64_t t, const int64_t* seg_tile0, const int64_t* seg_row0,
+                                        int nseg, int64_t ftiles, int64_t N, TileInfo* out) {
+  if (t >= seg_tile0[nseg]) return false;
+  int s = 0;
+  while (t >= seg_tile0[s + 1]) ++s;
+  const int64_t local = t - seg_tile0[s];
+  const int64_t tt = local / ftiles, ft = local % ftiles;
+  const int64_t rows = seg_row0[s + 1] - seg_row0[s];
+  out->seg = s;
+  out->row0 = seg_row0[s] + tt * BT;
+  const int64_t left = rows - tt * BT;
+  out->rows = static_cast<int>(left < BT ? left : BT);
+  out->f0 = ft * kBF;
+  (void)N;
+  return true;
+}
+
+template <int QK, typename XT, int BT>
+__global__ void __launch_bounds__(kThreads, 1)
+qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
+                   const TcParams p) {
+  using P = Plan<QK, BT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + P::kStages * P::kStageBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);      // [kStages] TMA landed
+  uint64_t* empty = full + P::kStages;                         // [kStages] stage consumed
+  uint64_t* a_full = empty + P::kStages;                       // [kAStages] A written to TMEM
+  uint64_t* a_empty = a_full + kAStages;                       // [kAStages] A consumed by MMA
+  uint64_t* d_full = a_empty + kAStages;                       // accumulator complete
+  uint64_t* d_empty = d_full + 1;                              // accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  __shared__ int64_t seg_tile0[kMaxSegments + 1];
+  __shared__ int64_t seg_row0[kMaxSegments + 1];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nseg = static_cast<int>(p.segments);
+  const int64_t ftiles = (p.N + kBF - 1) / kBF;
+  const int num_kb = static_cast<int>((p.K + kBK - 1) / kBK);
+
+  if (threadIdx.x == 0) {
+    int64_t tiles = 0, rows = 0;
+    for (int s = 0; s < nseg; ++s) {
+      seg_tile0[s] = tiles;
+      seg_row0[s] = rows;
+      int64_t r = p.group_sizes ? p.group_sizes[s] : p.M;
+      if (p.group_sizes && rows + r > p.M) r = p.M - rows;
+      if (r < 0) r = 0;
+      rows += r;
+      tiles += ((r + BT - 1) / BT) * ftiles;
+    }
+    seg_tile0[nseg] = tiles;
+    seg_row0[nseg] = rows;
+    for (int i = 0; i < P::kStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1 + 4);
+    }
+    for (int i = 0; i < kAStages; ++i) {
+      mbar_init(&a_full[i], 4);
+      mbar_init(&a_empty[i], 1);
+    }
+    mbar_init(d_full, 1);
+    mbar_init(d_empty, 8);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(P::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      TileInfo ti;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, &ti);
+           t += gridDim.x) {
+        const int64_t wrow = ti.seg * p.w_seg_rows + ti.f0;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % P::kStages;
+          const uint32_t ph = (it / P::kStages) & 1;
+          if (!(ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, 1))) break;
+          uint8_t* stage = smem + s * P::kStageBytes;
+          mbar_expect_tx(&full[s], P::kStageBytes);
+          tma_load_2d(&x_map, stage, &full[s], kb * kBK, static_cast<int>(ti.row0));
+          tma_load_2d(&w_map, stage + P::kXBytes, &full[s], kb * P::kWRowBytes, static_cast<int>(wrow));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(std::is_same<XT, __nv_bfloat16>::value ? 1 : 0, kBF, BT);
+      uint32_t it = 0, tile_n = 0;
+      TileInfo ti;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, &ti);
+           t += gridDim.x, ++tile_n) {
+        if (!(ok = mbar_wait(d_empty, (tile_n & 1) ^ 1, abort_flag, 2))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % P::kStages, a = it % kAStages;
+          if (!(ok = mbar_wait(&full[s], (it / P::kStages) & 1, abort_flag, 3))) break;
+          if (!(ok = mbar_wait(&a_full[a], (it / kAStages) & 1, abort_flag, 4))) break;
+          tc_fence_after();
+          const uint64_t bdesc = smem_desc_sw128(smem_u32(smem + s * P::kStageBytes));
+          const uint32_t acol = tmem_base + P::kACol0 + a * 32;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            tc_mma_ts(tmem_base, acol + k * 8, bdesc + static_cast<uint64_t>(k * 2), idesc,
+                      (kb | k) ? 1u : 0u);
+          tc_commit(&empty[s]);
+          tc_commit(&a_empty[a]);
+        }
+        if (ok) tc_commit(d_full);
+      }
+    }
+  } else {
+    // ---------------- dequant + epilogue warps ----------------
+    const int team = (warp - 2) >> 2;            // 0 or 1: takes K blocks with it % 2 == team
+    const int quarter = warp & 3;                // TMEM lane quarter this warp may touch
+    const int frow = quarter * 32 + lane;        // feature row within the tile
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int64_t groups = p.K / p.group_size;
+    uint32_t it = 0, tile_n = 0;
+    TileInfo ti;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, &ti);
+         t += gridDim.x, ++tile_n) {
+      int64_t feat = ti.f0 + frow;
+      const bool feat_ok = feat < p.N;
+      if (!feat_ok) feat = p.N - 1;
+      const int64_t trow = (ti.seg * p.w_seg_rows + feat) * groups;   // row of the scale tables
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if ((it & 1) != static_cast<uint32_t>(team)) continue;
+        const int s = it % P::kStages, a = it % kAStages;
+        // per-group constants for this K block, fetched before the waits
+        const int k0 = kb * kBK;
+        float sc[2], bi[2];
+        uint32_t e8[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          int64_t g = (k0 + h * 32) / p.group_size;
+          if (g >= groups) g = groups - 1;
+          if constexpr (QK == kMx4) {
+            e8[h] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + trow + g);
+            sc[h] = bi[h] = 0.0f;
+          } else {
+            sc[h] = table_f32(p.scales, p.table_dtype, trow + g);
+            bi[h] = table_f32(p.biases, p.table_dtype, trow + g);
+            e8[h] = 0;
+          }
+        }
+        if (!(ok = mbar_wait(&full[s], (it / P::kStages) & 1, abort_flag, 5))) break;
+        const uint8_t* wsm = smem + s * P::kStageBytes + P::kXBytes + frow * P::kWRowBytes;
+        uint32_t packed[P::kWRowBytes / 4];
+#pragma unroll
+        for (int i = 0; i < P::kWRowBytes / 16; ++i) {
+          const uint4 v = *reinterpret_cast<const uint4*>(wsm + i * 16);
+          packed[i * 4] = v.x; packed[i * 4 + 1] = v.y; packed[i * 4 + 2] = v.z; packed[i * 4 + 3] = v.w;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);     // this warp's share of the stage is in registers
+        uint32_t out[32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if constexpr (QK == kAff4) {
+            const uint32_t (&w4)[4] = *reinterpret_cast<const uint32_t (*)[4]>(&packed[h * 4]);
+            dequant_aff4<XT>(w4, sc[h], bi[h], &out[h * 16]);
+          } else if constexpr (QK == kAff8) {
+            const uint32_t (&w8)[8] = *reinterpret_cast<const uint32_t (*)[8]>(&packed[h * 8]);
+            dequant_aff8<XT>(w8, sc[h], bi[h], &out[h * 16]);
+          } else {
+            const uint32_t (&w4)[4] = *reinterpret_cast<const uint32_t (*)[4]>(&packed[h * 4]);
+            dequant_mx4<XT>(w4, e8[h], &out[h * 16]);
+          }
+        }
+        if (!(ok = mbar_wait(&a_empty[a], ((it / kAStages) & 1) ^ 1, abort_flag, 6))) break;
+        tc_fence_after();
+        tmem_st32(tmem_base + lane_addr + P::kACol0 + a * 32, out);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[a]);
+      }
+      if (!ok) break;
+      // ---- epilogue: this team drains its half of the accumulator columns ----
+      if (!(ok = mbar_wait(d_full, tile_n & 1, abort_flag, 7))) break;
+      tc_fence_after();
+      constexpr int kHalf = BT / 2;
+#pragma unroll 1
+      for (int c0 = team * kHalf; c0 < (team + 1) * kHalf; c0 += 32) {
+        if (c0 >= ti.rows) break;                  // warp-uniform: no valid token rows left
+        uint32_t r[32];
+        tmem_ld32(tmem_base + lane_addr + c0, r);
+        tmem_wait_ld();
+        if (feat_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (c0 + j < ti.rows) {
+              const int64_t o = (ti.row0 + c0 + j) * p.N + feat;
+              const float v = __uint_as_float(r[j]);
+              if (p.y_dtype == QMM_BF16) reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16_rn(v);
+              else if (p.y_dtype == QMM_F16) reinterpret_cast<__half*>(p.y)[o] = __float2half_rn(v);
+              else reinterpret_cast<float*>(p.y)[o] = v;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(d_empty);
+    }
+    // ragged: rows past the last group are zero
+    if (p.group_sizes) {
+      const int64_t used = seg_row0[nseg];
+      const int64_t total = (p.M - used) * p.N;
+      const int64_t tid = static_cast<int64_t>(blockIdx.x) * 256 + (threadIdx.x - 64);
+      for (int64_t i = tid; i < total; i += static_cast<int64_t>(gridDim.x) * 256) {
+        const int64_t o = used * p.N + i;
+        if (p.y_dtype == QMM_F32) reinterpret_cast<float*>(p.y)[o] = 0.0f;
+        else reinterpret_cast<uint16_t*>(p.y)[o] = 0;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P::kTmemCols)
+                 : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicCAS(p.status, 0, *abort_flag);
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+int make_map(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+             uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(QMM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(QMM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return QMM_OK;
+}
+
+int* status_word() {
+  static int* ptr = nullptr;   // one word per process, allocated on first use and kept
+  if (!ptr) {
+    if (cudaMalloc(&ptr, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(ptr, 0, sizeof(int));
+  }
+  return ptr;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int QK, typename XT, int BT>
+int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
+  using P = Plan<QK, BT>;
+  const bool ragged = p.group_sizes != nullptr;
+  const int64_t x_rows = ragged ? p.M : p.batch * p.M;
+  const int64_t w_rows = (p.w_batch_stride ? p.batch : 1) * p.N;
+  CUtensorMap xm, wm;
+  int rc;
+  const CUtensorMapDataType xdt =
+      std::is_same<XT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  if ((rc = make_map(&xm, xdt, p.x, static_cast<uint64_t>(p.K), static_cast<uint64_t>(x_rows),
+                     static_cast<uint64_t>(p.K) * 2, kBK, BT, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  const uint64_t wrow_bytes = static_cast<uint64_t>(p.K) * P::kBits / 8;
+  if ((rc = make_map(&wm, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.w, wrow_bytes, static_cast<uint64_t>(w_rows),
+                     wrow_bytes, P::kWRowBytes, kBF, CU_TENSOR_MAP_SWIZZLE_NONE)))
+    return rc;
+  TcParams tp;
+  tp.scales = p.scales; tp.biases = p.biases; tp.y = p.y; tp.group_sizes = p.group_sizes;
+  tp.status = status_word();
+  if (!tp.status) return fail(QMM_ERR_CUDA, "could not allocate the device status word");
+  tp.M = p.M; tp.K = p.K; tp.N = p.N;
+  tp.segments = p.batch;
+  tp.w_seg_rows = p.w_batch_stride ? p.N : 0;
+  tp.group_size = p.group_size; tp.table_dtype = p.table_dtype; tp.y_dtype = p.y_dtype;
+
+  auto kernel = qmm_gemm_tc_kernel<QK, XT, BT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmem);
+    if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int64_t ftiles = (p.N + kBF - 1) / kBF;
+  int64_t max_tiles = ragged ? ((p.M + BT - 1) / BT + p.batch) * ftiles
+                             : p.batch * ((p.M + BT - 1) / BT) * ftiles;
+  int grid = sm_count();
+  if (max_tiles < grid) grid = static_cast<int>(max_tiles < 1 ? 1 : max_tiles);
+  kernel<<<grid, kThreads, P::kSmem, stream>>>(xm, wm, tp);
+  count_launch();
+  return check_launch("qmm_gemm_tc_kernel");
+}
+
+template <int QK, typename XT>
+int launch_bt(const qmm_problem& p, cudaStream_t stream) {
+  // Token-tile width: wide tiles amortize the dequantization, narrow ones waste less MMA
+  // work on short row runs.
+  const int64_t rows = p.group_sizes ? (p.M + p.batch - 1) / (p.batch ? p.batch : 1) : p.M;
+  if (rows > 128) return launch_cfg<QK, XT, 256>(p, stream);
+  if (rows > 64) return launch_cfg<QK, XT, 128>(p, stream);
+  return launch_cfg<QK, XT, 64>(p, stream);
+}
+
+template <int QK>
+int launch_xt(const qmm_problem& p, cudaStream_t stream) {
+  if (p.x_dtype == QMM_BF16) return launch_bt<QK, __nv_bfloat16>(p, stream);
+  return launch_bt<QK, __half>(p, stream);
+}
+
+}  // namespace
+
+bool gemm_tc_supports(const qmm_problem& p) {
+  if (p.x_dtype != QMM_BF16 && p.x_dtype != QMM_F16) return false;
+  if (p.lhs_idx || p.rhs_idx) return false;                   // unsorted gathers go elsewhere
+  if (p.batch > kMaxSegments) return false;
+  if (p.K < kBK || p.K % 32) return false;
+  if ((p.K * 2) % 16) return false;
+  if (!p.group_sizes && p.batch > 1 && p.x_batch_stride != p.M * p.K) return false;
+  if (!p.group_sizes && p.batch > 1 && p.y_batch_stride != p.M * p.N) return false;
+  if (p.M * (p.group_sizes ? 1 : p.batch) >= (1LL << 31) || p.N * p.batch >= (1LL << 31)) return false;
+  return true;
+}
+
+int launch_gemm_tc(const qmm_problem& p, cudaStream_t stream) {
+  if (p.mode == QMM_MODE_MXFP4) return launch_xt<kMx4>(p, stream);
+  if (p.bits == 8) return launch_xt<kAff8>(p, stream);
+  return launch_xt<kAff4>(p, stream);
+}
+
+int gemm_tc_status(int* out) {
+  int* w = status_word();
+  if (!w) return fail(QMM_ERR_CUDA, "no status word");
+  cudaError_t e = cudaMemcpy(out, w, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaMemcpy(status): %s", cudaGetErrorString(e));
+  if (*out) cudaMemset(w, 0, sizeof(int));
+  return QMM_OK;
+}
+
+}  // namespace qmm

@@ -23,6 +23,8 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream);
 bool gemv_supports(const qmm_problem& p);
 int launch_gemm_tc(const qmm_problem& p, cudaStream_t stream);
 bool gemm_tc_supports(const qmm_problem& p);
+// Reads (and clears) the tensor-core kernel's device status word; synchronizes the device.
+int gemm_tc_status(int* out);
 
 int launch_dequantize(const uint32_t* w, const void* scales, const void* biases, int table_dtype,
                       void* out, int out_dtype, int64_t rows, int64_t K, int group_size, int bits,
