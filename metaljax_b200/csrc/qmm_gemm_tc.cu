@@ -474,26 +474,35 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       const bool feat_ok = feat < p.N;
       if (!feat_ok) feat = p.N - 1;
       const int64_t trow = (ti.seg * p.w_seg_rows + feat) * groups;   // row of the scale tables
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        if ((it & 1) != static_cast<uint32_t>(team)) continue;
-        const int s = it % P::kStages, a = it % kAStages;
-        // per-group constants for this K block, fetched before the waits
-        const int k0 = kb * kBK;
-        float sc[2], bi[2];
-        uint32_t e8[2];
+      // This team's K blocks of the tile are those whose global iteration index has the
+      // team's parity. The per-group constants of a block are requested one block ahead,
+      // so their global-memory latency hides behind the previous block's work.
+      const uint32_t it0 = it;
+      auto fetch_tables = [&](int kbb, float (&fs)[2], float (&fb)[2], uint32_t (&fe)[2]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          int64_t g = (k0 + h * 32) / p.group_size;
+          int64_t g = (kbb * kBK + h * 32) / p.group_size;
           if (g >= groups) g = groups - 1;
           if constexpr (QK == kMx4) {
-            e8[h] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + trow + g);
-            sc[h] = bi[h] = 0.0f;
+            fe[h] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + trow + g);
+            fs[h] = fb[h] = 0.0f;
           } else {
-            sc[h] = table_f32(p.scales, p.table_dtype, trow + g);
-            bi[h] = table_f32(p.biases, p.table_dtype, trow + g);
-            e8[h] = 0;
+            fs[h] = table_f32(p.scales, p.table_dtype, trow + g);
+            fb[h] = table_f32(p.biases, p.table_dtype, trow + g);
+            fe[h] = 0;
           }
         }
+      };
+      int kb = ((it0 & 1u) == static_cast<uint32_t>(team)) ? 0 : 1;
+      float sc[2] = {0.0f, 0.0f}, bi[2] = {0.0f, 0.0f};
+      uint32_t e8[2] = {0u, 0u};
+      if (kb < num_kb) fetch_tables(kb, sc, bi, e8);
+      for (; kb < num_kb; kb += 2) {
+        it = it0 + static_cast<uint32_t>(kb);
+        const int s = it % P::kStages, a = it % kAStages;
+        float nsc[2] = {0.0f, 0.0f}, nbi[2] = {0.0f, 0.0f};
+        uint32_t ne8[2] = {0u, 0u};
+        if (kb + 2 < num_kb) fetch_tables(kb + 2, nsc, nbi, ne8);
         if (!(ok = mbar_wait(&full[s], (it / P::kStages) & 1, abort_flag, 5))) break;
         const uint8_t* wsm = smem + s * P::kStageBytes + P::kXBytes + frow * P::kWRowBytes;
         uint32_t packed[P::kWRowBytes / 4];
@@ -525,8 +534,11 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_full[a]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) { sc[h] = nsc[h]; bi[h] = nbi[h]; e8[h] = ne8[h]; }
       }
       if (!ok) break;
+      it = it0 + static_cast<uint32_t>(num_kb);
       // ---- epilogue: this team drains its half of the accumulator columns ----
       if (!(ok = mbar_wait(d_full, tile_n & 1, abort_flag, 7))) break;
       tc_fence_after();

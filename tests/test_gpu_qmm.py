@@ -52,6 +52,8 @@ def _run_affine(rng, m, k, n, gs, bits, xdt="bf16", tdt="bf16", ydt=None, route=
     _, w, s, b = affine_case(rng, n, k, gs, bits, tdt)
     x = activations(rng, tuple(lead) + (m, k), xdt)
     ydt = ydt or xdt
+    if route == "gemv" and m > 16:
+        pytest.skip("the decode kernel takes M <= 16")
     args = [to_torch(a, DEV) for a in (x, w, s, b)]
     kw = dict(group_size=gs, bits=bits, out_dtype=TDT[ydt])
     if route:
@@ -131,14 +133,14 @@ SHAPES = [  # (M, K, N)
 ]
 
 
-@pytest.mark.parametrize("route", ["simt", "gemm_tc", None])
+@pytest.mark.parametrize("route", ["simt", "gemm_tc", "gemv", None])
 @pytest.mark.parametrize("m,k,n", SHAPES)
 def test_qmm_affine4_g64(route, m, k, n):
     rng = np.random.default_rng(m * 7 + n)
     _run_affine(rng, m, k, n, 64 if k % 64 == 0 else 32, 4, route=route)
 
 
-@pytest.mark.parametrize("route", ["simt", "gemm_tc", None])
+@pytest.mark.parametrize("route", ["simt", "gemm_tc", "gemv", None])
 @pytest.mark.parametrize("bits,gs", [(4, 32), (4, 128), (8, 32), (8, 64), (8, 128)])
 @pytest.mark.parametrize("m", [1, 7, 40, 300])
 def test_qmm_affine_variants(route, bits, gs, m):
@@ -146,7 +148,7 @@ def test_qmm_affine_variants(route, bits, gs, m):
     _run_affine(rng, m, 384, 200, gs, bits, route=route)
 
 
-@pytest.mark.parametrize("route", ["simt", "gemm_tc", None])
+@pytest.mark.parametrize("route", ["simt", "gemm_tc", "gemv", None])
 @pytest.mark.parametrize("xdt,tdt,ydt", [("f16", "f16", "f16"), ("bf16", "f32", "bf16"),
                                          ("bf16", "bf16", "f32"), ("f16", "bf16", "bf16"),
                                          ("bf16", "f16", "f16")])
@@ -168,12 +170,14 @@ def test_qmm_float32_activations(m):
         assert e.value.status == 7
 
 
-@pytest.mark.parametrize("route", ["simt", "gemm_tc", None])
+@pytest.mark.parametrize("route", ["simt", "gemm_tc", "gemv", None])
 @pytest.mark.parametrize("m", [1, 3, 64, 512])
 @pytest.mark.parametrize("xdt", ["bf16", "f16", "f32"])
 def test_qmm_mxfp4(route, m, xdt):
-    if xdt == "f32" and route == "gemm_tc":
+    if xdt == "f32" and route in ("gemm_tc", "gemv"):
         pytest.skip("float32 activations take the SIMT route")
+    if route == "gemv" and m > 16:
+        pytest.skip("the decode kernel takes M <= 16")
     rng = np.random.default_rng(m + 3)
     n, k = 192, 320
     codes, w, sb = mxfp4_case(rng, n, k)
@@ -201,11 +205,12 @@ def test_mxfp4_every_code_and_scale_extremes():
     w = O.pack_codes(codes, 4)
     wref = O.dequant_mxfp4(w, sb)
     x = np.eye(k, dtype=np.float32).astype(BF16)
-    for route in ("simt", "gemm_tc"):
+    for route in ("simt", "gemm_tc", "gemv"):
+        xs = x[:16] if route == "gemv" else x
         with _lib.force_route(route):
-            y = qmm.quantized_matmul(to_torch(x, DEV), to_torch(w, DEV), to_torch(sb, DEV), None,
+            y = qmm.quantized_matmul(to_torch(xs, DEV), to_torch(w, DEV), to_torch(sb, DEV), None,
                                      group_size=32, bits=4, mode="mxfp4", out_dtype=torch.float32)
-        np.testing.assert_array_equal(to_numpy(y), wref.T)
+        np.testing.assert_array_equal(to_numpy(y), wref.T[: len(xs)])
 
 
 def test_affine_one_hot_recovers_dequantized_weight():
@@ -215,21 +220,25 @@ def test_affine_one_hot_recovers_dequantized_weight():
     _, w, s, b = affine_case(rng, n, k, 64, 4, "bf16")
     x = np.eye(k, dtype=np.float32).astype(BF16)
     want = O.dequant_affine(w, s, b, 64, 4).T
-    for route, exact_bits in (("simt", True), ("gemm_tc", False)):
+    for route, exact_bits in (("simt", True), ("gemv", True), ("gemm_tc", False)):
+        xs = x[16:32] if route == "gemv" else x
         with _lib.force_route(route):
-            y = qmm.quantized_matmul(to_torch(x, DEV), to_torch(w, DEV), to_torch(s, DEV),
+            y = qmm.quantized_matmul(to_torch(xs, DEV), to_torch(w, DEV), to_torch(s, DEV),
                                      to_torch(b, DEV), group_size=64, bits=4, out_dtype=torch.float32)
         got = to_numpy(y)
-        if exact_bits:
+        if route == "gemv":
+            # one product per output: s*(128+q) + (b-128s), each term exact, one f32 rounding each
+            np.testing.assert_allclose(got, want[16:32], rtol=0, atol=2e-6)
+        elif exact_bits:
             np.testing.assert_array_equal(got, want)
         else:   # the tensor-core route rounds the dequantized weight once to bf16
             np.testing.assert_array_equal(got, want.astype(BF16).astype(np.float32))
 
 
-@pytest.mark.parametrize("route", ["simt", "gemm_tc", None])
+@pytest.mark.parametrize("route", ["simt", "gemm_tc", "gemv", None])
 def test_batched_and_shared_weights(route):
     rng = np.random.default_rng(5)
-    b_, m, k, n = 3, 20, 256, 72
+    b_, m, k, n = 3, (20 if route != "gemv" else 5), 256, 72
     _, w, s, bi = affine_case(rng, n, k, 64, 4, "bf16", lead=(b_,))
     x = activations(rng, (b_, m, k))
     tx = to_torch(x, DEV)
@@ -270,9 +279,11 @@ def test_gather_qmm(mode):
                        torch.from_numpy(tidx).to(DEV), torch.from_numpy(eidx).to(DEV))
 
 
-@pytest.mark.parametrize("route", ["simt", "gemm_tc", None])
+@pytest.mark.parametrize("route", ["simt", "gemm_tc", "gemv", None])
 @pytest.mark.parametrize("sizes", [[5, 0, 300, 7], [0, 0, 0, 0], [64, 64, 64, 64], [1, 1, 1, 1], [513, 0, 0, 2]])
 def test_ragged_dot(route, sizes):
+    if route == "gemv":
+        pytest.skip("ragged rows go to the tensor-core kernel")
     rng = np.random.default_rng(sum(sizes) + 1)
     g, k, n = len(sizes), 192, 136
     total = sum(sizes) + 3                                       # three rows belong to no group
@@ -368,6 +379,46 @@ def test_device_side_validation():
     assert rc == 4                                                # strided view
     empty = qmm.quantized_matmul(x[:0], w, s, s, group_size=64, bits=4)
     assert tuple(empty.shape) == (0, 8)
+
+
+@pytest.mark.parametrize("m", list(range(1, 17)))
+@pytest.mark.parametrize("kind", ["aff4g64", "aff4g32", "aff8g128", "mx4"])
+def test_decode_kernel_every_m(m, kind):
+    """The decode kernel for every M it accepts, N not a multiple of its 16-row tile, K that
+    does not divide evenly among its eight warps, against the oracle and the SIMT route."""
+    rng = np.random.default_rng(m)
+    n, k = 83, 2880 if kind == "mx4" else 1152
+    x = activations(rng, (m, k))
+    if kind == "mx4":
+        _, w, s = mxfp4_case(rng, n, k)
+        b, gs, bits, mode = None, 32, 4, "mxfp4"
+    else:
+        bits = 8 if kind.startswith("aff8") else 4
+        gs = int(kind.split("g")[1])
+        _, w, s, b = affine_case(rng, n, k, gs, bits, "bf16")
+        mode = "affine"
+    args = (to_torch(x, DEV), to_torch(w, DEV), to_torch(s, DEV), None if b is None else to_torch(b, DEV))
+    with _lib.force_route("gemv"):
+        y = qmm.quantized_matmul(*args, group_size=gs, bits=bits, mode=mode, out_dtype=torch.float32)
+    with _lib.force_route("simt"):
+        ys = qmm.quantized_matmul(*args, group_size=gs, bits=bits, mode=mode, out_dtype=torch.float32)
+    exact = O.qmm_exact(x, w, s, b, gs, bits, mode)
+    assert O.rel_err(to_numpy(y), exact) <= 2e-5
+    assert O.rel_err(to_numpy(y), to_numpy(ys).astype(np.float64)) <= 2e-5
+
+
+def test_decode_kernel_long_k_and_wide_batch():
+    """K longer than one staged pass (two passes at M <= 8, seven at M > 8) and a gather over
+    many pairs."""
+    rng = np.random.default_rng(77)
+    n, k = 48, 14336
+    _, w, s, b = affine_case(rng, n, k, 64, 4, "bf16")
+    for m in (3, 12):
+        x = activations(rng, (m, k))
+        with _lib.force_route("gemv"):
+            y = qmm.quantized_matmul(to_torch(x, DEV), to_torch(w, DEV), to_torch(s, DEV),
+                                     to_torch(b, DEV), group_size=64, bits=4, out_dtype=torch.float32)
+        assert O.rel_err(to_numpy(y), O.qmm_exact(x, w, s, b, 64, 4)) <= 2e-5
 
 
 # ---- benchmark configurations at full size ---------------------------------------------------
