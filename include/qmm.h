@@ -172,7 +172,8 @@ typedef struct {
   int32_t x_dtype;          /* qmm_elem: BF16 | F16 | F32 */
   int32_t table_dtype;      /* qmm_elem of scales/biases (U8 for mxfp4) */
   int32_t y_dtype;          /* qmm_elem: BF16 | F16 | F32 */
-  int32_t reserved0;
+  int32_t num_weights;     /* weight matrices behind `w` (experts E for a gather); 0 = batch
+                            * when w_batch_stride != 0, else 1 */
   int64_t batch;            /* B >= 1 */
   int64_t M, K, N;
   const void* x;            /* [B, M, K] */

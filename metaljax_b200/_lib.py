@@ -36,7 +36,7 @@ class Problem(ctypes.Structure):
         ("struct_size", ctypes.c_uint32), ("mode", ctypes.c_int32), ("bits", ctypes.c_int32),
         ("group_size", ctypes.c_int32), ("x_dtype", ctypes.c_int32),
         ("table_dtype", ctypes.c_int32), ("y_dtype", ctypes.c_int32),
-        ("reserved0", ctypes.c_int32),
+        ("num_weights", ctypes.c_int32),
         ("batch", ctypes.c_int64), ("M", ctypes.c_int64), ("K", ctypes.c_int64),
         ("N", ctypes.c_int64),
         ("x", ctypes.c_void_p), ("w", ctypes.c_void_p), ("scales", ctypes.c_void_p),

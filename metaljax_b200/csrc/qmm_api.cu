@@ -162,6 +162,8 @@ int validate_problem(const qmm_problem& p, bool pointers) {
   if ((p.lhs_idx != nullptr) != (p.rhs_idx != nullptr))
     return fail(QMM_ERR_NULL, "gather needs both lhs_idx and rhs_idx");
   if (p.group_sizes && p.lhs_idx) return fail(QMM_ERR_UNSUPPORTED, "ragged and gather are exclusive");
+  if (p.num_weights < 0 || (p.lhs_idx && p.num_weights < 1 && pointers))
+    return fail(QMM_ERR_SHAPE, "a gather needs num_weights (the number of experts behind w)");
   if (pointers && p.batch * p.M * p.N * p.K > 0) {
     if (!p.x || !p.w || !p.scales || !p.y) return fail(QMM_ERR_NULL, "a data pointer is NULL");
     if (p.mode == QMM_MODE_AFFINE && !p.biases) return fail(QMM_ERR_NULL, "affine mode needs biases");
@@ -360,6 +362,7 @@ int qmm_gather_qmm(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* s
   p.x = data_of(x); p.w = static_cast<const uint32_t*>(data_of(w));
   p.scales = data_of(scales); p.biases = biases ? data_of(biases) : nullptr; p.y = data_of(y);
   p.x_batch_stride = M * K; p.y_batch_stride = M * N; p.w_batch_stride = N;
+  p.num_weights = static_cast<int32_t>(w->shape[0]);
   p.lhs_idx = static_cast<const int32_t*>(data_of(lhs_idx));
   p.rhs_idx = static_cast<const int32_t*>(data_of(rhs_idx));
   if ((rc = validate_problem(p, true))) return rc;

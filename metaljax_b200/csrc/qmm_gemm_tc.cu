@@ -13,9 +13,9 @@
 // (float32) sits in TMEM; the epilogue reads it back with tcgen05.ld, casts and stores
 // y[token, feature].
 //
-// Warp roles (10 warps): 0 = TMA producer, 1 = MMA issuer (+ TMEM allocation),
-// 2..9 = eight dequant/epilogue warps in two teams of four (one warp per TMEM lane
-// quarter); the teams take alternate K blocks.
+// Warp roles (18 warps): 0 = TMA producer, 1 = MMA issuer (+ TMEM allocation),
+// 2..17 = sixteen dequant/epilogue warps in four teams of four (one warp per TMEM lane
+// quarter); the teams take K blocks round-robin.
 //
 // One persistent CTA per SM walks a list of tiles (segment, token tile, feature tile).
 // A segment is a run of x rows that meets one weight matrix: the whole of x for the plain
@@ -28,6 +28,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <type_traits>
 
 #include "qmm_internal.h"
@@ -38,7 +40,8 @@ namespace {
 constexpr int kBF = 128;        // features per tile (MMA M, TMEM lanes)
 constexpr int kBK = 64;         // K elements per pipeline stage
 constexpr int kAStages = 8;     // dequantized-A ring in TMEM (32 columns each)
-constexpr int kThreads = 320;   // 10 warps
+constexpr int kTeams = 4;        // dequant/epilogue teams of four warps (one per TMEM lane quarter)
+constexpr int kThreads = (2 + 4 * kTeams) * 32;
 constexpr int kMaxSegments = 256;
 constexpr long long kSpinLimit = 4000000000LL;  // SM clocks (~2 s)
 
@@ -50,6 +53,7 @@ struct TcParams {
   void* y;
   const int32_t* group_sizes;  // ragged: [segments]; else NULL
   int* status;                 // device status word (0 = ok)
+  long long* trace;            // development aid: per-CTA cycles spent in each wait site, or NULL
   int64_t M;                   // rows of x per segment (dense) or total rows (ragged)
   int64_t K, N;
   int64_t segments;            // weight matrices
@@ -213,12 +217,6 @@ struct Half2Ops<__half> {
     return *reinterpret_cast<uint32_t*>(&r);
   }
 };
-
-__device__ __forceinline__ float table_f32(const void* p, int dtype, int64_t i) {
-  if (dtype == QMM_BF16) return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p) + i));
-  if (dtype == QMM_F16) return __half2float(__ldg(reinterpret_cast<const __half*>(p) + i));
-  return __ldg(reinterpret_cast<const float*>(p) + i);
-}
 
 // 4-bit affine, one 32-element half of the K block (4 words -> 16 pairs). A byte holds
 // elements (2i, 2i+1): PRMT takes it from the word (even element in its low nibble) into
@@ -395,7 +393,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       mbar_init(&a_empty[i], 1);
     }
     mbar_init(d_full, 1);
-    mbar_init(d_empty, 8);
+    mbar_init(d_empty, 4 * kTeams);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -410,6 +408,22 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Waits go through here so that a development build can account the cycles per wait site.
+  long long waited[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const bool tracing = p.trace != nullptr;
+  long long trace_c0 = 0, trace_n0 = 0;
+  if (tracing && threadIdx.x == 0) {
+    trace_c0 = clock64();
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(trace_n0));
+  }
+  auto twait = [&](uint64_t* bar, uint32_t parity, volatile int* flag, int where) -> bool {
+    if (!tracing) return mbar_wait(bar, parity, flag, where);
+    const long long t0 = clock64();
+    const bool r = mbar_wait(bar, parity, flag, where);
+    waited[where] += clock64() - t0;
+    return r;
+  };
+
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
@@ -422,7 +436,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % P::kStages;
           const uint32_t ph = (it / P::kStages) & 1;
-          if (!(ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, 1))) break;
+          if (!(ok = twait(&empty[s], ph ^ 1, abort_flag, 1))) break;
           uint8_t* stage = smem + s * P::kStageBytes;
           mbar_expect_tx(&full[s], P::kStageBytes);
           tma_load_2d(&x_map, stage, &full[s], kb * kBK, static_cast<int>(ti.row0));
@@ -439,13 +453,14 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       bool ok = true;
       for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, &ti);
            t += gridDim.x, ++tile_n) {
-        if (!(ok = mbar_wait(d_empty, (tile_n & 1) ^ 1, abort_flag, 2))) break;
+        if (!(ok = twait(d_empty, (tile_n & 1) ^ 1, abort_flag, 2))) break;
         tc_fence_after();
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % P::kStages, a = it % kAStages;
-          if (!(ok = mbar_wait(&full[s], (it / P::kStages) & 1, abort_flag, 3))) break;
-          if (!(ok = mbar_wait(&a_full[a], (it / kAStages) & 1, abort_flag, 4))) break;
+          if (!(ok = twait(&full[s], (it / P::kStages) & 1, abort_flag, 3))) break;
+          if (!(ok = twait(&a_full[a], (it / kAStages) & 1, abort_flag, 4))) break;
           tc_fence_after();
+          const long long ti0 = tracing ? clock64() : 0;
           const uint64_t bdesc = smem_desc_sw128(smem_u32(smem + s * P::kStageBytes));
           const uint32_t acol = tmem_base + P::kACol0 + a * 32;
 #pragma unroll
@@ -454,13 +469,14 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
                       (kb | k) ? 1u : 0u);
           tc_commit(&empty[s]);
           tc_commit(&a_empty[a]);
+          if (tracing) waited[0] += clock64() - ti0;   // cycles spent issuing
         }
         if (ok) tc_commit(d_full);
       }
     }
   } else {
     // ---------------- dequant + epilogue warps ----------------
-    const int team = (warp - 2) >> 2;            // 0 or 1: takes K blocks with it % 2 == team
+    const int team = (warp - 2) >> 2;            // takes K blocks with it % kTeams == team
     const int quarter = warp & 3;                // TMEM lane quarter this warp may touch
     const int frow = quarter * 32 + lane;        // feature row within the tile
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
@@ -475,9 +491,10 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       if (!feat_ok) feat = p.N - 1;
       const int64_t trow = (ti.seg * p.w_seg_rows + feat) * groups;   // row of the scale tables
       // This team's K blocks of the tile are those whose global iteration index has the
-      // team's parity. The per-group constants of a block are requested one block ahead,
+      // team's residue. The per-group constants of a block are requested one block ahead,
       // so their global-memory latency hides behind the previous block's work.
       const uint32_t it0 = it;
+      const int tsize = (p.table_dtype == QMM_F32) ? 4 : 2;
       auto fetch_tables = [&](int kbb, float (&fs)[2], float (&fb)[2], uint32_t (&fe)[2]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -487,23 +504,23 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
             fe[h] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + trow + g);
             fs[h] = fb[h] = 0.0f;
           } else {
-            fs[h] = table_f32(p.scales, p.table_dtype, trow + g);
-            fb[h] = table_f32(p.biases, p.table_dtype, trow + g);
+            fs[h] = __uint_as_float(table_raw(p.scales, tsize, trow + g));   // raw bits until used
+            fb[h] = __uint_as_float(table_raw(p.biases, tsize, trow + g));
             fe[h] = 0;
           }
         }
       };
-      int kb = ((it0 & 1u) == static_cast<uint32_t>(team)) ? 0 : 1;
+      int kb = static_cast<int>((static_cast<uint32_t>(team) + kTeams - (it0 % kTeams)) % kTeams);
       float sc[2] = {0.0f, 0.0f}, bi[2] = {0.0f, 0.0f};
       uint32_t e8[2] = {0u, 0u};
       if (kb < num_kb) fetch_tables(kb, sc, bi, e8);
-      for (; kb < num_kb; kb += 2) {
+      for (; kb < num_kb; kb += kTeams) {
         it = it0 + static_cast<uint32_t>(kb);
         const int s = it % P::kStages, a = it % kAStages;
         float nsc[2] = {0.0f, 0.0f}, nbi[2] = {0.0f, 0.0f};
         uint32_t ne8[2] = {0u, 0u};
-        if (kb + 2 < num_kb) fetch_tables(kb + 2, nsc, nbi, ne8);
-        if (!(ok = mbar_wait(&full[s], (it / P::kStages) & 1, abort_flag, 5))) break;
+        if (kb + kTeams < num_kb) fetch_tables(kb + kTeams, nsc, nbi, ne8);
+        if (!(ok = twait(&full[s], (it / P::kStages) & 1, abort_flag, 5))) break;
         const uint8_t* wsm = smem + s * P::kStageBytes + P::kXBytes + frow * P::kWRowBytes;
         uint32_t packed[P::kWRowBytes / 4];
 #pragma unroll
@@ -518,19 +535,23 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
         for (int h = 0; h < 2; ++h) {
           if constexpr (QK == kAff4) {
             const uint32_t (&w4)[4] = *reinterpret_cast<const uint32_t (*)[4]>(&packed[h * 4]);
-            dequant_aff4<XT>(w4, sc[h], bi[h], &out[h * 16]);
+            dequant_aff4<XT>(w4, table_value(__float_as_uint(sc[h]), p.table_dtype),
+                             table_value(__float_as_uint(bi[h]), p.table_dtype), &out[h * 16]);
           } else if constexpr (QK == kAff8) {
             const uint32_t (&w8)[8] = *reinterpret_cast<const uint32_t (*)[8]>(&packed[h * 8]);
-            dequant_aff8<XT>(w8, sc[h], bi[h], &out[h * 16]);
+            dequant_aff8<XT>(w8, table_value(__float_as_uint(sc[h]), p.table_dtype),
+                             table_value(__float_as_uint(bi[h]), p.table_dtype), &out[h * 16]);
           } else {
             const uint32_t (&w4)[4] = *reinterpret_cast<const uint32_t (*)[4]>(&packed[h * 4]);
             dequant_mx4<XT>(w4, e8[h], &out[h * 16]);
           }
         }
-        if (!(ok = mbar_wait(&a_empty[a], ((it / kAStages) & 1) ^ 1, abort_flag, 6))) break;
+        if (!(ok = twait(&a_empty[a], ((it / kAStages) & 1) ^ 1, abort_flag, 6))) break;
         tc_fence_after();
+        const long long ts0 = tracing ? clock64() : 0;
         tmem_st32(tmem_base + lane_addr + P::kACol0 + a * 32, out);
         tmem_wait_st();
+        if (tracing) waited[0] += clock64() - ts0;   // cycles in tcgen05.st + wait
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_full[a]);
@@ -539,12 +560,11 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       }
       if (!ok) break;
       it = it0 + static_cast<uint32_t>(num_kb);
-      // ---- epilogue: this team drains its half of the accumulator columns ----
-      if (!(ok = mbar_wait(d_full, tile_n & 1, abort_flag, 7))) break;
+      // ---- epilogue: the teams drain disjoint 32-column chunks of the accumulator ----
+      if (!(ok = twait(d_full, tile_n & 1, abort_flag, 7))) break;
       tc_fence_after();
-      constexpr int kHalf = BT / 2;
 #pragma unroll 1
-      for (int c0 = team * kHalf; c0 < (team + 1) * kHalf; c0 += 32) {
+      for (int c0 = team * 32; c0 < BT; c0 += 32 * kTeams) {
         if (c0 >= ti.rows) break;                  // warp-uniform: no valid token rows left
         uint32_t r[32];
         tmem_ld32(tmem_base + lane_addr + c0, r);
@@ -570,8 +590,9 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
     if (p.group_sizes) {
       const int64_t used = seg_row0[nseg];
       const int64_t total = (p.M - used) * p.N;
-      const int64_t tid = static_cast<int64_t>(blockIdx.x) * 256 + (threadIdx.x - 64);
-      for (int64_t i = tid; i < total; i += static_cast<int64_t>(gridDim.x) * 256) {
+      const int64_t nth = 128 * kTeams;
+      const int64_t tid = static_cast<int64_t>(blockIdx.x) * nth + (threadIdx.x - 64);
+      for (int64_t i = tid; i < total; i += static_cast<int64_t>(gridDim.x) * nth) {
         const int64_t o = used * p.N + i;
         if (p.y_dtype == QMM_F32) reinterpret_cast<float*>(p.y)[o] = 0.0f;
         else reinterpret_cast<uint16_t*>(p.y)[o] = 0;
@@ -587,6 +608,15 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
                  : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag) atomicCAS(p.status, 0, *abort_flag);
+  if (tracing && threadIdx.x == 0) {
+    long long n1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(n1));
+    p.trace[blockIdx.x * 16 + 14] = clock64() - trace_c0;
+    p.trace[blockIdx.x * 16 + 15] = n1 - trace_n0;
+  }
+  if (tracing && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 6))
+    for (int i = 0; i < 8; ++i)
+      if (waited[i]) p.trace[blockIdx.x * 16 + (warp == 1 ? 8 : 0) + i] = waited[i];
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -623,12 +653,7 @@ int make_map(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_
 }
 
 int* status_word() {
-  static int* ptr = nullptr;   // one word per process, allocated on first use and kept
-  if (!ptr) {
-    if (cudaMalloc(&ptr, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(ptr, 0, sizeof(int));
-  }
-  return ptr;
+  return device_status_word();
 }
 
 int sm_count() {
@@ -662,6 +687,13 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   TcParams tp;
   tp.scales = p.scales; tp.biases = p.biases; tp.y = p.y; tp.group_sizes = p.group_sizes;
   tp.status = status_word();
+  static long long* trace_buf = nullptr;
+  static const bool trace_on = getenv("QMM_TC_TRACE") != nullptr;
+  if (trace_on && !trace_buf) {
+    cudaMalloc(&trace_buf, sizeof(long long) * 16 * 1024);
+  }
+  if (trace_on) cudaMemsetAsync(trace_buf, 0, sizeof(long long) * 16 * 1024, stream);
+  tp.trace = trace_on ? trace_buf : nullptr;
   if (!tp.status) return fail(QMM_ERR_CUDA, "could not allocate the device status word");
   tp.M = p.M; tp.K = p.K; tp.N = p.N;
   tp.segments = p.batch;
@@ -682,6 +714,19 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   if (max_tiles < grid) grid = static_cast<int>(max_tiles < 1 ? 1 : max_tiles);
   kernel<<<grid, kThreads, P::kSmem, stream>>>(xm, wm, tp);
   count_launch();
+  if (trace_on) {   // development aid: average cycles per wait site over the CTAs
+    cudaStreamSynchronize(stream);
+    static long long host[16 * 1024];
+    cudaMemcpy(host, trace_buf, sizeof(long long) * 16 * grid, cudaMemcpyDeviceToHost);
+    double avg[16] = {0};
+    for (int c = 0; c < grid; ++c)
+      for (int i = 0; i < 16; ++i) avg[i] += static_cast<double>(host[c * 16 + i]) / grid;
+    fprintf(stderr, "qmm_gemm_tc CTA lifetime %.0f cycles, %.1f us -> %.0f MHz\n", avg[14], avg[15] / 1e3,
+            avg[14] / (avg[15] / 1e3));
+    fprintf(stderr, "qmm_gemm_tc cycles/CTA: producer.empty %.0f | mma.issue %.0f mma.d_empty %.0f mma.full %.0f mma.a_full %.0f |"
+            " dequant.st %.0f dequant.full %.0f dequant.a_empty %.0f dequant.d_full %.0f\n",
+            avg[1], avg[8], avg[8 + 2], avg[8 + 3], avg[8 + 4], avg[0], avg[5], avg[6], avg[7]);
+  }
   return check_launch("qmm_gemm_tc_kernel");
 }
 

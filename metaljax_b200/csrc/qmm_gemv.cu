@@ -1,50 +1,64 @@
 // Decode kernel of the fused dequantize-and-matmul: up to 16 activation rows against a
 // streamed packed weight (M <= 16 of `y = x . deq(w)^T`, src/metaljax/qmm.py:2491).
 //
-// HBM-bound: every packed weight byte is read exactly once, straight from global memory
-// into registers, and never dequantized element by element. A CTA owns 16 weight rows; its
-// 8 warps split K. Per 32-wide K step a lane holds one packed word (two for 8-bit) of rows
-// g and g+8 and turns it into the A fragments of two m16n8k16 MMAs with a magic-number OR:
-// the 16-bit pattern 0x4300|q is the bf16 number 128+q (0x6400|q is the f16 number 1024+q),
-// so the tensor core accumulates  sum (C + q_k) x_k  exactly in float32. All 16 K slots of
-// such an MMA lie inside one 32-element span, hence inside one quantization group, so the
-// group's scale and bias are applied to the accumulators once per group:
+// HBM-bound: every packed weight byte is read exactly once and never dequantized element by
+// element. A CTA owns 16 weight rows and its 8 warps split K. The packed rows arrive by TMA in
+// boxes of 16 rows x 128 bytes (128-byte swizzle, so that the fragment reads below are free
+// of bank conflicts); every warp feeds its own ring of boxes from its own mbarriers, and the
+// first boxes are requested before anything else happens in the kernel.
+//
+// Per 32-wide K step a lane reads one packed word (two for 8-bit) of rows g and g+8 and turns
+// it into the A fragments of two m16n8k16 MMAs with a magic-number OR: the 16-bit pattern
+// 0x4300|q is the bf16 number 128+q (0x6400|q is the f16 number 1024+q), so the tensor core
+// accumulates  sum (C + q_k) x_k  exactly in float32. All 16 K slots of such an MMA lie
+// inside one 32-element span, hence inside one quantization group, so the group's scale and
+// bias are applied to the accumulators once per group:
 //     y += s * sum (C + q) x  +  (b - C s) * sum x ,
 // with  sum x  taken from one more MMA whose A fragment is all ones. The activations are
-// staged once per CTA in shared memory in the MMA's element type (for 4-bit codes with the
-// pair order the magic-number extraction produces), tokens beyond M being zero fragments.
-// MXFP4 converts code pairs with cvt.e2m1x2 to f16 and scales per 32-group by 2^(e8-127).
+// staged once per CTA in shared memory in the MMA's element type (for 4-bit codes in the pair
+// order the magic-number extraction produces), tokens beyond M being zero fragments, next to
+// the CTA's slice of the scale table and of the folded bias table  b - C s.
+// MXFP4 places each code's magnitude bits at the f16 exponent/mantissa boundary (the E2M1
+// value times 2^-14, exactly) and scales the accumulators per 32-group by 2^(e8-127+14).
 //
-// The K split is reduced across the CTA's warps in shared memory; there is no global
-// scratch and no atomics, and the summation order is fixed.
+// The K split is reduced across the CTA's warps in shared memory; there is no global scratch
+// and no atomics, and the summation order is fixed. Waits on the TMA barriers are bounded.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <type_traits>
 
 #include "qmm_internal.h"
+#include "qmm_ptx.cuh"
 
 namespace qmm {
 namespace {
 
+using namespace ptx;
+
 constexpr int kWarps = 8;
 constexpr int kRowsPerCta = 16;
-constexpr int kXPad = 32;        // elements of padding per staged activation row (64 bytes)
+constexpr int kXPad = 32;           // elements of padding per staged activation row (64 bytes)
+constexpr int kBoxBytes = 128;      // bytes of one weight row in a TMA box
+constexpr int kBoxSmem = kRowsPerCta * kBoxBytes;   // 2 KiB
+constexpr int kMaxRing = 4;         // boxes a warp keeps in flight
 
 enum { kAff4 = 0, kAff8 = 1, kMx4 = 2 };
 
 struct GemvParams {
   const void* x;
-  const uint32_t* w;
   const void* scales;
   const void* biases;
   void* y;
   const int32_t* lhs_idx;
   const int32_t* rhs_idx;
+  int* status;
   int64_t M, K, N, batch;
   int64_t x_batch_stride, y_batch_stride, w_batch_rows;
-  int group_size, table_dtype, y_dtype, x_dtype;
-  int kc;  // K elements staged per pass
+  int group_size, table_dtype, y_dtype;
+  int kc;     // K elements staged per pass (a multiple of the box width)
+  int ring;   // boxes per warp ring (1..kMaxRing)
 };
 
 template <typename AT>
@@ -55,11 +69,12 @@ struct MmaOps<__nv_bfloat16> {
   static constexpr uint32_t kMagic = 0x43004300u;
   static constexpr float kMagicValue = 128.0f;
   static constexpr uint32_t kOnes = 0x3F803F80u;
-  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  // d = a * b + c (m16n8k16, float32 accumulate)
+  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                             const float (&c)[4]) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
   }
 };
 
@@ -68,19 +83,14 @@ struct MmaOps<__half> {
   static constexpr uint32_t kMagic = 0x64006400u;
   static constexpr float kMagicValue = 1024.0f;
   static constexpr uint32_t kOnes = 0x3C003C00u;
-  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  // d = a * b + c (m16n8k16, float32 accumulate)
+  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                             const float (&c)[4]) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
   }
 };
-
-__device__ __forceinline__ float gv_table(const void* p, int dtype, int64_t i) {
-  if (dtype == QMM_BF16) return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p) + i));
-  if (dtype == QMM_F16) return __half2float(__ldg(reinterpret_cast<const __half*>(p) + i));
-  return __ldg(reinterpret_cast<const float*>(p) + i);
-}
 
 __device__ __forceinline__ void gv_store(void* p, int dtype, int64_t i, float v) {
   if (dtype == QMM_BF16) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
@@ -120,36 +130,65 @@ __device__ __forceinline__ void load8(const XT* p, float (&f)[8]) {
   }
 }
 
-// What one warp requests from global memory ahead of a run of MMAs: the packed words of
-// rows g and g+8 for up to kSteps K steps, and the group tables that go with them.
-template <int QK, int SPG>
-struct BatchShape {
-  static constexpr int kWpl = (QK == kAff8) ? 2 : 1;                       // words per lane per step
-  static constexpr int kMaxSteps = (QK == kAff8) ? 8 : 16;
-  static constexpr int kMaxGroups = (QK == kMx4) ? 16 : 8;
-  static constexpr int kGroups = (kMaxSteps / SPG < kMaxGroups) ? kMaxSteps / SPG : kMaxGroups;
-  static constexpr int kSteps = kGroups * SPG;
+// Walks one warp's boxes in the order they are consumed: chunk by chunk (a chunk is what the
+// CTA stages of x at a time), and inside a chunk the warp's contiguous share of its boxes.
+struct BoxCursor {
+  int chunk, j, hi;
 };
+
+__device__ __forceinline__ int boxes_in_chunk(int chunk, int64_t K, int kc, int boxk) {
+  const int64_t left = K - static_cast<int64_t>(chunk) * kc;
+  const int64_t span = left < kc ? left : kc;
+  return static_cast<int>((span + boxk - 1) / boxk);
+}
+
+__device__ __forceinline__ void cursor_seek(BoxCursor& c, int nchunks, int warp, int64_t K, int kc, int boxk) {
+  while (c.chunk < nchunks) {
+    const int nb = boxes_in_chunk(c.chunk, K, kc, boxk);
+    c.j = nb * warp / kWarps;
+    c.hi = nb * (warp + 1) / kWarps;
+    if (c.j < c.hi) return;
+    ++c.chunk;
+  }
+}
+
+__device__ __forceinline__ void cursor_next(BoxCursor& c, int nchunks, int warp, int64_t K, int kc, int boxk) {
+  if (++c.j < c.hi) return;
+  ++c.chunk;
+  cursor_seek(c, nchunks, warp, K, kc, boxk);
+}
 
 // QK: quantization kind. XT: activation type in memory. NT: token halves (1: M <= 8,
 // 2: M <= 16). SPG: 32-wide K steps per quantization group (1, 2, 4).
 template <int QK, typename XT, int NT, int SPG>
 __global__ void __launch_bounds__(kWarps * 32, 2)
-qmm_gemv_kernel(const GemvParams p) {
+qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   // MMA element type: 4-bit affine codes fit bf16's 7 mantissa bits; 8-bit codes and the
-  // E2M1 conversion need f16.
+  // E2M1 bit placement need f16.
   using AT = typename std::conditional<QK == kAff4, XT, __half>::type;
   using Ops = MmaOps<AT>;
-  using BS = BatchShape<QK, SPG>;
   constexpr int BITS = (QK == kAff8) ? 8 : 4;
-  constexpr int WPL = BS::kWpl;
+  constexpr int kBoxK = kBoxBytes * 8 / BITS;      // K elements per box: 256 or 128
+  constexpr int kStepsPerBox = kBoxK / 32;         // 8 or 4
+  constexpr int kGroupK = 32 * SPG;
 
-  extern __shared__ __align__(16) uint8_t gv_smem[];
+  extern __shared__ uint8_t gv_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gv_smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int xrow = p.kc + kXPad;                  // staged row stride in elements
-  AT* xs = reinterpret_cast<AT*>(gv_smem);
-  float* red = reinterpret_cast<float*>(gv_smem + static_cast<size_t>(p.M) * xrow * sizeof(AT));
+  const int ring = p.ring;
+  const int xrow = p.kc + kXPad;                   // staged row stride in elements
+  const int tgroups = p.kc / kGroupK;              // groups staged per pass
+  const int trow = tgroups + 1;                    // table row stride in floats (odd: no conflicts)
+
+  uint8_t* wring = smem + warp * ring * kBoxSmem;                                    // this warp's boxes
+  AT* xs = reinterpret_cast<AT*>(smem + kWarps * ring * kBoxSmem);
+  float* ts = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + static_cast<size_t>(p.M) * xrow * sizeof(AT));
+  float* tb = ts + kRowsPerCta * trow;
+  float* red = tb + kRowsPerCta * trow;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + kWarps * 2 * 4 * 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kWarps * kMaxRing);
+  uint64_t* full = bars + warp * kMaxRing;
 
   const int64_t seg = blockIdx.y;
   int64_t x_off, wb;
@@ -162,52 +201,37 @@ qmm_gemv_kernel(const GemvParams p) {
   }
   const int64_t y_off = seg * p.y_batch_stride;
   const XT* xg = reinterpret_cast<const XT*>(p.x) + x_off;
-
   const int64_t n0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta;
-  const int64_t words = p.K * BITS / 32;
-  const int64_t groups = p.K / (32 * SPG);
-  const int64_t r0 = wb * p.N + (n0 + g < p.N ? n0 + g : p.N - 1);
-  const int64_t r1 = wb * p.N + (n0 + g + 8 < p.N ? n0 + g + 8 : p.N - 1);
-  const uint32_t* w0 = p.w + r0 * words;
-  const uint32_t* w1 = p.w + r1 * words;
+  const int wrow0 = static_cast<int>(wb * p.N + n0);            // first weight row of this CTA
+  const int64_t groups = p.K / kGroupK;
+  const int nchunks = static_cast<int>((p.K + p.kc - 1) / p.kc);
+  const int boxes_per_chunk = p.kc / kBoxK;
 
-  uint32_t wr[BS::kSteps][2][WPL];
-  float sc[BS::kGroups][2], bi[BS::kGroups][2];
+  // Each warp owns its barriers: it initializes them itself and nobody else touches them.
+  if (lane == 0) {
+    for (int i = 0; i < kMaxRing; ++i) mbar_init(&full[i], 1);
+    if (warp == 0) *abort_flag = 0;
+    mbar_init_fence();
+  }
+  __syncwarp();
 
-  // Requests groups [gfirst, gfirst+ng) (absolute group indices) of this lane's two rows.
-  auto load_batch = [&](int64_t gfirst, int ng) {
-#pragma unroll
-    for (int q = 0; q < BS::kGroups; ++q) {
-      if (q < ng) {
-#pragma unroll
-        for (int s = 0; s < SPG; ++s) {
-          const int64_t wi = ((gfirst + q) * SPG + s) * (4 * WPL) + t * WPL;
-          if constexpr (WPL == 2) {
-            const uint2 a = __ldg(reinterpret_cast<const uint2*>(w0 + wi));
-            const uint2 b = __ldg(reinterpret_cast<const uint2*>(w1 + wi));
-            wr[q * SPG + s][0][0] = a.x; wr[q * SPG + s][0][1] = a.y;
-            wr[q * SPG + s][1][0] = b.x; wr[q * SPG + s][1][1] = b.y;
-          } else {
-            wr[q * SPG + s][0][0] = __ldg(w0 + wi);
-            wr[q * SPG + s][1][0] = __ldg(w1 + wi);
-          }
-        }
-        const int64_t gi = gfirst + q;
-        if constexpr (QK == kMx4) {
-          const uint32_t e0 = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + r0 * groups + gi);
-          const uint32_t e1 = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + r1 * groups + gi);
-          sc[q][0] = __uint_as_float(e0 ? (e0 << 23) : 0x00400000u);
-          sc[q][1] = __uint_as_float(e1 ? (e1 << 23) : 0x00400000u);
-          bi[q][0] = bi[q][1] = 0.0f;
-        } else {
-          sc[q][0] = gv_table(p.scales, p.table_dtype, r0 * groups + gi);
-          sc[q][1] = gv_table(p.scales, p.table_dtype, r1 * groups + gi);
-          bi[q][0] = gv_table(p.biases, p.table_dtype, r0 * groups + gi);
-          bi[q][1] = gv_table(p.biases, p.table_dtype, r1 * groups + gi);
-        }
-      }
-    }
+  // ---- request this warp's first boxes before anything else ----
+  BoxCursor issue = {0, 0, 0};
+  cursor_seek(issue, nchunks, warp, p.K, p.kc, kBoxK);
+  int issued = 0;
+  auto issue_box = [&]() {   // lane 0 only
+    const int slot = issued % ring;
+    mbar_expect_tx(&full[slot], kBoxSmem);
+    tma_load_2d(&w_map, wring + slot * kBoxSmem, &full[slot],
+                (issue.chunk * boxes_per_chunk + issue.j) * kBoxBytes, wrow0);
   };
+  if (lane == 0) {
+    while (issued < ring && issue.chunk < nchunks) {
+      issue_box();
+      ++issued;
+      cursor_next(issue, nchunks, warp, p.K, p.kc, kBoxK);
+    }
+  }
 
   float yacc[NT][4];
 #pragma unroll
@@ -215,103 +239,178 @@ qmm_gemv_kernel(const GemvParams p) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) yacc[h][i] = 0.0f;
 
-  for (int64_t kbase = 0; kbase < p.K; kbase += p.kc) {
-    const int kc = static_cast<int>(p.K - kbase < p.kc ? p.K - kbase : p.kc);   // multiple of 32
-    // this warp's share of the chunk's groups, as indices within the chunk
-    const int cgroups = kc / (32 * SPG);
-    const int glo = cgroups * warp / kWarps, ghi = cgroups * (warp + 1) / kWarps;
-    const int64_t gbase = kbase / (32 * SPG);
-    // The first batch's weights are requested before the activations are staged, so the
-    // two global-memory latencies overlap.
-    int ng = (ghi - glo < BS::kGroups) ? ghi - glo : BS::kGroups;
-    if (ng > 0) load_batch(gbase + glo, ng);
-
+  int consumed = 0;
+  bool ok = true;
+  const int tsize = (p.table_dtype == QMM_F32) ? 4 : 2;
+  for (int chunk = 0; chunk < nchunks; ++chunk) {
+    const int64_t kbase = static_cast<int64_t>(chunk) * p.kc;
+    const int kc = static_cast<int>(p.K - kbase < p.kc ? p.K - kbase : p.kc);     // multiple of 32
+    const int nb = (kc + kBoxK - 1) / kBoxK;
+    const int kfill = nb * kBoxK;                                                 // zero-padded extent
+    const int cgroups = kc / kGroupK;
+    // ---- stage x[0:M, kbase : kbase+kc] and the tables of this CTA's 16 rows ----
     __syncthreads();
-    for (int idx = threadIdx.x; idx < static_cast<int>(p.M) * (kc / 8); idx += blockDim.x) {
-      const int m = idx / (kc / 8), ch = idx % (kc / 8);
-      float f[8];
-      load8<XT>(xg + static_cast<int64_t>(m) * p.K + kbase + ch * 8, f);
-      uint4 o;
-      if constexpr (QK == kAff4) {  // pair order (0,4)(1,5)(2,6)(3,7): what one LOP3 extracts
-        o.x = pack_pair<AT>(f[0], f[4]); o.y = pack_pair<AT>(f[1], f[5]);
-        o.z = pack_pair<AT>(f[2], f[6]); o.w = pack_pair<AT>(f[3], f[7]);
-      } else {
-        o.x = pack_pair<AT>(f[0], f[1]); o.y = pack_pair<AT>(f[2], f[3]);
-        o.z = pack_pair<AT>(f[4], f[5]); o.w = pack_pair<AT>(f[6], f[7]);
+    {
+      // Tables first: thread (r, c) of a 16 x 16 arrangement takes groups c, c+16, ... of row
+      // r. All of a pass's loads are requested before the first one is used.
+      const int r = threadIdx.x >> 4, c = threadIdx.x & 15;
+      const int64_t row = wb * p.N + (n0 + r < p.N ? n0 + r : p.N - 1);
+      const int64_t ti0 = row * groups + kbase / kGroupK;
+      constexpr int kTU = 4;
+      for (int g0 = c; g0 < cgroups; g0 += 16 * kTU) {
+        uint32_t rs[kTU], rb[kTU];
+#pragma unroll
+        for (int u = 0; u < kTU; ++u) {
+          const int gi = g0 + 16 * u;
+          rs[u] = rb[u] = 0u;
+          if (gi < cgroups) {
+            if constexpr (QK == kMx4) {
+              rs[u] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + ti0 + gi);
+            } else {
+              rs[u] = table_raw(p.scales, tsize, ti0 + gi);
+              rb[u] = table_raw(p.biases, tsize, ti0 + gi);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kTU; ++u) {
+          const int gi = g0 + 16 * u;
+          if (gi < cgroups) {
+            if constexpr (QK == kMx4) {
+              ts[r * trow + gi] = __uint_as_float(rs[u] ? (rs[u] << 23) : 0x00400000u);   // 2^(e8-127)
+            } else {
+              const float sv = table_value(rs[u], p.table_dtype);
+              ts[r * trow + gi] = sv;
+              tb[r * trow + gi] = table_value(rb[u], p.table_dtype) - Ops::kMagicValue * sv;
+            }
+          }
+        }
       }
-      *reinterpret_cast<uint4*>(xs + static_cast<size_t>(m) * xrow + ch * 8) = o;
+      // Activations: items are (token, 8-element piece). When the MMA's element type is the
+      // activations' own, a piece is only re-paired with byte permutes; otherwise it is
+      // converted through float32.
+      constexpr int kXU = 4;
+      const int pieces = kfill / 8;
+      const float inv_pieces = 1.0f / static_cast<float>(pieces);
+      const int items = static_cast<int>(p.M) * pieces;
+      for (int e0 = threadIdx.x; e0 < items; e0 += blockDim.x * kXU) {
+        uint4 raw[kXU];
+        int mm[kXU], pc[kXU];
+#pragma unroll
+        for (int u = 0; u < kXU; ++u) {
+          const int e = e0 + u * blockDim.x;
+          mm[u] = __float2int_rz((static_cast<float>(e) + 0.5f) * inv_pieces);
+          pc[u] = e - mm[u] * pieces;
+          raw[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (e < items && pc[u] * 8 < kc)
+            raw[u] = __ldg(reinterpret_cast<const uint4*>(xg + static_cast<int64_t>(mm[u]) * p.K + kbase + pc[u] * 8));
+        }
+#pragma unroll
+        for (int u = 0; u < kXU; ++u) {
+          if (e0 + u * blockDim.x < items) {
+            uint4 o;
+            if constexpr (std::is_same<AT, XT>::value) {
+              if constexpr (QK == kAff4) {  // pair order (0,4)(1,5)(2,6)(3,7): what one LOP3 extracts
+                o.x = __byte_perm(raw[u].x, raw[u].z, 0x5410); o.y = __byte_perm(raw[u].x, raw[u].z, 0x7632);
+                o.z = __byte_perm(raw[u].y, raw[u].w, 0x5410); o.w = __byte_perm(raw[u].y, raw[u].w, 0x7632);
+              } else {
+                o = raw[u];
+              }
+            } else {                        // bf16 activations, f16 MMA
+              const uint32_t r4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+              uint32_t c4[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                c4[i] = pack_pair<AT>(__uint_as_float(r4[i] << 16), __uint_as_float(r4[i] & 0xffff0000u));
+              o = make_uint4(c4[0], c4[1], c4[2], c4[3]);
+            }
+            *reinterpret_cast<uint4*>(xs + mm[u] * xrow + pc[u] * 8) = o;
+          }
+        }
+      }
     }
     __syncthreads();
 
-    for (int gb = glo; gb < ghi; gb += BS::kGroups) {
-      if (gb != glo) {
-        ng = (ghi - gb < BS::kGroups) ? ghi - gb : BS::kGroups;
-        load_batch(gbase + gb, ng);
-      }
+    // ---- this warp's boxes of the chunk ----
+    const int jlo = nb * warp / kWarps, jhi = nb * (warp + 1) / kWarps;
+    for (int j = jlo; j < jhi && ok; ++j, ++consumed) {
+      const int slot = consumed % ring;
+      if (!(ok = mbar_wait(&full[slot], (consumed / ring) & 1, abort_flag, 11))) break;
+      const uint8_t* box = wring + slot * kBoxSmem;
+      const uint8_t* row0 = box + g * kBoxBytes;
+      const uint8_t* row1 = box + (g + 8) * kBoxBytes;
 #pragma unroll
-      for (int q = 0; q < BS::kGroups; ++q) {
-        if (q < ng) {
+      for (int q = 0; q < kStepsPerBox / SPG; ++q) {          // groups of this box
+        const int gi = (j * kBoxK) / kGroupK + q;             // group index within the chunk
+        if (gi < cgroups) {
           float acc[NT][4], ones[NT][4];
 #pragma unroll
-          for (int h = 0; h < NT; ++h)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[h][i] = ones[h][i] = 0.0f;
-#pragma unroll
           for (int s = 0; s < SPG; ++s) {
-            const int kloc = ((gb + q) * SPG + s) * 32 + t * 8;     // within the staged chunk
+            const int ks = q * SPG + s;                         // K step within the box
+            const int kloc = j * kBoxK + ks * 32 + t * 8;       // within the staged chunk
             uint32_t a[2][4];
-            if constexpr (QK == kAff4) {
-              const uint32_t u0 = wr[q * SPG + s][0][0], u1 = wr[q * SPG + s][1][0];
-              a[0][0] = (u0 & 0x000F000Fu) | Ops::kMagic;         a[0][1] = (u1 & 0x000F000Fu) | Ops::kMagic;
-              a[0][2] = ((u0 >> 4) & 0x000F000Fu) | Ops::kMagic;  a[0][3] = ((u1 >> 4) & 0x000F000Fu) | Ops::kMagic;
-              a[1][0] = ((u0 >> 8) & 0x000F000Fu) | Ops::kMagic;  a[1][1] = ((u1 >> 8) & 0x000F000Fu) | Ops::kMagic;
-              a[1][2] = ((u0 >> 12) & 0x000F000Fu) | Ops::kMagic; a[1][3] = ((u1 >> 12) & 0x000F000Fu) | Ops::kMagic;
-            } else if constexpr (QK == kAff8) {
-#pragma unroll
-              for (int j = 0; j < 2; ++j) {   // word j: bytes (0,1) and (2,3) under the f16 magic
-                a[j][0] = __byte_perm(wr[q * SPG + s][0][j], 0x64646464u, 0x4140);
-                a[j][1] = __byte_perm(wr[q * SPG + s][1][j], 0x64646464u, 0x4140);
-                a[j][2] = __byte_perm(wr[q * SPG + s][0][j], 0x64646464u, 0x4342);
-                a[j][3] = __byte_perm(wr[q * SPG + s][1][j], 0x64646464u, 0x4342);
-              }
+            if constexpr (QK == kAff8) {
+              // 32 bytes per row and step: lane t takes bytes [8t, 8t+8) of them
+              const int off = (((ks * 2 + (t >> 1)) ^ (g & 7)) << 4) + (t & 1) * 8;
+              const uint2 u0 = *reinterpret_cast<const uint2*>(row0 + off);
+              const uint2 u1 = *reinterpret_cast<const uint2*>(row1 + off);
+              a[0][0] = __byte_perm(u0.x, 0x64646464u, 0x4140); a[0][1] = __byte_perm(u1.x, 0x64646464u, 0x4140);
+              a[0][2] = __byte_perm(u0.x, 0x64646464u, 0x4342); a[0][3] = __byte_perm(u1.x, 0x64646464u, 0x4342);
+              a[1][0] = __byte_perm(u0.y, 0x64646464u, 0x4140); a[1][1] = __byte_perm(u1.y, 0x64646464u, 0x4140);
+              a[1][2] = __byte_perm(u0.y, 0x64646464u, 0x4342); a[1][3] = __byte_perm(u1.y, 0x64646464u, 0x4342);
             } else {
+              // 16 bytes per row and step: lane t takes word t
+              const int off = ((ks ^ (g & 7)) << 4) + t * 4;
+              const uint32_t u0 = *reinterpret_cast<const uint32_t*>(row0 + off);
+              const uint32_t u1 = *reinterpret_cast<const uint32_t*>(row1 + off);
+              if constexpr (QK == kAff4) {
+                a[0][0] = (u0 & 0x000F000Fu) | Ops::kMagic;         a[0][1] = (u1 & 0x000F000Fu) | Ops::kMagic;
+                a[0][2] = ((u0 >> 4) & 0x000F000Fu) | Ops::kMagic;  a[0][3] = ((u1 >> 4) & 0x000F000Fu) | Ops::kMagic;
+                a[1][0] = ((u0 >> 8) & 0x000F000Fu) | Ops::kMagic;  a[1][1] = ((u1 >> 8) & 0x000F000Fu) | Ops::kMagic;
+                a[1][2] = ((u0 >> 12) & 0x000F000Fu) | Ops::kMagic; a[1][3] = ((u1 >> 12) & 0x000F000Fu) | Ops::kMagic;
+              } else {
+                // The three magnitude bits of an E2M1 code at f16's exponent/mantissa boundary
+                // are the code's value times 2^-14 (code 1 = 0.5 lands on a subnormal); the
+                // sign bit goes to bit 15. The 2^14 is restored in the fold.
 #pragma unroll
-              for (int r = 0; r < 2; ++r) {
-                const uint32_t u = wr[q * SPG + s][r][0];
+                for (int r = 0; r < 2; ++r) {
+                  const uint32_t u = r ? u1 : u0;
+                  const uint32_t uh = u >> 4;
 #pragma unroll
-                for (int bb = 0; bb < 4; ++bb) {  // byte bb -> elements (2bb, 2bb+1)
-                  uint32_t h2;
-                  const uint16_t byte = static_cast<uint16_t>((u >> (8 * bb)) & 0xFFu);
-                  asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h2) : "h"(byte));
-                  a[bb >> 1][(bb & 1) * 2 + r] = h2;
+                  for (int bb = 0; bb < 4; ++bb) {  // byte bb -> elements (2bb, 2bb+1)
+                    const uint32_t tt = __byte_perm(u, uh, bb | ((4 + bb) << 8));
+                    a[bb >> 1][(bb & 1) * 2 + r] = ((tt << 9) & 0x0E000E00u) | ((tt << 12) & 0x80008000u);
+                  }
                 }
               }
             }
+            const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             const uint32_t one4[4] = {Ops::kOnes, Ops::kOnes, Ops::kOnes, Ops::kOnes};
 #pragma unroll
             for (int h = 0; h < NT; ++h) {
               uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-              if (h * 8 + g < p.M)
-                xv = *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(h * 8 + g) * xrow + kloc);
-              Ops::mma(acc[h], a[0], xv.x, xv.y);
-              Ops::mma(acc[h], a[1], xv.z, xv.w);
-              if constexpr (QK != kMx4) {
-                Ops::mma(ones[h], one4, xv.x, xv.y);
-                Ops::mma(ones[h], one4, xv.z, xv.w);
+              if (h * 8 + g < p.M) xv = *reinterpret_cast<const uint4*>(xs + (h * 8 + g) * xrow + kloc);
+              if (s == 0) Ops::mma(acc[h], a[0], xv.x, xv.y, zero4);
+              else Ops::mma(acc[h], a[0], xv.x, xv.y, acc[h]);
+              Ops::mma(acc[h], a[1], xv.z, xv.w, acc[h]);
+              if constexpr (QK != kMx4) {   // sum of x over the group: A = all ones
+                if (s == 0) Ops::mma(ones[h], one4, xv.x, xv.y, zero4);
+                else Ops::mma(ones[h], one4, xv.x, xv.y, ones[h]);
+                Ops::mma(ones[h], one4, xv.z, xv.w, ones[h]);
               }
             }
           }
           // fold the group: rows g (c0, c1) and g+8 (c2, c3), tokens 2t and 2t+1
-          const float s0 = sc[q][0], s1 = sc[q][1];
-          const float b0 = bi[q][0] - Ops::kMagicValue * s0, b1 = bi[q][1] - Ops::kMagicValue * s1;
+          const float s0 = ts[g * trow + gi], s1 = ts[(g + 8) * trow + gi];
 #pragma unroll
           for (int h = 0; h < NT; ++h) {
             if constexpr (QK == kMx4) {
-              yacc[h][0] = fmaf(s0, acc[h][0], yacc[h][0]);
-              yacc[h][1] = fmaf(s0, acc[h][1], yacc[h][1]);
-              yacc[h][2] = fmaf(s1, acc[h][2], yacc[h][2]);
-              yacc[h][3] = fmaf(s1, acc[h][3], yacc[h][3]);
+              yacc[h][0] = fmaf(s0, acc[h][0] * 16384.0f, yacc[h][0]);
+              yacc[h][1] = fmaf(s0, acc[h][1] * 16384.0f, yacc[h][1]);
+              yacc[h][2] = fmaf(s1, acc[h][2] * 16384.0f, yacc[h][2]);
+              yacc[h][3] = fmaf(s1, acc[h][3] * 16384.0f, yacc[h][3]);
             } else {
+              const float b0 = tb[g * trow + gi], b1 = tb[(g + 8) * trow + gi];
               yacc[h][0] = fmaf(s0, acc[h][0], fmaf(b0, ones[h][0], yacc[h][0]));
               yacc[h][1] = fmaf(s0, acc[h][1], fmaf(b0, ones[h][1], yacc[h][1]));
               yacc[h][2] = fmaf(s1, acc[h][2], fmaf(b1, ones[h][0], yacc[h][2]));
@@ -319,6 +418,14 @@ qmm_gemv_kernel(const GemvParams p) {
             }
           }
         }
+      }
+      // the slot is free again: refill it with the next box this warp will need
+      __syncwarp();
+      if (lane == 0 && issue.chunk < nchunks) {
+        fence_proxy_async();
+        issue_box();
+        ++issued;
+        cursor_next(issue, nchunks, warp, p.K, p.kc, kBoxK);
       }
     }
   }
@@ -330,6 +437,10 @@ qmm_gemv_kernel(const GemvParams p) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) red[(warp * NT * 4 + h * 4 + i) * 32 + lane] = yacc[h][i];
   __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, *abort_flag);
+    return;
+  }
   if (warp == 0) {
 #pragma unroll
     for (int h = 0; h < NT; ++h)
@@ -346,38 +457,42 @@ qmm_gemv_kernel(const GemvParams p) {
 }
 
 template <int QK, typename XT, int NT, int SPG>
-int launch_kernel(const GemvParams& gp, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(gp.M) * (gp.kc + kXPad) * 2 +
-                      static_cast<size_t>(kWarps) * 2 * 4 * 32 * sizeof(float);
+int launch_kernel(const CUtensorMap& wm, const GemvParams& gp, cudaStream_t stream) {
+  const int tgroups = gp.kc / (32 * SPG);
+  const size_t smem = 1024 + static_cast<size_t>(kWarps) * gp.ring * kBoxSmem +
+                      static_cast<size_t>(gp.M) * (gp.kc + kXPad) * 2 +
+                      static_cast<size_t>(2) * kRowsPerCta * (tgroups + 1) * sizeof(float) +
+                      static_cast<size_t>(kWarps) * 2 * 4 * 32 * sizeof(float) +
+                      static_cast<size_t>(kWarps) * kMaxRing * sizeof(uint64_t) + 16;
   dim3 grid(static_cast<unsigned>((gp.N + kRowsPerCta - 1) / kRowsPerCta), static_cast<unsigned>(gp.batch));
   auto kernel = qmm_gemv_kernel<QK, XT, NT, SPG>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
   }
-  kernel<<<grid, kWarps * 32, smem, stream>>>(gp);
+  kernel<<<grid, kWarps * 32, smem, stream>>>(wm, gp);
   count_launch();
   return check_launch("qmm_gemv_kernel");
 }
 
 template <int QK, typename XT, int NT>
-int launch_spg(const GemvParams& gp, cudaStream_t stream) {
+int launch_spg(const CUtensorMap& wm, const GemvParams& gp, cudaStream_t stream) {
   if constexpr (QK == kMx4) {
-    return launch_kernel<QK, XT, NT, 1>(gp, stream);
+    return launch_kernel<QK, XT, NT, 1>(wm, gp, stream);
   } else {
-    if (gp.group_size == 32) return launch_kernel<QK, XT, NT, 1>(gp, stream);
-    if (gp.group_size == 64) return launch_kernel<QK, XT, NT, 2>(gp, stream);
-    return launch_kernel<QK, XT, NT, 4>(gp, stream);
+    if (gp.group_size == 32) return launch_kernel<QK, XT, NT, 1>(wm, gp, stream);
+    if (gp.group_size == 64) return launch_kernel<QK, XT, NT, 2>(wm, gp, stream);
+    return launch_kernel<QK, XT, NT, 4>(wm, gp, stream);
   }
 }
 
 template <int QK>
-int launch_xt(const GemvParams& gp, cudaStream_t stream) {
-  if (gp.x_dtype == QMM_BF16)
-    return gp.M <= 8 ? launch_spg<QK, __nv_bfloat16, 1>(gp, stream) : launch_spg<QK, __nv_bfloat16, 2>(gp, stream);
-  return gp.M <= 8 ? launch_spg<QK, __half, 1>(gp, stream) : launch_spg<QK, __half, 2>(gp, stream);
+int launch_xt(const CUtensorMap& wm, const GemvParams& gp, int x_dtype, cudaStream_t stream) {
+  if (x_dtype == QMM_BF16)
+    return gp.M <= 8 ? launch_spg<QK, __nv_bfloat16, 1>(wm, gp, stream) : launch_spg<QK, __nv_bfloat16, 2>(wm, gp, stream);
+  return gp.M <= 8 ? launch_spg<QK, __half, 1>(wm, gp, stream) : launch_spg<QK, __half, 2>(wm, gp, stream);
 }
 
 }  // namespace
@@ -388,25 +503,45 @@ bool gemv_supports(const qmm_problem& p) {
   if (p.M < 1 || p.M > 16) return false;
   if (p.batch > 65535) return false;
   if (p.K % 32) return false;
+  const int64_t nw = p.num_weights > 0 ? p.num_weights : (p.w_batch_stride ? p.batch : 1);
+  if (nw * p.N >= (1LL << 31)) return false;        // TMA row coordinates are 32-bit
   return true;
 }
 
 int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   GemvParams gp;
-  gp.x = p.x; gp.w = p.w; gp.scales = p.scales; gp.biases = p.biases; gp.y = p.y;
+  gp.x = p.x; gp.scales = p.scales; gp.biases = p.biases; gp.y = p.y;
   gp.lhs_idx = p.lhs_idx; gp.rhs_idx = p.rhs_idx;
+  gp.status = device_status_word();
+  if (!gp.status) return fail(QMM_ERR_CUDA, "could not allocate the device status word");
   gp.M = p.M; gp.K = p.K; gp.N = p.N; gp.batch = p.batch;
   gp.x_batch_stride = p.x_batch_stride; gp.y_batch_stride = p.y_batch_stride;
   gp.w_batch_rows = p.rhs_idx ? p.N : p.w_batch_stride;
   gp.group_size = p.group_size; gp.table_dtype = p.table_dtype; gp.y_dtype = p.y_dtype;
-  gp.x_dtype = p.x_dtype;
-  // K elements staged per pass: the staged activations stay under ~64 KiB per CTA.
+  const int bits = (p.mode == QMM_MODE_AFFINE && p.bits == 8) ? 8 : 4;
+  const int boxk = kBoxBytes * 8 / bits;
+  // K elements staged per pass: the staged activations stay under ~64 KiB per CTA, and a
+  // pass is a whole number of boxes.
   int kc = p.M <= 8 ? 4096 : 2048;
-  if (p.K < kc) kc = static_cast<int>(p.K);
+  const int64_t kround = (p.K + boxk - 1) / boxk * boxk;
+  if (kround < kc) kc = static_cast<int>(kround);
   gp.kc = kc;
-  if (p.mode == QMM_MODE_MXFP4) return launch_xt<kMx4>(gp, stream);
-  if (p.bits == 8) return launch_xt<kAff8>(gp, stream);
-  return launch_xt<kAff4>(gp, stream);
+  // Ring depth: as many boxes as a warp consumes over the whole of K, up to kMaxRing.
+  const int64_t boxes = (p.K + boxk - 1) / boxk;
+  int64_t per_warp = (boxes + kWarps - 1) / kWarps + ((p.K + kc - 1) / kc > 1 ? 1 : 0);
+  gp.ring = static_cast<int>(per_warp < 1 ? 1 : (per_warp > kMaxRing ? kMaxRing : per_warp));
+
+  // The packed weight as a 2-D byte tensor [rows, K*bits/8] over every weight matrix behind
+  // `w`; a box that reaches past the last row is zero-filled by the TMA unit.
+  const uint64_t row_bytes = static_cast<uint64_t>(p.K) * bits / 8;
+  const uint64_t nw = p.num_weights > 0 ? p.num_weights : (p.w_batch_stride ? p.batch : 1);
+  const uint64_t rows = static_cast<uint64_t>(p.N) * nw;
+  CUtensorMap wm;
+  int rc = tensor_map_2d(&wm, QMM_U8, p.w, row_bytes, rows, row_bytes, kBoxBytes, kRowsPerCta, 1);
+  if (rc) return rc;
+  if (p.mode == QMM_MODE_MXFP4) return launch_xt<kMx4>(wm, gp, p.x_dtype, stream);
+  if (p.bits == 8) return launch_xt<kAff8>(wm, gp, p.x_dtype, stream);
+  return launch_xt<kAff4>(wm, gp, p.x_dtype, stream);
 }
 
 }  // namespace qmm

@@ -26,11 +26,48 @@ bool gemm_tc_supports(const qmm_problem& p);
 // Reads (and clears) the tensor-core kernel's device status word; synchronizes the device.
 int gemm_tc_status(int* out);
 
+// Encodes a 2-D TMA descriptor (a CUtensorMap, 128 bytes at `map_out`): `inner` x `outer`
+// elements of kind `elem_kind` (a qmm_elem; QMM_U8 for raw bytes), rows `row_bytes` apart,
+// copied in boxes of box_inner x box_outer, optionally in the 128-byte swizzle.
+int tensor_map_2d(void* map_out, int elem_kind, const void* base, uint64_t inner, uint64_t outer,
+                  uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle128);
+
+// The process-wide device word in which kernels record a bounded wait that ran out.
+int* device_status_word();
+
+int device_sm_count();
+
 int launch_dequantize(const uint32_t* w, const void* scales, const void* biases, int table_dtype,
                       void* out, int out_dtype, int64_t rows, int64_t K, int group_size, int bits,
                       int mode, cudaStream_t stream);
 int launch_pack_codes(const uint8_t* codes, uint32_t* out, int64_t rows, int64_t K, int bits,
                       cudaStream_t stream);
+
+#ifdef __CUDACC__
+// Raw bits of element i of a scale/bias table whose elements are `esz` (2 or 4) bytes wide.
+// Both candidate loads are predicated instead of branched over, so a run of calls issues all
+// of its loads back to back and waits once, not once per element.
+__device__ __forceinline__ uint32_t table_raw(const void* p, int esz, int64_t i) {
+  const char* a = static_cast<const char*>(p) + i * esz;
+  uint32_t v;
+  asm("{ .reg .pred p2; .reg .b16 h; setp.eq.s32 p2, %2, 2; mov.b16 h, 0; mov.b32 %0, 0;\n"
+      "@p2 ld.global.nc.u16 h, [%1];\n @!p2 ld.global.nc.u32 %0, [%1];\n @p2 cvt.u32.u16 %0, h; }"
+      : "=r"(v)
+      : "l"(a), "r"(esz));
+  return v;
+}
+
+// The float value of such raw bits (QMM_BF16 / QMM_F16 / QMM_F32).
+__device__ __forceinline__ float table_value(uint32_t raw, int dtype) {
+  if (dtype == QMM_BF16) return __uint_as_float(raw << 16);
+  if (dtype == QMM_F16) {
+    float f;
+    asm("{ .reg .b16 h; cvt.u16.u32 h, %1; cvt.f32.f16 %0, h; }" : "=f"(f) : "r"(raw));
+    return f;
+  }
+  return __uint_as_float(raw);
+}
+#endif
 
 inline int elem_size(int e) {
   switch (e) {

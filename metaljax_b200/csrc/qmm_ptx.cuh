@@ -1,0 +1,78 @@
+// Thin wrappers over the PTX this library's kernels share: shared-memory mbarriers with
+// bounded waits, and 2-D TMA loads. Device code only.
+#pragma once
+
+#include <cuda.h>
+#include <stdint.h>
+
+namespace qmm {
+namespace ptx {
+
+constexpr long long kSpinLimit = 4000000000LL;  // SM clocks (~2 s) a wait may last
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: false (with `where` recorded in *abort_flag) when the barrier does not flip
+// within kSpinLimit clocks, or as soon as another waiter of the CTA has given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int where) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++spins & 1023) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kSpinLimit) {
+        *abort_flag = where;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Tile (c0 = innermost coordinate, c1 = row) of a 2-D tensor map into shared memory; completion
+// is counted in bytes on `bar`. c0 times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, void* dst, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// Orders this thread's earlier generic-proxy accesses to shared memory before later
+// async-proxy (TMA) writes to the same bytes.
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+}  // namespace ptx
+}  // namespace qmm
