@@ -39,7 +39,6 @@ namespace {
 
 constexpr int kBF = 128;        // features per tile (MMA M, TMEM lanes)
 constexpr int kBK = 64;         // K elements per pipeline stage
-constexpr int kAStages = 8;     // dequantized-A ring in TMEM (32 columns each)
 constexpr int kTeams = 4;        // dequant/epilogue teams of four warps (one per TMEM lane quarter)
 constexpr int kThreads = (2 + 4 * kTeams) * 32;
 constexpr int kMaxSegments = 256;
@@ -156,6 +155,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
+// 32 lanes x 8 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+               QMM_ASM_R(0)
+               : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -218,18 +224,18 @@ struct Half2Ops<__half> {
   }
 };
 
-// 4-bit affine, one 32-element half of the K block (4 words -> 16 pairs). A byte holds
-// elements (2i, 2i+1): PRMT takes it from the word (even element in its low nibble) into
-// byte 0 and from the word shifted right by four (odd element) into byte 2, one LOP3 keeps
-// the two nibbles under the magic exponent (128 + q, or 1024 + q for f16, both exact), an
-// exact subtraction removes the magic, and one FMA with (s, s), (b, b) rounds once.
-template <typename XT>
-__device__ __forceinline__ void dequant_aff4(const uint32_t (&w)[4], float s, float b, uint32_t* out) {
+// 4-bit affine, NW packed words -> NW*4 pairs. A byte holds elements (2i, 2i+1): PRMT takes
+// it from the word (even element in its low nibble) into byte 0 and from the word shifted
+// right by four (odd element) into byte 2, one LOP3 keeps the two nibbles under the magic
+// exponent (128 + q, or 1024 + q for f16, both exact), an exact subtraction removes the
+// magic, and one FMA with (s, s), (b, b) rounds once.
+template <typename XT, int NW>
+__device__ __forceinline__ void dequant_aff4(const uint32_t (&w)[NW], float s, float b, uint32_t* out) {
   using H = Half2Ops<XT>;
   const uint32_t s2 = H::pack(s, s);
   const uint32_t b2 = H::pack(b, b);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < NW; ++j) {
     const uint32_t hi = w[j] >> 4;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -240,13 +246,13 @@ __device__ __forceinline__ void dequant_aff4(const uint32_t (&w)[4], float s, fl
   }
 }
 
-// 8-bit affine, one 32-element half of the K block (8 words): float32 FMA per element,
-// rounded to the 16-bit type in pairs.
-template <typename XT>
-__device__ __forceinline__ void dequant_aff8(const uint32_t (&w)[8], float s, float b, uint32_t* out) {
+// 8-bit affine, NW packed words -> NW*2 pairs: float32 FMA per element, rounded to the
+// 16-bit type in pairs.
+template <typename XT, int NW>
+__device__ __forceinline__ void dequant_aff8(const uint32_t (&w)[NW], float s, float b, uint32_t* out) {
   using H = Half2Ops<XT>;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < NW; ++j) {
     float q[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e)
@@ -256,12 +262,12 @@ __device__ __forceinline__ void dequant_aff8(const uint32_t (&w)[8], float s, fl
   }
 }
 
-// MXFP4, one 32-element group (4 words -> 16 pairs). The three magnitude bits of a code,
-// placed at the 16-bit type's exponent/mantissa boundary, are the E2M1 value scaled by
+// MXFP4, NW packed words of one 32-element group -> NW*4 pairs. The three magnitude bits of a
+// code, placed at the 16-bit type's exponent/mantissa boundary, are the E2M1 value scaled by
 // 2^-126 (bf16) or 2^-14 (f16), including the subnormal code 1 = 0.5; two exact power-of-two
 // multiplies undo that and apply the group's E8M0 scale.
-template <typename XT>
-__device__ __forceinline__ void dequant_mx4(const uint32_t (&w)[4], uint32_t e8, uint32_t* out) {
+template <typename XT, int NW>
+__device__ __forceinline__ void dequant_mx4(const uint32_t (&w)[NW], uint32_t e8, uint32_t* out) {
   using H = Half2Ops<XT>;
   constexpr bool kBf = std::is_same<XT, __nv_bfloat16>::value;
   constexpr int kShift = kBf ? 6 : 9;  // magnitude bit 0 -> top mantissa bit
@@ -270,12 +276,12 @@ __device__ __forceinline__ void dequant_mx4(const uint32_t (&w)[4], uint32_t e8,
   const float sc = __uint_as_float(e8 ? (e8 << 23) : 0x00400000u);
   const uint32_t s2 = H::pack(sc, sc);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < NW; ++j) {
     const uint32_t hi = w[j] >> 4;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       // byte 0 <- byte i of w (even element in its low nibble), byte 2 <- byte i of w>>4
-      const uint32_t t = __byte_perm(w[j], hi, 0x0000u | i | ((4 + i) << 8)) & 0x000F000Fu;
+      const uint32_t t = __byte_perm(w[j], hi, i | ((4 + i) << 8)) & 0x000F000Fu;
       const uint32_t bits = ((t & 0x00070007u) << kShift) | ((t & 0x00080008u) << 12);
       out[j * 4 + i] = H::mul(H::mul(bits, u2), s2);
     }
@@ -310,7 +316,10 @@ struct Plan {
   static constexpr int kXBytes = BT * kBK * 2;                // one activation stage
   static constexpr int kWBytes = kBF * kWRowBytes;            // one packed-weight stage
   static constexpr int kStageBytes = kXBytes + kWBytes;
-  static constexpr int kStages = (BT >= 256) ? 5 : 6;
+  // as many stages as fit next to the barriers and the tile tables, at most 8 (the
+  // dequantized-A ring in TMEM has one 32-column slot per stage)
+  static constexpr int kFit = (232448 - 4200 - 2048) / kStageBytes;
+  static constexpr int kStages = kFit > 8 ? 8 : kFit;
   static constexpr int kBarBytes = 1024;
   static constexpr int kSmem = kStages * kStageBytes + kBarBytes + 1024 /* alignment slack */;
   static constexpr int kDCols = BT;                           // accumulator columns
@@ -356,9 +365,8 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
   uint8_t* bar_base = smem + P::kStages * P::kStageBytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);      // [kStages] TMA landed
   uint64_t* empty = full + P::kStages;                         // [kStages] stage consumed
-  uint64_t* a_full = empty + P::kStages;                       // [kAStages] A written to TMEM
-  uint64_t* a_empty = a_full + kAStages;                       // [kAStages] A consumed by MMA
-  uint64_t* d_full = a_empty + kAStages;                       // accumulator complete
+  uint64_t* a_full = empty + P::kStages;                       // [kStages] dequantized A is in TMEM
+  uint64_t* d_full = a_full + P::kStages;                      // accumulator complete
   uint64_t* d_empty = d_full + 1;                              // accumulator drained
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -388,10 +396,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1 + 4);
     }
-    for (int i = 0; i < kAStages; ++i) {
-      mbar_init(&a_full[i], 4);
-      mbar_init(&a_empty[i], 1);
-    }
+    for (int i = 0; i < P::kStages; ++i) mbar_init(&a_full[i], 4);
     mbar_init(d_full, 1);
     mbar_init(d_empty, 4 * kTeams);
     *abort_flag = 0;
@@ -446,33 +451,39 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(std::is_same<XT, __nv_bfloat16>::value ? 1 : 0, kBF, BT);
-      uint32_t it = 0, tile_n = 0;
-      TileInfo ti;
-      bool ok = true;
-      for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, &ti);
-           t += gridDim.x, ++tile_n) {
-        if (!(ok = twait(d_empty, (tile_n & 1) ^ 1, abort_flag, 2))) break;
+    // The whole warp walks the loop so that stage indices, descriptors and TMEM addresses
+    // are warp-uniform values; one lane issues the tensor-core instructions.
+    constexpr uint32_t idesc = instr_desc(std::is_same<XT, __nv_bfloat16>::value ? 1 : 0, kBF, BT);
+    uint32_t tile_n = 0, ph = 0;
+    int s = 0;
+    TileInfo ti;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, &ti);
+         t += gridDim.x, ++tile_n) {
+      if (!(ok = twait(d_empty, (tile_n & 1) ^ 1, abort_flag, 2))) break;
+      tc_fence_after();
+      for (int kb = 0; kb < num_kb; ++kb) {
+        // The dequantized A of this K block sits in TMEM slot s, the slot of its shared-
+        // memory stage. Its writers waited for the stage's TMA barrier themselves, so
+        // their barrier also says that the activation tile has landed.
+        if (!(ok = twait(&a_full[s], ph, abort_flag, 4))) break;
+        const long long tf0 = tracing ? clock64() : 0;
         tc_fence_after();
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % P::kStages, a = it % kAStages;
-          if (!(ok = twait(&full[s], (it / P::kStages) & 1, abort_flag, 3))) break;
-          if (!(ok = twait(&a_full[a], (it / kAStages) & 1, abort_flag, 4))) break;
-          tc_fence_after();
-          const long long ti0 = tracing ? clock64() : 0;
-          const uint64_t bdesc = smem_desc_sw128(smem_u32(smem + s * P::kStageBytes));
-          const uint32_t acol = tmem_base + P::kACol0 + a * 32;
+        const long long ti0 = tracing ? clock64() : 0;
+        if (tracing) waited[3] += ti0 - tf0;         // cycles in the fence
+        const uint64_t bdesc = smem_desc_sw128(smem_u32(smem + s * P::kStageBytes));
+        const uint32_t acol = tmem_base + P::kACol0 + s * 32;
+        if (lane == 0) {
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k)
             tc_mma_ts(tmem_base, acol + k * 8, bdesc + static_cast<uint64_t>(k * 2), idesc,
                       (kb | k) ? 1u : 0u);
-          tc_commit(&empty[s]);
-          tc_commit(&a_empty[a]);
-          if (tracing) waited[0] += clock64() - ti0;   // cycles spent issuing
+          tc_commit(&empty[s]);     // frees the stage and its TMEM slot together
         }
-        if (ok) tc_commit(d_full);
+        if (tracing) waited[0] += clock64() - ti0;   // cycles spent issuing
+        if (++s == P::kStages) { s = 0; ph ^= 1u; }
       }
+      if (ok && lane == 0) tc_commit(d_full);
     }
   } else {
     // ---------------- dequant + epilogue warps ----------------
@@ -490,43 +501,47 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       const bool feat_ok = feat < p.N;
       if (!feat_ok) feat = p.N - 1;
       const int64_t trow = (ti.seg * p.w_seg_rows + feat) * groups;   // row of the scale tables
-      // This team's K blocks of the tile are those whose global iteration index has the
-      // team's residue. The per-group constants of a block are requested one block ahead,
-      // so their global-memory latency hides behind the previous block's work.
-      const uint32_t it0 = it;
+      // The teams take the tile's K blocks round-robin (block kb belongs to the team whose
+      // number is the block's global iteration index modulo kTeams). The per-group constants
+      // of a block are requested one of the team's blocks ahead, so their global-memory
+      // latency hides behind the previous block's work.
       const int tsize = (p.table_dtype == QMM_F32) ? 4 : 2;
       auto fetch_tables = [&](int kbb, float (&fs)[2], float (&fb)[2], uint32_t (&fe)[2]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           int64_t g = (kbb * kBK + h * 32) / p.group_size;
           if (g >= groups) g = groups - 1;
+          fs[h] = fb[h] = 0.0f;
+          fe[h] = 0u;
           if constexpr (QK == kMx4) {
             fe[h] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + trow + g);
-            fs[h] = fb[h] = 0.0f;
           } else {
             fs[h] = __uint_as_float(table_raw(p.scales, tsize, trow + g));   // raw bits until used
             fb[h] = __uint_as_float(table_raw(p.biases, tsize, trow + g));
-            fe[h] = 0;
           }
         }
       };
+      constexpr int kHalfWords = P::kWRowBytes / 8;                // packed words per 32 elements
+      const uint32_t it0 = it;
       int kb = static_cast<int>((static_cast<uint32_t>(team) + kTeams - (it0 % kTeams)) % kTeams);
-      float sc[2] = {0.0f, 0.0f}, bi[2] = {0.0f, 0.0f};
-      uint32_t e8[2] = {0u, 0u};
+      float sc[2], bi[2];
+      uint32_t e8[2];
       if (kb < num_kb) fetch_tables(kb, sc, bi, e8);
       for (; kb < num_kb; kb += kTeams) {
         it = it0 + static_cast<uint32_t>(kb);
-        const int s = it % P::kStages, a = it % kAStages;
+        const int s = it % P::kStages;
         float nsc[2] = {0.0f, 0.0f}, nbi[2] = {0.0f, 0.0f};
         uint32_t ne8[2] = {0u, 0u};
         if (kb + kTeams < num_kb) fetch_tables(kb + kTeams, nsc, nbi, ne8);
         if (!(ok = twait(&full[s], (it / P::kStages) & 1, abort_flag, 5))) break;
         const uint8_t* wsm = smem + s * P::kStageBytes + P::kXBytes + frow * P::kWRowBytes;
-        uint32_t packed[P::kWRowBytes / 4];
+        uint32_t packed[2][kHalfWords];
 #pragma unroll
         for (int i = 0; i < P::kWRowBytes / 16; ++i) {
           const uint4 v = *reinterpret_cast<const uint4*>(wsm + i * 16);
-          packed[i * 4] = v.x; packed[i * 4 + 1] = v.y; packed[i * 4 + 2] = v.z; packed[i * 4 + 3] = v.w;
+          const uint32_t q4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) packed[(i * 4 + e) / kHalfWords][(i * 4 + e) % kHalfWords] = q4[e];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);     // this warp's share of the stage is in registers
@@ -534,32 +549,30 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if constexpr (QK == kAff4) {
-            const uint32_t (&w4)[4] = *reinterpret_cast<const uint32_t (*)[4]>(&packed[h * 4]);
-            dequant_aff4<XT>(w4, table_value(__float_as_uint(sc[h]), p.table_dtype),
-                             table_value(__float_as_uint(bi[h]), p.table_dtype), &out[h * 16]);
+            dequant_aff4<XT, kHalfWords>(packed[h], table_value(__float_as_uint(sc[h]), p.table_dtype),
+                                         table_value(__float_as_uint(bi[h]), p.table_dtype), &out[h * 16]);
           } else if constexpr (QK == kAff8) {
-            const uint32_t (&w8)[8] = *reinterpret_cast<const uint32_t (*)[8]>(&packed[h * 8]);
-            dequant_aff8<XT>(w8, table_value(__float_as_uint(sc[h]), p.table_dtype),
-                             table_value(__float_as_uint(bi[h]), p.table_dtype), &out[h * 16]);
+            dequant_aff8<XT, kHalfWords>(packed[h], table_value(__float_as_uint(sc[h]), p.table_dtype),
+                                         table_value(__float_as_uint(bi[h]), p.table_dtype), &out[h * 16]);
           } else {
-            const uint32_t (&w4)[4] = *reinterpret_cast<const uint32_t (*)[4]>(&packed[h * 4]);
-            dequant_mx4<XT>(w4, e8[h], &out[h * 16]);
+            dequant_mx4<XT, kHalfWords>(packed[h], e8[h], &out[h * 16]);
           }
         }
-        if (!(ok = twait(&a_empty[a], ((it / kAStages) & 1) ^ 1, abort_flag, 6))) break;
+        // TMEM slot s is free: the TMA for this stage was only issued after the MMAs that
+        // read the slot's previous contents had completed (the producer waited for them).
         tc_fence_after();
         const long long ts0 = tracing ? clock64() : 0;
-        tmem_st32(tmem_base + lane_addr + P::kACol0 + a * 32, out);
+        tmem_st32(tmem_base + lane_addr + P::kACol0 + s * 32, out);
         tmem_wait_st();
         if (tracing) waited[0] += clock64() - ts0;   // cycles in tcgen05.st + wait
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&a_full[a]);
+        if (lane == 0) mbar_arrive(&a_full[s]);
 #pragma unroll
         for (int h = 0; h < 2; ++h) { sc[h] = nsc[h]; bi[h] = nbi[h]; e8[h] = ne8[h]; }
       }
-      if (!ok) break;
       it = it0 + static_cast<uint32_t>(num_kb);
+      if (!ok) break;
       // ---- epilogue: the teams drain disjoint 32-column chunks of the accumulator ----
       if (!(ok = twait(d_full, tile_n & 1, abort_flag, 7))) break;
       tc_fence_after();
@@ -723,7 +736,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
       for (int i = 0; i < 16; ++i) avg[i] += static_cast<double>(host[c * 16 + i]) / grid;
     fprintf(stderr, "qmm_gemm_tc CTA lifetime %.0f cycles, %.1f us -> %.0f MHz\n", avg[14], avg[15] / 1e3,
             avg[14] / (avg[15] / 1e3));
-    fprintf(stderr, "qmm_gemm_tc cycles/CTA: producer.empty %.0f | mma.issue %.0f mma.d_empty %.0f mma.full %.0f mma.a_full %.0f |"
+    fprintf(stderr, "qmm_gemm_tc cycles/CTA: producer.empty %.0f | mma.issue %.0f mma.d_empty %.0f mma.fence %.0f mma.a_full %.0f |"
             " dequant.st %.0f dequant.full %.0f dequant.a_empty %.0f dequant.d_full %.0f\n",
             avg[1], avg[8], avg[8 + 2], avg[8 + 3], avg[8 + 4], avg[0], avg[5], avg[6], avg[7]);
   }
