@@ -176,6 +176,7 @@ def cpu_baseline(name, budget_rows=None):
     from oracle import qmm_oracle as O
     import ml_dtypes
     m, k, n, gs, bits, mode = WORKLOADS[name]
+    clib.use_all_cores()
     rng = np.random.default_rng(0)
     rows = min(m, budget_rows or (64 if m > 1 else 1))
     w = rng.integers(0, 1 << 32, size=(n, k * bits // 32), dtype=np.uint64).astype(np.uint32)

@@ -37,6 +37,12 @@ def lib():
     return _lib
 
 
+def use_all_cores() -> int:
+    """Run the C loops on every host core, whatever OMP_NUM_THREADS a launcher exported."""
+    lib().oracle_set_threads(os.cpu_count() or 1)
+    return num_threads()
+
+
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
 

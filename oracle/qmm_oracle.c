@@ -49,6 +49,15 @@ static inline float load_elem(const void* p, int dtype, long i) {
   return dtype == 2 ? ((const float*)p)[i] : bf16_to_f32(((const uint16_t*)p)[i]);
 }
 
+/* Use `n` threads from now on (a launcher may have pinned OMP_NUM_THREADS to 1). */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

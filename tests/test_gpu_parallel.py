@@ -1,0 +1,82 @@
+"""The two multi-GPU shardings on real GPUs (NCCL, one process per GPU): a column-parallel
+decode product with its all-gather, and the expert-parallel mixture-of-experts block with its
+token all-to-all, each against the oracle. Skipped when fewer than two GPUs are visible."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    import torch.distributed as dist
+    from helpers import activations, affine_case, to_numpy, to_torch
+    from metaljax_b200 import _lib, parallel
+    from oracle import qmm_oracle as O
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        rng = np.random.default_rng(0)                   # identical draws on every rank
+        # column-parallel linear at decode and prefill sizes
+        n, k = 1000, 512
+        _, w, s, b = affine_case(rng, n, k, 64, 4, "bf16")
+        lin = parallel.ColumnParallelLinear(to_torch(w, dev), to_torch(s, dev), to_torch(b, dev))
+        for m in (1, 7, 96):
+            x = activations(rng, (m, k))
+            y = lin(to_torch(x, dev))
+            err = O.rel_err(to_numpy(y).astype(np.float32), O.qmm_exact(x, w, s, b, 64, 4))
+            assert tuple(y.shape) == (m, n) and err <= 1e-2, (m, err)
+        # expert-parallel MoE: every rank routes its own tokens
+        e, kk, d, f, t = 4, 2, 128, 256, 40 + 8 * rank
+        packs = [affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:],
+                 affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:],
+                 affine_case(rng, d, f, 64, 4, "bf16", lead=(e,))[1:]]
+        moe = parallel.ExpertParallelMoE(*[tuple(to_torch(a, dev) for a in p) for p in packs])
+        rr = np.random.default_rng(100 + rank)
+        x = activations(rr, (t, d), "bf16", 0.5)
+        idx, wts = O.topk_router(rr.standard_normal((t, e)).astype(np.float32), kk)
+        y = moe(to_torch(x, dev), torch.from_numpy(idx).to(dev), torch.from_numpy(wts).to(dev))
+        tidx, eidx = np.repeat(np.arange(t), kk), idx.reshape(-1)
+        gate = O.gather_qmm_exact(x[:, None, :], *packs[0], tidx, eidx)[:, 0]
+        up = O.gather_qmm_exact(x[:, None, :], *packs[1], tidx, eidx)[:, 0]
+        act = (gate / (1 + np.exp(-gate))) * up
+        down = O.gather_qmm_exact(act[:, None, :], *packs[2], np.arange(len(tidx)), eidx)[:, 0]
+        want = O.moe_combine_exact(down, wts)
+        err = O.rel_err(to_numpy(y).astype(np.float32), want)
+        assert err <= 2e-2, err                           # two bf16 hand-offs inside the block
+        assert _lib.poll_status() == 0
+        ret[rank] = "ok"
+    except Exception as exc:                              # surfaced by the parent
+        ret[rank] = repr(exc)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_ranks():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+        assert not p.is_alive(), "rank did not finish"
+    assert dict(ret) == {0: "ok", 1: "ok"}, dict(ret)
