@@ -15,14 +15,18 @@
 // bias are applied to the accumulators once per group:
 //     y += s * sum (C + q) x  +  (b - C s) * sum x ,
 // with  sum x  taken from one more MMA whose A fragment is all ones. The activations are
-// staged once per CTA in shared memory in the MMA's element type (for 4-bit codes in the pair
-// order the magic-number extraction produces), tokens beyond M being zero fragments, next to
-// the CTA's slice of the scale table and of the folded bias table  b - C s.
+// staged in shared memory in the MMA's element type (for 4-bit codes in the pair order the
+// magic-number extraction produces), tokens beyond M being zero fragments, next to the
+// tile's slice of the scale table and of the folded bias table  b - C s.
 // MXFP4 places each code's magnitude bits at the f16 exponent/mantissa boundary (the E2M1
 // value times 2^-14, exactly) and scales the accumulators per 32-group by 2^(e8-127+14).
 //
-// The K split is reduced across the CTA's warps in shared memory; there is no global scratch
-// and no atomics, and the summation order is fixed. Waits on the TMA barriers are bounded.
+// CTAs are persistent: a CTA walks 16-row tiles with a grid stride, keeps the staged
+// activations for all of them, requests the next tile's tables
+// while it computes the current one, and its warps' TMA rings run ahead across tile
+// boundaries. The K split is reduced across the CTA's warps in shared memory; there is no
+// global scratch and no atomics, and the summation order is fixed. Waits on the TMA barriers
+// are bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -59,6 +63,7 @@ struct GemvParams {
   int group_size, table_dtype, y_dtype;
   int kc;     // K elements staged per pass (a multiple of the box width)
   int ring;   // boxes per warp ring (1..kMaxRing)
+  int tiles;  // 16-row tiles per weight matrix
 };
 
 template <typename AT>
@@ -130,32 +135,36 @@ __device__ __forceinline__ void load8(const XT* p, float (&f)[8]) {
   }
 }
 
-// Walks one warp's boxes in the order they are consumed: chunk by chunk (a chunk is what the
-// CTA stages of x at a time), and inside a chunk the warp's contiguous share of its boxes.
+// Walks one warp's boxes in the order they are consumed: tile by tile (grid stride), inside a
+// tile chunk by chunk (a chunk is what the CTA stages of x at a time), and inside a chunk the
+// warp's contiguous share of its boxes.
 struct BoxCursor {
-  int chunk, j, hi;
+  int tile, chunk, j, hi;
 };
 
-__device__ __forceinline__ int boxes_in_chunk(int chunk, int64_t K, int kc, int boxk) {
-  const int64_t left = K - static_cast<int64_t>(chunk) * kc;
-  const int64_t span = left < kc ? left : kc;
-  return static_cast<int>((span + boxk - 1) / boxk);
-}
-
-__device__ __forceinline__ void cursor_seek(BoxCursor& c, int nchunks, int warp, int64_t K, int kc, int boxk) {
-  while (c.chunk < nchunks) {
-    const int nb = boxes_in_chunk(c.chunk, K, kc, boxk);
-    c.j = nb * warp / kWarps;
-    c.hi = nb * (warp + 1) / kWarps;
-    if (c.j < c.hi) return;
-    ++c.chunk;
+template <int BOXK>
+__device__ __forceinline__ void cursor_seek(BoxCursor& c, int ntiles, int tstride, int nchunks, int warp,
+                                            int K, int kc) {
+  while (c.tile < ntiles) {
+    while (c.chunk < nchunks) {
+      const int left = K - c.chunk * kc;                    // 32-bit on purpose: no 64-bit division
+      const int nb = ((left < kc ? left : kc) + BOXK - 1) / BOXK;
+      c.j = nb * warp / kWarps;
+      c.hi = nb * (warp + 1) / kWarps;
+      if (c.j < c.hi) return;
+      ++c.chunk;
+    }
+    c.tile += tstride;
+    c.chunk = 0;
   }
 }
 
-__device__ __forceinline__ void cursor_next(BoxCursor& c, int nchunks, int warp, int64_t K, int kc, int boxk) {
+template <int BOXK>
+__device__ __forceinline__ void cursor_next(BoxCursor& c, int ntiles, int tstride, int nchunks, int warp,
+                                            int K, int kc) {
   if (++c.j < c.hi) return;
   ++c.chunk;
-  cursor_seek(c, nchunks, warp, K, kc, boxk);
+  cursor_seek<BOXK>(c, ntiles, tstride, nchunks, warp, K, kc);
 }
 
 // QK: quantization kind. XT: activation type in memory. NT: token halves (1: M <= 8,
@@ -171,6 +180,7 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   constexpr int kBoxK = kBoxBytes * 8 / BITS;      // K elements per box: 256 or 128
   constexpr int kStepsPerBox = kBoxK / 32;         // 8 or 4
   constexpr int kGroupK = 32 * SPG;
+  constexpr int kTU = 4;                           // table loads per thread kept in flight
 
   extern __shared__ uint8_t gv_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gv_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -179,14 +189,13 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   const int ring = p.ring;
   const int xrow = p.kc + kXPad;                   // staged row stride in elements
   const int tgroups = p.kc / kGroupK;              // groups staged per pass
-  const int trow = tgroups + 1;                    // table row stride in floats (odd: no conflicts)
+  const int trow = tgroups + 1;                    // table row stride in float2 (odd: no conflicts)
 
   uint8_t* wring = smem + warp * ring * kBoxSmem;                                    // this warp's boxes
   AT* xs = reinterpret_cast<AT*>(smem + kWarps * ring * kBoxSmem);
-  float* ts = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + static_cast<size_t>(p.M) * xrow * sizeof(AT));
-  float* tb = ts + kRowsPerCta * trow;
-  float* red = tb + kRowsPerCta * trow;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(red + kWarps * 2 * 4 * 32);
+  float2* tbl = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(xs) + static_cast<size_t>(p.M) * xrow * sizeof(AT));
+  float* red = reinterpret_cast<float*>(tbl + 2 * kRowsPerCta * trow);   // two buffers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + 2 * kWarps * NT * 4 * 32);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kWarps * kMaxRing);
   uint64_t* full = bars + warp * kMaxRing;
 
@@ -201,11 +210,11 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   }
   const int64_t y_off = seg * p.y_batch_stride;
   const XT* xg = reinterpret_cast<const XT*>(p.x) + x_off;
-  const int64_t n0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta;
-  const int wrow0 = static_cast<int>(wb * p.N + n0);            // first weight row of this CTA
   const int64_t groups = p.K / kGroupK;
   const int nchunks = static_cast<int>((p.K + p.kc - 1) / p.kc);
   const int boxes_per_chunk = p.kc / kBoxK;
+  const int ntiles = p.tiles, tstride = gridDim.x;
+  const int tsize = (p.table_dtype == QMM_F32) ? 4 : 2;
 
   // Each warp owns its barriers: it initializes them itself and nobody else touches them.
   if (lane == 0) {
@@ -216,243 +225,266 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   __syncwarp();
 
   // ---- request this warp's first boxes before anything else ----
-  BoxCursor issue = {0, 0, 0};
-  cursor_seek(issue, nchunks, warp, p.K, p.kc, kBoxK);
+  BoxCursor issue = {static_cast<int>(blockIdx.x), 0, 0, 0};
+  cursor_seek<kBoxK>(issue, ntiles, tstride, nchunks, warp, static_cast<int>(p.K), p.kc);
   int issued = 0;
   auto issue_box = [&]() {   // lane 0 only
     const int slot = issued % ring;
     mbar_expect_tx(&full[slot], kBoxSmem);
     tma_load_2d(&w_map, wring + slot * kBoxSmem, &full[slot],
-                (issue.chunk * boxes_per_chunk + issue.j) * kBoxBytes, wrow0);
+                (issue.chunk * boxes_per_chunk + issue.j) * kBoxBytes,
+                static_cast<int>(wb * p.N) + issue.tile * kRowsPerCta);
+    ++issued;
+    cursor_next<kBoxK>(issue, ntiles, tstride, nchunks, warp, static_cast<int>(p.K), p.kc);
   };
-  if (lane == 0) {
-    while (issued < ring && issue.chunk < nchunks) {
-      issue_box();
-      ++issued;
-      cursor_next(issue, nchunks, warp, p.K, p.kc, kBoxK);
-    }
-  }
+  if (lane == 0)
+    while (issued < ring && issue.tile < ntiles) issue_box();
 
-  float yacc[NT][4];
+  // ---- staging helpers ----
+  // Activations of one chunk. Items are (token, 8-element piece). When the MMA's element type
+  // is the activations' own, a piece is only re-paired with byte permutes; otherwise it is
+  // converted through float32.
+  auto stage_x = [&](int64_t kbase, int kc, int kfill) {
+    constexpr int kXU = 4;
+    const int pieces = kfill / 8;
+    const int pieces_pad = (pieces + 31) & ~31;
+    const float inv_pad = 1.0f / static_cast<float>(pieces_pad);
+    const int items = static_cast<int>(p.M) * pieces_pad;
+    for (int e0 = threadIdx.x; e0 < items; e0 += blockDim.x * kXU) {
+      uint4 raw[kXU];
+      int mm[kXU], pc[kXU];
 #pragma unroll
-  for (int h = 0; h < NT; ++h)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) yacc[h][i] = 0.0f;
-
-  int consumed = 0;
-  bool ok = true;
-  const int tsize = (p.table_dtype == QMM_F32) ? 4 : 2;
-  for (int chunk = 0; chunk < nchunks; ++chunk) {
-    const int64_t kbase = static_cast<int64_t>(chunk) * p.kc;
-    const int kc = static_cast<int>(p.K - kbase < p.kc ? p.K - kbase : p.kc);     // multiple of 32
-    const int nb = (kc + kBoxK - 1) / kBoxK;
-    const int kfill = nb * kBoxK;                                                 // zero-padded extent
-    const int cgroups = kc / kGroupK;
-    // ---- stage x[0:M, kbase : kbase+kc] and the tables of this CTA's 16 rows ----
-    __syncthreads();
-    {
-      // Tables first: thread (r, c) of a 16 x 16 arrangement takes groups c, c+16, ... of row
-      // r. All of a pass's loads are requested before the first one is used.
-      const int r = threadIdx.x >> 4, c = threadIdx.x & 15;
-      const int64_t row = wb * p.N + (n0 + r < p.N ? n0 + r : p.N - 1);
-      const int64_t ti0 = row * groups + kbase / kGroupK;
-      constexpr int kTU = 4;
-      for (int g0 = c; g0 < cgroups; g0 += 16 * kTU) {
-        uint32_t rs[kTU], rb[kTU];
-#pragma unroll
-        for (int u = 0; u < kTU; ++u) {
-          const int gi = g0 + 16 * u;
-          rs[u] = rb[u] = 0u;
-          if (gi < cgroups) {
-            if constexpr (QK == kMx4) {
-              rs[u] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + ti0 + gi);
-            } else {
-              rs[u] = table_raw(p.scales, tsize, ti0 + gi);
-              rb[u] = table_raw(p.biases, tsize, ti0 + gi);
-            }
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < kTU; ++u) {
-          const int gi = g0 + 16 * u;
-          if (gi < cgroups) {
-            if constexpr (QK == kMx4) {
-              ts[r * trow + gi] = __uint_as_float(rs[u] ? (rs[u] << 23) : 0x00400000u);   // 2^(e8-127)
-            } else {
-              const float sv = table_value(rs[u], p.table_dtype);
-              ts[r * trow + gi] = sv;
-              tb[r * trow + gi] = table_value(rb[u], p.table_dtype) - Ops::kMagicValue * sv;
-            }
-          }
-        }
+      for (int u = 0; u < kXU; ++u) {
+        const int e = e0 + u * blockDim.x;
+        mm[u] = __float2int_rz((static_cast<float>(e) + 0.5f) * inv_pad);
+        pc[u] = e - mm[u] * pieces_pad;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (e < items && pc[u] * 8 < kc)
+          raw[u] = __ldg(reinterpret_cast<const uint4*>(xg + static_cast<int64_t>(mm[u]) * p.K + kbase + pc[u] * 8));
       }
-      // Activations: items are (token, 8-element piece). When the MMA's element type is the
-      // activations' own, a piece is only re-paired with byte permutes; otherwise it is
-      // converted through float32.
-      constexpr int kXU = 4;
-      const int pieces = kfill / 8;
-      const float inv_pieces = 1.0f / static_cast<float>(pieces);
-      const int items = static_cast<int>(p.M) * pieces;
-      for (int e0 = threadIdx.x; e0 < items; e0 += blockDim.x * kXU) {
-        uint4 raw[kXU];
-        int mm[kXU], pc[kXU];
 #pragma unroll
-        for (int u = 0; u < kXU; ++u) {
-          const int e = e0 + u * blockDim.x;
-          mm[u] = __float2int_rz((static_cast<float>(e) + 0.5f) * inv_pieces);
-          pc[u] = e - mm[u] * pieces;
-          raw[u] = make_uint4(0u, 0u, 0u, 0u);
-          if (e < items && pc[u] * 8 < kc)
-            raw[u] = __ldg(reinterpret_cast<const uint4*>(xg + static_cast<int64_t>(mm[u]) * p.K + kbase + pc[u] * 8));
-        }
-#pragma unroll
-        for (int u = 0; u < kXU; ++u) {
-          if (e0 + u * blockDim.x < items) {
-            uint4 o;
-            if constexpr (std::is_same<AT, XT>::value) {
-              if constexpr (QK == kAff4) {  // pair order (0,4)(1,5)(2,6)(3,7): what one LOP3 extracts
-                o.x = __byte_perm(raw[u].x, raw[u].z, 0x5410); o.y = __byte_perm(raw[u].x, raw[u].z, 0x7632);
-                o.z = __byte_perm(raw[u].y, raw[u].w, 0x5410); o.w = __byte_perm(raw[u].y, raw[u].w, 0x7632);
-              } else {
-                o = raw[u];
-              }
-            } else {                        // bf16 activations, f16 MMA
-              const uint32_t r4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-              uint32_t c4[4];
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                c4[i] = pack_pair<AT>(__uint_as_float(r4[i] << 16), __uint_as_float(r4[i] & 0xffff0000u));
-              o = make_uint4(c4[0], c4[1], c4[2], c4[3]);
+      for (int u = 0; u < kXU; ++u) {
+        if (e0 + u * static_cast<int>(blockDim.x) - lane < items) {     // whole warps only
+          uint4 o;
+          if constexpr (std::is_same<AT, XT>::value) {
+            if constexpr (QK == kAff4) {  // pair order (0,4)(1,5)(2,6)(3,7): what one LOP3 extracts
+              o.x = __byte_perm(raw[u].x, raw[u].z, 0x5410); o.y = __byte_perm(raw[u].x, raw[u].z, 0x7632);
+              o.z = __byte_perm(raw[u].y, raw[u].w, 0x5410); o.w = __byte_perm(raw[u].y, raw[u].w, 0x7632);
+            } else {
+              o = raw[u];
             }
-            *reinterpret_cast<uint4*>(xs + mm[u] * xrow + pc[u] * 8) = o;
+          } else {                        // bf16 activations, f16 MMA
+            const uint32_t r4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+            uint32_t c4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              c4[i] = pack_pair<AT>(__uint_as_float(r4[i] << 16), __uint_as_float(r4[i] & 0xffff0000u));
+            o = make_uint4(c4[0], c4[1], c4[2], c4[3]);
           }
+          if (pc[u] < pieces) *reinterpret_cast<uint4*>(xs + mm[u] * xrow + pc[u] * 8) = o;
         }
       }
     }
-    __syncthreads();
+  };
 
-    // ---- this warp's boxes of the chunk ----
-    const int jlo = nb * warp / kWarps, jhi = nb * (warp + 1) / kWarps;
-    for (int j = jlo; j < jhi && ok; ++j, ++consumed) {
-      const int slot = consumed % ring;
-      if (!(ok = mbar_wait(&full[slot], (consumed / ring) & 1, abort_flag, 11))) break;
-      const uint8_t* box = wring + slot * kBoxSmem;
-      const uint8_t* row0 = box + g * kBoxBytes;
-      const uint8_t* row1 = box + (g + 8) * kBoxBytes;
+  // Tables of one tile's 16 rows for one chunk: thread (r, c) of a 16 x 16 arrangement takes
+  // groups c, c+16, ... of row r. `load` requests kTU of them, `store` converts and writes
+  // (scale, bias - C*scale) pairs; the two halves can be separated by other work.
+  const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
+  auto table_load = [&](int tile, int64_t kbase, int cgroups, int g0, uint32_t (&rs)[kTU], uint32_t (&rb)[kTU]) {
+    const int64_t n0 = static_cast<int64_t>(tile) * kRowsPerCta;
+    const int64_t row = wb * p.N + (n0 + tr < p.N ? n0 + tr : p.N - 1);
+    const int64_t ti0 = row * groups + kbase / kGroupK;
 #pragma unroll
-      for (int q = 0; q < kStepsPerBox / SPG; ++q) {          // groups of this box
-        const int gi = (j * kBoxK) / kGroupK + q;             // group index within the chunk
-        if (gi < cgroups) {
-          float acc[NT][4], ones[NT][4];
-#pragma unroll
-          for (int s = 0; s < SPG; ++s) {
-            const int ks = q * SPG + s;                         // K step within the box
-            const int kloc = j * kBoxK + ks * 32 + t * 8;       // within the staged chunk
-            uint32_t a[2][4];
-            if constexpr (QK == kAff8) {
-              // 32 bytes per row and step: lane t takes bytes [8t, 8t+8) of them
-              const int off = (((ks * 2 + (t >> 1)) ^ (g & 7)) << 4) + (t & 1) * 8;
-              const uint2 u0 = *reinterpret_cast<const uint2*>(row0 + off);
-              const uint2 u1 = *reinterpret_cast<const uint2*>(row1 + off);
-              a[0][0] = __byte_perm(u0.x, 0x64646464u, 0x4140); a[0][1] = __byte_perm(u1.x, 0x64646464u, 0x4140);
-              a[0][2] = __byte_perm(u0.x, 0x64646464u, 0x4342); a[0][3] = __byte_perm(u1.x, 0x64646464u, 0x4342);
-              a[1][0] = __byte_perm(u0.y, 0x64646464u, 0x4140); a[1][1] = __byte_perm(u1.y, 0x64646464u, 0x4140);
-              a[1][2] = __byte_perm(u0.y, 0x64646464u, 0x4342); a[1][3] = __byte_perm(u1.y, 0x64646464u, 0x4342);
-            } else {
-              // 16 bytes per row and step: lane t takes word t
-              const int off = ((ks ^ (g & 7)) << 4) + t * 4;
-              const uint32_t u0 = *reinterpret_cast<const uint32_t*>(row0 + off);
-              const uint32_t u1 = *reinterpret_cast<const uint32_t*>(row1 + off);
-              if constexpr (QK == kAff4) {
-                a[0][0] = (u0 & 0x000F000Fu) | Ops::kMagic;         a[0][1] = (u1 & 0x000F000Fu) | Ops::kMagic;
-                a[0][2] = ((u0 >> 4) & 0x000F000Fu) | Ops::kMagic;  a[0][3] = ((u1 >> 4) & 0x000F000Fu) | Ops::kMagic;
-                a[1][0] = ((u0 >> 8) & 0x000F000Fu) | Ops::kMagic;  a[1][1] = ((u1 >> 8) & 0x000F000Fu) | Ops::kMagic;
-                a[1][2] = ((u0 >> 12) & 0x000F000Fu) | Ops::kMagic; a[1][3] = ((u1 >> 12) & 0x000F000Fu) | Ops::kMagic;
-              } else {
-                // The three magnitude bits of an E2M1 code at f16's exponent/mantissa boundary
-                // are the code's value times 2^-14 (code 1 = 0.5 lands on a subnormal); the
-                // sign bit goes to bit 15. The 2^14 is restored in the fold.
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                  const uint32_t u = r ? u1 : u0;
-                  const uint32_t uh = u >> 4;
-#pragma unroll
-                  for (int bb = 0; bb < 4; ++bb) {  // byte bb -> elements (2bb, 2bb+1)
-                    const uint32_t tt = __byte_perm(u, uh, bb | ((4 + bb) << 8));
-                    a[bb >> 1][(bb & 1) * 2 + r] = ((tt << 9) & 0x0E000E00u) | ((tt << 12) & 0x80008000u);
-                  }
-                }
-              }
-            }
-            const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const uint32_t one4[4] = {Ops::kOnes, Ops::kOnes, Ops::kOnes, Ops::kOnes};
-#pragma unroll
-            for (int h = 0; h < NT; ++h) {
-              uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-              if (h * 8 + g < p.M) xv = *reinterpret_cast<const uint4*>(xs + (h * 8 + g) * xrow + kloc);
-              if (s == 0) Ops::mma(acc[h], a[0], xv.x, xv.y, zero4);
-              else Ops::mma(acc[h], a[0], xv.x, xv.y, acc[h]);
-              Ops::mma(acc[h], a[1], xv.z, xv.w, acc[h]);
-              if constexpr (QK != kMx4) {   // sum of x over the group: A = all ones
-                if (s == 0) Ops::mma(ones[h], one4, xv.x, xv.y, zero4);
-                else Ops::mma(ones[h], one4, xv.x, xv.y, ones[h]);
-                Ops::mma(ones[h], one4, xv.z, xv.w, ones[h]);
-              }
-            }
-          }
-          // fold the group: rows g (c0, c1) and g+8 (c2, c3), tokens 2t and 2t+1
-          const float s0 = ts[g * trow + gi], s1 = ts[(g + 8) * trow + gi];
-#pragma unroll
-          for (int h = 0; h < NT; ++h) {
-            if constexpr (QK == kMx4) {
-              yacc[h][0] = fmaf(s0, acc[h][0] * 16384.0f, yacc[h][0]);
-              yacc[h][1] = fmaf(s0, acc[h][1] * 16384.0f, yacc[h][1]);
-              yacc[h][2] = fmaf(s1, acc[h][2] * 16384.0f, yacc[h][2]);
-              yacc[h][3] = fmaf(s1, acc[h][3] * 16384.0f, yacc[h][3]);
-            } else {
-              const float b0 = tb[g * trow + gi], b1 = tb[(g + 8) * trow + gi];
-              yacc[h][0] = fmaf(s0, acc[h][0], fmaf(b0, ones[h][0], yacc[h][0]));
-              yacc[h][1] = fmaf(s0, acc[h][1], fmaf(b0, ones[h][1], yacc[h][1]));
-              yacc[h][2] = fmaf(s1, acc[h][2], fmaf(b1, ones[h][0], yacc[h][2]));
-              yacc[h][3] = fmaf(s1, acc[h][3], fmaf(b1, ones[h][1], yacc[h][3]));
-            }
-          }
+    for (int u = 0; u < kTU; ++u) {
+      const int gi = g0 + 16 * u;
+      rs[u] = rb[u] = 0u;
+      if (gi < cgroups) {
+        if constexpr (QK == kMx4) {
+          rs[u] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + ti0 + gi);
+        } else {
+          rs[u] = table_raw(p.scales, tsize, ti0 + gi);
+          rb[u] = table_raw(p.biases, tsize, ti0 + gi);
         }
       }
-      // the slot is free again: refill it with the next box this warp will need
-      __syncwarp();
-      if (lane == 0 && issue.chunk < nchunks) {
-        fence_proxy_async();
-        issue_box();
-        ++issued;
-        cursor_next(issue, nchunks, warp, p.K, p.kc, kBoxK);
+    }
+  };
+  auto table_store = [&](float2* dst, int cgroups, int g0, const uint32_t (&rs)[kTU], const uint32_t (&rb)[kTU]) {
+#pragma unroll
+    for (int u = 0; u < kTU; ++u) {
+      const int gi = g0 + 16 * u;
+      if (gi < cgroups) {
+        if constexpr (QK == kMx4) {
+          dst[tr * trow + gi] = make_float2(__uint_as_float(rs[u] ? (rs[u] << 23) : 0x00400000u), 0.0f);
+        } else {
+          const float sv = table_value(rs[u], p.table_dtype);
+          dst[tr * trow + gi] = make_float2(sv, table_value(rb[u], p.table_dtype) - Ops::kMagicValue * sv);
+        }
       }
     }
-  }
+  };
+  auto stage_tables = [&](float2* dst, int tile, int64_t kbase, int cgroups) {
+    for (int g0 = tc; g0 < cgroups; g0 += 16 * kTU) {
+      uint32_t rs[kTU], rb[kTU];
+      table_load(tile, kbase, cgroups, g0, rs, rb);
+      table_store(dst, cgroups, g0, rs, rb);
+    }
+  };
 
-  // ---- reduce the K split across warps (fixed order) and store ----
-  __syncthreads();
-#pragma unroll
-  for (int h = 0; h < NT; ++h)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) red[(warp * NT * 4 + h * 4 + i) * 32 + lane] = yacc[h][i];
-  __syncthreads();
-  if (*abort_flag) {
-    if (threadIdx.x == 0) atomicCAS(p.status, 0, *abort_flag);
-    return;
-  }
-  if (warp == 0) {
+  // With a single chunk the activations are staged once and the next tile's tables are
+  // requested while the current tile is computed (one batch of kTU loads per thread).
+  const bool resident = nchunks == 1 && tgroups <= 16 * kTU;
+  int consumed = 0, tbuf = 0, rbuf = 0;
+  bool ok = true, first = true;
+  for (int tile = blockIdx.x; tile < ntiles; tile += tstride) {
+    const int64_t n0 = static_cast<int64_t>(tile) * kRowsPerCta;
+    float yacc[NT][4];
 #pragma unroll
     for (int h = 0; h < NT; ++h)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float v = 0.0f;
-#pragma unroll
-        for (int wv = 0; wv < kWarps; ++wv) v += red[(wv * NT * 4 + h * 4 + i) * 32 + lane];
-        const int64_t row = n0 + g + (i >> 1) * 8;
-        const int64_t tok = h * 8 + 2 * t + (i & 1);
-        if (row < p.N && tok < p.M) gv_store(p.y, p.y_dtype, y_off + tok * p.N + row, v);
+      for (int i = 0; i < 4; ++i) yacc[h][i] = 0.0f;
+
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+      const int64_t kbase = static_cast<int64_t>(chunk) * p.kc;
+      const int kc = static_cast<int>(p.K - kbase < p.kc ? p.K - kbase : p.kc);     // multiple of 32
+      const int nb = (kc + kBoxK - 1) / kBoxK;
+      const int kfill = nb * kBoxK;                                                 // zero-padded extent
+      const int cgroups = kc / kGroupK;
+      if (!resident || first) {
+        __syncthreads();                       // everyone is done with the previous contents
+        if (nchunks > 1 || first) stage_x(kbase, kc, kfill);
+        stage_tables(tbl + tbuf * kRowsPerCta * trow, tile, kbase, cgroups);
+        __syncthreads();
+        first = false;
       }
+      const float2* tcur = tbl + tbuf * kRowsPerCta * trow;
+      uint32_t prs[kTU], prb[kTU];
+      const bool prefetch = resident && tile + tstride < ntiles;
+      if (prefetch) table_load(tile + tstride, 0, cgroups, tc, prs, prb);
+
+      // ---- this warp's boxes of the chunk ----
+      const int jlo = nb * warp / kWarps, jhi = nb * (warp + 1) / kWarps;
+      for (int j = jlo; j < jhi && ok; ++j, ++consumed) {
+        const int slot = consumed % ring;
+        if (!(ok = mbar_wait(&full[slot], (consumed / ring) & 1, abort_flag, 11))) break;
+        const uint8_t* box = wring + slot * kBoxSmem;
+        const uint8_t* row0 = box + g * kBoxBytes;
+        const uint8_t* row1 = box + (g + 8) * kBoxBytes;
+#pragma unroll
+        for (int q = 0; q < kStepsPerBox / SPG; ++q) {          // groups of this box
+          const int gi = (j * kBoxK) / kGroupK + q;             // group index within the chunk
+          if (gi < cgroups) {
+            float acc[NT][4], ones[NT][4];
+#pragma unroll
+            for (int s = 0; s < SPG; ++s) {
+              const int ks = q * SPG + s;                         // K step within the box
+              const int kloc = j * kBoxK + ks * 32 + t * 8;       // within the staged chunk
+              uint32_t a[2][4];
+              if constexpr (QK == kAff8) {
+                // 32 bytes per row and step: lane t takes bytes [8t, 8t+8) of them
+                const int off = (((ks * 2 + (t >> 1)) ^ (g & 7)) << 4) + (t & 1) * 8;
+                const uint2 u0 = *reinterpret_cast<const uint2*>(row0 + off);
+                const uint2 u1 = *reinterpret_cast<const uint2*>(row1 + off);
+                a[0][0] = __byte_perm(u0.x, 0x64646464u, 0x4140); a[0][1] = __byte_perm(u1.x, 0x64646464u, 0x4140);
+                a[0][2] = __byte_perm(u0.x, 0x64646464u, 0x4342); a[0][3] = __byte_perm(u1.x, 0x64646464u, 0x4342);
+                a[1][0] = __byte_perm(u0.y, 0x64646464u, 0x4140); a[1][1] = __byte_perm(u1.y, 0x64646464u, 0x4140);
+                a[1][2] = __byte_perm(u0.y, 0x64646464u, 0x4342); a[1][3] = __byte_perm(u1.y, 0x64646464u, 0x4342);
+              } else {
+                // 16 bytes per row and step: lane t takes word t
+                const int off = ((ks ^ (g & 7)) << 4) + t * 4;
+                const uint32_t u0 = *reinterpret_cast<const uint32_t*>(row0 + off);
+                const uint32_t u1 = *reinterpret_cast<const uint32_t*>(row1 + off);
+                if constexpr (QK == kAff4) {
+                  a[0][0] = (u0 & 0x000F000Fu) | Ops::kMagic;         a[0][1] = (u1 & 0x000F000Fu) | Ops::kMagic;
+                  a[0][2] = ((u0 >> 4) & 0x000F000Fu) | Ops::kMagic;  a[0][3] = ((u1 >> 4) & 0x000F000Fu) | Ops::kMagic;
+                  a[1][0] = ((u0 >> 8) & 0x000F000Fu) | Ops::kMagic;  a[1][1] = ((u1 >> 8) & 0x000F000Fu) | Ops::kMagic;
+                  a[1][2] = ((u0 >> 12) & 0x000F000Fu) | Ops::kMagic; a[1][3] = ((u1 >> 12) & 0x000F000Fu) | Ops::kMagic;
+                } else {
+                  // The three magnitude bits of an E2M1 code at f16's exponent/mantissa boundary
+                  // are the code's value times 2^-14 (code 1 = 0.5 lands on a subnormal); the
+                  // sign bit goes to bit 15. The 2^14 is restored in the fold.
+#pragma unroll
+                  for (int r = 0; r < 2; ++r) {
+                    const uint32_t u = r ? u1 : u0;
+                    const uint32_t uh = u >> 4;
+#pragma unroll
+                    for (int bb = 0; bb < 4; ++bb) {  // byte bb -> elements (2bb, 2bb+1)
+                      const uint32_t tt = __byte_perm(u, uh, bb | ((4 + bb) << 8));
+                      a[bb >> 1][(bb & 1) * 2 + r] = ((tt << 9) & 0x0E000E00u) | ((tt << 12) & 0x80008000u);
+                    }
+                  }
+                }
+              }
+              const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+              const uint32_t one4[4] = {Ops::kOnes, Ops::kOnes, Ops::kOnes, Ops::kOnes};
+#pragma unroll
+              for (int h = 0; h < NT; ++h) {
+                uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+                if (h * 8 + g < p.M) xv = *reinterpret_cast<const uint4*>(xs + (h * 8 + g) * xrow + kloc);
+                if (s == 0) Ops::mma(acc[h], a[0], xv.x, xv.y, zero4);
+                else Ops::mma(acc[h], a[0], xv.x, xv.y, acc[h]);
+                Ops::mma(acc[h], a[1], xv.z, xv.w, acc[h]);
+                if constexpr (QK != kMx4) {   // sum of x over the group: A = all ones
+                  if (s == 0) Ops::mma(ones[h], one4, xv.x, xv.y, zero4);
+                  else Ops::mma(ones[h], one4, xv.x, xv.y, ones[h]);
+                  Ops::mma(ones[h], one4, xv.z, xv.w, ones[h]);
+                }
+              }
+            }
+            // fold the group: rows g (c0, c1) and g+8 (c2, c3), tokens 2t and 2t+1
+            const float2 sb0 = tcur[g * trow + gi], sb1 = tcur[(g + 8) * trow + gi];
+#pragma unroll
+            for (int h = 0; h < NT; ++h) {
+              if constexpr (QK == kMx4) {
+                yacc[h][0] = fmaf(sb0.x, acc[h][0] * 16384.0f, yacc[h][0]);
+                yacc[h][1] = fmaf(sb0.x, acc[h][1] * 16384.0f, yacc[h][1]);
+                yacc[h][2] = fmaf(sb1.x, acc[h][2] * 16384.0f, yacc[h][2]);
+                yacc[h][3] = fmaf(sb1.x, acc[h][3] * 16384.0f, yacc[h][3]);
+              } else {
+                yacc[h][0] = fmaf(sb0.x, acc[h][0], fmaf(sb0.y, ones[h][0], yacc[h][0]));
+                yacc[h][1] = fmaf(sb0.x, acc[h][1], fmaf(sb0.y, ones[h][1], yacc[h][1]));
+                yacc[h][2] = fmaf(sb1.x, acc[h][2], fmaf(sb1.y, ones[h][0], yacc[h][2]));
+                yacc[h][3] = fmaf(sb1.x, acc[h][3], fmaf(sb1.y, ones[h][1], yacc[h][3]));
+              }
+            }
+          }
+        }
+        // the slot is free again: refill it with the next box this warp will need
+        __syncwarp();
+        if (lane == 0 && issue.tile < ntiles) {
+          fence_proxy_async();
+          issue_box();
+        }
+      }
+      if (prefetch) table_store(tbl + (tbuf ^ 1) * kRowsPerCta * trow, cgroups, tc, prs, prb);
+      if (resident) tbuf ^= 1;
+    }
+
+    // ---- reduce the K split across warps (fixed order) and store this tile ----
+    float* rcur = red + rbuf * kWarps * NT * 4 * 32;
+#pragma unroll
+    for (int h = 0; h < NT; ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) rcur[(warp * NT * 4 + h * 4 + i) * 32 + lane] = yacc[h][i];
+    __syncthreads();
+    if (*abort_flag) {
+      if (threadIdx.x == 0) atomicCAS(p.status, 0, *abort_flag);
+      return;
+    }
+    if (warp == 0) {
+#pragma unroll
+      for (int h = 0; h < NT; ++h)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float v = 0.0f;
+#pragma unroll
+          for (int wv = 0; wv < kWarps; ++wv) v += rcur[(wv * NT * 4 + h * 4 + i) * 32 + lane];
+          const int64_t row = n0 + g + (i >> 1) * 8;
+          const int64_t tok = h * 8 + 2 * t + (i & 1);
+          if (row < p.N && tok < p.M) gv_store(p.y, p.y_dtype, y_off + tok * p.N + row, v);
+        }
+    }
+    rbuf ^= 1;
   }
 }
 
@@ -461,10 +493,14 @@ int launch_kernel(const CUtensorMap& wm, const GemvParams& gp, cudaStream_t stre
   const int tgroups = gp.kc / (32 * SPG);
   const size_t smem = 1024 + static_cast<size_t>(kWarps) * gp.ring * kBoxSmem +
                       static_cast<size_t>(gp.M) * (gp.kc + kXPad) * 2 +
-                      static_cast<size_t>(2) * kRowsPerCta * (tgroups + 1) * sizeof(float) +
-                      static_cast<size_t>(kWarps) * 2 * 4 * 32 * sizeof(float) +
+                      static_cast<size_t>(2) * kRowsPerCta * (tgroups + 1) * sizeof(float2) +
+                      static_cast<size_t>(2) * kWarps * NT * 4 * 32 * sizeof(float) +
                       static_cast<size_t>(kWarps) * kMaxRing * sizeof(uint64_t) + 16;
-  dim3 grid(static_cast<unsigned>((gp.N + kRowsPerCta - 1) / kRowsPerCta), static_cast<unsigned>(gp.batch));
+  // Persistent CTAs: two per SM share the machine's segments; a CTA walks tiles with a grid stride.
+  int64_t per_seg = (2LL * device_sm_count() + gp.batch - 1) / gp.batch;
+  if (per_seg < 1) per_seg = 1;
+  if (per_seg > gp.tiles) per_seg = gp.tiles;
+  dim3 grid(static_cast<unsigned>(per_seg), static_cast<unsigned>(gp.batch));
   auto kernel = qmm_gemv_kernel<QK, XT, NT, SPG>;
   static bool configured = false;
   if (!configured) {
@@ -518,17 +554,19 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   gp.x_batch_stride = p.x_batch_stride; gp.y_batch_stride = p.y_batch_stride;
   gp.w_batch_rows = p.rhs_idx ? p.N : p.w_batch_stride;
   gp.group_size = p.group_size; gp.table_dtype = p.table_dtype; gp.y_dtype = p.y_dtype;
+  gp.tiles = static_cast<int>((p.N + kRowsPerCta - 1) / kRowsPerCta);
   const int bits = (p.mode == QMM_MODE_AFFINE && p.bits == 8) ? 8 : 4;
   const int boxk = kBoxBytes * 8 / bits;
   // K elements staged per pass: the staged activations stay under ~64 KiB per CTA, and a
   // pass is a whole number of boxes.
-  int kc = p.M <= 8 ? 4096 : 2048;
+  int kc = static_cast<int>(65536 / (2 * p.M) / boxk * boxk);
   const int64_t kround = (p.K + boxk - 1) / boxk * boxk;
   if (kround < kc) kc = static_cast<int>(kround);
   gp.kc = kc;
-  // Ring depth: as many boxes as a warp consumes over the whole of K, up to kMaxRing.
+  // Ring depth: two tiles' worth of a warp's boxes, up to kMaxRing, so that a warp's requests
+  // run ahead across tile boundaries.
   const int64_t boxes = (p.K + boxk - 1) / boxk;
-  int64_t per_warp = (boxes + kWarps - 1) / kWarps + ((p.K + kc - 1) / kc > 1 ? 1 : 0);
+  int64_t per_warp = 2 * ((boxes + kWarps - 1) / kWarps);
   gp.ring = static_cast<int>(per_warp < 1 ? 1 : (per_warp > kMaxRing ? kMaxRing : per_warp));
 
   // The packed weight as a 2-D byte tensor [rows, K*bits/8] over every weight matrix behind
