@@ -319,7 +319,11 @@ struct Plan {
   // as many stages as fit next to the barriers and the tile tables, at most 8 (the
   // dequantized-A ring in TMEM has one 32-column slot per stage)
   static constexpr int kFit = (232448 - 4200 - 2048) / kStageBytes;
-  static constexpr int kStages = kFit > 8 ? 8 : kFit;
+  // The depth is a multiple of the number of dequant teams, so that a ring slot is always
+  // handled by the same team: a waiter then never lags its barrier by two phases, which a
+  // parity wait could not tell from "ready".
+  static constexpr int kStages = kFit >= 8 ? 8 : 4;
+  static_assert(kFit >= 4, "a ring of four stages must fit");
   static constexpr int kBarBytes = 1024;
   static constexpr int kSmem = kStages * kStageBytes + kBarBytes + 1024 /* alignment slack */;
   static constexpr int kDCols = BT;                           // accumulator columns
@@ -575,6 +579,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       if (!ok) break;
       // ---- epilogue: the teams drain disjoint 32-column chunks of the accumulator ----
       if (!(ok = twait(d_full, tile_n & 1, abort_flag, 7))) break;
+      __syncwarp();      // lanes leave the wait loop one by one; tcgen05.ld needs the whole warp
       tc_fence_after();
 #pragma unroll 1
       for (int c0 = team * 32; c0 < BT; c0 += 32 * kTeams) {

@@ -538,7 +538,7 @@ bool gemv_supports(const qmm_problem& p) {
   if (p.group_sizes) return false;                 // ragged rows go to the tensor-core kernel
   if (p.M < 1 || p.M > 16) return false;
   if (p.batch > 65535) return false;
-  if (p.K % 32) return false;
+  if (p.K % 32 || p.K >= (1LL << 30)) return false;
   const int64_t nw = p.num_weights > 0 ? p.num_weights : (p.w_batch_stride ? p.batch : 1);
   if (nw * p.N >= (1LL << 31)) return false;        // TMA row coordinates are 32-bit
   return true;
