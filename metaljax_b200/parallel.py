@@ -83,15 +83,16 @@ class ColumnParallelLinear:
         m = y.shape[0]
         if len(set(self.sizes)) == 1:
             # equal shards: one all-gather into [world, M, N/world], then interleave on N
-            buf = torch.empty((self.world,) + tuple(y.shape), dtype=y.dtype, device=y.device)
+            buf = torch.empty((self.world * m, y.shape[1]), dtype=y.dtype, device=y.device)
             dist.all_gather_into_tensor(buf, y.contiguous(), group=self.group)
-            return buf.permute(1, 0, 2).reshape(m, self.n)
+            return buf.view(self.world, m, -1).permute(1, 0, 2).reshape(m, self.n)
         # uneven shards: pad every slice to the widest, gather once, cut the padding out
         widest = max(self.sizes)
         padded = torch.zeros((m, widest), dtype=y.dtype, device=y.device)
         padded[:, : y.shape[1]] = y
-        buf = torch.empty((self.world, m, widest), dtype=y.dtype, device=y.device)
+        buf = torch.empty((self.world * m, widest), dtype=y.dtype, device=y.device)
         dist.all_gather_into_tensor(buf, padded, group=self.group)
+        buf = buf.view(self.world, m, widest)
         return torch.cat([buf[r, :, :s] for r, s in enumerate(self.sizes)], dim=-1)
 
 
