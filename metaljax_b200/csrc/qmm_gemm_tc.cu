@@ -510,18 +510,30 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       // of a block are requested one of the team's blocks ahead, so their global-memory
       // latency hides behind the previous block's work.
       const int tsize = (p.table_dtype == QMM_F32) ? 4 : 2;
+      const bool twide = p.table_dtype == QMM_F32;
       auto fetch_tables = [&](int kbb, float (&fs)[2], float (&fb)[2], uint32_t (&fe)[2]) {
+        int64_t gidx[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           int64_t g = (kbb * kBK + h * 32) / p.group_size;
-          if (g >= groups) g = groups - 1;
+          gidx[h] = trow + (g >= groups ? groups - 1 : g);
           fs[h] = fb[h] = 0.0f;
           fe[h] = 0u;
-          if constexpr (QK == kMx4) {
-            fe[h] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + trow + g);
-          } else {
-            fs[h] = __uint_as_float(table_raw(p.scales, tsize, trow + g));   // raw bits until used
-            fb[h] = __uint_as_float(table_raw(p.biases, tsize, trow + g));
+        }
+        if constexpr (QK == kMx4) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) fe[h] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + gidx[h]);
+        } else if (twide) {          // raw bits until used; the width is decided outside the loads
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            fs[h] = __uint_as_float(table_raw(p.scales, true, gidx[h]));
+            fb[h] = __uint_as_float(table_raw(p.biases, true, gidx[h]));
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            fs[h] = __uint_as_float(table_raw(p.scales, false, gidx[h]));
+            fb[h] = __uint_as_float(table_raw(p.biases, false, gidx[h]));
           }
         }
       };

@@ -2,10 +2,12 @@
 // streamed packed weight (M <= 16 of `y = x . deq(w)^T`, src/metaljax/qmm.py:2491).
 //
 // HBM-bound: every packed weight byte is read exactly once and never dequantized element by
-// element. A CTA owns 16 weight rows and its 8 warps split K. The packed rows arrive by TMA in
-// boxes of 16 rows x 128 bytes (128-byte swizzle, so that the fragment reads below are free
-// of bank conflicts); every warp feeds its own ring of boxes from its own mbarriers, and the
-// first boxes are requested before anything else happens in the kernel.
+// element. A CTA owns 16 weight rows at a time and its 8 warps split K. The packed
+// rows arrive by TMA in boxes of 16 rows x 128 bytes (128-byte swizzle, so that the fragment
+// reads below are free of bank conflicts). Every warp has its own ring of boxes with one
+// mbarrier per slot; its lane 0 requests the first boxes before anything else happens in the
+// kernel and refills a slot as soon as the warp has consumed it, running ahead across tile
+// boundaries.
 //
 // Per 32-wide K step a lane reads one packed word (two for 8-bit) of rows g and g+8 and turns
 // it into the A fragments of two m16n8k16 MMAs with a magic-number OR: the 16-bit pattern
@@ -13,24 +15,30 @@
 // accumulates  sum (C + q_k) x_k  exactly in float32. All 16 K slots of such an MMA lie
 // inside one 32-element span, hence inside one quantization group, so the group's scale and
 // bias are applied to the accumulators once per group:
-//     y += s * sum (C + q) x  +  (b - C s) * sum x ,
-// with  sum x  taken from one more MMA whose A fragment is all ones. The activations are
-// staged in shared memory in the MMA's element type (for 4-bit codes in the pair order the
-// magic-number extraction produces), tokens beyond M being zero fragments, next to the
-// tile's slice of the scale table and of the folded bias table  b - C s.
+//     y += s * sum (C + q) x  +  (b - C s) * sum x .
+// The activations are staged once in shared memory in the MMA's element type (for 4-bit
+// codes in the pair order the magic-number extraction produces), tokens beyond M being zero
+// fragments; each warp then takes  sum x  of its groups from MMAs whose A fragment is all
+// ones and keeps them in shared memory for all the tiles it will process. The tile's
+// (s, b - C s) pairs are staged next to them as float32, those of the next tile being
+// requested while the current tile is computed.
 // MXFP4 places each code's magnitude bits at the f16 exponent/mantissa boundary (the E2M1
 // value times 2^-14, exactly) and scales the accumulators per 32-group by 2^(e8-127+14).
 //
-// CTAs are persistent: a CTA walks 16-row tiles with a grid stride, keeps the staged
-// activations for all of them, requests the next tile's tables
-// while it computes the current one, and its warps' TMA rings run ahead across tile
-// boundaries. The K split is reduced across the CTA's warps in shared memory; there is no
-// global scratch and no atomics, and the summation order is fixed. Waits on the TMA barriers
-// are bounded.
+// CTAs are persistent (grid stride over 16-row tiles). The K split is reduced across the
+// consumer warps in shared memory; there is no global scratch and no atomics, and the
+// summation order is fixed. Every wait on an mbarrier is bounded.
+//
+// The kernel is launched with programmatic stream serialization: it lets the next kernel in
+// the stream start early, and itself touches only the weights (which no earlier kernel of
+// the stream produces) before `griddepcontrol.wait`; the activations are read and the
+// output is written after it.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <type_traits>
 
 #include "qmm_internal.h"
@@ -42,11 +50,17 @@ namespace {
 using namespace ptx;
 
 constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kConsumerThreads = kThreads;
+#ifndef QMM_GEMV_TRACING
+#define QMM_GEMV_TRACING 0          // development builds: per-phase cycle counts (costs registers)
+#endif
 constexpr int kRowsPerCta = 16;
 constexpr int kXPad = 32;           // elements of padding per staged activation row (64 bytes)
 constexpr int kBoxBytes = 128;      // bytes of one weight row in a TMA box
 constexpr int kBoxSmem = kRowsPerCta * kBoxBytes;   // 2 KiB
 constexpr int kMaxRing = 4;         // boxes a warp keeps in flight
+constexpr int kSmemBudget = 112 * 1024;   // two CTAs per SM
 
 enum { kAff4 = 0, kAff8 = 1, kMx4 = 2 };
 
@@ -61,9 +75,15 @@ struct GemvParams {
   int64_t M, K, N, batch;
   int64_t x_batch_stride, y_batch_stride, w_batch_rows;
   int group_size, table_dtype, y_dtype;
-  int kc;     // K elements staged per pass (a multiple of the box width)
-  int ring;   // boxes per warp ring (1..kMaxRing)
-  int tiles;  // 16-row tiles per weight matrix
+  int kc;          // K elements per pass: the tile's tables are staged pass by pass (a multiple
+                   // of the box width)
+  int xk;          // K elements of the activations held in shared memory: all of K (rounded up
+                   // to boxes) when that fits, else kc
+  int ring_shift;  // log2 of the boxes per warp ring (0..2)
+  int xshift;      // log2 of the 8-element pieces per staged row, rounded up to a power of two
+  int tiles;       // 16-row tiles per weight matrix
+  int nchunks;     // staging passes over K: ceil(K / kc)
+  long long* trace;   // development aid: cycles per phase of consumer warp 0 of every CTA, or NULL
 };
 
 template <typename AT>
@@ -159,18 +179,29 @@ __device__ __forceinline__ void cursor_seek(BoxCursor& c, int ntiles, int tstrid
   }
 }
 
-template <int BOXK>
-__device__ __forceinline__ void cursor_next(BoxCursor& c, int ntiles, int tstride, int nchunks, int warp,
-                                            int K, int kc) {
-  if (++c.j < c.hi) return;
-  ++c.chunk;
-  cursor_seek<BOXK>(c, ntiles, tstride, nchunks, warp, K, kc);
+__device__ __forceinline__ void consumer_barrier() { __syncthreads(); }
+
+// (a & b) | c as one LOP3 with all three operands in registers: left to itself the compiler
+// may keep the two constants as immediates and spend two instructions.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// Compile-time loop: f(integral_constant<int, 0>) ... f(integral_constant<int, N-1>).
+template <int N, int I = 0, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<N, I + 1>(f);
+  }
 }
 
 // QK: quantization kind. XT: activation type in memory. NT: token halves (1: M <= 8,
 // 2: M <= 16). SPG: 32-wide K steps per quantization group (1, 2, 4).
 template <int QK, typename XT, int NT, int SPG>
-__global__ void __launch_bounds__(kWarps * 32, 2)
+__global__ void __launch_bounds__(kThreads, 2)
 qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   // MMA element type: 4-bit affine codes fit bf16's 7 mantissa bits; 8-bit codes and the
   // E2M1 bit placement need f16.
@@ -181,23 +212,28 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   constexpr int kStepsPerBox = kBoxK / 32;         // 8 or 4
   constexpr int kGroupK = 32 * SPG;
   constexpr int kTU = 4;                           // table loads per thread kept in flight
+  constexpr int kSumTok = 8 * NT;                  // tokens per row of the sum-of-x table
 
   extern __shared__ uint8_t gv_smem_raw[];
+  const long long tr_entry = (QMM_GEMV_TRACING && p.trace) ? clock64() : 0;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gv_smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const int ring = p.ring;
-  const int xrow = p.kc + kXPad;                   // staged row stride in elements
+  const int ring = 1 << p.ring_shift, rmask = ring - 1;
+  const int xrow = p.xk + kXPad;                   // staged row stride in elements
+  const bool xres = p.xk > p.kc || p.nchunks == 1;  // the activations of all of K are staged once
   const int tgroups = p.kc / kGroupK;              // groups staged per pass
-  const int trow = tgroups + 1;                    // table row stride in float2 (odd: no conflicts)
+  const int trow = tgroups + 1;                    // table row stride in entries (odd: no conflicts)
+  const int tsize = (p.table_dtype == QMM_F32) ? 4 : 2;
+  constexpr int tent = (QK == kMx4) ? 1 : 2;             // 32-bit words per table entry
 
-  uint8_t* wring = smem + warp * ring * kBoxSmem;                                    // this warp's boxes
   AT* xs = reinterpret_cast<AT*>(smem + kWarps * ring * kBoxSmem);
-  float2* tbl = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(xs) + static_cast<size_t>(p.M) * xrow * sizeof(AT));
-  float* red = reinterpret_cast<float*>(tbl + 2 * kRowsPerCta * trow);   // two buffers
-  uint64_t* bars = reinterpret_cast<uint64_t*>(red + 2 * kWarps * NT * 4 * 32);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kWarps * kMaxRing);
-  uint64_t* full = bars + warp * kMaxRing;
+  float* sumx = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + static_cast<size_t>(p.M) * xrow * sizeof(AT));
+  uint32_t* tbl = reinterpret_cast<uint32_t*>(sumx + (QK == kMx4 ? 0 : (p.xk / kGroupK) * kSumTok));
+  float* red = reinterpret_cast<float*>(tbl + 2 * kRowsPerCta * trow * tent);   // two buffers
+  uint64_t* full_all = reinterpret_cast<uint64_t*>(red + 2 * kWarps * NT * 4 * 32);
+  uint8_t* zeros = reinterpret_cast<uint8_t*>(full_all + kWarps * kMaxRing);      // 512 zero bytes: the
+                                                                                  // "activations" of tokens >= M
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(zeros + 512);
 
   const int64_t seg = blockIdx.y;
   int64_t x_off, wb;
@@ -208,134 +244,229 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
     x_off = seg * p.x_batch_stride;
     wb = p.w_batch_rows ? seg : 0;
   }
-  const int64_t y_off = seg * p.y_batch_stride;
-  const XT* xg = reinterpret_cast<const XT*>(p.x) + x_off;
-  const int64_t groups = p.K / kGroupK;
-  const int nchunks = static_cast<int>((p.K + p.kc - 1) / p.kc);
+  const int nchunks = p.nchunks;
   const int boxes_per_chunk = p.kc / kBoxK;
   const int ntiles = p.tiles, tstride = gridDim.x;
-  const int tsize = (p.table_dtype == QMM_F32) ? 4 : 2;
-
-  // Each warp owns its barriers: it initializes them itself and nobody else touches them.
-  if (lane == 0) {
-    for (int i = 0; i < kMaxRing; ++i) mbar_init(&full[i], 1);
-    if (warp == 0) *abort_flag = 0;
-    mbar_init_fence();
-  }
-  __syncwarp();
-
-  // ---- request this warp's first boxes before anything else ----
-  BoxCursor issue = {static_cast<int>(blockIdx.x), 0, 0, 0};
-  cursor_seek<kBoxK>(issue, ntiles, tstride, nchunks, warp, static_cast<int>(p.K), p.kc);
-  int issued = 0;
-  auto issue_box = [&]() {   // lane 0 only
-    const int slot = issued % ring;
-    mbar_expect_tx(&full[slot], kBoxSmem);
-    tma_load_2d(&w_map, wring + slot * kBoxSmem, &full[slot],
-                (issue.chunk * boxes_per_chunk + issue.j) * kBoxBytes,
-                static_cast<int>(wb * p.N) + issue.tile * kRowsPerCta);
-    ++issued;
-    cursor_next<kBoxK>(issue, ntiles, tstride, nchunks, warp, static_cast<int>(p.K), p.kc);
-  };
-  if (lane == 0)
-    while (issued < ring && issue.tile < ntiles) issue_box();
-
-  // ---- staging helpers ----
-  // Activations of one chunk. Items are (token, 8-element piece). When the MMA's element type
-  // is the activations' own, a piece is only re-paired with byte permutes; otherwise it is
-  // converted through float32.
-  auto stage_x = [&](int64_t kbase, int kc, int kfill) {
-    constexpr int kXU = 4;
-    const int pieces = kfill / 8;
-    const int pieces_pad = (pieces + 31) & ~31;
-    const float inv_pad = 1.0f / static_cast<float>(pieces_pad);
-    const int items = static_cast<int>(p.M) * pieces_pad;
-    for (int e0 = threadIdx.x; e0 < items; e0 += blockDim.x * kXU) {
-      uint4 raw[kXU];
-      int mm[kXU], pc[kXU];
-#pragma unroll
-      for (int u = 0; u < kXU; ++u) {
-        const int e = e0 + u * blockDim.x;
-        mm[u] = __float2int_rz((static_cast<float>(e) + 0.5f) * inv_pad);
-        pc[u] = e - mm[u] * pieces_pad;
-        raw[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (e < items && pc[u] * 8 < kc)
-          raw[u] = __ldg(reinterpret_cast<const uint4*>(xg + static_cast<int64_t>(mm[u]) * p.K + kbase + pc[u] * 8));
-      }
-#pragma unroll
-      for (int u = 0; u < kXU; ++u) {
-        if (e0 + u * static_cast<int>(blockDim.x) - lane < items) {     // whole warps only
-          uint4 o;
-          if constexpr (std::is_same<AT, XT>::value) {
-            if constexpr (QK == kAff4) {  // pair order (0,4)(1,5)(2,6)(3,7): what one LOP3 extracts
-              o.x = __byte_perm(raw[u].x, raw[u].z, 0x5410); o.y = __byte_perm(raw[u].x, raw[u].z, 0x7632);
-              o.z = __byte_perm(raw[u].y, raw[u].w, 0x5410); o.w = __byte_perm(raw[u].y, raw[u].w, 0x7632);
-            } else {
-              o = raw[u];
-            }
-          } else {                        // bf16 activations, f16 MMA
-            const uint32_t r4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-            uint32_t c4[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              c4[i] = pack_pair<AT>(__uint_as_float(r4[i] << 16), __uint_as_float(r4[i] & 0xffff0000u));
-            o = make_uint4(c4[0], c4[1], c4[2], c4[3]);
-          }
-          if (pc[u] < pieces) *reinterpret_cast<uint4*>(xs + mm[u] * xrow + pc[u] * 8) = o;
-        }
-      }
-    }
-  };
+  const int64_t groups = p.K / kGroupK;
 
   // Tables of one tile's 16 rows for one chunk: thread (r, c) of a 16 x 16 arrangement takes
-  // groups c, c+16, ... of row r. `load` requests kTU of them, `store` converts and writes
-  // (scale, bias - C*scale) pairs; the two halves can be separated by other work.
+  // the four consecutive groups 4c .. 4c+3 (+ 64 per batch) of row r. `load` requests them
+  // (one 8-byte load per table when the tables are 16-bit and suitably aligned), `store`
+  // converts and writes (scale, bias - C*scale) pairs; the two halves can be separated by
+  // other work. Every load is unconditional: a group index past the end is clamped and its
+  // entry is zeroed when stored, which makes that group's fold a no-op.
   const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
+  const bool tvec = QK != kMx4 && tsize == 2 && (groups & 3) == 0 &&
+                    ((reinterpret_cast<uintptr_t>(p.scales) | reinterpret_cast<uintptr_t>(p.biases)) & 7) == 0;
   auto table_load = [&](int tile, int64_t kbase, int cgroups, int g0, uint32_t (&rs)[kTU], uint32_t (&rb)[kTU]) {
     const int64_t n0 = static_cast<int64_t>(tile) * kRowsPerCta;
     const int64_t row = wb * p.N + (n0 + tr < p.N ? n0 + tr : p.N - 1);
     const int64_t ti0 = row * groups + kbase / kGroupK;
+    if constexpr (QK == kMx4) {
 #pragma unroll
-    for (int u = 0; u < kTU; ++u) {
-      const int gi = g0 + 16 * u;
-      rs[u] = rb[u] = 0u;
-      if (gi < cgroups) {
-        if constexpr (QK == kMx4) {
-          rs[u] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + ti0 + gi);
-        } else {
-          rs[u] = table_raw(p.scales, tsize, ti0 + gi);
-          rb[u] = table_raw(p.biases, tsize, ti0 + gi);
-        }
+      for (int u = 0; u < kTU; ++u) {
+        const int gi = g0 + u;
+        rs[u] = __ldg(reinterpret_cast<const uint8_t*>(p.scales) + ti0 + (gi < cgroups ? gi : cgroups - 1));
+        rb[u] = 0u;
+      }
+    } else if (tvec && ((kbase / kGroupK) & 3) == 0 && (cgroups & 3) == 0) {
+      const int64_t i = ti0 + (g0 < cgroups ? g0 : 0);
+      const uint2 vs = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p.scales) + i));
+      const uint2 vb = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p.biases) + i));
+      rs[0] = vs.x; rs[1] = vs.y; rb[0] = vb.x; rb[1] = vb.y;     // unpacked when stored: nothing here
+      rs[2] = rs[3] = rb[2] = rb[3] = 0u;                         // may depend on the loaded values
+    } else if (tsize == 2) {
+#pragma unroll
+      for (int u = 0; u < kTU; ++u) {
+        const int gi = g0 + u;
+        const int64_t i = ti0 + (gi < cgroups ? gi : cgroups - 1);
+        rs[u] = table_raw(p.scales, false, i);
+        rb[u] = table_raw(p.biases, false, i);
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < kTU; ++u) {
+        const int gi = g0 + u;
+        const int64_t i = ti0 + (gi < cgroups ? gi : cgroups - 1);
+        rs[u] = table_raw(p.scales, true, i);
+        rb[u] = table_raw(p.biases, true, i);
       }
     }
   };
-  auto table_store = [&](float2* dst, int cgroups, int g0, const uint32_t (&rs)[kTU], const uint32_t (&rb)[kTU]) {
-#pragma unroll
-    for (int u = 0; u < kTU; ++u) {
-      const int gi = g0 + 16 * u;
-      if (gi < cgroups) {
-        if constexpr (QK == kMx4) {
-          dst[tr * trow + gi] = make_float2(__uint_as_float(rs[u] ? (rs[u] << 23) : 0x00400000u), 0.0f);
-        } else {
-          const float sv = table_value(rs[u], p.table_dtype);
-          dst[tr * trow + gi] = make_float2(sv, table_value(rb[u], p.table_dtype) - Ops::kMagicValue * sv);
-        }
-      }
+  // The first tile's tables are requested before anything else: their DRAM latency then runs
+  // under the whole prologue.
+  const int tg0 = tc * kTU;                                // this thread's first group of a batch
+  uint32_t frs[kTU], frb[kTU];
+  table_load(static_cast<int>(blockIdx.x), 0, static_cast<int>((p.K < p.kc ? p.K : p.kc) / kGroupK), tg0, frs, frb);
+
+
+  // Each warp owns its barriers: it initializes them itself and nobody else touches them. The
+  // block of zeros and the abort flag are first needed after the staging barrier further down.
+  if (lane == 0) {
+    if (warp == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&w_map)) : "memory");
+    for (int i = 0; i < kMaxRing; ++i) mbar_init(&full_all[warp * kMaxRing + i], 1);
+    if (warp == 0) *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (threadIdx.x < 128) reinterpret_cast<uint32_t*>(zeros)[threadIdx.x] = 0u;
+  // The next kernel of the stream may start; whatever it reads of ours it reads after its own
+  // griddepcontrol.wait, that is after this grid has completed.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __syncwarp();
+
+  const bool tracing = QMM_GEMV_TRACING && p.trace != nullptr;
+  long long tr_t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const long long tr_c0 = tr_entry;
+
+  const int g = lane >> 2, t = lane & 3;
+  uint8_t* wring = smem + warp * ring * kBoxSmem;
+  uint64_t* full = full_all + warp * kMaxRing;
+
+  // ---- lane 0 requests this warp's first boxes before anything else ----
+  BoxCursor issue = {static_cast<int>(blockIdx.x), 0, 0, 0};
+  int issued = 0;
+  const int row_base = static_cast<int>(wb * p.N);
+  auto issue_box = [&]() {   // lane 0 only; issue.tile < ntiles
+    const int slot = issued & rmask;
+    mbar_expect_tx(&full[slot], kBoxSmem);
+    tma_load_2d(&w_map, wring + slot * kBoxSmem, &full[slot], (issue.chunk * boxes_per_chunk + issue.j) * kBoxBytes,
+                row_base + issue.tile * kRowsPerCta);
+    ++issued;
+    if (++issue.j >= issue.hi) {
+      ++issue.chunk;
+      cursor_seek<kBoxK>(issue, ntiles, tstride, nchunks, warp, static_cast<int>(p.K), p.kc);
     }
   };
-  auto stage_tables = [&](float2* dst, int tile, int64_t kbase, int cgroups) {
-    for (int g0 = tc; g0 < cgroups; g0 += 16 * kTU) {
-      uint32_t rs[kTU], rb[kTU];
-      table_load(tile, kbase, cgroups, g0, rs, rb);
-      table_store(dst, cgroups, g0, rs, rb);
+  if (lane == 0) {
+    cursor_seek<kBoxK>(issue, ntiles, tstride, nchunks, warp, static_cast<int>(p.K), p.kc);
+    while (issued < ring && issue.tile < ntiles) issue_box();
+  }
+  const int64_t y_off = seg * p.y_batch_stride;
+  const XT* xg = reinterpret_cast<const XT*>(p.x) + x_off;
+
+  // The two constants of the magic-number extraction, pinned in registers (see and_or).
+  uint32_t nib_mask = 0x000F000Fu, magic = Ops::kMagic;
+  asm volatile("" : "+r"(nib_mask), "+r"(magic));
+
+  // Per-thread shared addresses for the main loop.
+  constexpr int kGroupsPerBox = kStepsPerBox / SPG;
+  constexpr int kStepBytes = 4 * BITS;              // bytes of one row in a 32-wide K step
+  const uint32_t wthread = smem_u32(wring) + g * kBoxBytes +
+                           (QK == kAff8 ? ((((t >> 1) ^ (g & 7)) << 4) + (t & 1) * 8) : (((g & 7) << 4) + t * 4));
+  const uint32_t zero_u32 = smem_u32(zeros);
+  const uint32_t sumx_u32 = smem_u32(sumx);
+  uint32_t xthread[NT];
+  bool xvalid[NT];
+#pragma unroll
+  for (int h = 0; h < NT; ++h) {
+    xvalid[h] = h * 8 + g < p.M;
+    xthread[h] = smem_u32(xs) + ((h * 8 + g) * xrow + t * 8) * 2;
+  }
+
+  // Activations of one chunk. Items are (token, 8-element piece) with the pieces per token
+  // padded to a power of two. When the MMA's element type is the activations' own, a piece is
+  // only re-paired with byte permutes; otherwise it is converted through float32.
+  auto stage_x = [&](int64_t kbase, int kc, int kfill) {
+    constexpr int kXU = 4;
+    const int pieces = kfill >> 3;
+    const int pmask = (1 << p.xshift) - 1;
+    const int items = static_cast<int>(p.M) << p.xshift;
+    for (int e0 = threadIdx.x; e0 < items; e0 += kConsumerThreads * kXU) {
+      uint4 raw[kXU];
+#pragma unroll
+      for (int u = 0; u < kXU; ++u) {
+        const int e = e0 + u * kConsumerThreads;
+        const int mm = e >> p.xshift, pc = e & pmask;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (e < items && pc * 8 < kc)
+          raw[u] = __ldg(reinterpret_cast<const uint4*>(xg + static_cast<int64_t>(mm) * p.K + kbase + pc * 8));
+      }
+#pragma unroll
+      for (int u = 0; u < kXU; ++u) {
+        const int e = e0 + u * kConsumerThreads;
+        const int mm = e >> p.xshift, pc = e & pmask;
+        uint4 o;
+        if constexpr (std::is_same<AT, XT>::value) {
+          if constexpr (QK == kAff4) {  // pair order (0,4)(1,5)(2,6)(3,7): what one LOP3 extracts
+            o.x = __byte_perm(raw[u].x, raw[u].z, 0x5410); o.y = __byte_perm(raw[u].x, raw[u].z, 0x7632);
+            o.z = __byte_perm(raw[u].y, raw[u].w, 0x5410); o.w = __byte_perm(raw[u].y, raw[u].w, 0x7632);
+          } else {
+            o = raw[u];
+          }
+        } else {                        // bf16 activations, f16 MMA
+          const uint32_t r4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+          uint32_t c4[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            c4[i] = pack_pair<AT>(__uint_as_float(r4[i] << 16), __uint_as_float(r4[i] & 0xffff0000u));
+          o = make_uint4(c4[0], c4[1], c4[2], c4[3]);
+        }
+        if (e < items && pc < pieces) *reinterpret_cast<uint4*>(xs + mm * xrow + pc * 8) = o;
+      }
     }
   };
 
-  // With a single chunk the activations are staged once and the next tile's tables are
-  // requested while the current tile is computed (one batch of kTU loads per thread).
-  const bool resident = nchunks == 1 && tgroups <= 16 * kTU;
+  auto table_store = [&](uint32_t* dst, int64_t kbase, int cgroups, int g0, uint32_t (&rs)[kTU], uint32_t (&rb)[kTU]) {
+    if (QK != kMx4 && tvec && ((kbase / kGroupK) & 3) == 0 && (cgroups & 3) == 0) {   // as in table_load
+      rs[3] = rs[1] >> 16; rs[2] = rs[1] & 0xffffu; rs[1] = rs[0] >> 16; rs[0] &= 0xffffu;
+      rb[3] = rb[1] >> 16; rb[2] = rb[1] & 0xffffu; rb[1] = rb[0] >> 16; rb[0] &= 0xffffu;
+    }
+#pragma unroll
+    for (int u = 0; u < kTU; ++u) {
+      const int gi = g0 + u;
+      if (gi < tgroups) {
+        if constexpr (QK == kMx4) {
+          dst[tr * trow + gi] = gi >= cgroups ? 0u : (rs[u] ? (rs[u] << 23) : 0x00400000u);   // 2^(e8 - 127)
+        } else {
+          const float sv = table_value(rs[u], p.table_dtype);
+          const float bv = table_value(rb[u], p.table_dtype) - Ops::kMagicValue * sv;
+          *reinterpret_cast<float2*>(dst + (tr * trow + gi) * 2) = gi >= cgroups ? make_float2(0.0f, 0.0f) : make_float2(sv, bv);
+        }
+      }
+    }
+  };
+
+  // When the activations of all of K fit (xres), they and the sums of x are staged once, the
+  // tables are staged pass by pass, and the tables of the next pass (of this tile or of the
+  // CTA's next tile) are requested while the current pass is computed. Otherwise every pass
+  // restages its slice of the activations, the sums and the tables.
+  const int nbatch = (tgroups + 16 * kTU - 1) / (16 * kTU);
   int consumed = 0, tbuf = 0, rbuf = 0;
   bool ok = true, first = true;
+  if (tracing) tr_t[1] = clock64() - tr_entry;        // prologue
+
+  // sums of x over this warp's groups of one pass (A = all ones); every row of the result is
+  // the same, the lanes of row 0 keep it. `xoff` is the pass's first K element in `xs`.
+  auto sum_x = [&](int xoff, int jlo, int jhi) {
+    if constexpr (QK != kMx4) {
+      const uint32_t one4[4] = {Ops::kOnes, Ops::kOnes, Ops::kOnes, Ops::kOnes};
+      for (int j = jlo; j < jhi; ++j) {
+#pragma unroll
+        for (int q = 0; q < kGroupsPerBox; ++q) {
+          const int gi = xoff / kGroupK + j * kGroupsPerBox + q;     // zero-padded x past K: those sums are 0
+#pragma unroll
+          for (int h = 0; h < NT; ++h) {
+            float o0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, o1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int s = 0; s < SPG; ++s) {
+              uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+              if (h * 8 + g < p.M) xv = *reinterpret_cast<const uint4*>(xs + (h * 8 + g) * xrow + (gi * SPG + s) * 32 + t * 8);
+              Ops::mma(o0, one4, xv.x, xv.y, o0);
+              Ops::mma(o1, one4, xv.z, xv.w, o1);
+            }
+            if (g == 0)
+              *reinterpret_cast<float2*>(sumx + gi * kSumTok + h * 8 + 2 * t) = make_float2(o0[0] + o1[0], o0[1] + o1[1]);
+          }
+        }
+      }
+    }
+  };
+  auto pass_extent = [&](int chunk, int& kc, int& nb) {
+    const int left = static_cast<int>(p.K) - chunk * p.kc;
+    kc = left < p.kc ? left : p.kc;                   // multiple of 32
+    nb = (kc + kBoxK - 1) / kBoxK;
+  };
+
   for (int tile = blockIdx.x; tile < ntiles; tile += tstride) {
     const int64_t n0 = static_cast<int64_t>(tile) * kRowsPerCta;
     float yacc[NT][4];
@@ -346,118 +477,176 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
 
     for (int chunk = 0; chunk < nchunks; ++chunk) {
       const int64_t kbase = static_cast<int64_t>(chunk) * p.kc;
-      const int kc = static_cast<int>(p.K - kbase < p.kc ? p.K - kbase : p.kc);     // multiple of 32
-      const int nb = (kc + kBoxK - 1) / kBoxK;
-      const int kfill = nb * kBoxK;                                                 // zero-padded extent
+      int kc, nb;
+      pass_extent(chunk, kc, nb);
       const int cgroups = kc / kGroupK;
-      if (!resident || first) {
-        __syncthreads();                       // everyone is done with the previous contents
-        if (nchunks > 1 || first) stage_x(kbase, kc, kfill);
-        stage_tables(tbl + tbuf * kRowsPerCta * trow, tile, kbase, cgroups);
-        __syncthreads();
+      const int jlo = nb * warp / kWarps, jhi = nb * (warp + 1) / kWarps;
+      const int xoff = xres ? static_cast<int>(kbase) : 0;        // this pass's first K element in xs
+      if (!xres || first) {
+        const long long ts0 = tracing ? clock64() : 0;
+        uint32_t* tdst = tbl + tbuf * kRowsPerCta * trow * tent;
+        uint32_t rs[kTU], rb[kTU];
+        if (first) {
+#pragma unroll
+          for (int u = 0; u < kTU; ++u) { rs[u] = frs[u]; rb[u] = frb[u]; }
+        } else {
+          table_load(tile, kbase, cgroups, tg0, rs, rb);
+        }
+        if (first) asm volatile("griddepcontrol.wait;" ::: "memory");
+        else consumer_barrier();                              // everyone is done with the previous contents
+        if (xres) stage_x(0, static_cast<int>(p.K), p.xk);
+        else stage_x(kbase, kc, nb * kBoxK);
+        consumer_barrier();
+        if (tracing) tr_t[3] += clock64() - ts0;
+        const long long tp0 = tracing ? clock64() : 0;
+        if (xres) {                                            // every pass's sums, once
+          for (int c = 0; c < nchunks; ++c) {
+            int ckc, cnb;
+            pass_extent(c, ckc, cnb);
+            sum_x(c * p.kc, cnb * warp / kWarps, cnb * (warp + 1) / kWarps);
+          }
+        } else {
+          sum_x(0, jlo, jhi);
+        }
+        table_store(tdst, kbase, cgroups, tg0, rs, rb);       // requested long ago: in flight meanwhile
+        for (int g0 = tg0 + 16 * kTU; g0 < tgroups; g0 += 16 * kTU) {
+          table_load(tile, kbase, cgroups, g0, rs, rb);
+          table_store(tdst, kbase, cgroups, g0, rs, rb);
+        }
+        consumer_barrier();
         first = false;
+        if (tracing) tr_t[6] += clock64() - tp0;
       }
-      const float2* tcur = tbl + tbuf * kRowsPerCta * trow;
+      const uint32_t* tcur = tbl + tbuf * kRowsPerCta * trow * tent;
+      uint32_t* tnext = tbl + (tbuf ^ 1) * kRowsPerCta * trow * tent;
+      // the pass after this one: the tile's next pass, or the first pass of the CTA's next tile
+      const bool last_pass = chunk + 1 == nchunks;
+      const int ptile = last_pass ? tile + tstride : tile;
+      const int pchunk = last_pass ? 0 : chunk + 1;
+      int pkc, pnb;
+      pass_extent(pchunk, pkc, pnb);
+      const int64_t pkbase = static_cast<int64_t>(pchunk) * p.kc;
+      const int pgroups = pkc / kGroupK;
       uint32_t prs[kTU], prb[kTU];
-      const bool prefetch = resident && tile + tstride < ntiles;
-      if (prefetch) table_load(tile + tstride, 0, cgroups, tc, prs, prb);
+      const bool prefetch = xres && ptile < ntiles;
+      int pb = prefetch ? 0 : nbatch + 1;
+      auto prefetch_step = [&]() {
+        if (pb > 0) table_store(tnext, pkbase, pgroups, tg0 + 16 * kTU * (pb - 1), prs, prb);
+        if (pb < nbatch) table_load(ptile, pkbase, pgroups, tg0 + 16 * kTU * pb, prs, prb);
+        ++pb;
+      };
 
       // ---- this warp's boxes of the chunk ----
-      const int jlo = nb * warp / kWarps, jhi = nb * (warp + 1) / kWarps;
+      // All shared-memory reads of the loop below go through 32-bit shared addresses that
+      // are fixed per thread, plus compile-time offsets.
+      const uint32_t tcur_u32 = smem_u32(tcur);
       for (int j = jlo; j < jhi && ok; ++j, ++consumed) {
-        const int slot = consumed % ring;
-        if (!(ok = mbar_wait(&full[slot], (consumed / ring) & 1, abort_flag, 11))) break;
-        const uint8_t* box = wring + slot * kBoxSmem;
-        const uint8_t* row0 = box + g * kBoxBytes;
-        const uint8_t* row1 = box + (g + 8) * kBoxBytes;
+        const long long tq0 = tracing ? clock64() : 0;
+        if (pb < nbatch) prefetch_step();                 // the last store waits for the tile's end
+        const long long tq1 = tracing ? clock64() : 0;
+        const int slot = consumed & rmask;
+        if (!(ok = mbar_wait(&full[slot], (consumed >> p.ring_shift) & 1, abort_flag, 11))) break;
+        const long long tq2 = tracing ? clock64() : 0;
+        if (tracing) { tr_t[7] += tq1 - tq0; tr_t[0] += tq2 - tq1; }
+        // Row g of the box, with the swizzle term of K step 0 folded in: K step ks of the box
+        // is at this address XOR ks * kStepBytes (the box is 2 KiB aligned, so bits 4..6 of the
+        // address are exactly the swizzle term); row g + 8 is 1 KiB further.
+        const uint32_t wrow = wthread + slot * kBoxSmem;
+        uint32_t xbox[NT];
 #pragma unroll
-        for (int q = 0; q < kStepsPerBox / SPG; ++q) {          // groups of this box
-          const int gi = (j * kBoxK) / kGroupK + q;             // group index within the chunk
-          if (gi < cgroups) {
-            float acc[NT][4], ones[NT][4];
-#pragma unroll
-            for (int s = 0; s < SPG; ++s) {
-              const int ks = q * SPG + s;                         // K step within the box
-              const int kloc = j * kBoxK + ks * 32 + t * 8;       // within the staged chunk
-              uint32_t a[2][4];
-              if constexpr (QK == kAff8) {
-                // 32 bytes per row and step: lane t takes bytes [8t, 8t+8) of them
-                const int off = (((ks * 2 + (t >> 1)) ^ (g & 7)) << 4) + (t & 1) * 8;
-                const uint2 u0 = *reinterpret_cast<const uint2*>(row0 + off);
-                const uint2 u1 = *reinterpret_cast<const uint2*>(row1 + off);
-                a[0][0] = __byte_perm(u0.x, 0x64646464u, 0x4140); a[0][1] = __byte_perm(u1.x, 0x64646464u, 0x4140);
-                a[0][2] = __byte_perm(u0.x, 0x64646464u, 0x4342); a[0][3] = __byte_perm(u1.x, 0x64646464u, 0x4342);
-                a[1][0] = __byte_perm(u0.y, 0x64646464u, 0x4140); a[1][1] = __byte_perm(u1.y, 0x64646464u, 0x4140);
-                a[1][2] = __byte_perm(u0.y, 0x64646464u, 0x4342); a[1][3] = __byte_perm(u1.y, 0x64646464u, 0x4342);
+        for (int h = 0; h < NT; ++h) xbox[h] = xvalid[h] ? xthread[h] + (xoff + j * kBoxK) * 2 : zero_u32;
+        const uint32_t tb0 = tcur_u32 + (g * trow + j * kGroupsPerBox) * 4 * tent;
+        const uint32_t tb1 = tb0 + 8 * trow * 4 * tent;
+        const uint32_t sxb = sumx_u32 + ((xoff / kGroupK + j * kGroupsPerBox) * kSumTok + 2 * t) * 4;
+        static_for<kGroupsPerBox>([&](auto qc) {               // groups of this box
+          constexpr int q = decltype(qc)::value;
+          float acc[NT][4];
+          static_for<SPG>([&](auto sc) {
+            constexpr int s = decltype(sc)::value;
+            constexpr int ks = q * SPG + s;                       // K step within the box
+            const uint32_t waddr = wrow ^ (ks * kStepBytes);
+            uint32_t a[2][4];
+            if constexpr (QK == kAff8) {
+              // 32 bytes per row and step: lane t takes bytes [8t, 8t+8) of them
+              const uint2 u0 = lds64<0>(waddr);
+              const uint2 u1 = lds64<8 * kBoxBytes>(waddr);
+              a[0][0] = __byte_perm(u0.x, 0x64646464u, 0x4140); a[0][1] = __byte_perm(u1.x, 0x64646464u, 0x4140);
+              a[0][2] = __byte_perm(u0.x, 0x64646464u, 0x4342); a[0][3] = __byte_perm(u1.x, 0x64646464u, 0x4342);
+              a[1][0] = __byte_perm(u0.y, 0x64646464u, 0x4140); a[1][1] = __byte_perm(u1.y, 0x64646464u, 0x4140);
+              a[1][2] = __byte_perm(u0.y, 0x64646464u, 0x4342); a[1][3] = __byte_perm(u1.y, 0x64646464u, 0x4342);
+            } else {
+              // 16 bytes per row and step: lane t takes word t
+              const uint32_t u0 = lds32<0>(waddr);
+              const uint32_t u1 = lds32<8 * kBoxBytes>(waddr);
+              if constexpr (QK == kAff4) {
+                a[0][0] = and_or(u0, nib_mask, magic);       a[0][1] = and_or(u1, nib_mask, magic);
+                a[0][2] = and_or(u0 >> 4, nib_mask, magic);  a[0][3] = and_or(u1 >> 4, nib_mask, magic);
+                a[1][0] = and_or(u0 >> 8, nib_mask, magic);  a[1][1] = and_or(u1 >> 8, nib_mask, magic);
+                a[1][2] = and_or(u0 >> 12, nib_mask, magic); a[1][3] = and_or(u1 >> 12, nib_mask, magic);
               } else {
-                // 16 bytes per row and step: lane t takes word t
-                const int off = ((ks ^ (g & 7)) << 4) + t * 4;
-                const uint32_t u0 = *reinterpret_cast<const uint32_t*>(row0 + off);
-                const uint32_t u1 = *reinterpret_cast<const uint32_t*>(row1 + off);
-                if constexpr (QK == kAff4) {
-                  a[0][0] = (u0 & 0x000F000Fu) | Ops::kMagic;         a[0][1] = (u1 & 0x000F000Fu) | Ops::kMagic;
-                  a[0][2] = ((u0 >> 4) & 0x000F000Fu) | Ops::kMagic;  a[0][3] = ((u1 >> 4) & 0x000F000Fu) | Ops::kMagic;
-                  a[1][0] = ((u0 >> 8) & 0x000F000Fu) | Ops::kMagic;  a[1][1] = ((u1 >> 8) & 0x000F000Fu) | Ops::kMagic;
-                  a[1][2] = ((u0 >> 12) & 0x000F000Fu) | Ops::kMagic; a[1][3] = ((u1 >> 12) & 0x000F000Fu) | Ops::kMagic;
-                } else {
-                  // The three magnitude bits of an E2M1 code at f16's exponent/mantissa boundary
-                  // are the code's value times 2^-14 (code 1 = 0.5 lands on a subnormal); the
-                  // sign bit goes to bit 15. The 2^14 is restored in the fold.
+                // The three magnitude bits of an E2M1 code at f16's exponent/mantissa boundary
+                // are the code's value times 2^-14 (code 1 = 0.5 lands on a subnormal); the
+                // sign bit goes to bit 15. The 2^14 is restored in the fold.
 #pragma unroll
-                  for (int r = 0; r < 2; ++r) {
-                    const uint32_t u = r ? u1 : u0;
-                    const uint32_t uh = u >> 4;
+                for (int r = 0; r < 2; ++r) {
+                  const uint32_t u = r ? u1 : u0;
+                  const uint32_t uh = u >> 4;
 #pragma unroll
-                    for (int bb = 0; bb < 4; ++bb) {  // byte bb -> elements (2bb, 2bb+1)
-                      const uint32_t tt = __byte_perm(u, uh, bb | ((4 + bb) << 8));
-                      a[bb >> 1][(bb & 1) * 2 + r] = ((tt << 9) & 0x0E000E00u) | ((tt << 12) & 0x80008000u);
-                    }
+                  for (int bb = 0; bb < 4; ++bb) {  // byte bb -> elements (2bb, 2bb+1)
+                    const uint32_t tt = __byte_perm(u, uh, bb | ((4 + bb) << 8));
+                    a[bb >> 1][(bb & 1) * 2 + r] = ((tt << 9) & 0x0E000E00u) | ((tt << 12) & 0x80008000u);
                   }
                 }
               }
-              const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-              const uint32_t one4[4] = {Ops::kOnes, Ops::kOnes, Ops::kOnes, Ops::kOnes};
-#pragma unroll
-              for (int h = 0; h < NT; ++h) {
-                uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-                if (h * 8 + g < p.M) xv = *reinterpret_cast<const uint4*>(xs + (h * 8 + g) * xrow + kloc);
-                if (s == 0) Ops::mma(acc[h], a[0], xv.x, xv.y, zero4);
-                else Ops::mma(acc[h], a[0], xv.x, xv.y, acc[h]);
-                Ops::mma(acc[h], a[1], xv.z, xv.w, acc[h]);
-                if constexpr (QK != kMx4) {   // sum of x over the group: A = all ones
-                  if (s == 0) Ops::mma(ones[h], one4, xv.x, xv.y, zero4);
-                  else Ops::mma(ones[h], one4, xv.x, xv.y, ones[h]);
-                  Ops::mma(ones[h], one4, xv.z, xv.w, ones[h]);
-                }
-              }
             }
-            // fold the group: rows g (c0, c1) and g+8 (c2, c3), tokens 2t and 2t+1
-            const float2 sb0 = tcur[g * trow + gi], sb1 = tcur[(g + 8) * trow + gi];
+            const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int h = 0; h < NT; ++h) {
-              if constexpr (QK == kMx4) {
-                yacc[h][0] = fmaf(sb0.x, acc[h][0] * 16384.0f, yacc[h][0]);
-                yacc[h][1] = fmaf(sb0.x, acc[h][1] * 16384.0f, yacc[h][1]);
-                yacc[h][2] = fmaf(sb1.x, acc[h][2] * 16384.0f, yacc[h][2]);
-                yacc[h][3] = fmaf(sb1.x, acc[h][3] * 16384.0f, yacc[h][3]);
-              } else {
-                yacc[h][0] = fmaf(sb0.x, acc[h][0], fmaf(sb0.y, ones[h][0], yacc[h][0]));
-                yacc[h][1] = fmaf(sb0.x, acc[h][1], fmaf(sb0.y, ones[h][1], yacc[h][1]));
-                yacc[h][2] = fmaf(sb1.x, acc[h][2], fmaf(sb1.y, ones[h][0], yacc[h][2]));
-                yacc[h][3] = fmaf(sb1.x, acc[h][3], fmaf(sb1.y, ones[h][1], yacc[h][3]));
-              }
+              const uint4 xv = lds128<ks * 64>(xbox[h]);
+              if (s == 0) Ops::mma(acc[h], a[0], xv.x, xv.y, zero4);
+              else Ops::mma(acc[h], a[0], xv.x, xv.y, acc[h]);
+              Ops::mma(acc[h], a[1], xv.z, xv.w, acc[h]);
             }
+          });
+          // fold the group: rows g (c0, c1) and g+8 (c2, c3), tokens 2t and 2t+1
+          if constexpr (QK == kMx4) {
+            const float s0 = __uint_as_float(lds32<q * 4>(tb0)), s1 = __uint_as_float(lds32<q * 4>(tb1));
+#pragma unroll
+            for (int h = 0; h < NT; ++h) {
+              yacc[h][0] = fmaf(s0, acc[h][0] * 16384.0f, yacc[h][0]);
+              yacc[h][1] = fmaf(s0, acc[h][1] * 16384.0f, yacc[h][1]);
+              yacc[h][2] = fmaf(s1, acc[h][2] * 16384.0f, yacc[h][2]);
+              yacc[h][3] = fmaf(s1, acc[h][3] * 16384.0f, yacc[h][3]);
+            }
+          } else {
+            const uint2 v0 = lds64<q * 8>(tb0), v1 = lds64<q * 8>(tb1);      // (scale, bias - C*scale)
+            const float s0 = __uint_as_float(v0.x), b0 = __uint_as_float(v0.y);
+            const float s1 = __uint_as_float(v1.x), b1 = __uint_as_float(v1.y);
+            static_for<NT>([&](auto hc) {
+              constexpr int h = decltype(hc)::value;
+              const uint2 sxr = lds64<(q * kSumTok + h * 8) * 4>(sxb);
+              const float sx0 = __uint_as_float(sxr.x), sx1 = __uint_as_float(sxr.y);
+              yacc[h][0] = fmaf(s0, acc[h][0], fmaf(b0, sx0, yacc[h][0]));
+              yacc[h][1] = fmaf(s0, acc[h][1], fmaf(b0, sx1, yacc[h][1]));
+              yacc[h][2] = fmaf(s1, acc[h][2], fmaf(b1, sx0, yacc[h][2]));
+              yacc[h][3] = fmaf(s1, acc[h][3], fmaf(b1, sx1, yacc[h][3]));
+            });
           }
-        }
+        });
         // the slot is free again: refill it with the next box this warp will need
         __syncwarp();
-        if (lane == 0 && issue.tile < ntiles) {
-          fence_proxy_async();
-          issue_box();
-        }
+        // (Every read of the slot has been consumed by an MMA issued before the __syncwarp, so the
+        // refill needs no further ordering.)
+        if (lane == 0 && issue.tile < ntiles) issue_box();
+        if (tracing) tr_t[4] += clock64() - tq2;
       }
-      if (prefetch) table_store(tbl + (tbuf ^ 1) * kRowsPerCta * trow, cgroups, tc, prs, prb);
-      if (resident) tbuf ^= 1;
+      const long long tq3 = tracing ? clock64() : 0;
+      while (pb <= nbatch) prefetch_step();
+      if (tracing) tr_t[7] += clock64() - tq3;
+      if (xres) {
+        tbuf ^= 1;
+        if (!last_pass) consumer_barrier();      // the next pass's tables are complete; the tile's
+      }                                          // last pass shares the reduce barrier below
     }
 
     // ---- reduce the K split across warps (fixed order) and store this tile ----
@@ -466,7 +655,9 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
     for (int h = 0; h < NT; ++h)
 #pragma unroll
       for (int i = 0; i < 4; ++i) rcur[(warp * NT * 4 + h * 4 + i) * 32 + lane] = yacc[h][i];
-    __syncthreads();
+    const long long tb0 = tracing ? clock64() : 0;
+    consumer_barrier();
+    if (tracing) tr_t[2] += clock64() - tb0;
     if (*abort_flag) {
       if (threadIdx.x == 0) atomicCAS(p.status, 0, *abort_flag);
       return;
@@ -486,21 +677,40 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
     }
     rbuf ^= 1;
   }
+  if (tracing && threadIdx.x == 32 * 3) {     // warp 3 speaks for the CTA
+    for (int i = 0; i < 8; ++i) p.trace[blockIdx.x * 8 + i] = tr_t[i];
+    p.trace[blockIdx.x * 8 + 5] = clock64() - tr_c0;
+  }
+}
+
+// Shared memory one CTA needs: rings, activations of `xk` K elements, their group sums, two
+// table buffers of `kc` K elements, two reduce buffers, barriers, the block of zeros.
+size_t smem_bytes(const GemvParams& gp, int nt, int group_k, bool mx, int ring) {
+  const size_t tgroups = gp.kc / group_k;
+  const size_t tent = mx ? 1 : 2;
+  return 1024 + static_cast<size_t>(kWarps) * ring * kBoxSmem +
+         static_cast<size_t>(gp.M) * (gp.xk + kXPad) * 2 +
+         (mx ? 0 : static_cast<size_t>(gp.xk / group_k) * 8 * nt * sizeof(float)) +
+         static_cast<size_t>(2) * kRowsPerCta * (tgroups + 1) * tent * sizeof(uint32_t) +
+         static_cast<size_t>(2) * kWarps * nt * 4 * 32 * sizeof(float) +
+         static_cast<size_t>(kWarps) * kMaxRing * sizeof(uint64_t) + 512 + 16;
+}
+
+bool use_pdl() {
+  static const bool on = [] {
+    const char* e = getenv("QMM_GEMV_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 template <int QK, typename XT, int NT, int SPG>
 int launch_kernel(const CUtensorMap& wm, const GemvParams& gp, cudaStream_t stream) {
-  const int tgroups = gp.kc / (32 * SPG);
-  const size_t smem = 1024 + static_cast<size_t>(kWarps) * gp.ring * kBoxSmem +
-                      static_cast<size_t>(gp.M) * (gp.kc + kXPad) * 2 +
-                      static_cast<size_t>(2) * kRowsPerCta * (tgroups + 1) * sizeof(float2) +
-                      static_cast<size_t>(2) * kWarps * NT * 4 * 32 * sizeof(float) +
-                      static_cast<size_t>(kWarps) * kMaxRing * sizeof(uint64_t) + 16;
+  const size_t smem = smem_bytes(gp, NT, 32 * SPG, QK == kMx4, 1 << gp.ring_shift);
   // Persistent CTAs: two per SM share the machine's segments; a CTA walks tiles with a grid stride.
   int64_t per_seg = (2LL * device_sm_count() + gp.batch - 1) / gp.batch;
   if (per_seg < 1) per_seg = 1;
   if (per_seg > gp.tiles) per_seg = gp.tiles;
-  dim3 grid(static_cast<unsigned>(per_seg), static_cast<unsigned>(gp.batch));
   auto kernel = qmm_gemv_kernel<QK, XT, NT, SPG>;
   static bool configured = false;
   if (!configured) {
@@ -508,7 +718,18 @@ int launch_kernel(const CUtensorMap& wm, const GemvParams& gp, cudaStream_t stre
     if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
   }
-  kernel<<<grid, kWarps * 32, smem, stream>>>(wm, gp);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(per_seg), static_cast<unsigned>(gp.batch));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, wm, gp);
+  if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "qmm_gemv_kernel launch: %s", cudaGetErrorString(e));
   count_launch();
   return check_launch("qmm_gemv_kernel");
 }
@@ -555,19 +776,37 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   gp.w_batch_rows = p.rhs_idx ? p.N : p.w_batch_stride;
   gp.group_size = p.group_size; gp.table_dtype = p.table_dtype; gp.y_dtype = p.y_dtype;
   gp.tiles = static_cast<int>((p.N + kRowsPerCta - 1) / kRowsPerCta);
-  const int bits = (p.mode == QMM_MODE_AFFINE && p.bits == 8) ? 8 : 4;
+  const bool mx = p.mode == QMM_MODE_MXFP4;
+  const int bits = (!mx && p.bits == 8) ? 8 : 4;
   const int boxk = kBoxBytes * 8 / bits;
-  // K elements staged per pass: the staged activations stay under ~64 KiB per CTA, and a
-  // pass is a whole number of boxes.
-  int kc = static_cast<int>(65536 / (2 * p.M) / boxk * boxk);
-  const int64_t kround = (p.K + boxk - 1) / boxk * boxk;
-  if (kround < kc) kc = static_cast<int>(kround);
-  gp.kc = kc;
-  // Ring depth: two tiles' worth of a warp's boxes, up to kMaxRing, so that a warp's requests
-  // run ahead across tile boundaries.
-  const int64_t boxes = (p.K + boxk - 1) / boxk;
-  int64_t per_warp = 2 * ((boxes + kWarps - 1) / kWarps);
-  gp.ring = static_cast<int>(per_warp < 1 ? 1 : (per_warp > kMaxRing ? kMaxRing : per_warp));
+  const int group_k = mx ? 32 : p.group_size;
+  const int nt = p.M <= 8 ? 1 : 2;
+  // Tables are staged in passes of at most 64 groups (what one batch of table loads covers).
+  // The activations of all of K stay in shared memory when that fits the budget of two CTAs
+  // per SM (with a shallower ring if need be); otherwise they are restaged pass by pass, in
+  // passes of as many boxes as fit.
+  const int kround = static_cast<int>((p.K + boxk - 1) / boxk * boxk);
+  const int pass_k = 64 * group_k / boxk * boxk;           // group_k >= 32: at least 2048
+  gp.kc = kround < pass_k ? kround : pass_k;
+  gp.xk = kround;
+  gp.ring_shift = 2;
+  if (smem_bytes(gp, nt, group_k, mx, 4) > kSmemBudget) {
+    if (smem_bytes(gp, nt, group_k, mx, 2) <= kSmemBudget) {
+      gp.ring_shift = 1;
+    } else {
+      gp.xk = gp.kc;
+      while (gp.kc > boxk && smem_bytes(gp, nt, group_k, mx, 4) > kSmemBudget) gp.xk = gp.kc -= boxk;
+    }
+  }
+  static long long* trace_buf = nullptr;
+  static const bool trace_on = getenv("QMM_GEMV_TRACE") != nullptr;
+  if (trace_on && !trace_buf) cudaMalloc(&trace_buf, sizeof(long long) * 8 * 1024);
+  if (trace_on) cudaMemsetAsync(trace_buf, 0, sizeof(long long) * 8 * 1024, stream);
+  gp.trace = trace_on ? trace_buf : nullptr;
+  gp.nchunks = static_cast<int>((p.K + gp.kc - 1) / gp.kc);
+  int pieces = gp.xk / 8, xs = 5;
+  while ((1 << xs) < pieces) ++xs;
+  gp.xshift = xs;
 
   // The packed weight as a 2-D byte tensor [rows, K*bits/8] over every weight matrix behind
   // `w`; a box that reaches past the last row is zero-filled by the TMA unit.
@@ -577,9 +816,25 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   CUtensorMap wm;
   int rc = tensor_map_2d(&wm, QMM_U8, p.w, row_bytes, rows, row_bytes, kBoxBytes, kRowsPerCta, 1);
   if (rc) return rc;
-  if (p.mode == QMM_MODE_MXFP4) return launch_xt<kMx4>(wm, gp, p.x_dtype, stream);
-  if (p.bits == 8) return launch_xt<kAff8>(wm, gp, p.x_dtype, stream);
-  return launch_xt<kAff4>(wm, gp, p.x_dtype, stream);
+  if (p.mode == QMM_MODE_MXFP4) rc = launch_xt<kMx4>(wm, gp, p.x_dtype, stream);
+  else if (p.bits == 8) rc = launch_xt<kAff8>(wm, gp, p.x_dtype, stream);
+  else rc = launch_xt<kAff4>(wm, gp, p.x_dtype, stream);
+  if (trace_on && rc == 0) {   // development aid: average cycles per phase over the CTAs
+    cudaStreamSynchronize(stream);
+    static long long host[8 * 1024];
+    int64_t grid = (2LL * device_sm_count() + gp.batch - 1) / gp.batch;
+    if (grid > gp.tiles) grid = gp.tiles;
+    if (grid > 1024) grid = 1024;
+    cudaMemcpy(host, trace_buf, sizeof(long long) * 8 * grid, cudaMemcpyDeviceToHost);
+    double avg[8] = {0};
+    for (int64_t c = 0; c < grid; ++c)
+      for (int i = 0; i < 8; ++i) avg[i] += static_cast<double>(host[c * 8 + i]) / grid;
+    fprintf(stderr,
+            "qmm_gemv cycles/CTA (warp 3): full-wait %.0f | prologue %.0f | reduce barrier %.0f | staging %.0f | "
+            "compute %.0f | sum-x %.0f | total %.0f | table prefetch %.0f | tiles/CTA %.2f\n",
+            avg[0], avg[1], avg[2], avg[3], avg[4], avg[6], avg[5], avg[7], static_cast<double>(gp.tiles) / grid);
+  }
+  return rc;
 }
 
 }  // namespace qmm

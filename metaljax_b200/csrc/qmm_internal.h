@@ -44,17 +44,13 @@ int launch_pack_codes(const uint8_t* codes, uint32_t* out, int64_t rows, int64_t
                       cudaStream_t stream);
 
 #ifdef __CUDACC__
-// Raw bits of element i of a scale/bias table whose elements are `esz` (2 or 4) bytes wide.
-// Both candidate loads are predicated instead of branched over, so a run of calls issues all
-// of its loads back to back and waits once, not once per element.
-__device__ __forceinline__ uint32_t table_raw(const void* p, int esz, int64_t i) {
-  const char* a = static_cast<const char*>(p) + i * esz;
-  uint32_t v;
-  asm("{ .reg .pred p2; .reg .b16 h; setp.eq.s32 p2, %2, 2; mov.b16 h, 0; mov.b32 %0, 0;\n"
-      "@p2 ld.global.nc.u16 h, [%1];\n @!p2 ld.global.nc.u32 %0, [%1];\n @p2 cvt.u32.u16 %0, h; }"
-      : "=r"(v)
-      : "l"(a), "r"(esz));
-  return v;
+// Raw bits of element i of a 16-bit (`wide` false) or 32-bit (`wide` true) table, zero-extended.
+// Nothing here depends on the loaded value, so a caller can request many elements before it
+// uses the first; callers keep `wide` loop-invariant so that the loads of a batch do not end
+// up in separate branches.
+__device__ __forceinline__ uint32_t table_raw(const void* p, bool wide, int64_t i) {
+  if (wide) return __ldg(static_cast<const uint32_t*>(p) + i);
+  return __ldg(static_cast<const uint16_t*>(p) + i);
 }
 
 // The float value of such raw bits (QMM_BF16 / QMM_F16 / QMM_F32).

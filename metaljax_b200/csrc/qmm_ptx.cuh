@@ -68,6 +68,30 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, void* dst, u
       : "memory");
 }
 
+// Shared-memory loads from a 32-bit shared address plus a compile-time byte offset (one
+// instruction, no 64-bit address arithmetic). volatile keeps them behind the barrier waits
+// they follow in program order.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr), "n"(OFF));
+  return v;
+}
+
 // Orders this thread's earlier generic-proxy accesses to shared memory before later
 // async-proxy (TMA) writes to the same bytes.
 __device__ __forceinline__ void fence_proxy_async() {
