@@ -60,7 +60,8 @@ constexpr int kXPad = 32;           // elements of padding per staged activation
 constexpr int kBoxBytes = 128;      // bytes of one weight row in a TMA box
 constexpr int kBoxSmem = kRowsPerCta * kBoxBytes;   // 2 KiB
 constexpr int kMaxRing = 4;         // boxes a warp keeps in flight
-constexpr int kSmemBudget = 112 * 1024;   // two CTAs per SM
+constexpr int kSmemBudget = 112 * 1024;      // two CTAs per SM
+constexpr int kSmemBudgetOne = 220 * 1024;   // one CTA per SM
 
 enum { kAff4 = 0, kAff8 = 1, kMx4 = 2 };
 
@@ -83,6 +84,8 @@ struct GemvParams {
   int xshift;      // log2 of the 8-element pieces per staged row, rounded up to a power of two
   int tiles;       // 16-row tiles per weight matrix
   int nchunks;     // staging passes over K: ceil(K / kc)
+  int tiles_per_cta;   // most tiles any CTA walks: ceil(tiles / grid)
+  int grid;        // CTAs per weight matrix
   long long* trace;   // development aid: cycles per phase of consumer warp 0 of every CTA, or NULL
 };
 
@@ -155,28 +158,26 @@ __device__ __forceinline__ void load8(const XT* p, float (&f)[8]) {
   }
 }
 
-// Walks one warp's boxes in the order they are consumed: tile by tile (grid stride), inside a
-// tile chunk by chunk (a chunk is what the CTA stages of x at a time), and inside a chunk the
-// warp's contiguous share of its boxes.
+// Walks one warp's boxes in the order they are consumed: pass by pass over K (a pass is what
+// the CTA stages of the tables at a time), inside a pass tile by tile (grid stride), and
+// inside a tile the warp's contiguous share of the pass's boxes. Done when chunk == nchunks.
 struct BoxCursor {
-  int tile, chunk, j, hi;
+  int chunk, tile, j, lo, hi;
 };
 
+// Positions the cursor on the first box of pass c.chunk (or of the next pass in which this
+// warp has boxes) of tile `tile0`.
 template <int BOXK>
-__device__ __forceinline__ void cursor_seek(BoxCursor& c, int ntiles, int tstride, int nchunks, int warp,
-                                            int K, int kc) {
-  while (c.tile < ntiles) {
-    while (c.chunk < nchunks) {
-      const int left = K - c.chunk * kc;                    // 32-bit on purpose: no 64-bit division
-      const int nb = ((left < kc ? left : kc) + BOXK - 1) / BOXK;
-      c.j = nb * warp / kWarps;
-      c.hi = nb * (warp + 1) / kWarps;
-      if (c.j < c.hi) return;
-      ++c.chunk;
-    }
-    c.tile += tstride;
-    c.chunk = 0;
+__device__ __forceinline__ void cursor_seek(BoxCursor& c, int tile0, int nchunks, int warp, int K, int kc) {
+  for (; c.chunk < nchunks; ++c.chunk) {
+    const int left = K - c.chunk * kc;                    // 32-bit on purpose: no 64-bit division
+    const int nb = ((left < kc ? left : kc) + BOXK - 1) / BOXK;
+    c.lo = nb * warp / kWarps;
+    c.hi = nb * (warp + 1) / kWarps;
+    if (c.lo < c.hi) break;
   }
+  c.tile = tile0;
+  c.j = c.lo;
 }
 
 __device__ __forceinline__ void consumer_barrier() { __syncthreads(); }
@@ -219,6 +220,7 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gv_smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ring = 1 << p.ring_shift, rmask = ring - 1;
+  const int nchunks = p.nchunks;
   const int xrow = p.xk + kXPad;                   // staged row stride in elements
   const bool xres = p.xk > p.kc || p.nchunks == 1;  // the activations of all of K are staged once
   const int tgroups = p.kc / kGroupK;              // groups staged per pass
@@ -230,7 +232,8 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   float* sumx = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + static_cast<size_t>(p.M) * xrow * sizeof(AT));
   uint32_t* tbl = reinterpret_cast<uint32_t*>(sumx + (QK == kMx4 ? 0 : (p.xk / kGroupK) * kSumTok));
   float* red = reinterpret_cast<float*>(tbl + 2 * kRowsPerCta * trow * tent);   // two buffers
-  uint64_t* full_all = reinterpret_cast<uint64_t*>(red + 2 * kWarps * NT * 4 * 32);
+  float* accs = red + 2 * kWarps * NT * 4 * 32;     // per local tile, warp 0's partial sums between passes
+  uint64_t* full_all = reinterpret_cast<uint64_t*>(accs + (nchunks > 1 ? p.tiles_per_cta * NT * 4 * 32 : 0));
   uint8_t* zeros = reinterpret_cast<uint8_t*>(full_all + kWarps * kMaxRing);      // 512 zero bytes: the
                                                                                   // "activations" of tokens >= M
   volatile int* abort_flag = reinterpret_cast<volatile int*>(zeros + 512);
@@ -244,7 +247,6 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
     x_off = seg * p.x_batch_stride;
     wb = p.w_batch_rows ? seg : 0;
   }
-  const int nchunks = p.nchunks;
   const int boxes_per_chunk = p.kc / kBoxK;
   const int ntiles = p.tiles, tstride = gridDim.x;
   const int64_t groups = p.K / kGroupK;
@@ -323,23 +325,27 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   uint64_t* full = full_all + warp * kMaxRing;
 
   // ---- lane 0 requests this warp's first boxes before anything else ----
-  BoxCursor issue = {static_cast<int>(blockIdx.x), 0, 0, 0};
+  BoxCursor issue = {0, 0, 0, 0, 0};
   int issued = 0;
   const int row_base = static_cast<int>(wb * p.N);
-  auto issue_box = [&]() {   // lane 0 only; issue.tile < ntiles
+  auto issue_box = [&]() {   // lane 0 only; issue.chunk < nchunks
     const int slot = issued & rmask;
     mbar_expect_tx(&full[slot], kBoxSmem);
     tma_load_2d(&w_map, wring + slot * kBoxSmem, &full[slot], (issue.chunk * boxes_per_chunk + issue.j) * kBoxBytes,
                 row_base + issue.tile * kRowsPerCta);
     ++issued;
     if (++issue.j >= issue.hi) {
-      ++issue.chunk;
-      cursor_seek<kBoxK>(issue, ntiles, tstride, nchunks, warp, static_cast<int>(p.K), p.kc);
+      issue.j = issue.lo;
+      issue.tile += tstride;
+      if (issue.tile >= ntiles) {
+        ++issue.chunk;
+        cursor_seek<kBoxK>(issue, static_cast<int>(blockIdx.x), nchunks, warp, static_cast<int>(p.K), p.kc);
+      }
     }
   };
   if (lane == 0) {
-    cursor_seek<kBoxK>(issue, ntiles, tstride, nchunks, warp, static_cast<int>(p.K), p.kc);
-    while (issued < ring && issue.tile < ntiles) issue_box();
+    cursor_seek<kBoxK>(issue, static_cast<int>(blockIdx.x), nchunks, warp, static_cast<int>(p.K), p.kc);
+    while (issued < ring && issue.chunk < nchunks) issue_box();
   }
   const int64_t y_off = seg * p.y_batch_stride;
   const XT* xg = reinterpret_cast<const XT*>(p.x) + x_off;
@@ -467,69 +473,68 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
     nb = (kc + kBoxK - 1) / kBoxK;
   };
 
-  for (int tile = blockIdx.x; tile < ntiles; tile += tstride) {
-    const int64_t n0 = static_cast<int64_t>(tile) * kRowsPerCta;
-    float yacc[NT][4];
-#pragma unroll
-    for (int h = 0; h < NT; ++h)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) yacc[h][i] = 0.0f;
-
-    for (int chunk = 0; chunk < nchunks; ++chunk) {
-      const int64_t kbase = static_cast<int64_t>(chunk) * p.kc;
-      int kc, nb;
-      pass_extent(chunk, kc, nb);
-      const int cgroups = kc / kGroupK;
-      const int jlo = nb * warp / kWarps, jhi = nb * (warp + 1) / kWarps;
-      const int xoff = xres ? static_cast<int>(kbase) : 0;        // this pass's first K element in xs
-      if (!xres || first) {
-        const long long ts0 = tracing ? clock64() : 0;
-        uint32_t* tdst = tbl + tbuf * kRowsPerCta * trow * tent;
-        uint32_t rs[kTU], rb[kTU];
-        if (first) {
-#pragma unroll
-          for (int u = 0; u < kTU; ++u) { rs[u] = frs[u]; rb[u] = frb[u]; }
-        } else {
-          table_load(tile, kbase, cgroups, tg0, rs, rb);
+  for (int chunk = 0; chunk < nchunks; ++chunk) {
+    const int64_t kbase = static_cast<int64_t>(chunk) * p.kc;
+    int kc, nb;
+    pass_extent(chunk, kc, nb);
+    const int cgroups = kc / kGroupK;
+    const int jlo = nb * warp / kWarps, jhi = nb * (warp + 1) / kWarps;
+    const int xoff = xres ? static_cast<int>(kbase) : 0;        // this pass's first K element in xs
+    if (first) {
+      // ---- the CTA's first unit: its tables were requested at kernel entry ----
+      const long long ts0 = tracing ? clock64() : 0;
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (xres) stage_x(0, static_cast<int>(p.K), p.xk);
+      else stage_x(kbase, kc, nb * kBoxK);
+      consumer_barrier();
+      if (tracing) tr_t[3] += clock64() - ts0;
+      const long long tp0 = tracing ? clock64() : 0;
+      if (xres) {                                            // every pass's sums, once
+        for (int c = 0; c < nchunks; ++c) {
+          int ckc, cnb;
+          pass_extent(c, ckc, cnb);
+          sum_x(c * p.kc, cnb * warp / kWarps, cnb * (warp + 1) / kWarps);
         }
-        if (first) asm volatile("griddepcontrol.wait;" ::: "memory");
-        else consumer_barrier();                              // everyone is done with the previous contents
-        if (xres) stage_x(0, static_cast<int>(p.K), p.xk);
-        else stage_x(kbase, kc, nb * kBoxK);
-        consumer_barrier();
-        if (tracing) tr_t[3] += clock64() - ts0;
-        const long long tp0 = tracing ? clock64() : 0;
-        if (xres) {                                            // every pass's sums, once
-          for (int c = 0; c < nchunks; ++c) {
-            int ckc, cnb;
-            pass_extent(c, ckc, cnb);
-            sum_x(c * p.kc, cnb * warp / kWarps, cnb * (warp + 1) / kWarps);
-          }
-        } else {
-          sum_x(0, jlo, jhi);
-        }
-        table_store(tdst, kbase, cgroups, tg0, rs, rb);       // requested long ago: in flight meanwhile
-        for (int g0 = tg0 + 16 * kTU; g0 < tgroups; g0 += 16 * kTU) {
-          table_load(tile, kbase, cgroups, g0, rs, rb);
-          table_store(tdst, kbase, cgroups, g0, rs, rb);
-        }
-        consumer_barrier();
-        first = false;
-        if (tracing) tr_t[6] += clock64() - tp0;
+      } else {
+        sum_x(0, jlo, jhi);
       }
+      table_store(tbl, kbase, cgroups, tg0, frs, frb);       // requested long ago: in flight meanwhile
+      for (int g0 = tg0 + 16 * kTU; g0 < tgroups; g0 += 16 * kTU) {
+        table_load(static_cast<int>(blockIdx.x), kbase, cgroups, g0, frs, frb);
+        table_store(tbl, kbase, cgroups, g0, frs, frb);
+      }
+      consumer_barrier();
+      first = false;
+      if (tracing) tr_t[6] += clock64() - tp0;
+    } else if (!xres) {
+      // ---- a later pass of activations that do not fit: restage this pass's slice. Everyone
+      // is past the previous unit's barrier, so nobody reads the old slice any more; the
+      // pass's first tables were requested during the previous unit. ----
+      stage_x(kbase, kc, nb * kBoxK);
+      consumer_barrier();
+      sum_x(0, jlo, jhi);
+    }
+
+    int tl = 0;                                             // index of the tile among this CTA's tiles
+    for (int tile = blockIdx.x; tile < ntiles; tile += tstride, ++tl) {
+      const int64_t n0 = static_cast<int64_t>(tile) * kRowsPerCta;
+      float yacc[NT][4];
+#pragma unroll
+      for (int h = 0; h < NT; ++h)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) yacc[h][i] = 0.0f;
       const uint32_t* tcur = tbl + tbuf * kRowsPerCta * trow * tent;
       uint32_t* tnext = tbl + (tbuf ^ 1) * kRowsPerCta * trow * tent;
-      // the pass after this one: the tile's next pass, or the first pass of the CTA's next tile
-      const bool last_pass = chunk + 1 == nchunks;
-      const int ptile = last_pass ? tile + tstride : tile;
-      const int pchunk = last_pass ? 0 : chunk + 1;
+      // the unit after this one: the pass's next tile, or the first tile of the next pass
+      const bool last_tile = tile + tstride >= ntiles;
+      const int ptile = last_tile ? static_cast<int>(blockIdx.x) : tile + tstride;
+      const int pchunk = last_tile ? chunk + 1 : chunk;
       int pkc, pnb;
       pass_extent(pchunk, pkc, pnb);
       const int64_t pkbase = static_cast<int64_t>(pchunk) * p.kc;
       const int pgroups = pkc / kGroupK;
       uint32_t prs[kTU], prb[kTU];
-      const bool prefetch = xres && ptile < ntiles;
-      int pb = prefetch ? 0 : nbatch + 1;
+      int pb = pchunk < nchunks ? 0 : nbatch + 1;
       auto prefetch_step = [&]() {
         if (pb > 0) table_store(tnext, pkbase, pgroups, tg0 + 16 * kTU * (pb - 1), prs, prb);
         if (pb < nbatch) table_load(ptile, pkbase, pgroups, tg0 + 16 * kTU * pb, prs, prb);
@@ -637,45 +642,48 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
         __syncwarp();
         // (Every read of the slot has been consumed by an MMA issued before the __syncwarp, so the
         // refill needs no further ordering.)
-        if (lane == 0 && issue.tile < ntiles) issue_box();
+        if (lane == 0 && issue.chunk < nchunks) issue_box();
         if (tracing) tr_t[4] += clock64() - tq2;
       }
       const long long tq3 = tracing ? clock64() : 0;
       while (pb <= nbatch) prefetch_step();
       if (tracing) tr_t[7] += clock64() - tq3;
-      if (xres) {
-        tbuf ^= 1;
-        if (!last_pass) consumer_barrier();      // the next pass's tables are complete; the tile's
-      }                                          // last pass shares the reduce barrier below
-    }
+      tbuf ^= 1;
 
-    // ---- reduce the K split across warps (fixed order) and store this tile ----
-    float* rcur = red + rbuf * kWarps * NT * 4 * 32;
-#pragma unroll
-    for (int h = 0; h < NT; ++h)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) rcur[(warp * NT * 4 + h * 4 + i) * 32 + lane] = yacc[h][i];
-    const long long tb0 = tracing ? clock64() : 0;
-    consumer_barrier();
-    if (tracing) tr_t[2] += clock64() - tb0;
-    if (*abort_flag) {
-      if (threadIdx.x == 0) atomicCAS(p.status, 0, *abort_flag);
-      return;
-    }
-    if (warp == 0) {
+      // ---- reduce the K split across warps (fixed order); the pass's partial sums of the
+      // tile wait in shared memory for the next pass, the last pass stores the tile ----
+      float* rcur = red + rbuf * kWarps * NT * 4 * 32;
 #pragma unroll
       for (int h = 0; h < NT; ++h)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float v = 0.0f;
+        for (int i = 0; i < 4; ++i) rcur[(warp * NT * 4 + h * 4 + i) * 32 + lane] = yacc[h][i];
+      const long long tb0 = tracing ? clock64() : 0;
+      consumer_barrier();                        // also: the next unit's tables are complete
+      if (tracing) tr_t[2] += clock64() - tb0;
+      if (*abort_flag) {
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, *abort_flag);
+        return;
+      }
+      if (warp == 0) {
+        float* acc = accs + tl * NT * 4 * 32;
 #pragma unroll
-          for (int wv = 0; wv < kWarps; ++wv) v += rcur[(wv * NT * 4 + h * 4 + i) * 32 + lane];
-          const int64_t row = n0 + g + (i >> 1) * 8;
-          const int64_t tok = h * 8 + 2 * t + (i & 1);
-          if (row < p.N && tok < p.M) gv_store(p.y, p.y_dtype, y_off + tok * p.N + row, v);
-        }
+        for (int h = 0; h < NT; ++h)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float v = chunk > 0 ? acc[(h * 4 + i) * 32 + lane] : 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < kWarps; ++wv) v += rcur[(wv * NT * 4 + h * 4 + i) * 32 + lane];
+            if (chunk + 1 < nchunks) {
+              acc[(h * 4 + i) * 32 + lane] = v;
+            } else {
+              const int64_t row = n0 + g + (i >> 1) * 8;
+              const int64_t tok = h * 8 + 2 * t + (i & 1);
+              if (row < p.N && tok < p.M) gv_store(p.y, p.y_dtype, y_off + tok * p.N + row, v);
+            }
+          }
+      }
+      rbuf ^= 1;
     }
-    rbuf ^= 1;
   }
   if (tracing && threadIdx.x == 32 * 3) {     // warp 3 speaks for the CTA
     for (int i = 0; i < 8; ++i) p.trace[blockIdx.x * 8 + i] = tr_t[i];
@@ -693,6 +701,7 @@ size_t smem_bytes(const GemvParams& gp, int nt, int group_k, bool mx, int ring) 
          (mx ? 0 : static_cast<size_t>(gp.xk / group_k) * 8 * nt * sizeof(float)) +
          static_cast<size_t>(2) * kRowsPerCta * (tgroups + 1) * tent * sizeof(uint32_t) +
          static_cast<size_t>(2) * kWarps * nt * 4 * 32 * sizeof(float) +
+         (gp.nchunks > 1 ? static_cast<size_t>(gp.tiles_per_cta) * nt * 4 * 32 * sizeof(float) : 0) +
          static_cast<size_t>(kWarps) * kMaxRing * sizeof(uint64_t) + 512 + 16;
 }
 
@@ -707,14 +716,12 @@ bool use_pdl() {
 template <int QK, typename XT, int NT, int SPG>
 int launch_kernel(const CUtensorMap& wm, const GemvParams& gp, cudaStream_t stream) {
   const size_t smem = smem_bytes(gp, NT, 32 * SPG, QK == kMx4, 1 << gp.ring_shift);
-  // Persistent CTAs: two per SM share the machine's segments; a CTA walks tiles with a grid stride.
-  int64_t per_seg = (2LL * device_sm_count() + gp.batch - 1) / gp.batch;
-  if (per_seg < 1) per_seg = 1;
-  if (per_seg > gp.tiles) per_seg = gp.tiles;
+  // Persistent CTAs share the machine's segments; a CTA walks tiles with a grid stride.
+  const int64_t per_seg = gp.grid;
   auto kernel = qmm_gemv_kernel<QK, XT, NT, SPG>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudgetOne);
     if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
   }
@@ -781,29 +788,43 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   const int boxk = kBoxBytes * 8 / bits;
   const int group_k = mx ? 32 : p.group_size;
   const int nt = p.M <= 8 ? 1 : 2;
-  // Tables are staged in passes of at most 64 groups (what one batch of table loads covers).
-  // The activations of all of K stay in shared memory when that fits the budget of two CTAs
-  // per SM (with a shallower ring if need be); otherwise they are restaged pass by pass, in
-  // passes of as many boxes as fit.
+  // Tables are staged in passes of 64 or 128 groups (one or two batches of table loads).
+  // Preference order: (1) the activations of all of K stay in shared memory, two CTAs per SM,
+  // ring of 4 then of 2 boxes per warp, passes of 128 then of 64 groups; (2) the activations are restaged pass by pass, a pass
+  // being a multiple of 8 boxes (one per warp), two CTAs per SM; (3) the same with one CTA
+  // per SM and its larger shared memory; (4) whatever pass fits.
   const int kround = static_cast<int>((p.K + boxk - 1) / boxk * boxk);
   const int pass_k = 64 * group_k / boxk * boxk;           // group_k >= 32: at least 2048
-  gp.kc = kround < pass_k ? kround : pass_k;
-  gp.xk = kround;
-  gp.ring_shift = 2;
-  if (smem_bytes(gp, nt, group_k, mx, 4) > kSmemBudget) {
-    if (smem_bytes(gp, nt, group_k, mx, 2) <= kSmemBudget) {
-      gp.ring_shift = 1;
-    } else {
-      gp.xk = gp.kc;
-      while (gp.kc > boxk && smem_bytes(gp, nt, group_k, mx, 4) > kSmemBudget) gp.xk = gp.kc -= boxk;
+  const int sms = device_sm_count();
+  auto configure = [&](int xk, int kc, int ring_shift, int ctas_per_sm) -> size_t {
+    gp.xk = xk; gp.kc = kc; gp.ring_shift = ring_shift;
+    gp.nchunks = static_cast<int>((p.K + kc - 1) / kc);
+    int64_t grid = (static_cast<int64_t>(ctas_per_sm) * sms + gp.batch - 1) / gp.batch;
+    if (grid < 1) grid = 1;
+    if (grid > gp.tiles) grid = gp.tiles;
+    gp.grid = static_cast<int>(grid);
+    gp.tiles_per_cta = static_cast<int>((gp.tiles + grid - 1) / grid);
+    return smem_bytes(gp, nt, group_k, mx, 1 << ring_shift);
+  };
+  bool done = false;
+  for (int ring_shift = 2; !done && ring_shift >= 1; --ring_shift)
+    for (int mult = 2; !done && mult >= 1; --mult) {       // passes of 128, then of 64 groups
+      const int want = mult * pass_k;
+      done = configure(kround, kround < want ? kround : want, ring_shift, 2) <= kSmemBudget;
     }
+  const int kc_res = kround < pass_k ? kround : pass_k;
+  for (int ctas = 2; !done && ctas >= 1; --ctas) {
+    const size_t budget = ctas == 2 ? kSmemBudget : kSmemBudgetOne;
+    for (int kc = kc_res / (8 * boxk) * (8 * boxk); !done && kc >= 8 * boxk; kc -= 8 * boxk)
+      done = configure(kc, kc, 2, ctas) <= budget || configure(kc, kc, 1, ctas) <= budget;
   }
+  for (int kc = kc_res; !done && kc >= boxk; kc -= boxk) done = configure(kc, kc, 1, 1) <= kSmemBudgetOne;
+  if (!done) return fail(QMM_ERR_UNSUPPORTED, "decode kernel: no staging plan fits shared memory");
   static long long* trace_buf = nullptr;
   static const bool trace_on = getenv("QMM_GEMV_TRACE") != nullptr;
   if (trace_on && !trace_buf) cudaMalloc(&trace_buf, sizeof(long long) * 8 * 1024);
   if (trace_on) cudaMemsetAsync(trace_buf, 0, sizeof(long long) * 8 * 1024, stream);
   gp.trace = trace_on ? trace_buf : nullptr;
-  gp.nchunks = static_cast<int>((p.K + gp.kc - 1) / gp.kc);
   int pieces = gp.xk / 8, xs = 5;
   while ((1 << xs) < pieces) ++xs;
   gp.xshift = xs;
@@ -822,9 +843,7 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   if (trace_on && rc == 0) {   // development aid: average cycles per phase over the CTAs
     cudaStreamSynchronize(stream);
     static long long host[8 * 1024];
-    int64_t grid = (2LL * device_sm_count() + gp.batch - 1) / gp.batch;
-    if (grid > gp.tiles) grid = gp.tiles;
-    if (grid > 1024) grid = 1024;
+    int64_t grid = gp.grid > 1024 ? 1024 : gp.grid;
     cudaMemcpy(host, trace_buf, sizeof(long long) * 8 * grid, cudaMemcpyDeviceToHost);
     double avg[8] = {0};
     for (int64_t c = 0; c < grid; ++c)
