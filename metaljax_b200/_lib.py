@@ -72,12 +72,20 @@ _SIGNATURES = {
                                       ctypes.c_void_p]),
     "qmm_pack_codes": (ctypes.c_int, [_T, _T, ctypes.c_int, ctypes.c_void_p]),
     "qmm_launch": (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.c_void_p]),
+    # include/qmm_decode.h
+    "qmm_decode_add_rmsnorm": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int64, ctypes.c_int64,
+                                                                     ctypes.c_float, ctypes.c_void_p]),
+    "qmm_decode_rope_kv": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int, ctypes.c_int,
+                                                                 ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
+                                                                 ctypes.c_float, ctypes.c_void_p]),
+    "qmm_decode_silu_mul": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                           ctypes.c_void_p]),
     "qmm_route": (ctypes.c_int, [ctypes.POINTER(Problem)]),
 }
 
 
 def exported_symbols() -> list[str]:
-    """Every entry point include/qmm.h declares (and this binding expects)."""
+    """Every entry point include/*.h declares (and this binding expects)."""
     return sorted(_SIGNATURES)
 
 

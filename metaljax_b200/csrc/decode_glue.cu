@@ -1,0 +1,211 @@
+// Element-wise glue of one decoder step around the fused quantized linears: residual add +
+// RMS normalisation, rotary embedding + key/value cache append, and the SwiGLU gate. The
+// reference reaches these through its generic op handlers (src/metaljax/ops/elementwise.py,
+// src/metaljax/ops/reduce.py); here each is one memory-bound kernel so that a decode step is
+// a short chain of launches between the weight streams. bf16 in and out, float32 arithmetic.
+//
+// Every kernel is launched with programmatic stream serialization, lets its successor start at
+// once (`griddepcontrol.launch_dependents`), and touches memory only after
+// `griddepcontrol.wait`, so the decode kernel that follows can request its weights while the
+// glue kernel is still running.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "qmm_internal.h"
+
+namespace qmm {
+namespace {
+
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(u[i] << 16);
+    f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint32_t u[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    u[i] = *reinterpret_cast<const uint32_t*>(&p);
+  }
+  return make_uint4(u[0], u[1], u[2], u[3]);
+}
+
+// h = x (+ residual); residual_out = h (optional); y = h * rsqrt(mean(h^2) + eps) * weight.
+// One CTA per row; dim is a multiple of 8.
+constexpr int kNormThreads = 256;
+__global__ void __launch_bounds__(kNormThreads)
+add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* residual_in,
+                   const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* residual_out, int64_t dim, float eps) {   // residual_out may be residual_in
+  pdl_enter();
+  extern __shared__ uint4 row_cache[];               // the row as bf16, dim / 8 pieces
+  __shared__ float partial[kNormThreads / 32];
+  const int64_t row = blockIdx.x;
+  const int pieces = static_cast<int>(dim / 8);
+  float ss = 0.0f;
+  for (int p = threadIdx.x; p < pieces; p += kNormThreads) {
+    uint4 v = *reinterpret_cast<const uint4*>(x + row * dim + p * 8);
+    float f[8];
+    unpack8(v, f);
+    if (residual_in) {
+      float r[8];
+      unpack8(*reinterpret_cast<const uint4*>(residual_in + row * dim + p * 8), r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += r[i];
+      v = pack8(f);
+      unpack8(v, f);                                  // the sum as it is stored: bf16
+    }
+    if (residual_out) *reinterpret_cast<uint4*>(residual_out + row * dim + p * 8) = v;
+    row_cache[p] = v;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kNormThreads / 32; ++i) total += partial[i];
+  const float inv = rsqrtf(total / static_cast<float>(dim) + eps);
+  for (int p = threadIdx.x; p < pieces; p += kNormThreads) {
+    float f[8], w[8];
+    unpack8(row_cache[p], f);
+    unpack8(*reinterpret_cast<const uint4*>(weight + p * 8), w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * inv * w[i];
+    *reinterpret_cast<uint4*>(y + row * dim + p * 8) = pack8(f);
+  }
+}
+
+// qkv[b] = [q heads | k heads | v heads], each head_dim wide. Rotates q and k (rotate-half
+// pairing: element i with i + head_dim/2, angle pos * theta^(-2i/head_dim)), writes q to
+// q_out[b, head, :] and k, v to the caches [b, kv_head, pos, :].
+__global__ void rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                               __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                               int heads, int kv_heads, int head_dim, int64_t ctx, int64_t pos, float theta) {
+  pdl_enter();
+  const int b = blockIdx.y;
+  const int half = head_dim / 2;
+  const int total_heads = heads + 2 * kv_heads;
+  const int64_t row = static_cast<int64_t>(b) * total_heads * head_dim;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total_heads * half; i += gridDim.x * blockDim.x) {
+    const int head = i / half, j = i % half;
+    const float lo = __bfloat162float(qkv[row + head * head_dim + j]);
+    const float hi = __bfloat162float(qkv[row + head * head_dim + j + half]);
+    if (head < heads + kv_heads) {
+      float s, c;
+      const float freq = __powf(theta, -2.0f * static_cast<float>(j) / static_cast<float>(head_dim));
+      sincosf(static_cast<float>(pos) * freq, &s, &c);
+      const float rlo = lo * c - hi * s, rhi = hi * c + lo * s;
+      if (head < heads) {
+        __nv_bfloat16* dst = q_out + (static_cast<int64_t>(b) * heads + head) * head_dim;
+        dst[j] = __float2bfloat16_rn(rlo);
+        dst[j + half] = __float2bfloat16_rn(rhi);
+      } else {
+        __nv_bfloat16* dst = k_cache + ((static_cast<int64_t>(b) * kv_heads + (head - heads)) * ctx + pos) * head_dim;
+        dst[j] = __float2bfloat16_rn(rlo);
+        dst[j + half] = __float2bfloat16_rn(rhi);
+      }
+    } else {
+      __nv_bfloat16* dst = v_cache + ((static_cast<int64_t>(b) * kv_heads + (head - heads - kv_heads)) * ctx + pos) * head_dim;
+      dst[j] = __float2bfloat16_rn(lo);
+      dst[j + half] = __float2bfloat16_rn(hi);
+    }
+  }
+}
+
+// gate_up[r] = [gate | up], each `ffn` wide: out[r, i] = silu(gate[i]) * up[i].
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                int64_t rows, int64_t ffn) {
+  pdl_enter();
+  const int64_t pieces = ffn / 8;
+  const int64_t total = rows * pieces;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / pieces, p = i % pieces;
+    float g[8], u[8];
+    unpack8(*reinterpret_cast<const uint4*>(gate_up + r * 2 * ffn + p * 8), g);
+    unpack8(*reinterpret_cast<const uint4*>(gate_up + r * 2 * ffn + ffn + p * 8), u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.0f + __expf(-g[k])) * u[k];
+    *reinterpret_cast<uint4*>(out + r * ffn + p * 8) = pack8(g);
+  }
+}
+
+template <typename... Args>
+int launch_pdl(const char* what, void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+               Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
+  if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
+  count_launch();
+  return check_launch(what);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace qmm
+
+using namespace qmm;
+
+extern "C" int qmm_decode_add_rmsnorm(const void* x, const void* residual_in, const void* weight, void* y,
+                                      void* residual_out, int64_t rows, int64_t dim, float eps, void* stream) {
+  if (!x || !weight || !y) return fail(QMM_ERR_NULL, "add_rmsnorm: x, weight and y are required");
+  if (rows < 0 || dim <= 0 || dim % 8 || dim > 24576) return fail(QMM_ERR_SHAPE, "add_rmsnorm: dim must be a multiple of 8, at most 24576");
+  if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || !aligned16(residual_in) || !aligned16(residual_out))
+    return fail(QMM_ERR_LAYOUT, "add_rmsnorm: pointers must be 16-byte aligned");
+  if (rows == 0) return QMM_OK;
+  return launch_pdl("add_rmsnorm_kernel", add_rmsnorm_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads),
+                    static_cast<size_t>(dim) * 2, static_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual_in),
+                    static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(y),
+                    static_cast<__nv_bfloat16*>(residual_out), dim, eps);
+}
+
+extern "C" int qmm_decode_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_cache, int64_t batch,
+                                  int heads, int kv_heads, int head_dim, int64_t ctx, int64_t pos, float theta,
+                                  void* stream) {
+  if (!qkv || !q_out || !k_cache || !v_cache) return fail(QMM_ERR_NULL, "rope_kv: null pointer");
+  if (batch < 0 || batch > 65535 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || head_dim % 2 || pos < 0 || pos >= ctx)
+    return fail(QMM_ERR_SHAPE, "rope_kv: bad shape or position");
+  if (batch == 0) return QMM_OK;
+  const int work = (heads + 2 * kv_heads) * (head_dim / 2);
+  return launch_pdl("rope_kv_kernel", rope_kv_kernel, dim3(static_cast<unsigned>((work + 255) / 256), static_cast<unsigned>(batch)),
+                    dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(qkv),
+                    static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+                    static_cast<__nv_bfloat16*>(v_cache), heads, kv_heads, head_dim, ctx, pos, theta);
+}
+
+extern "C" int qmm_decode_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t ffn, void* stream) {
+  if (!gate_up || !out) return fail(QMM_ERR_NULL, "silu_mul: null pointer");
+  if (rows < 0 || ffn <= 0 || ffn % 8) return fail(QMM_ERR_SHAPE, "silu_mul: ffn must be a multiple of 8");
+  if (!aligned16(gate_up) || !aligned16(out)) return fail(QMM_ERR_LAYOUT, "silu_mul: pointers must be 16-byte aligned");
+  if (rows == 0) return QMM_OK;
+  const int64_t total = rows * (ffn / 8);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return launch_pdl("silu_mul_kernel", silu_mul_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(gate_up),
+                    static_cast<__nv_bfloat16*>(out), rows, ffn);
+}

@@ -14,9 +14,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _declared():
-    text = open(os.path.join(ROOT, "include", "qmm.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(qmm_[a-z_0-9]+)\s*\(", text)))
+    names = set()
+    for header in ("qmm.h", "qmm_decode.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(qmm_[a-z_0-9]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_and_library_agree():
