@@ -46,6 +46,16 @@ WORKLOADS = {
 DEFAULT = "prefill_int4_g64_m2048_14336x4096"
 DECODE = "decode_int4_g64_m1_4096x4096"
 L2_BYTES = 126 * 1024 * 1024
+# Whole decode steps of a Llama-3-8B-shaped model (32 layers, d 4096, 32/8 heads, ffn 14336,
+# vocabulary 128256, int4 group-64 linears, bf16 KV cache of 2048 positions): name -> batch.
+# The weights are sharded on N over the ranks, so these scale strongly.
+DECODE_STEPS = {"decode_llama3_8b_b1": 1, "decode_llama3_8b_b16": 16, "decode_llama3_8b_b64": 64}
+# DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures
+# summarized under profiles/ (qmm_gemm_tc_int4_g64_m2048.md, qmm_gemv_int4_g64_m1_4096x4096.md).
+MEASURED_TRAFFIC = {
+    "prefill_int4_g64_m2048_14336x4096": 56048384 + 27941888,    # read + write; part of y is still in L2
+    "decode_int4_g64_m1_4096x4096": 9480000,                      # every weight byte read once
+}
 
 
 def peaks():
@@ -207,6 +217,18 @@ def run_reference(args, rank):
     if rank != 0:
         return
     name = args.workload
+    if name in DECODE_STEPS:
+        vals = [decode_step_cpu(DECODE_STEPS[name]) for _ in range(args.warmup + args.steps)][args.warmup:]
+        value = statistics.mean(v["value"] for v in vals)
+        cb = dict(vals[-1], value=value)
+        print(json.dumps({
+            "impl": "reference", "metric": "decode_tok_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": DECODE_STEPS[name] / value * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": name, "batch": DECODE_STEPS[name]}, "cpu_baseline": cb,
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}), flush=True)
+        return
     m, k, n, gs, bits, mode = WORKLOADS[name]
     flops, weight_bytes, _ = work_of(name)
     res = None
@@ -302,13 +324,107 @@ def measure(name, args, torch, qmm, _lib, dist, device):
     return res
 
 
+def decode_step_bytes(batch, world):
+    """Algorithmic HBM bytes one rank touches per decode step: its shard of the packed weights
+    and tables, and its heads' KV cache of `batch` sequences."""
+    from metaljax_b200 import llama
+    sh = llama.LLAMA3_8B
+    kv = 2 * sh.layers * batch * sh.kv_heads * sh.ctx * sh.head_dim * 2
+    return sh.weight_bytes() / world, kv / world
+
+
+def measure_decode_step(batch, steps, warmup, torch, dist, device):
+    """One Llama-3-8B-shaped decode step per timed step, replayed from a CUDA graph: device
+    time (tokens resident) and end to end (token ids from pinned host memory, next ids back)."""
+    from metaljax_b200 import _lib, llama
+    n0 = _lib.launch_count()
+    step = llama.DecodeStep(llama.LLAMA3_8B, batch, device, seed=7)
+    n1 = _lib.launch_count()
+    step.capture(warmup=max(warmup, 3))
+    per_step = (_lib.launch_count() - n1) // (max(warmup, 3) + 1)
+    del n0
+    ms = time_device(lambda i: step.replay(), steps, 3, torch, dist)
+    host_in = torch.zeros((batch,), dtype=torch.int64).pin_memory()
+    host_out = torch.zeros((batch,), dtype=torch.int64).pin_memory()
+
+    def e2e_step(i):
+        host_in.fill_(i % 1000)
+        step.tokens.copy_(host_in, non_blocking=True)
+        step.replay()
+        host_out.copy_(step.next_tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    esteps = max(3, min(steps, 20))
+    ems = time_device(e2e_step, esteps, 3, torch, dist)
+    res = {"ms_per_step": ms / steps, "e2e_ms_per_step": ems / esteps, "launches_per_step": per_step,
+           "h2d": batch * 8, "d2h": batch * 8, "steps": steps}
+    del step
+    torch.cuda.empty_cache()
+    return res
+
+
+def decode_step_cpu(batch):
+    """The CPU port on one decoder layer's linears at `batch` rows, extrapolated to the whole
+    step by parameter count (the other 31 layers and the lm_head repeat the same loop)."""
+    from oracle import clib
+    import ml_dtypes
+    from metaljax_b200 import llama
+    sh = llama.LLAMA3_8B
+    clib.use_all_cores()
+    rng = np.random.default_rng(0)
+    shapes = [((sh.heads + 2 * sh.kv_heads) * sh.head_dim, sh.d_model), (sh.d_model, sh.heads * sh.head_dim),
+              (2 * sh.ffn, sh.d_model), (sh.d_model, sh.ffn)]
+    sec, params = 0.0, 0
+    for n, k in shapes:
+        w = rng.integers(0, 1 << 32, size=(n, k // 8), dtype=np.uint64).astype(np.uint32)
+        s = rng.uniform(0.002, 0.02, size=(n, k // 64)).astype(ml_dtypes.bfloat16)
+        b = (-8.0 * s.astype(np.float32)).astype(ml_dtypes.bfloat16)
+        x = rng.standard_normal((batch, k)).astype(np.float32).astype(ml_dtypes.bfloat16)
+        clib.qmm(x[:1], w, s, b, 1, k, n, 64, 4, "affine")
+        t0 = time.perf_counter()
+        clib.qmm(x, w, s, b, batch, k, n, 64, 4, "affine")
+        sec += time.perf_counter() - t0
+        params += n * k
+    step_sec = sec * sh.linear_params() / params
+    return {"value": batch / step_sec, "unit": "tok/s", "cores": clib.num_threads(), "kind": "port",
+            "sample": f"the 4 fused linears of one of {sh.layers} layers at {batch} rows "
+                      f"({sec:.2f} s), extrapolated to the step by parameter count; attention and glue not counted"}
+
+
+def decode_step_line(name, args, torch, dist, device, world, pk, clk_fn=None):
+    batch = DECODE_STEPS[name]
+    res = measure_decode_step(batch, args.steps, args.warmup, torch, dist, device)
+    t = torch.tensor([res["ms_per_step"], res["e2e_ms_per_step"]], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step, e2e_ms = float(t[0]), float(t[1])
+    wb, kvb = decode_step_bytes(batch, world)
+    achieved = (wb + kvb) / (res["ms_per_step"] * 1e-3) / 1e9
+    return {
+        "metric": "decode_tok_s", "value": batch / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
+        "steps": res["steps"], "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": name, "batch": batch, "layers": 32, "d_model": 4096, "ffn": 14336, "vocab": 128256,
+                   "context": 2048, "group_size": 64, "bits": 4,
+                   "l2": f"one step streams {wb / 2**20:.0f} MiB of weights per GPU (> L2)",
+                   "parallelism": f"tp{world}: every weight sharded on its output rows, all-gather after each linear",
+                   "timed": "cuda graph replay of the whole step"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                     "bytes": "this rank's packed weights + tables and its KV cache, read once per step"},
+        "e2e": {"value": batch / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": res["h2d"],
+                "d2h_bytes_per_step": res["d2h"], "ms_per_step": e2e_ms},
+        "gpu_launches": int(res["launches_per_step"] * res["steps"]),
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS) + sorted(DECODE_STEPS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-also", action="store_true", help="skip the decode side measurement")
     args = ap.parse_args()
@@ -334,8 +450,21 @@ def main():
         dist = dist_mod
 
     name = args.workload
-    m, k, n, gs, bits, mode = WORKLOADS[name]
     pk = peaks()
+    if name in DECODE_STEPS:
+        with ClockSampler(local) as clocks:
+            line = decode_step_line(name, args, torch, dist, device, world, pk)
+        line["clocks"] = clocks.summary()
+        _lib.poll_status()
+        if rank == 0 and not args.no_cpu:
+            line["cpu_baseline"] = decode_step_cpu(DECODE_STEPS[name])
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+    m, k, n, gs, bits, mode = WORKLOADS[name]
     with ClockSampler(local) as clocks:
         res = measure(name, args, torch, qmm, _lib, dist, device)
     clk = clocks.summary()
@@ -353,7 +482,8 @@ def main():
         e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
         achieved = flops / (res["ms_per_step"] * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": unit,
-                "frac": achieved / pk["bf16_tflops"], "traffic": None, "peak_source": pk["source"],
+                "frac": achieved / pk["bf16_tflops"], "traffic": MEASURED_TRAFFIC.get(name),
+                "peak_source": pk["source"],
                 "frac_of_nominal_2250": achieved / 2250.0}
     else:
         unit = "GB/s"
@@ -362,8 +492,8 @@ def main():
         best = min(res["ms_per_step"], res.get("graph_ms_per_step", 1e9))
         achieved = total_bytes / (best * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": unit,
-                "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                "frac_of_nominal_8000": achieved / 8000.0,
+                "frac": achieved / pk["hbm_gbs"], "traffic": MEASURED_TRAFFIC.get(name),
+                "peak_source": pk["source"], "frac_of_nominal_8000": achieved / 8000.0,
                 "timed": "cuda graph replay" if best != res["ms_per_step"] else "stream launches"}
 
     line = {
@@ -394,8 +524,16 @@ def main():
             "route": qmm.route(1, 4096, 4096),
             "roofline": {"bound": "hbm", "achieved": tb / (best * 1e-3) / 1e9, "peak": pk["hbm_gbs"],
                          "unit": "GB/s", "frac": tb / (best * 1e-3) / 1e9 / pk["hbm_gbs"],
-                         "traffic": None, "peak_source": pk["source"]},
+                         "traffic": MEASURED_TRAFFIC.get(DECODE), "peak_source": pk["source"]},
         }]
+
+    if not args.no_also and name == DEFAULT:
+        # the decode-step tokens/s at this N (weights sharded on N: strong scaling), all ranks
+        for side_name in ("decode_llama3_8b_b1", "decode_llama3_8b_b16"):
+            side_line = decode_step_line(side_name, args, torch, dist, device, world, pk)
+            line.setdefault("also", []).append(
+                {key: side_line[key] for key in ("metric", "value", "unit", "n_gpus", "ms_per_step", "scaling",
+                                                 "config", "roofline", "e2e", "gpu_launches")})
 
     if rank == 0 and not args.no_cpu and world >= 1:
         cb = cpu_baseline(name)

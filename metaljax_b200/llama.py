@@ -266,8 +266,9 @@ class DecodeStep:
         """Full `[batch, vocab]` logits of the last step (float32), gathered over ranks."""
         if self.world == 1:
             return self.logits_l[:, : self.v_l].float()
-        sizes = [None] * self.world
-        dist.all_gather_object(sizes, self.v_l, group=self.group)
+        v_per = -(-(-(-self.shape.vocab // self.world)) // 16) * 16            # as in __init__
+        sizes = [max(0, min(self.shape.vocab, (r + 1) * v_per) - min(self.shape.vocab, r * v_per))
+                 for r in range(self.world)]
         widest = max(sizes)
         padded = torch.zeros((self.batch, widest), device=self.device, dtype=torch.float32)
         padded[:, : self.v_l] = self.logits_l[:, : self.v_l].float()

@@ -1,9 +1,11 @@
-"""The two multi-GPU shardings on real GPUs (NCCL, one process per GPU): a column-parallel
-decode product with its all-gather, and the expert-parallel mixture-of-experts block with its
-token all-to-all, each against the oracle. Skipped when fewer than two GPUs are visible."""
+"""The multi-GPU shardings on real GPUs (NCCL, one process per GPU): a column-parallel decode
+product with its all-gather and the expert-parallel mixture-of-experts block with its token
+all-to-all, each against the oracle, and the N-sharded Llama-shaped decode step against its
+float reference. Skipped when fewer than two GPUs are visible."""
 
 import os
 import socket
+import time
 
 import numpy as np
 import pytest
@@ -24,10 +26,14 @@ def _worker(rank, world, port, ret):
     from metaljax_b200 import _lib, parallel
     from oracle import qmm_oracle as O
 
+    import datetime
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    # a rank that fails leaves the others in a collective: a short timeout ends those with an error
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=90))
+    stage = "start"
     try:
         rng = np.random.default_rng(0)                   # identical draws on every rank
         # column-parallel linear at decode and prefill sizes
@@ -39,6 +45,7 @@ def _worker(rank, world, port, ret):
             y = lin(to_torch(x, dev))
             err = O.rel_err(to_numpy(y).astype(np.float32), O.qmm_exact(x, w, s, b, 64, 4))
             assert tuple(y.shape) == (m, n) and err <= 1e-2, (m, err)
+        stage = "column-parallel done"
         # expert-parallel MoE: every rank routes its own tokens
         e, kk, d, f, t = 4, 2, 128, 256, 40 + 8 * rank
         packs = [affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:],
@@ -57,10 +64,28 @@ def _worker(rank, world, port, ret):
         want = O.moe_combine_exact(down, wts)
         err = O.rel_err(to_numpy(y).astype(np.float32), want)
         assert err <= 2e-2, err                           # two bf16 hand-offs inside the block
+        stage = "expert-parallel done"
+        # the Llama-shaped decode step sharded over the ranks: same logits as the float reference
+        from metaljax_b200 import llama
+        shape = llama.Shape(layers=2, d_model=256, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1000, ctx=48)
+        for batch in (1, 5):
+            fw = llama.random_full_weights(shape, batch, dev, seed=3)         # identical on every rank
+            step = llama.DecodeStep(shape, batch, dev, full_weights=fw)
+            tokens = torch.arange(batch, device=dev) * 11 % shape.vocab
+            step.tokens.copy_(tokens)
+            nxt = step.step().clone()
+            got = step.logits()
+            want = llama.reference_logits(fw, shape, tokens, batch)
+            err = (got - want).abs().max().item() / want.abs().max().item()
+            assert err <= 3e-2, ("decode step", batch, err)
+            top2 = want.topk(2, dim=-1).values
+            clear = (top2[:, 0] - top2[:, 1]) > 2 * 3e-2 * want.abs().max()
+            assert torch.equal(nxt[clear], want.argmax(-1)[clear])
+            stage = f"decode step batch {batch} done"
         assert _lib.poll_status() == 0
         ret[rank] = "ok"
     except Exception as exc:                              # surfaced by the parent
-        ret[rank] = repr(exc)
+        ret[rank] = f"after '{stage}': {exc!r}"
     finally:
         dist.destroy_process_group()
 
@@ -76,7 +101,11 @@ def test_two_gpu_ranks():
     procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
     for p in procs:
         p.start()
+    deadline = time.time() + 300
     for p in procs:
-        p.join(600)
-        assert not p.is_alive(), "rank did not finish"
+        p.join(max(1.0, deadline - time.time()))
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:                                       # exactly the processes started above
+        p.terminate()
+    assert not stuck, f"ranks did not finish: {dict(ret)}"
     assert dict(ret) == {0: "ok", 1: "ok"}, dict(ret)
