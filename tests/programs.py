@@ -1,0 +1,135 @@
+"""StableHLO programs in jax's print syntax for the recognizer tests, with matching inputs.
+They restate, op for op, the chains of the reference's own tests: keras' sub-channel and
+per-channel int4 Dense (tests/test_qmm.py:179-205) and the MXFP4 weight built from a table
+gather and a per-32 scale (tests/test_qmm_mxfp4.py:282-299)."""
+
+import numpy as np
+import torch
+
+_SUB = """
+module @jit_dense_sub {{
+  func.func public @main(%arg0: tensor<5x256xbf16>, %arg1: tensor<16x256xi8>{donor}, %arg2: tensor<16x4xbf16>, %arg3: tensor<16x4xbf16>) -> ({results}) {{
+    %0 = stablehlo.convert %arg1 : (tensor<16x256xi8>) -> tensor<16x256xbf16>
+    %1 = stablehlo.broadcast_in_dim %arg3, dims = [0, 1] : (tensor<16x4xbf16>) -> tensor<16x4x64xbf16>
+    %2 = stablehlo.reshape %1 : (tensor<16x4x64xbf16>) -> tensor<16x256xbf16>
+    %3 = stablehlo.subtract %0, %2 : tensor<16x256xbf16>
+    %4 = stablehlo.broadcast_in_dim %arg2, dims = [0, 1] : (tensor<16x4xbf16>) -> tensor<16x4x64xbf16>
+    %5 = stablehlo.reshape %4 : (tensor<16x4x64xbf16>) -> tensor<16x256xbf16>
+    %6 = stablehlo.multiply %3, %5 : tensor<16x256xbf16>
+    {dot}
+    return {ret} : {results}
+  }}
+}}
+"""
+_DOT_RHS = "%7 = stablehlo.dot_general %arg0, %6, contracting_dims = [1] x [1] : (tensor<5x256xbf16>, tensor<16x256xbf16>) -> tensor<5x16xbf16>"
+_DOT_LHS = "%7 = stablehlo.dot_general %6, %arg0, contracting_dims = [1] x [1] : (tensor<16x256xbf16>, tensor<5x256xbf16>) -> tensor<16x5xbf16>"
+
+SUB_CHANNEL = _SUB.format(donor="", dot=_DOT_RHS, ret="%7", results="tensor<5x16xbf16>")
+DONATED = _SUB.format(donor=" {jax.buffer_donor = true}", dot=_DOT_RHS, ret="%7", results="tensor<5x16xbf16>")
+LHS_QUANT = _SUB.format(donor="", dot=_DOT_LHS, ret="%7", results="tensor<16x5xbf16>")
+SHARED_WEIGHT = _SUB.format(donor="", dot=_DOT_RHS, ret="%7, %6", results="tensor<5x16xbf16>, tensor<16x256xbf16>")
+
+PER_CHANNEL = """
+module @jit_dense_perchannel {
+  func.func public @main(%arg0: tensor<5x128xbf16>, %arg1: tensor<128x16xi8>, %arg2: tensor<16xbf16>) -> (tensor<5x16xbf16>) {
+    %0 = stablehlo.convert %arg1 : (tensor<128x16xi8>) -> tensor<128x16xbf16>
+    %1 = stablehlo.dot_general %arg0, %0, contracting_dims = [1] x [0] : (tensor<5x128xbf16>, tensor<128x16xbf16>) -> tensor<5x16xbf16>
+    %2 = stablehlo.broadcast_in_dim %arg2, dims = [1] : (tensor<16xbf16>) -> tensor<5x16xbf16>
+    %3 = stablehlo.divide %1, %2 : tensor<5x16xbf16>
+    return %3 : tensor<5x16xbf16>
+  }
+}
+"""
+
+_E2M1 = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+_VTABLE = ", ".join(f"{v:.6e}" for v in _E2M1 + [-v for v in _E2M1])
+_STABLE = ", ".join(f"{2.0 ** (b - 127):.9e}" if 0 < b < 255 else "0.000000e+00" for b in range(256))
+
+MXFP4 = f"""
+module @jit_dense_mxfp4 {{
+  func.func public @main(%arg0: tensor<3x64xbf16>, %arg1: tensor<8x64xui8>, %arg2: tensor<8x2xui8>) -> (tensor<3x8xbf16>) {{
+    %cst = stablehlo.constant dense<[{_VTABLE}]> : tensor<16xbf16>
+    %cst_0 = stablehlo.constant dense<[{_STABLE}]> : tensor<256xf32>
+    %0 = stablehlo.convert %arg1 : (tensor<8x64xui8>) -> tensor<8x64xi32>
+    %1 = stablehlo.reshape %0 : (tensor<8x64xi32>) -> tensor<8x64x1xi32>
+    %2 = "stablehlo.gather"(%cst, %1) <{{dimension_numbers = #stablehlo.gather<collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 2>, indices_are_sorted = false, slice_sizes = array<i64: 1>}}> : (tensor<16xbf16>, tensor<8x64x1xi32>) -> tensor<8x64xbf16>
+    %3 = stablehlo.convert %arg2 : (tensor<8x2xui8>) -> tensor<8x2xi32>
+    %4 = stablehlo.reshape %3 : (tensor<8x2xi32>) -> tensor<8x2x1xi32>
+    %5 = "stablehlo.gather"(%cst_0, %4) <{{dimension_numbers = #stablehlo.gather<collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 2>, indices_are_sorted = false, slice_sizes = array<i64: 1>}}> : (tensor<256xf32>, tensor<8x2x1xi32>) -> tensor<8x2xf32>
+    %6 = stablehlo.convert %5 : (tensor<8x2xf32>) -> tensor<8x2xbf16>
+    %7 = stablehlo.reshape %2 : (tensor<8x64xbf16>) -> tensor<8x2x32xbf16>
+    %8 = stablehlo.broadcast_in_dim %6, dims = [0, 1] : (tensor<8x2xbf16>) -> tensor<8x2x32xbf16>
+    %9 = stablehlo.multiply %7, %8 : tensor<8x2x32xbf16>
+    %10 = stablehlo.reshape %9 : (tensor<8x2x32xbf16>) -> tensor<8x64xbf16>
+    %11 = stablehlo.dot_general %arg0, %10, contracting_dims = [1] x [1] : (tensor<3x64xbf16>, tensor<8x64xbf16>) -> tensor<3x8xbf16>
+    return %11 : tensor<3x8xbf16>
+  }}
+}}
+"""
+
+RMS_NORM = """
+module @jit_embed_norm_dot {
+  func.func public @main(%arg0: tensor<3x64xf32>, %arg1: tensor<4x1xi32>, %arg2: tensor<100x64xf32>, %arg3: tensor<4xf32>) -> (tensor<3x4xf32>) {
+    %0 = "stablehlo.gather"(%arg2, %arg1) <{dimension_numbers = #stablehlo.gather<offset_dims = [1], collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 1>, indices_are_sorted = false, slice_sizes = array<i64: 1, 64>}> : (tensor<100x64xf32>, tensor<4x1xi32>) -> tensor<4x64xf32>
+    %1 = stablehlo.rsqrt %arg3 : tensor<4xf32>
+    %2 = stablehlo.broadcast_in_dim %1, dims = [0] : (tensor<4xf32>) -> tensor<4x64xf32>
+    %3 = stablehlo.multiply %0, %2 : tensor<4x64xf32>
+    %4 = stablehlo.dot_general %arg0, %3, contracting_dims = [1] x [1] : (tensor<3x64xf32>, tensor<4x64xf32>) -> tensor<3x4xf32>
+    return %4 : tensor<3x4xf32>
+  }
+}
+"""
+
+
+def sub_channel_inputs(seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((5, 256), generator=g).to(torch.bfloat16)
+    codes = torch.randint(-8, 8, (16, 256), generator=g, dtype=torch.int8)
+    scales = (torch.rand((16, 4), generator=g) * 0.02 + 0.002).to(torch.bfloat16)
+    zeros = torch.randint(-3, 4, (16, 4), generator=g).to(torch.bfloat16)
+    return [t.to(device) for t in (x, codes, scales, zeros)]
+
+
+def per_channel_inputs(seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((5, 128), generator=g).to(torch.bfloat16)
+    codes = torch.randint(-8, 8, (128, 16), generator=g, dtype=torch.int8)
+    scale = (torch.rand((16,), generator=g) * 40 + 10).to(torch.bfloat16)
+    return [t.to(device) for t in (x, codes, scale)]
+
+
+def mxfp4_inputs(seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((3, 64), generator=g).to(torch.bfloat16)
+    nib = torch.randint(0, 16, (8, 64), generator=g, dtype=torch.uint8)
+    sbytes = torch.randint(119, 128, (8, 2), generator=g, dtype=torch.uint8)
+    return [t.to(device) for t in (x, nib, sbytes)]
+
+
+def sub_channel_program(m, k, n, gs=64, el="bf16"):
+    """The sub-channel chain at any size (quantized operand on the right)."""
+    g = k // gs
+    return f"""
+module @jit_dense_sub {{
+  func.func public @main(%arg0: tensor<{m}x{k}x{el}>, %arg1: tensor<{n}x{k}xi8>, %arg2: tensor<{n}x{g}x{el}>, %arg3: tensor<{n}x{g}x{el}>) -> (tensor<{m}x{n}x{el}>) {{
+    %0 = stablehlo.convert %arg1 : (tensor<{n}x{k}xi8>) -> tensor<{n}x{k}x{el}>
+    %1 = stablehlo.broadcast_in_dim %arg3, dims = [0, 1] : (tensor<{n}x{g}x{el}>) -> tensor<{n}x{g}x{gs}x{el}>
+    %2 = stablehlo.reshape %1 : (tensor<{n}x{g}x{gs}x{el}>) -> tensor<{n}x{k}x{el}>
+    %3 = stablehlo.subtract %0, %2 : tensor<{n}x{k}x{el}>
+    %4 = stablehlo.broadcast_in_dim %arg2, dims = [0, 1] : (tensor<{n}x{g}x{el}>) -> tensor<{n}x{g}x{gs}x{el}>
+    %5 = stablehlo.reshape %4 : (tensor<{n}x{g}x{gs}x{el}>) -> tensor<{n}x{k}x{el}>
+    %6 = stablehlo.multiply %3, %5 : tensor<{n}x{k}x{el}>
+    %7 = stablehlo.dot_general %arg0, %6, contracting_dims = [1] x [1] : (tensor<{m}x{k}x{el}>, tensor<{n}x{k}x{el}>) -> tensor<{m}x{n}x{el}>
+    return %7 : tensor<{m}x{n}x{el}>
+  }}
+}}
+"""
+
+
+def sub_channel_inputs_at(m, k, n, gs=64, seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((m, k), generator=g).to(torch.bfloat16)
+    codes = torch.randint(-8, 8, (n, k), generator=g, dtype=torch.int8)
+    scales = (torch.rand((n, k // gs), generator=g) * 0.02 + 0.002).to(torch.bfloat16)
+    zeros = torch.randint(-3, 4, (n, k // gs), generator=g).to(torch.bfloat16)
+    return [t.to(device) for t in (x, codes, scales, zeros)]

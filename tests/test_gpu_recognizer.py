@@ -1,0 +1,69 @@
+"""The recognizer end to end on the GPU: a program executed with its dequantize-and-dot chain
+fused into one quantized matmul against the same program executed literally and against the
+exact float32 answer, with the reference's gate (tests/test_qmm.py:261-282): the fused result
+must be within 1e-2 of the exact answer's largest magnitude and no worse than 1.5x the literal
+chain's own error."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _exact(fn, args):
+    """The program in float64 on the host: every float tensor widened, integer ones as they are."""
+    from metaljax_b200 import hlo
+    wide = [a.double().cpu() if a.dtype.is_floating_point else a.cpu() for a in args]
+    f = hlo.parse(fn) if isinstance(fn, str) else fn
+    for v in list(f.args) + [r for o in f.ops for r in o.results]:
+        if v.type.el in hlo.FLOAT_ELS:
+            v.type = hlo.TensorType(v.type.shape, "f64")
+    return hlo.evaluate(f, wide)[0]
+
+
+def _gate(text, args, expect_fused=1):
+    from metaljax_b200 import _lib, recognizer
+    it = recognizer.Interpreter(text)
+    fused = it.execute(args)[0]
+    literal = it.execute(args, fused=False)[0]
+    assert it.fused_calls == expect_fused, it.rejections
+    exact = _exact(text, args)
+    scale = exact.abs().max().item()
+    err_f = (fused.double().cpu() - exact).abs().max().item() / scale
+    err_l = (literal.double().cpu() - exact).abs().max().item() / scale
+    assert fused.shape == literal.shape and fused.dtype == literal.dtype
+    assert err_f <= 1e-2, err_f
+    assert err_f <= 1.5 * err_l + 1e-6, (err_f, err_l)
+    assert _lib.poll_status() == 0
+    return it
+
+
+def test_sub_channel_rhs_and_lhs():
+    from programs import LHS_QUANT, SUB_CHANNEL, sub_channel_inputs
+    args = sub_channel_inputs(seed=5, device=DEV)
+    _gate(SUB_CHANNEL, args)
+    _gate(LHS_QUANT, args)
+
+
+def test_per_channel_and_mxfp4():
+    from programs import MXFP4, PER_CHANNEL, mxfp4_inputs, per_channel_inputs
+    _gate(PER_CHANNEL, per_channel_inputs(seed=6, device=DEV))
+    it = _gate(MXFP4, mxfp4_inputs(seed=7, device=DEV))
+    assert it._qmm.matches[0].mode == "mxfp4"
+
+
+@pytest.mark.parametrize("m,k,n,gs", [(1, 512, 256, 64), (64, 512, 384, 128), (300, 1024, 256, 32)])
+def test_sub_channel_sizes(m, k, n, gs):
+    from programs import sub_channel_inputs_at, sub_channel_program
+    it = _gate(sub_channel_program(m, k, n, gs), sub_channel_inputs_at(m, k, n, gs, seed=m, device=DEV))
+    assert it._qmm.matches[0].gs >= gs
+
+
+def test_rejected_program_runs_literally():
+    from metaljax_b200 import recognizer
+    from programs import SHARED_WEIGHT, sub_channel_inputs
+    it = recognizer.Interpreter(SHARED_WEIGHT)
+    out = it.execute(sub_channel_inputs(seed=8, device=DEV))
+    assert it.fused_calls == 0 and len(out) == 2
