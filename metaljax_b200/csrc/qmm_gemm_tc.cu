@@ -248,6 +248,34 @@ __device__ __forceinline__ void dequant_aff4(const uint32_t (&w)[NW], float s, f
 
 // 8-bit affine, NW packed words -> NW*2 pairs: float32 FMA per element, rounded to the
 // 16-bit type in pairs.
+// The same for float32 tables (what the packer emits when a bias is not exactly
+// representable in the narrow type): the magic pair is widened to float32, one float32 FMA
+// per element with (s, b - C s), one rounding to the pair type.
+template <typename XT, int NW>
+__device__ __forceinline__ void dequant_aff4_wide(const uint32_t (&w)[NW], float s, float b, uint32_t* out) {
+  using H = Half2Ops<XT>;
+  const float c = std::is_same<XT, __nv_bfloat16>::value ? 128.0f : 1024.0f;
+  const float bc = fmaf(-c, s, b);
+#pragma unroll
+  for (int j = 0; j < NW; ++j) {
+    const uint32_t hi = w[j] >> 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t t = __byte_perm(w[j], hi, i | ((4 + i) << 8));
+      const uint32_t v = (t & 0x000F000Fu) | H::kMagic;
+      float lo, up;
+      if constexpr (std::is_same<XT, __nv_bfloat16>::value) {
+        lo = __uint_as_float(v << 16);
+        up = __uint_as_float(v & 0xffff0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+        lo = f.x; up = f.y;
+      }
+      out[j * 4 + i] = H::pack(fmaf(s, lo, bc), fmaf(s, up, bc));
+    }
+  }
+}
+
 template <typename XT, int NW>
 __device__ __forceinline__ void dequant_aff8(const uint32_t (&w)[NW], float s, float b, uint32_t* out) {
   using H = Half2Ops<XT>;
@@ -565,8 +593,11 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if constexpr (QK == kAff4) {
-            dequant_aff4<XT, kHalfWords>(packed[h], table_value(__float_as_uint(sc[h]), p.table_dtype),
-                                         table_value(__float_as_uint(bi[h]), p.table_dtype), &out[h * 16]);
+            if (twide)
+              dequant_aff4_wide<XT, kHalfWords>(packed[h], sc[h], bi[h], &out[h * 16]);
+            else
+              dequant_aff4<XT, kHalfWords>(packed[h], table_value(__float_as_uint(sc[h]), p.table_dtype),
+                                           table_value(__float_as_uint(bi[h]), p.table_dtype), &out[h * 16]);
           } else if constexpr (QK == kAff8) {
             dequant_aff8<XT, kHalfWords>(packed[h], table_value(__float_as_uint(sc[h]), p.table_dtype),
                                          table_value(__float_as_uint(bi[h]), p.table_dtype), &out[h * 16]);
