@@ -50,6 +50,10 @@ L2_BYTES = 126 * 1024 * 1024
 # vocabulary 128256, int4 group-64 linears, bf16 KV cache of 2048 positions): name -> batch.
 # The weights are sharded on N over the ranks, so these scale strongly.
 DECODE_STEPS = {"decode_llama3_8b_b1": 1, "decode_llama3_8b_b16": 16, "decode_llama3_8b_b64": 64}
+# The expert block of a Mixtral-8x7B-shaped mixture-of-experts layer: 4096 tokens, top-2 of 8
+# experts, d 4096, ffn 14336, int4 group-64 expert weights; three grouped ragged products over
+# 8192 (token, expert) pairs plus the routed weighted sum.
+MOE_BLOCKS = {"moe_mixtral_t4096": (4096, 2, 8, 4096, 14336)}
 # DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures
 # summarized under profiles/ (qmm_gemm_tc_int4_g64_m2048.md, qmm_gemv_int4_g64_m1_4096x4096.md).
 MEASURED_TRAFFIC = {
@@ -418,13 +422,69 @@ def decode_step_line(name, args, torch, dist, device, world, pk, clk_fn=None):
     }
 
 
+def moe_line(name, args, torch, dist, device, world, pk):
+    """One step = the whole expert block (`moe.moe_experts`) on this rank's own tokens."""
+    from metaljax_b200 import _lib, moe
+    t, k, e, d, f = MOE_BLOCKS[name]
+    g = torch.Generator(device=device).manual_seed(11 + int(os.environ.get("RANK", "0")))
+
+    def pack(n, kk):
+        w = torch.randint(-(1 << 31), (1 << 31) - 1, (e, n, kk // 8), generator=g, device=device,
+                          dtype=torch.int64).to(torch.int32).view(torch.uint32)
+        s = (torch.rand((e, n, kk // 64), generator=g, device=device) * 0.018 + 0.002).to(torch.bfloat16)
+        return w, s, (-8.0 * s.float()).to(torch.bfloat16)
+
+    w1, w3, w2 = pack(f, d), pack(f, d), pack(d, f)
+    sets = 3
+    xs = [(torch.randn((t, d), generator=g, device=device) * 0.5).to(torch.bfloat16) for _ in range(sets)]
+    logits = torch.randn((t, e), generator=g, device=device)
+    wts, idx = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    wts = (wts / wts.sum(-1, keepdim=True)).float()
+    flops = 2.0 * t * k * (3 * d * f)
+    n0 = _lib.launch_count()
+    ms = time_device(lambda i: moe.moe_experts(xs[i % sets], idx, wts, w1, w3, w2), args.steps, max(args.warmup, 3),
+                     torch, dist)
+    launches = (_lib.launch_count() - n0) * args.steps // (args.steps + max(args.warmup, 3))
+    hx = torch.empty_like(xs[0], device="cpu").pin_memory().copy_(xs[0])
+    hy = torch.empty_like(xs[0], device="cpu").pin_memory()
+    dx = torch.empty_like(xs[0])
+
+    def e2e_step(i):
+        dx.copy_(hx, non_blocking=True)
+        y = moe.moe_experts(dx, idx, wts, w1, w3, w2)
+        hy.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    esteps = max(3, min(args.steps, 10))
+    ems = time_device(e2e_step, esteps, 3, torch, dist)
+    tt = torch.tensor([ms / args.steps, ems / esteps], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms_step, e2e_ms = float(tt[0]), float(tt[1])
+    achieved = flops / (ms / args.steps * 1e-3) / 1e12
+    return {
+        "metric": "moe_block_tflops", "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": name, "tokens": t, "top_k": k, "experts": e, "d_model": d, "ffn": f, "group_size": 64,
+                   "bits": 4, "l2": f"{3 * e * d * f // 2 >> 20} MiB of expert weights per step (> L2)",
+                   "parallelism": f"dp{world}: every rank routes its own tokens against replicated experts",
+                   "includes": "pair sort, 3 grouped ragged products, SwiGLU, routed weighted sum"},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": achieved / pk["bf16_tflops"], "traffic": None, "peak_source": pk["source"]},
+        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": t * d * 2, "d2h_bytes_per_step": t * d * 2, "ms_per_step": e2e_ms},
+        "gpu_launches": int(launches),
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS) + sorted(DECODE_STEPS))
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS) + sorted(DECODE_STEPS) + sorted(MOE_BLOCKS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-also", action="store_true", help="skip the decode side measurement")
     args = ap.parse_args()
@@ -451,12 +511,12 @@ def main():
 
     name = args.workload
     pk = peaks()
-    if name in DECODE_STEPS:
+    if name in DECODE_STEPS or name in MOE_BLOCKS:
         with ClockSampler(local) as clocks:
-            line = decode_step_line(name, args, torch, dist, device, world, pk)
+            line = (decode_step_line if name in DECODE_STEPS else moe_line)(name, args, torch, dist, device, world, pk)
         line["clocks"] = clocks.summary()
         _lib.poll_status()
-        if rank == 0 and not args.no_cpu:
+        if rank == 0 and not args.no_cpu and name in DECODE_STEPS:
             line["cpu_baseline"] = decode_step_cpu(DECODE_STEPS[name])
         if rank == 0:
             print(json.dumps(line), flush=True)

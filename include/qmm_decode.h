@@ -35,6 +35,23 @@ int qmm_decode_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_cach
 /* gate_up: [rows, 2*ffn] = gate, then up.  out[r, i] = silu(gate[r, i]) * up[r, i]. */
 int qmm_decode_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t ffn, void* stream);
 
+/* One-shot all-gather over peer memory (one call per rank, each on its own GPU): this rank's
+ * slice `local` [rows, slice_bytes] is stored into every rank's gather buffer
+ * `peer_bufs[r] + slot*slot_bytes` at column offset rank*slice_bytes of rows world*slice_bytes
+ * apart; then a flag is raised on every rank and the kernel waits (bounded; a timeout is
+ * reported by qmm_poll_status) until every rank's flag for this call has been raised here, so
+ * the next kernel of the stream reads the complete [rows, world*slice_bytes] matrix.
+ *   peer_bufs[r], peer_flags[r]  rank r's gather buffer (3 slots of slot_bytes) and flag words
+ *                                (24 uint32, zero-initialised once), mapped into this process
+ *                                (CUDA IPC / symmetric memory); world entries each
+ *   state                        16 uint32 of this rank's own device memory, zeroed once
+ *   slot                         0..2; consecutive calls must use different slots, and every
+ *                                rank must make the same sequence of calls.
+ * slice_bytes is a multiple of 16. */
+int qmm_decode_allgather(const void* local, void* const* peer_bufs, void* const* peer_flags, void* state,
+                         int rank, int world, int slot, int64_t rows, int64_t slice_bytes,
+                         int64_t slot_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -143,6 +143,83 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_
   }
 }
 
+// ---- one-shot all-gather over peer memory ------------------------------------------------
+// Every rank copies its slice [rows, slice_bytes] into every rank's gather buffer (plain peer
+// stores through NVLink; its own copy included) at column offset rank * slice_bytes of rows
+// that are world * slice_bytes apart, then raises a flag word on every rank, then waits until
+// all ranks' flags for this call have been raised on itself. The next kernel of the stream
+// therefore finds the gathered [rows, world * slice_bytes] matrix complete. One kernel per
+// rank, each on its own GPU; the waits are bounded (a second or so of SM clock) and report
+// through the status word, after which later calls skip their waits.
+//
+// state (device memory of this rank, zero-initialised once): [slot] calls completed on that
+// slot (slots 0..2), [4] CTAs finished in the current call, [8 + r] CTAs that finished copying
+// to rank r in the current call.
+constexpr int kAgThreads = 256;
+constexpr long long kAgSpinLimit = 2000000000LL;
+
+struct AllGatherParams {
+  const uint8_t* local;
+  uint8_t* peer_buf[8];
+  uint32_t* peer_flags[8];       // every rank's flag words: [slot][source rank], 3 x 8
+  uint32_t* state;
+  int* status;
+  int64_t rows, slice_bytes, slot_bytes;
+  int rank, world, slot;
+};
+
+__global__ void __launch_bounds__(kAgThreads) allgather_push_kernel(const AllGatherParams p) {
+  pdl_enter();                                        // `local` is the previous kernel's output
+  const int peer = blockIdx.x, part = blockIdx.y, parts = gridDim.y;
+  const uint32_t seq = reinterpret_cast<volatile uint32_t*>(p.state)[p.slot] + 1;
+  // copy this CTA's share of the slice to `peer`
+  const int64_t chunks_per_row = p.slice_bytes / 16;
+  const int64_t total = p.rows * chunks_per_row;
+  const int64_t dst_row = static_cast<int64_t>(p.world) * p.slice_bytes;
+  uint8_t* dst = p.peer_buf[peer] + static_cast<int64_t>(p.slot) * p.slot_bytes + static_cast<int64_t>(p.rank) * p.slice_bytes;
+  for (int64_t i = static_cast<int64_t>(part) * kAgThreads + threadIdx.x; i < total;
+       i += static_cast<int64_t>(parts) * kAgThreads) {
+    const int64_t r = i / chunks_per_row, c = i % chunks_per_row;
+    const uint4 v = *reinterpret_cast<const uint4*>(p.local + r * p.slice_bytes + c * 16);
+    *reinterpret_cast<uint4*>(dst + r * dst_row + c * 16) = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // the last CTA that finished copying to `peer` raises this rank's flag there
+    if (atomicAdd(&p.state[8 + peer], 1u) == static_cast<unsigned>(parts - 1)) {
+      p.state[8 + peer] = 0;
+      __threadfence_system();
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[peer] + p.slot * 8 + p.rank), "r"(seq) : "memory");
+    }
+  }
+  // CTA (0, 0): wait for every rank's flag of this call on this rank
+  if (peer == 0 && part == 0 && threadIdx.x < p.world) {
+    const uint32_t* flag = p.peer_flags[p.rank] + p.slot * 8 + threadIdx.x;
+    if (*reinterpret_cast<volatile int*>(p.status) == 0) {
+      const long long t0 = clock64();
+      for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (static_cast<int32_t>(v - seq) >= 0) break;
+        if (clock64() - t0 > kAgSpinLimit) {
+          atomicCAS(p.status, 0, 100 + static_cast<int>(threadIdx.x));   // which rank never arrived
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // the last CTA of the call publishes the call count of this slot and clears the counter
+  if (threadIdx.x == 0) {
+    const unsigned all = gridDim.x * gridDim.y;
+    if (atomicAdd(&p.state[4], 1u) == all - 1) {
+      p.state[4] = 0;
+      reinterpret_cast<volatile uint32_t*>(p.state)[p.slot] = seq;
+    }
+  }
+}
+
 template <typename... Args>
 int launch_pdl(const char* what, void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                Args... args) {
@@ -208,4 +285,32 @@ extern "C" int qmm_decode_silu_mul(const void* gate_up, void* out, int64_t rows,
   return launch_pdl("silu_mul_kernel", silu_mul_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0,
                     static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(gate_up),
                     static_cast<__nv_bfloat16*>(out), rows, ffn);
+}
+
+extern "C" int qmm_decode_allgather(const void* local, void* const* peer_bufs, void* const* peer_flags, void* state,
+                                    int rank, int world, int slot, int64_t rows, int64_t slice_bytes,
+                                    int64_t slot_bytes, void* stream) {
+  if (!local || !peer_bufs || !peer_flags || !state) return fail(QMM_ERR_NULL, "allgather: null pointer");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0 || slot > 2)
+    return fail(QMM_ERR_SHAPE, "allgather: world must be 1..8, slot 0..2");
+  if (rows < 0 || slice_bytes <= 0 || slice_bytes % 16 || rows * slice_bytes * world > slot_bytes)
+    return fail(QMM_ERR_SHAPE, "allgather: slices are multiples of 16 bytes and must fit the slot");
+  if (!aligned16(local)) return fail(QMM_ERR_LAYOUT, "allgather: pointers must be 16-byte aligned");
+  if (rows == 0) return QMM_OK;
+  AllGatherParams p = {};
+  p.local = static_cast<const uint8_t*>(local);
+  for (int r = 0; r < world; ++r) {
+    if (!peer_bufs[r] || !peer_flags[r] || !aligned16(peer_bufs[r])) return fail(QMM_ERR_NULL, "allgather: bad peer pointer");
+    p.peer_buf[r] = static_cast<uint8_t*>(peer_bufs[r]);
+    p.peer_flags[r] = static_cast<uint32_t*>(peer_flags[r]);
+  }
+  p.state = static_cast<uint32_t*>(state);
+  p.status = device_status_word();
+  if (!p.status) return fail(QMM_ERR_CUDA, "could not allocate the device status word");
+  p.rows = rows; p.slice_bytes = slice_bytes; p.slot_bytes = slot_bytes;
+  p.rank = rank; p.world = world; p.slot = slot;
+  int64_t parts = (rows * slice_bytes + 32767) / 32768;
+  if (parts > 16) parts = 16;
+  return launch_pdl("allgather_push_kernel", allgather_push_kernel, dim3(static_cast<unsigned>(world), static_cast<unsigned>(parts)),
+                    dim3(kAgThreads), 0, static_cast<cudaStream_t>(stream), p);
 }

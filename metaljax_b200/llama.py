@@ -17,7 +17,10 @@ With a process group of g ranks the step is sharded on the output rows of every 
 (packing is per output row, so a shard is a row slice): q/k/v by attention head (attention
 and the KV cache stay local), the other linears on N, each followed by an all-gather of the
 `[batch, N/g]` slices; lm_head shards the vocabulary and the argmax is reduced from per-rank
-(max, index) pairs. The collectives are NCCL's (torch.distributed).
+(max, index) pairs. The all-gathers are this package's one-shot peer-store kernel
+(`qmm_decode_allgather`: every rank writes its slice straight into every rank's buffer over
+NVLink and raises a flag; symmetric memory from torch.distributed) or, with `gather="nccl"`,
+NCCL's; the final argmax reduction is NCCL's.
 """
 
 from __future__ import annotations
@@ -129,7 +132,7 @@ class DecodeStep:
     """Weights, KV cache and buffers of one rank, and the step itself."""
 
     def __init__(self, shape: Shape, batch: int, device, group=None, seed: int = 0, weights: str = "codes",
-                 full_weights=None):
+                 full_weights=None, gather: str = "peer"):
         self.shape, self.batch, self.device, self.group = shape, batch, torch.device(device), group
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
@@ -190,7 +193,27 @@ class DecodeStep:
         self.down_l = torch.empty((b, self.d_l), **bf)
         self.down_full = torch.empty((b, sh.d_model), **bf)
         self.logits_l = torch.empty((b, max(self.v_l, 1)), **bf)
-        self.gather_buf = torch.empty((g * b * max(sh.ffn // g, sh.d_model // g, self.h_l * hd),), **bf) if g > 1 else None
+        widest = g * b * max(sh.ffn // g, sh.d_model // g, self.h_l * hd)            # elements of one gathered matrix
+        self.gather_buf = torch.empty((widest,), **bf) if g > 1 else None
+        self.gather_mode = gather if g > 1 else "none"
+        self._site = 0
+        self._sites_per_step = 4 * sh.layers
+        if self.gather_mode == "peer":
+            # one symmetric allocation per rank: 24 flag words, then three gather slots; every
+            # rank maps every other rank's allocation (CUDA IPC under torch's symmetric memory)
+            import torch.distributed._symmetric_memory as symm_mem
+            self._slot_bytes = -(-widest * 2 // 256) * 256
+            self._symm = symm_mem.empty((256 + 3 * self._slot_bytes,), dtype=torch.uint8, device=dev)
+            self._symm.zero_()
+            self._symm_hdl = symm_mem.rendezvous(self._symm, group if group is not None else dist.group.WORLD)
+            ptrs = [int(p_) for p_ in self._symm_hdl.buffer_ptrs]
+            self._peer_flags = (ctypes.c_void_p * g)(*ptrs)
+            self._peer_bufs = (ctypes.c_void_p * g)(*[p_ + 256 for p_ in ptrs])
+            self._ag_state = torch.zeros((16,), device=dev, dtype=torch.int32)
+            self._slots = [self._symm[256 + i * self._slot_bytes: 256 + (i + 1) * self._slot_bytes].view(torch.bfloat16)
+                           for i in range(3)]
+            torch.cuda.synchronize(dev)
+            dist.barrier(group)                                   # every rank's flags are zero before any call
         self.graph = None
         self.tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
         self.next_tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
@@ -220,6 +243,16 @@ class DecodeStep:
         if self.world == 1:
             return local
         b, n_l = local.shape
+        if self.gather_mode == "peer":
+            # consecutive calls use different slots (a slot is rewritten by the peers as soon as
+            # they have seen this rank's flag of the call after it)
+            site, total = self._site, self._sites_per_step
+            slot = 1 if (total % 3 == 1 and site == total - 1) else site % 3
+            self._site = (site + 1) % total
+            _lib.check(_lib.lib().qmm_decode_allgather(
+                _ptr(local), self._peer_bufs, self._peer_flags, _ptr(self._ag_state), self.rank, self.world, slot,
+                b, n_l * 2, self._slot_bytes, _lib.stream_ptr(local)))
+            return self._slots[slot][: b * self.world * n_l].view(b, self.world * n_l)
         buf = self.gather_buf[: self.world * b * n_l].view(self.world * b, n_l)
         dist.all_gather_into_tensor(buf, local, group=self.group)
         if b == 1:
@@ -231,6 +264,7 @@ class DecodeStep:
     def step(self, tokens=None):
         sh, b, hd = self.shape, self.batch, self.shape.head_dim
         tok = self.tokens if tokens is None else tokens
+        self._site = 0
         torch.index_select(self.embedding, 0, tok, out=self.res)
         pos = sh.ctx - 1
         add_rmsnorm(self.res, self.layers[0]["ln1"], self.normed, eps=sh.eps)

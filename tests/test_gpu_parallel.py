@@ -68,9 +68,9 @@ def _worker(rank, world, port, ret):
         # the Llama-shaped decode step sharded over the ranks: same logits as the float reference
         from metaljax_b200 import llama
         shape = llama.Shape(layers=2, d_model=256, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1000, ctx=48)
-        for batch in (1, 5):
+        for batch, gather in ((1, "peer"), (5, "peer"), (5, "nccl")):
             fw = llama.random_full_weights(shape, batch, dev, seed=3)         # identical on every rank
-            step = llama.DecodeStep(shape, batch, dev, full_weights=fw)
+            step = llama.DecodeStep(shape, batch, dev, full_weights=fw, gather=gather)
             tokens = torch.arange(batch, device=dev) * 11 % shape.vocab
             step.tokens.copy_(tokens)
             nxt = step.step().clone()
@@ -81,7 +81,9 @@ def _worker(rank, world, port, ret):
             top2 = want.topk(2, dim=-1).values
             clear = (top2[:, 0] - top2[:, 1]) > 2 * 3e-2 * want.abs().max()
             assert torch.equal(nxt[clear], want.argmax(-1)[clear])
-            stage = f"decode step batch {batch} done"
+            for _ in range(3):                                                # slots and flags cycle correctly
+                assert torch.equal(step.step(), nxt)
+            stage = f"decode step batch {batch} ({gather}) done"
         assert _lib.poll_status() == 0
         ret[rank] = "ok"
     except Exception as exc:                              # surfaced by the parent
