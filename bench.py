@@ -411,7 +411,8 @@ def decode_step_line(name, args, torch, dist, device, world, pk, clk_fn=None):
         "config": {"workload": name, "batch": batch, "layers": 32, "d_model": 4096, "ffn": 14336, "vocab": 128256,
                    "context": 2048, "group_size": 64, "bits": 4,
                    "l2": f"one step streams {wb / 2**20:.0f} MiB of weights per GPU (> L2)",
-                   "parallelism": f"tp{world}: every weight sharded on its output rows, all-gather after each linear",
+                   "parallelism": f"tp{world}: every weight sharded on its output rows, all-gather after each linear"
+                                  + ("" if world == 1 else " (one-shot peer-store kernel over NVLink; QMM_DECODE_GATHER=nccl for NCCL)"),
                    "timed": "cuda graph replay of the whole step"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],

@@ -26,6 +26,7 @@ NCCL's; the final argmax reduction is NCCL's.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -195,7 +196,9 @@ class DecodeStep:
         self.logits_l = torch.empty((b, max(self.v_l, 1)), **bf)
         widest = g * b * max(sh.ffn // g, sh.d_model // g, self.h_l * hd)            # elements of one gathered matrix
         self.gather_buf = torch.empty((widest,), **bf) if g > 1 else None
-        self.gather_mode = gather if g > 1 else "none"
+        # QMM_DECODE_GATHER overrides the mode for experiments: "peer", "nccl", or "skip" (no
+        # exchange at all: timing of the compute alone, the results are meaningless)
+        self.gather_mode = os.environ.get("QMM_DECODE_GATHER", gather) if g > 1 else "none"
         self._site = 0
         self._sites_per_step = 4 * sh.layers
         if self.gather_mode == "peer":
@@ -254,6 +257,8 @@ class DecodeStep:
                 b, n_l * 2, self._slot_bytes, _lib.stream_ptr(local)))
             return self._slots[slot][: b * self.world * n_l].view(b, self.world * n_l)
         buf = self.gather_buf[: self.world * b * n_l].view(self.world * b, n_l)
+        if self.gather_mode == "skip":
+            return buf.view(b, self.world * n_l)
         dist.all_gather_into_tensor(buf, local, group=self.group)
         if b == 1:
             return buf.view(1, self.world * n_l)
