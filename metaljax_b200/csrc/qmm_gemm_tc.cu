@@ -58,6 +58,8 @@ struct TcParams {
   int64_t segments;            // weight matrices
   int64_t w_seg_rows;          // rows of the packed weight between segments (N, or 0 = shared)
   int group_size, table_dtype, y_dtype;
+  int splits;                  // > 1: the K blocks of a tile are divided among `splits` CTAs, each
+  float* partial;              // of which writes its float32 partial tile to partial[split][M][N]
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -360,6 +362,7 @@ struct Plan {
 };
 
 struct TileInfo {
+  int split, kb_lo, kb_hi;   // this work item's share of the tile's K blocks
   int seg;
   int64_t row0;      // first x / y row of this tile
   int rows;          // valid rows in the tile (<= BT)
@@ -370,9 +373,19 @@ struct TileInfo {
 // fastest inside a token tile so that concurrently running CTAs share the activation tile
 // and stream disjoint weight rows.
 template <int BT>
-__device__ __forceinline__ bool tile_at(int64_t t, const int64_t* seg_tile0, const int64_t* seg_row0,
-                                        int nseg, int64_t ftiles, int64_t N, TileInfo* out) {
+__device__ __forceinline__ bool tile_at(int64_t item, const int64_t* seg_tile0, const int64_t* seg_row0,
+                                        int nseg, int64_t ftiles, int64_t N, int splits, int num_kb,
+                                        TileInfo* out) {
+  // work item -> (tile, split): the splits of a tile are adjacent items, so they run together
+  int64_t t = item;
+  out->split = 0;
+  if (splits > 1) {                                   // (the common case divides nothing)
+    t = item / splits;
+    out->split = static_cast<int>(item - t * splits);
+  }
   if (t >= seg_tile0[nseg]) return false;
+  out->kb_lo = static_cast<int>(static_cast<int64_t>(out->split) * num_kb / splits);
+  out->kb_hi = static_cast<int>(static_cast<int64_t>(out->split + 1) * num_kb / splits);
   int s = 0;
   while (t >= seg_tile0[s + 1]) ++s;
   const int64_t local = t - seg_tile0[s];
@@ -387,7 +400,9 @@ __device__ __forceinline__ bool tile_at(int64_t t, const int64_t* seg_tile0, con
   return true;
 }
 
-template <int QK, typename XT, int BT>
+// SPLIT: the K blocks of a tile are shared among p.splits CTAs (float32 partial tiles). A
+// separate instantiation, so that the unsplit kernel keeps compile-time K bounds.
+template <int QK, typename XT, int BT, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
                    const TcParams p) {
@@ -467,10 +482,10 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       uint32_t it = 0;
       TileInfo ti;
       bool ok = true;
-      for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, &ti);
+      for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
            t += gridDim.x) {
         const int64_t wrow = ti.seg * p.w_seg_rows + ti.f0;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = ti.kb_lo; kb < ti.kb_hi; ++kb, ++it) {
           const int s = it % P::kStages;
           const uint32_t ph = (it / P::kStages) & 1;
           if (!(ok = twait(&empty[s], ph ^ 1, abort_flag, 1))) break;
@@ -490,11 +505,11 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
     int s = 0;
     TileInfo ti;
     bool ok = true;
-    for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, &ti);
+    for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
          t += gridDim.x, ++tile_n) {
       if (!(ok = twait(d_empty, (tile_n & 1) ^ 1, abort_flag, 2))) break;
       tc_fence_after();
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = ti.kb_lo; kb < ti.kb_hi; ++kb) {
         // The dequantized A of this K block sits in TMEM slot s, the slot of its shared-
         // memory stage. Its writers waited for the stage's TMA barrier themselves, so
         // their barrier also says that the activation tile has landed.
@@ -509,7 +524,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k)
             tc_mma_ts(tmem_base, acol + k * 8, bdesc + static_cast<uint64_t>(k * 2), idesc,
-                      (kb | k) ? 1u : 0u);
+                      (kb > ti.kb_lo || k) ? 1u : 0u);
           tc_commit(&empty[s]);     // frees the stage and its TMEM slot together
         }
         if (tracing) waited[0] += clock64() - ti0;   // cycles spent issuing
@@ -527,7 +542,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
     uint32_t it = 0, tile_n = 0;
     TileInfo ti;
     bool ok = true;
-    for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, &ti);
+    for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
          t += gridDim.x, ++tile_n) {
       int64_t feat = ti.f0 + frow;
       const bool feat_ok = feat < p.N;
@@ -567,16 +582,17 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       };
       constexpr int kHalfWords = P::kWRowBytes / 8;                // packed words per 32 elements
       const uint32_t it0 = it;
-      int kb = static_cast<int>((static_cast<uint32_t>(team) + kTeams - (it0 % kTeams)) % kTeams);
+      int kb = ti.kb_lo + static_cast<int>((static_cast<uint32_t>(team) + kTeams - (it0 % kTeams)) % kTeams);
+      const int kb_end = ti.kb_hi;
       float sc[2], bi[2];
       uint32_t e8[2];
-      if (kb < num_kb) fetch_tables(kb, sc, bi, e8);
-      for (; kb < num_kb; kb += kTeams) {
-        it = it0 + static_cast<uint32_t>(kb);
+      if (kb < kb_end) fetch_tables(kb, sc, bi, e8);
+      for (; kb < kb_end; kb += kTeams) {
+        it = it0 + static_cast<uint32_t>(kb - ti.kb_lo);
         const int s = it % P::kStages;
         float nsc[2] = {0.0f, 0.0f}, nbi[2] = {0.0f, 0.0f};
         uint32_t ne8[2] = {0u, 0u};
-        if (kb + kTeams < num_kb) fetch_tables(kb + kTeams, nsc, nbi, ne8);
+        if (kb + kTeams < kb_end) fetch_tables(kb + kTeams, nsc, nbi, ne8);
         if (!(ok = twait(&full[s], (it / P::kStages) & 1, abort_flag, 5))) break;
         const uint8_t* wsm = smem + s * P::kStageBytes + P::kXBytes + frow * P::kWRowBytes;
         uint32_t packed[2][kHalfWords];
@@ -618,7 +634,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
 #pragma unroll
         for (int h = 0; h < 2; ++h) { sc[h] = nsc[h]; bi[h] = nbi[h]; e8[h] = ne8[h]; }
       }
-      it = it0 + static_cast<uint32_t>(num_kb);
+      it = it0 + static_cast<uint32_t>(kb_end - ti.kb_lo);
       if (!ok) break;
       // ---- epilogue: the teams drain disjoint 32-column chunks of the accumulator ----
       if (!(ok = twait(d_full, tile_n & 1, abort_flag, 7))) break;
@@ -630,7 +646,12 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
         uint32_t r[32];
         tmem_ld32(tmem_base + lane_addr + c0, r);
         tmem_wait_ld();
-        if (feat_ok) {
+        if (SPLIT && feat_ok) {                    // a share of the tile's K: float32 partial sums
+          float* part = p.partial + static_cast<int64_t>(ti.split) * p.M * p.N;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < ti.rows) part[(ti.row0 + c0 + j) * p.N + feat] = __uint_as_float(r[j]);
+        } else if (feat_ok) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (c0 + j < ti.rows) {
@@ -728,6 +749,42 @@ int sm_count() {
   return n;
 }
 
+// Sums the float32 partial tiles of a split product in split order and casts to y's type.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ y, int y_dtype,
+                                     int64_t total, int splits) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * 4;
+  for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < total; i += stride) {
+    float4 acc = *reinterpret_cast<const float4*>(partial + i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + static_cast<int64_t>(s) * total + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (y_dtype == QMM_BF16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(y) + i) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    } else if (y_dtype == QMM_F16) {
+      __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(static_cast<__half*>(y) + i) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    } else {
+      *reinterpret_cast<float4*>(static_cast<float*>(y) + i) = acc;
+    }
+  }
+}
+
+// How many CTAs share one tile's K blocks. A short row run against a narrow weight leaves most
+// SMs without a tile while each busy CTA walks all of K alone; dividing K among CTAs fills the
+// machine. Only for one dense segment, N a multiple of 4 (the reduce kernel's vectors), and
+// never fewer than 8 K blocks per share.
+int choose_splits(const qmm_problem& p, int64_t tiles, int num_kb) {
+  if (p.group_sizes || p.batch != 1 || (p.N & 3)) return 1;
+  int64_t s = sm_count() / (tiles < 1 ? 1 : tiles);
+  if (s > num_kb / 8) s = num_kb / 8;
+  if (s > 8) s = 8;
+  return s < 2 ? 1 : static_cast<int>(s);
+}
+
 template <int QK, typename XT, int BT>
 int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   using P = Plan<QK, BT>;
@@ -760,21 +817,62 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   tp.segments = p.batch;
   tp.w_seg_rows = p.w_batch_stride ? p.N : 0;
   tp.group_size = p.group_size; tp.table_dtype = p.table_dtype; tp.y_dtype = p.y_dtype;
+  tp.splits = 1;
+  tp.partial = nullptr;
 
-  auto kernel = qmm_gemm_tc_kernel<QK, XT, BT>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmem);
+    cudaError_t e = cudaFuncSetAttribute(qmm_gemm_tc_kernel<QK, XT, BT, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(qmm_gemm_tc_kernel<QK, XT, BT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               P::kSmem);
     if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
   }
   const int64_t ftiles = (p.N + kBF - 1) / kBF;
   int64_t max_tiles = ragged ? ((p.M + BT - 1) / BT + p.batch) * ftiles
                              : p.batch * ((p.M + BT - 1) / BT) * ftiles;
+  // Split products need float32 scratch for the partial tiles: the caller's static block
+  // (qmm_quantized_matmul_static) or a stream-ordered allocation that lives until the reduce
+  // kernel has run. No scratch, no split.
+  const int num_kb = static_cast<int>((p.K + kBK - 1) / kBK);
+  int splits = choose_splits(p, max_tiles, num_kb);
+  bool scratch_async = false;
+  if (splits > 1) {
+    const size_t need = static_cast<size_t>(splits) * p.M * p.N * sizeof(float);
+    const ScratchBlock* block = scratch_override();
+    if (block) {
+      if (need > block->bytes)
+        return fail(QMM_ERR_TOO_LARGE, "split product needs %zu bytes of scratch, the static block has %zu", need,
+                    block->bytes);
+      tp.partial = static_cast<float*>(block->ptr);
+    } else {
+      void* ptr = nullptr;
+      if (cudaMallocAsync(&ptr, need, stream) == cudaSuccess) {
+        tp.partial = static_cast<float*>(ptr);
+        scratch_async = true;
+      } else {
+        cudaGetLastError();
+        splits = 1;
+      }
+    }
+  }
+  tp.splits = splits;
+  int64_t items = max_tiles * splits;
   int grid = sm_count();
-  if (max_tiles < grid) grid = static_cast<int>(max_tiles < 1 ? 1 : max_tiles);
-  kernel<<<grid, kThreads, P::kSmem, stream>>>(xm, wm, tp);
+  if (items < grid) grid = static_cast<int>(items < 1 ? 1 : items);
+  if (splits > 1) qmm_gemm_tc_kernel<QK, XT, BT, true><<<grid, kThreads, P::kSmem, stream>>>(xm, wm, tp);
+  else qmm_gemm_tc_kernel<QK, XT, BT, false><<<grid, kThreads, P::kSmem, stream>>>(xm, wm, tp);
   count_launch();
+  if (splits > 1) {
+    const int64_t total = p.M * p.N;
+    int64_t blocks = (total / 4 + 255) / 256;
+    if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(tp.partial, p.y, p.y_dtype, total, splits);
+    count_launch();
+    if (scratch_async) cudaFreeAsync(tp.partial, stream);
+  }
   if (trace_on) {   // development aid: average cycles per wait site over the CTAs
     cudaStreamSynchronize(stream);
     static long long host[16 * 1024];

@@ -19,6 +19,15 @@ int check_launch(const char* what);
 
 // Kernel families. Each validates nothing: `qmm_launch` has already done so.
 int launch_simt(const qmm_problem& p, cudaStream_t stream);
+// Scratch memory a caller lends for the duration of one call on this thread (set by the entry
+// point that works without allocating); NULL when the library may allocate its own.
+struct ScratchBlock {
+  void* ptr;
+  size_t bytes;
+};
+const ScratchBlock* scratch_override();
+void set_scratch_override(const ScratchBlock* block);
+
 int launch_gemv(const qmm_problem& p, cudaStream_t stream);
 bool gemv_supports(const qmm_problem& p);
 int launch_gemm_tc(const qmm_problem& p, cudaStream_t stream);

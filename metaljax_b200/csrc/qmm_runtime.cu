@@ -65,4 +65,11 @@ int device_sm_count() {
   return n;
 }
 
+namespace {
+thread_local const ScratchBlock* t_scratch = nullptr;
+}
+
+const ScratchBlock* scratch_override() { return t_scratch; }
+void set_scratch_override(const ScratchBlock* block) { t_scratch = block; }
+
 }  // namespace qmm
