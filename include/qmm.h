@@ -158,6 +158,34 @@ int qmm_ragged_dot(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* s
 int qmm_dequantize(const qmm_tensor* w, const qmm_tensor* scales, const qmm_tensor* biases,
                    qmm_tensor* out, int group_size, int bits, int mode, void* stream);
 
+/* `qmm_quantized_matmul` for callers that must not allocate. (No counterpart in the
+ * reference: MLX allocates inside `mx.quantized_matmul` as it pleases.)
+ *
+ * Same arguments, meaning, results and status codes as `qmm_quantized_matmul`, restricted to
+ * what the tensor-core kernel takes (bf16 / f16 activations, K >= 64; QMM_ERR_UNSUPPORTED
+ * otherwise). It exists for call sites where device memory cannot be requested while the call
+ * is made -- a serving loop that has handed every byte to its own pool, a real-time thread that
+ * may not block in the driver, code running under a tool that forbids allocation between two
+ * marks. For a short, narrow product the kernel shares a tile's K range among several CTAs and
+ * needs float32 scratch for their partial results; here that scratch is a fixed 8 MiB block of
+ * device memory that belongs to the library image, and the call performs no cudaMalloc,
+ * cudaMallocAsync, cudaFree or other allocating call.
+ *   - A product whose partial results need more than the block (splits * M * N * 4 bytes, with
+ *     at most 8 splits; about M * N <= 260k at full split) is refused with QMM_ERR_TOO_LARGE and
+ *     a message naming both sizes; nothing is launched.
+ *   - The first call on a device looks the block's address up and configures the kernels
+ *     (one-time host-side setup); make that first call before any stream capture begins.
+ *   - The block is one per device and shared by every caller in the process: two calls of this
+ *     entry point that can overlap in time (different streams, different threads) race on it.
+ *     Calls on one stream are safe.
+ *   - Nothing in the block has to be cleared between calls. Its last 256 bytes hold the status
+ *     word of the calls made through this entry point; it is zero when the library is loaded
+ *     and becomes non-zero only if a bounded device-side wait runs out (the output of that
+ *     call is then undefined). `qmm_poll_status` does not report this word. */
+int qmm_quantized_matmul_static(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* scales,
+                                const qmm_tensor* biases, qmm_tensor* y, int transpose,
+                                int group_size, int bits, int mode, void* stream);
+
 /* Replaces `pack_codes(codes, bits)` (src/metaljax/qmm.py:206-232) for device
  * tensors: codes uint8 [.., K] -> out uint32 [.., K*bits/32], masked to `bits`. */
 int qmm_pack_codes(const qmm_tensor* codes, qmm_tensor* out, int bits, void* stream);

@@ -62,6 +62,8 @@ _SIGNATURES = {
     "qmm_set_route_override": (ctypes.c_int, [ctypes.c_int]),
     "qmm_quantized_matmul": (ctypes.c_int, [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
                                             ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "qmm_quantized_matmul_static": (ctypes.c_int, [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
+                                                   ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "qmm_check_quantized_matmul": (ctypes.c_int, [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
                                                   ctypes.c_int, ctypes.c_int]),
     "qmm_gather_qmm": (ctypes.c_int, [_T, _T, _T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,

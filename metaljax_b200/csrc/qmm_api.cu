@@ -267,6 +267,62 @@ int build_dense(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* scal
 
 using namespace qmm;
 
+// ---- the entry point that allocates nothing ------------------------------------------------
+// The tensor-core kernel divides the K blocks of a short, narrow product among several CTAs and
+// needs float32 scratch for their partial tiles. The ordinary entry points take that scratch
+// from the stream-ordered allocator; this one takes it from a fixed block of device memory that
+// is part of the library image, so that it can be called where allocating is not an option.
+constexpr size_t kStaticScratchBytes = 8u << 20;      // 8 MiB: the stated maximum
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+
+// Address of the block on the current device, looked up once per device. The last 256 bytes
+// hold the status word of the calls made through this entry point (zero at load, like the
+// whole block; nothing else in the block has to start at any particular value: every partial
+// sum is written before it is read).
+int static_scratch(qmm::ScratchBlock* out) {
+  constexpr int kMaxDevices = 64;
+  static void* base[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return qmm::fail(QMM_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return qmm::fail(QMM_ERR_DEVICE, "device ordinal %d is out of range", dev);
+  if (!base[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      return qmm::fail(QMM_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    base[dev] = ptr;
+  }
+  out->ptr = base[dev];
+  out->bytes = kStaticScratchBytes - 256;
+  out->status = reinterpret_cast<int*>(static_cast<unsigned char*>(base[dev]) + kStaticScratchBytes - 256);
+  return QMM_OK;
+}
+
+}  // namespace
+
+extern "C" int qmm_quantized_matmul_static(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* scales,
+                                           const qmm_tensor* biases, qmm_tensor* y, int transpose, int group_size,
+                                           int bits, int mode, void* stream) {
+  using namespace qmm;
+  qmm_problem p;
+  int rc = build_dense(x, w, scales, biases, y, transpose, group_size, bits, mode, true, &p);
+  if (rc) return rc;
+  if ((rc = validate_problem(p, true))) return rc;
+  if (p.K == 0 || p.batch * p.M * p.N == 0 || !gemm_tc_supports(p))
+    return fail(QMM_ERR_UNSUPPORTED,
+                "qmm_quantized_matmul_static runs the tensor-core kernel only: 16-bit activations, K >= 64, "
+                "a non-empty product");
+  ScratchBlock block;
+  if ((rc = static_scratch(&block))) return rc;
+  set_scratch_override(&block);
+  rc = launch_gemm_tc(p, static_cast<cudaStream_t>(stream));
+  set_scratch_override(nullptr);
+  return rc;
+}
+
 extern "C" {
 
 int qmm_version(void) { return QMM_VERSION; }

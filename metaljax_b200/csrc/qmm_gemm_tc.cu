@@ -804,7 +804,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
     return rc;
   TcParams tp;
   tp.scales = p.scales; tp.biases = p.biases; tp.y = p.y; tp.group_sizes = p.group_sizes;
-  tp.status = status_word();
+  tp.status = scratch_override() ? scratch_override()->status : status_word();
   static long long* trace_buf = nullptr;
   static const bool trace_on = getenv("QMM_TC_TRACE") != nullptr;
   if (trace_on && !trace_buf) {

@@ -24,6 +24,7 @@ int launch_simt(const qmm_problem& p, cudaStream_t stream);
 struct ScratchBlock {
   void* ptr;
   size_t bytes;
+  int* status;     // where the kernels of this call record a device wait that ran out
 };
 const ScratchBlock* scratch_override();
 void set_scratch_override(const ScratchBlock* block);
