@@ -182,7 +182,10 @@ int route_of(const qmm_problem& p) {
   if (forced == QMM_ROUTE_GEMV) return gemv_supports(p) ? forced : -QMM_ERR_UNSUPPORTED;
   if (forced == QMM_ROUTE_GEMM_TC) return gemm_tc_supports(p) ? forced : -QMM_ERR_UNSUPPORTED;
   if (forced == QMM_ROUTE_SIMT) return forced;
-  if (gemv_supports(p)) return QMM_ROUTE_GEMV;
+  // More than 8 rows against a long K (the activations no longer fit next to the decode
+  // kernel's rings) go to the tensor-core kernel, whose K split then fills the machine.
+  const bool long_k = p.M > 8 && p.K >= 8192 && p.batch == 1 && !p.lhs_idx && gemm_tc_supports(p);
+  if (gemv_supports(p) && !long_k) return QMM_ROUTE_GEMV;
   if (gemm_tc_supports(p)) return QMM_ROUTE_GEMM_TC;
   return QMM_ROUTE_SIMT;
 }

@@ -62,41 +62,80 @@ class Value:
     """An SSA value: a function argument (`op is None`, `index` = argument number) or result
     `index` of `op`. Hashable by identity; `uses` lists the `(op, operand position)` pairs."""
 
-    __slots__ = ("name", "type", "op", "index", "uses")
+    __slots__ = ("name", "type", "op", "index", "uses", "block")
 
-    def __init__(self, name, type_, op, index):
+    def __init__(self, name, type_, op, index, block=None):
         self.name, self.type, self.op, self.index = name, type_, op, index
         self.uses = []
+        self.block = block           # the Block whose argument this is (None for op results)
 
     @property
     def is_argument(self):
         return self.op is None
+
+    @property
+    def is_main_argument(self):
+        return self.op is None and (self.block is None or self.block.owner is None)
 
     def __repr__(self):
         return f"%{self.name}: {self.type}"
 
 
 class Op:
-    __slots__ = ("name", "operands", "results", "attrs", "text", "opaque", "position")
+    __slots__ = ("name", "operands", "results", "attrs", "text", "opaque", "position", "regions")
 
     def __init__(self, name, operands, attrs, text, opaque=False):
         self.name, self.operands, self.attrs, self.text, self.opaque = name, operands, attrs, text, opaque
         self.results = []
         self.position = -1
+        self.regions = []            # Blocks (stablehlo.while: [cond, body]); other region ops are opaque
 
     def __repr__(self):
         return f"<{self.name} -> {[r.name for r in self.results]}>"
 
 
-class Func:
-    """`func.func @main`: arguments, ops in program order, returned values, and the argument
-    numbers the caller donates (`tf.aliasing_output` / `jax.buffer_donor`)."""
+class Block:
+    """Arguments, ops in program order and the values its terminator returns. `owner` is the op
+    whose region this is (None for a function body)."""
 
-    def __init__(self, name):
-        self.name = name
+    def __init__(self, owner=None):
+        self.owner = owner
         self.args, self.ops, self.returns = [], [], []
         self.return_op = None
+
+
+class Func(Block):
+    """`func.func @main`: a Block plus the argument numbers the caller donates
+    (`tf.aliasing_output` / `jax.buffer_donor`)."""
+
+    def __init__(self, name):
+        super().__init__(None)
+        self.name = name
         self.donated = set()
+
+    def walk(self):
+        """Every op, those inside while regions included, in program order."""
+        def rec(block):
+            for op in block.ops:
+                yield op
+                for region in op.regions:
+                    yield from rec(region)
+        return rec(self)
+
+
+def invariant_init(v):
+    """For an argument of a while region that the loop hands on unchanged (jax lowers a loop's
+    closed-over weights as such carries, src/metaljax/qmm.py:714-740): the while's initial
+    operand. None when `v` is anything else."""
+    if v.op is not None or v.block is None or v.block.owner is None:
+        return None
+    loop = v.block.owner
+    if loop.name != "stablehlo.while" or len(loop.regions) != 2:
+        return None
+    body = loop.regions[1]
+    if v.index >= len(body.returns) or body.returns[v.index] is not body.args[v.index]:
+        return None
+    return loop.operands[v.index]
 
 
 # ---------------------------------------------------------------------------------------
@@ -207,12 +246,21 @@ def parse(text: str) -> Func:
         fn.args.append(v)
         env[v.name] = v
 
+        v.block = fn
+    counter = [0]
+    _parse_block(lines, start + 1, env, fn, counter)
+    return fn
+
+
+def _parse_block(lines, i, env, block, counter):
+    """Ops of one block, from line `i` up to (and including) the line that closes it; returns
+    the index after that line. `env` maps names to Values (a region sees its parents' names)."""
+
     def lookup(tok):
         name, _, idx = tok.partition("#")
         v = env[name]
         return v[int(idx)] if isinstance(v, list) else v
 
-    i = start + 1
     while i < len(lines):
         ln = lines[i].strip()
         i += 1
@@ -220,7 +268,18 @@ def parse(text: str) -> Func:
             continue
         if ln.startswith("}"):
             break
-        # an op with regions: swallow lines until its braces balance, keep it opaque
+        m = re.match(r"(?:(%[\w.$-]+)(?::(\d+))?\s*=\s*)?\"?([\w.]+)\"?\s*(.*)", ln, re.S)
+        res_name, res_count, name, rest = m.group(1), m.group(2), m.group(3), m.group(4)
+        if name in ("return", "func.return", "stablehlo.return"):
+            block.returns = [lookup(t[1:]) for t in re.findall(r"%[\w.$#-]+", rest.split(" : ")[0])]
+            block.return_op = Op("func.return" if block.owner is None else "stablehlo.return", block.returns, {}, "")
+            for k, v in enumerate(block.returns):
+                v.uses.append((block.return_op, k))                # a use like any other
+            continue
+        if name == "stablehlo.while":
+            i = _parse_while(lines, i, ln, res_name, res_count, rest, env, block, counter, lookup)
+            continue
+        # any other op with regions: swallow lines until its braces balance, keep it opaque
         body = ln
         if ln.endswith("{") or ln.endswith("({"):
             depth = ln.count("{") - ln.count("}")
@@ -229,14 +288,7 @@ def parse(text: str) -> Func:
                 i += 1
                 depth += nxt.count("{") - nxt.count("}")
                 body += "\n" + nxt
-        m = re.match(r"(?:(%[\w.$-]+)(?::(\d+))?\s*=\s*)?\"?([\w.]+)\"?\s*(.*)", body, re.S)
-        res_name, res_count, name, rest = m.group(1), m.group(2), m.group(3), m.group(4)
-        if name in ("return", "func.return", "stablehlo.return"):
-            fn.returns = [lookup(t[1:]) for t in re.findall(r"%[\w.$#-]+", rest.split(" : ")[0])]
-            fn.return_op = Op("func.return", fn.returns, {}, "")          # a use like any other
-            for k, v in enumerate(fn.returns):
-                v.uses.append((fn.return_op, k))
-            continue
+            rest = body[body.index(name) + len(name):].lstrip('"').lstrip()
         opaque = "\n" in body
         parts = _top_level_split(rest, " : ")
         pre, sig_text = (" : ".join(parts[:-1]), parts[-1]) if len(parts) > 1 else (rest, "")
@@ -251,16 +303,54 @@ def parse(text: str) -> Func:
         else:
             result_types = types[-1:] if res_name else []
         op = Op(name, operands, {}, pre, opaque)
-        op.position = len(fn.ops)
-        for k, v in enumerate(operands):
-            v.uses.append((op, k))
-        if res_name:
-            res = [Value(res_name[1:] + (f"#{k}" if res_count else ""), t, op, k) for k, t in enumerate(result_types)]
-            op.results = res
-            env[res_name[1:]] = res if res_count else res[0]
+        _register(op, res_name, res_count, result_types, env, block, counter)
         _attrs(op)
-        fn.ops.append(op)
-    return fn
+    return i
+
+
+def _register(op, res_name, res_count, result_types, env, block, counter):
+    op.position = counter[0]
+    counter[0] += 1
+    for k, v in enumerate(op.operands):
+        v.uses.append((op, k))
+    if res_name:
+        res = [Value(res_name[1:] + (f"#{k}" if res_count else ""), t, op, k) for k, t in enumerate(result_types)]
+        op.results = res
+        env[res_name[1:]] = res if res_count else res[0]
+    block.ops.append(op)
+
+
+def _parse_while(lines, i, ln, res_name, res_count, rest, env, block, counter, lookup):
+    """`%r:N = stablehlo.while(%iterArg = %init, ...) : types  cond { ... } do { ... }`."""
+    head = ln
+    while not re.search(r"\bcond\s*\{", head) and i < len(lines):
+        head += " " + lines[i].strip()                             # `cond {` may sit on the next line
+        i += 1
+    inside = head[head.index("(") + 1:]
+    depth, end = 1, 0
+    for end, c in enumerate(inside):
+        depth += c == "("
+        depth -= c == ")"
+        if depth == 0:
+            break
+    pairs = [p.split("=") for p in _top_level_split(inside[:end], ",") if p.strip()]
+    names = [a.strip()[1:] for a, _ in pairs]
+    inits = [lookup(b.strip()[1:]) for _, b in pairs]
+    types = [parse_type(t) for t in re.findall(r"tensor<[^<>]*>", inside[end:].split("cond")[0])]
+    op = Op("stablehlo.while", inits, {}, "")
+    _register(op, res_name, res_count if res_count else None, types if res_name else [], env, block, counter)
+    if res_name and not res_count:                                 # a single carried value
+        env[res_name[1:]] = op.results[0]
+    for _ in range(2):                                             # cond, then body
+        region = Block(op)
+        renv = dict(env)
+        for k, (nm, t) in enumerate(zip(names, types)):
+            v = Value(nm, t, None, k, region)
+            region.args.append(v)
+            renv[nm] = v
+        i = _parse_block(lines, i, renv, region, counter)
+        op.regions.append(region)
+    return i
 
 
 def _attrs(op):
@@ -421,7 +511,8 @@ def eval_op(op, ins, device=None):
 
 def evaluate_value(value, env):
     """`value` on concrete buffers: `env` maps Values (the function's arguments at least) to
-    tensors and memoizes every intermediate. Iterative (subtrees can be deep)."""
+    tensors and memoizes every intermediate. Iterative (subtrees can be deep). An argument of a
+    while region that the loop hands on unchanged evaluates to the loop's initial operand."""
     stack = [value]
     device = next((t.device for t in env.values() if isinstance(t, torch.Tensor)), None)
     while stack:
@@ -430,7 +521,17 @@ def evaluate_value(value, env):
             stack.pop()
             continue
         if v.op is None:
-            raise KeyError(f"argument %{v.name} has no buffer")
+            init = invariant_init(v)
+            if init is None:
+                raise KeyError(f"argument %{v.name} has no buffer")
+            if init not in env:
+                stack.append(init)
+                continue
+            env[v] = env[init]
+            stack.pop()
+            continue
+        if v.op.name == "stablehlo.while":
+            raise NotImplementedError("a while result is not evaluated as a subtree")
         missing = [o for o in v.op.operands if o not in env]
         if missing:
             stack.extend(missing)
@@ -442,7 +543,36 @@ def evaluate_value(value, env):
     return env[value]
 
 
+def run_block(block, env, hook=None, device=None):
+    """The ops of `block` in order on the buffers in `env` (updated in place). `hook(op, env)`
+    may take an op over (it returns True when it did: a fused root or a skipped op); while loops
+    run their regions through the same hook."""
+    for op in block.ops:
+        if hook is not None and hook(op, env):
+            continue
+        if op.name == "stablehlo.while":
+            cond, body = op.regions
+            carries = [env[o] for o in op.operands]
+            for _ in range(1 << 20):
+                for a, t in zip(cond.args, carries):
+                    env[a] = t
+                run_block(cond, env, hook, device)
+                if not bool(env[cond.returns[0]]):
+                    break
+                for a, t in zip(body.args, carries):
+                    env[a] = t
+                run_block(body, env, hook, device)
+                carries = [env[r] for r in body.returns]
+            for r, t in zip(op.results, carries):
+                env[r] = t
+            continue
+        outs = eval_op(op, [env[o] for o in op.operands], device)
+        for r, t in zip(op.results, outs):
+            env[r] = t
+
+
 def evaluate(fn: Func, args):
     """The whole function, literally."""
     env = dict(zip(fn.args, args))
-    return [evaluate_value(v, env) for v in fn.returns]
+    run_block(fn, env, None, args[0].device if args else None)
+    return [env[v] for v in fn.returns]

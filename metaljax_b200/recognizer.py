@@ -163,9 +163,17 @@ def _closure(values, fn, ops, arg_indices, register=()):
             continue
         seen.add(v)
         if v.op is None:
-            arg_indices.add(v.index)
+            if v.is_main_argument:
+                arg_indices.add(v.index)
+                continue
+            # a loop's closed-over weight arrives as a carry the body returns unchanged: follow
+            # it out to the value the loop was handed (src/metaljax/qmm.py:714-740)
+            outer = hlo.invariant_init(v)
+            if outer is None:
+                raise _Reject("operand depends on an inner block argument")
+            stack.append(outer)
             continue
-        if v.op.opaque:
+        if v.op.opaque or v.op.regions:
             raise _Reject(f"operand subtree contains {v.op.name}")
         ops.setdefault(id(v.op), v.op)
         stack.extend(v.op.operands)
@@ -316,7 +324,7 @@ def analyze(interp) -> State:
             raise _Reject("recognizer disabled")
         fn = interp.func
         cands = []
-        for op in fn.ops:
+        for op in fn.walk():
             try:
                 if op.name == "stablehlo.dot_general":
                     cands.append(_try_scaled(fn, op))
@@ -367,7 +375,8 @@ def _fingerprint(m):
     for o in ops:
         ins = []
         for v in o.operands:
-            ins.append(f"a{v.index}" if v.op is None else names.get(v, f"x{v.name}"))
+            ins.append((f"a{v.index}" if v.is_main_argument else f"b{v.name}") if v.op is None
+                       else names.get(v, f"x{v.name}"))
         for r in o.results:
             names[r] = f"v{len(names)}"
         lines.append(f"{o.name}({','.join(ins)})[{sorted(o.attrs.items())}]{[r.type for r in o.results]}"
@@ -501,18 +510,16 @@ class Interpreter:
         prologue(self, args)
         st = self._qmm
         env = dict(zip(fn.args, args))
-        device = args[0].device if args else None
-        for op in fn.ops:
+
+        def hook(op, env):
             key = id(op)
             root = st.roots.get(key)
             if root is not None:
                 for r, t in zip(op.results, qmm.emit(self, root, env)):
                     env[r] = t
                 self.fused_calls += 1
-                continue
-            if key in st.skip:
-                continue
-            outs = hlo.eval_op(op, [env[o] for o in op.operands], device)
-            for r, t in zip(op.results, outs):
-                env[r] = t
+                return True
+            return key in st.skip
+
+        hlo.run_block(fn, env, hook, args[0].device if args else None)
         return [env[v] for v in fn.returns]

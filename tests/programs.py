@@ -133,3 +133,43 @@ def sub_channel_inputs_at(m, k, n, gs=64, seed=0, device="cpu"):
     scales = (torch.rand((n, k // gs), generator=g) * 0.02 + 0.002).to(torch.bfloat16)
     zeros = torch.randint(-3, 4, (n, k // gs), generator=g).to(torch.bfloat16)
     return [t.to(device) for t in (x, codes, scales, zeros)]
+
+
+# A decode-style loop: three iterations of y <- dot(y_prev-shaped activations, W) with the
+# quantized weight's parts closed over. jax lowers closed-over arrays as loop carries that the
+# body returns unchanged, so inside the body they are block arguments (%iterArg_*), not @main's.
+WHILE_LOOP = """
+module @jit_decode_loop {
+  func.func public @main(%arg0: tensor<5x256xbf16>, %arg1: tensor<256x256xi8>, %arg2: tensor<256x4xbf16>, %arg3: tensor<256x4xbf16>) -> (tensor<5x256xbf16>) {
+    %c = stablehlo.constant dense<0> : tensor<i32>
+    %c_0 = stablehlo.constant dense<3> : tensor<i32>
+    %c_1 = stablehlo.constant dense<1> : tensor<i32>
+    %0:5 = stablehlo.while(%iterArg = %c, %iterArg_2 = %arg1, %iterArg_3 = %arg2, %iterArg_4 = %arg3, %iterArg_5 = %arg0) : tensor<i32>, tensor<256x256xi8>, tensor<256x4xbf16>, tensor<256x4xbf16>, tensor<5x256xbf16>
+     cond {
+      %1 = stablehlo.compare LT, %iterArg, %c_0, SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>
+      stablehlo.return %1 : tensor<i1>
+    } do {
+      %1 = stablehlo.convert %iterArg_2 : (tensor<256x256xi8>) -> tensor<256x256xbf16>
+      %2 = stablehlo.broadcast_in_dim %iterArg_4, dims = [0, 1] : (tensor<256x4xbf16>) -> tensor<256x4x64xbf16>
+      %3 = stablehlo.reshape %2 : (tensor<256x4x64xbf16>) -> tensor<256x256xbf16>
+      %4 = stablehlo.subtract %1, %3 : tensor<256x256xbf16>
+      %5 = stablehlo.broadcast_in_dim %iterArg_3, dims = [0, 1] : (tensor<256x4xbf16>) -> tensor<256x4x64xbf16>
+      %6 = stablehlo.reshape %5 : (tensor<256x4x64xbf16>) -> tensor<256x256xbf16>
+      %7 = stablehlo.multiply %4, %6 : tensor<256x256xbf16>
+      %8 = stablehlo.dot_general %iterArg_5, %7, contracting_dims = [1] x [1] : (tensor<5x256xbf16>, tensor<256x256xbf16>) -> tensor<5x256xbf16>
+      %9 = stablehlo.add %iterArg, %c_1 : tensor<i32>
+      stablehlo.return %9, %iterArg_2, %iterArg_3, %iterArg_4, %8 : tensor<i32>, tensor<256x256xi8>, tensor<256x4xbf16>, tensor<256x4xbf16>, tensor<5x256xbf16>
+    }
+    return %0#4 : tensor<5x256xbf16>
+  }
+}
+"""
+
+
+def while_loop_inputs(seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((5, 256), generator=g).to(torch.bfloat16)
+    codes = torch.randint(-8, 8, (256, 256), generator=g, dtype=torch.int8)
+    scales = (torch.rand((256, 4), generator=g) * 0.01 + 0.004).to(torch.bfloat16)
+    zeros = torch.randint(-2, 3, (256, 4), generator=g).to(torch.bfloat16)
+    return [t.to(device) for t in (x, codes, scales, zeros)]

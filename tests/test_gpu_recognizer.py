@@ -17,7 +17,12 @@ def _exact(fn, args):
     from metaljax_b200 import hlo
     wide = [a.double().cpu() if a.dtype.is_floating_point else a.cpu() for a in args]
     f = hlo.parse(fn) if isinstance(fn, str) else fn
-    for v in list(f.args) + [r for o in f.ops for r in o.results]:
+    values = list(f.args)
+    for o in f.walk():
+        values += o.results
+        for region in o.regions:
+            values += region.args
+    for v in values:
         if v.type.el in hlo.FLOAT_ELS:
             v.type = hlo.TensorType(v.type.shape, "f64")
     return hlo.evaluate(f, wide)[0]
@@ -67,3 +72,9 @@ def test_rejected_program_runs_literally():
     it = recognizer.Interpreter(SHARED_WEIGHT)
     out = it.execute(sub_channel_inputs(seed=8, device=DEV))
     assert it.fused_calls == 0 and len(out) == 2
+
+
+def test_loop_with_carried_weights_fuses_every_iteration():
+    from programs import WHILE_LOOP, while_loop_inputs
+    it = _gate(WHILE_LOOP, while_loop_inputs(seed=9, device=DEV), expect_fused=3)
+    assert it._qmm.matches[0].arg_indices == (1, 2, 3)

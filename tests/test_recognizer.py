@@ -8,7 +8,8 @@ import torch
 from metaljax_b200 import hlo, qmm, recognizer
 from oracle import qmm_oracle as O
 
-from programs import SUB_CHANNEL, PER_CHANNEL, MXFP4, SHARED_WEIGHT, LHS_QUANT, DONATED, RMS_NORM, sub_channel_inputs, mxfp4_inputs
+from programs import (DONATED, LHS_QUANT, MXFP4, PER_CHANNEL, RMS_NORM, SHARED_WEIGHT, SUB_CHANNEL, WHILE_LOOP,
+                      mxfp4_inputs, sub_channel_inputs, while_loop_inputs)
 
 
 def test_parser_round_trip():
@@ -106,3 +107,29 @@ def test_mxfp4_prologue():
     np.testing.assert_array_equal(w.view(torch.int32).numpy().view(np.uint32),
                                   O.pack_codes(nib.numpy().astype(np.uint8), 4))
     np.testing.assert_array_equal(s.numpy(), sbytes.numpy())
+
+
+def test_weights_carried_through_a_loop():
+    """A while loop's closed-over weights are loop carries the body returns unchanged: the
+    recognizer follows them out to @main's arguments and fuses the dot inside the body."""
+    it = recognizer.Interpreter(WHILE_LOOP)
+    fn = it.func
+    loop = next(o for o in fn.ops if o.name == "stablehlo.while")
+    assert len(loop.regions) == 2 and len(loop.regions[1].args) == 5
+    assert hlo.invariant_init(loop.regions[1].args[1]) is fn.args[1]
+    assert hlo.invariant_init(loop.regions[1].args[4]) is None          # the activations change
+    st = recognizer.analyze(it)
+    assert len(st.matches) == 1
+    m = st.matches[0]
+    assert m.arg_indices == (1, 2, 3) and (m.M, m.K, m.N) == (5, 256, 256)
+    assert m.root.name == "stablehlo.dot_general" and m.lhs is loop.regions[1].args[4]
+    # literal evaluation of the loop, and the pack built from @main's buffers
+    args = while_loop_inputs(seed=4)
+    lit = hlo.evaluate(fn, args)[0]
+    x, codes, scales, zeros = args
+    w = ((codes.float() - zeros.float().repeat_interleave(64, 1)) * scales.float().repeat_interleave(64, 1))
+    want = x.float()
+    for _ in range(3):
+        want = (want.to(torch.bfloat16).float() @ w.to(torch.bfloat16).float().T)
+    assert torch.allclose(lit.float(), want.to(torch.bfloat16).float(), rtol=5e-2, atol=5e-2 * float(want.abs().max()))
+    assert recognizer.prologue(it, args) is False and not m.disabled and (m.gs, m.bits) == (64, 4)
