@@ -376,6 +376,12 @@ def _attrs(op):
         a["slices"] = [tuple(int(x) for x in s.split(":")) for s in m.group(1).split(",")] if m else []
     elif n == "stablehlo.compare":
         a["direction"] = re.search(r"\b(EQ|NE|LT|LE|GT|GE)\b", t).group(1)
+    elif n == "stablehlo.reduce":
+        m = re.search(r"applies\s+([\w.]+)\s+across\s+dimensions\s*=\s*(\[[^\]]*\])", t)
+        if m:                                               # the one-line form of a plain reduction
+            a["applies"], a["dims"] = m.group(1), _int_list(m.group(2))
+    elif n == "chlo.top_k":
+        a["k"] = _attr(t, "k", 1)
     elif n == "stablehlo.gather":
         for key in ("offset_dims", "collapsed_slice_dims", "start_index_map", "slice_sizes", "operand_batching_dims"):
             a[key] = _attr(t, key, [])
@@ -438,6 +444,29 @@ def _gather(op, operand, indices):
     return out.reshape(op.results[0].type.shape)
 
 
+_REDUCERS = {"stablehlo.add": lambda x, d: x.sum(dim=d), "stablehlo.maximum": lambda x, d: x.amax(dim=d),
+             "stablehlo.minimum": lambda x, d: x.amin(dim=d), "stablehlo.multiply": lambda x, d: x.prod(dim=d)}
+_COMBINE = {"stablehlo.add": torch.add, "stablehlo.maximum": torch.maximum, "stablehlo.minimum": torch.minimum,
+            "stablehlo.multiply": torch.mul}
+
+
+def _reduce(op, x, init):
+    kind = op.attrs.get("applies")
+    if kind not in _REDUCERS:
+        raise NotImplementedError("reduce: only the one-line add / max / min / multiply forms are evaluated")
+    dt = op.results[0].type.dtype
+    wide = x.to(torch.float32) if dt.is_floating_point else x
+    out = _REDUCERS[kind](wide, tuple(op.attrs["dims"]))
+    return _COMBINE[kind](out, init.to(out.dtype)).to(dt)
+
+
+def _top_k(op, x):
+    """Largest k along the last axis, descending; ties keep the lower index first (stable)."""
+    order = torch.sort(x, dim=-1, descending=True, stable=True)
+    k = op.attrs["k"]
+    return [order.values[..., :k].contiguous(), order.indices[..., :k].to(op.results[1].type.dtype).contiguous()]
+
+
 def _prod(xs):
     p = 1
     for x in xs:
@@ -476,6 +505,8 @@ EVAL = {
     "stablehlo.negate": lambda op, x: -x, "stablehlo.abs": lambda op, x: x.abs(),
     "stablehlo.exponential": lambda op, x: torch.exp(x), "stablehlo.rsqrt": lambda op, x: torch.rsqrt(x),
     "stablehlo.logistic": lambda op, x: torch.sigmoid(x),
+    "stablehlo.sqrt": lambda op, x: torch.sqrt(x), "stablehlo.tanh": lambda op, x: torch.tanh(x),
+    "stablehlo.log": lambda op, x: torch.log(x),
     "stablehlo.power": _binary(torch.pow),
     "stablehlo.convert": _convert,
     "stablehlo.bitcast_convert": lambda op, x: x.contiguous().view(op.results[0].type.dtype).reshape(op.results[0].type.shape),
@@ -487,6 +518,7 @@ EVAL = {
     "stablehlo.compare": lambda op, x, y: _CMP[op.attrs["direction"]](x, y),
     "stablehlo.select": lambda op, p, x, y: torch.where(p, x, y),
     "stablehlo.dot_general": _dot,
+    "stablehlo.reduce": lambda op, x, init: _reduce(op, x, init),
     "stablehlo.gather": _gather,
 }
 
@@ -502,6 +534,8 @@ def eval_op(op, ins, device=None):
         view = [1] * len(t.shape)
         view[op.attrs["dim"]] = t.shape[op.attrs["dim"]]
         return [torch.arange(t.shape[op.attrs["dim"]], device=device).reshape(view).expand(t.shape).to(t.dtype)]
+    if op.name == "chlo.top_k":
+        return _top_k(op, *ins)
     fn = EVAL.get(op.name)
     if fn is None:
         raise NotImplementedError(f"{op.name} is not evaluated here")

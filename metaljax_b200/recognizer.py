@@ -340,6 +340,10 @@ def analyze(interp) -> State:
         qmm.STATS["recognized"] += len(st.matches)
     except Exception:                                            # analysis must never break a program
         st.matches = []
+    # Expert-gather rewrites are found on top of the quantized ones: a dense mixture-of-experts
+    # block whose dots were matched here adopts those matches (src/metaljax/qmm.py:1085-1091).
+    from . import moe_recognizer
+    moe_recognizer.analyze(interp, st)
     st.rebuild()
     return st
 
@@ -466,7 +470,8 @@ def prologue(interp, args) -> bool:
     st = analyze(interp)
     if not st.matches:
         return False
-    changed = False
+    from . import moe_recognizer
+    changed = moe_recognizer.prologue(interp, st, args[0].device if args else None)
     vals = []
     for m in st.matches:
         if m.disabled:
@@ -515,7 +520,9 @@ class Interpreter:
             key = id(op)
             root = st.roots.get(key)
             if root is not None:
-                for r, t in zip(op.results, qmm.emit(self, root, env)):
+                from . import moe_recognizer
+                fused = (moe_recognizer.emit if isinstance(root, moe_recognizer.ExpertBlock) else qmm.emit)
+                for r, t in zip(op.results, fused(self, root, env)):
                     env[r] = t
                 self.fused_calls += 1
                 return True

@@ -173,3 +173,70 @@ def while_loop_inputs(seed=0, device="cpu"):
     scales = (torch.rand((256, 4), generator=g) * 0.01 + 0.004).to(torch.bfloat16)
     zeros = torch.randint(-2, 3, (256, 4), generator=g).to(torch.bfloat16)
     return [t.to(device) for t in (x, codes, scales, zeros)]
+
+
+def moe_program(t=6, d=64, e=4, f=64, gs=32, k=2):
+    """A dense SwiGLU mixture-of-experts layer as jax.numpy code lowers it: every expert runs
+    for every token, a top-k router's one-hot weights null the unselected ones
+    (the reference's tests/test_moe.py:60-81 writes the same layer in jax)."""
+    dg, fg = d // gs, f // gs
+    return f"""
+module @jit_moe {{
+  func.func public @main(%arg0: tensor<{t}x{d}xbf16>, %arg1: tensor<{t}x{e}xf32>, %arg2: tensor<{e}x{f}x{d}xi8>, %arg3: tensor<{e}x{f}x{dg}xbf16>, %arg4: tensor<{e}x{f}x{d}xi8>, %arg5: tensor<{e}x{f}x{dg}xbf16>, %arg6: tensor<{e}x{d}x{f}xi8>, %arg7: tensor<{e}x{d}x{fg}xbf16>) -> (tensor<{t}x{d}xbf16>) {{
+    %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %cst_0 = stablehlo.constant dense<0.000000e+00> : tensor<bf16>
+    %0:2 = chlo.top_k(%arg1, k = {k}) : tensor<{t}x{e}xf32> -> (tensor<{t}x{k}xf32>, tensor<{t}x{k}xi32>)
+    %1 = stablehlo.exponential %0#0 : tensor<{t}x{k}xf32>
+    %2 = stablehlo.reduce(%1 init: %cst) applies stablehlo.add across dimensions = [1] : (tensor<{t}x{k}xf32>, tensor<f32>) -> tensor<{t}xf32>
+    %3 = stablehlo.broadcast_in_dim %2, dims = [0] : (tensor<{t}xf32>) -> tensor<{t}x{k}xf32>
+    %4 = stablehlo.divide %1, %3 : tensor<{t}x{k}xf32>
+    %5 = stablehlo.iota dim = 2 : tensor<{t}x{k}x{e}xi32>
+    %6 = stablehlo.broadcast_in_dim %0#1, dims = [0, 1] : (tensor<{t}x{k}xi32>) -> tensor<{t}x{k}x{e}xi32>
+    %7 = stablehlo.compare EQ, %6, %5, SIGNED : (tensor<{t}x{k}x{e}xi32>, tensor<{t}x{k}x{e}xi32>) -> tensor<{t}x{k}x{e}xi1>
+    %8 = stablehlo.convert %7 : (tensor<{t}x{k}x{e}xi1>) -> tensor<{t}x{k}x{e}xf32>
+    %9 = stablehlo.broadcast_in_dim %4, dims = [0, 1] : (tensor<{t}x{k}xf32>) -> tensor<{t}x{k}x{e}xf32>
+    %10 = stablehlo.multiply %8, %9 : tensor<{t}x{k}x{e}xf32>
+    %11 = stablehlo.reduce(%10 init: %cst) applies stablehlo.add across dimensions = [1] : (tensor<{t}x{k}x{e}xf32>, tensor<f32>) -> tensor<{t}x{e}xf32>
+    %12 = stablehlo.convert %arg2 : (tensor<{e}x{f}x{d}xi8>) -> tensor<{e}x{f}x{d}xbf16>
+    %13 = stablehlo.broadcast_in_dim %arg3, dims = [0, 1, 2] : (tensor<{e}x{f}x{dg}xbf16>) -> tensor<{e}x{f}x{dg}x{gs}xbf16>
+    %14 = stablehlo.reshape %13 : (tensor<{e}x{f}x{dg}x{gs}xbf16>) -> tensor<{e}x{f}x{d}xbf16>
+    %15 = stablehlo.multiply %12, %14 : tensor<{e}x{f}x{d}xbf16>
+    %16 = stablehlo.dot_general %arg0, %15, contracting_dims = [1] x [2] : (tensor<{t}x{d}xbf16>, tensor<{e}x{f}x{d}xbf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %17 = stablehlo.convert %arg4 : (tensor<{e}x{f}x{d}xi8>) -> tensor<{e}x{f}x{d}xbf16>
+    %18 = stablehlo.broadcast_in_dim %arg5, dims = [0, 1, 2] : (tensor<{e}x{f}x{dg}xbf16>) -> tensor<{e}x{f}x{dg}x{gs}xbf16>
+    %19 = stablehlo.reshape %18 : (tensor<{e}x{f}x{dg}x{gs}xbf16>) -> tensor<{e}x{f}x{d}xbf16>
+    %20 = stablehlo.multiply %17, %19 : tensor<{e}x{f}x{d}xbf16>
+    %21 = stablehlo.dot_general %arg0, %20, contracting_dims = [1] x [2] : (tensor<{t}x{d}xbf16>, tensor<{e}x{f}x{d}xbf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %22 = stablehlo.logistic %16 : tensor<{t}x{e}x{f}xbf16>
+    %23 = stablehlo.multiply %16, %22 : tensor<{t}x{e}x{f}xbf16>
+    %24 = stablehlo.multiply %23, %21 : tensor<{t}x{e}x{f}xbf16>
+    %25 = stablehlo.transpose %24, dims = [1, 0, 2] : (tensor<{t}x{e}x{f}xbf16>) -> tensor<{e}x{t}x{f}xbf16>
+    %26 = stablehlo.convert %arg6 : (tensor<{e}x{d}x{f}xi8>) -> tensor<{e}x{d}x{f}xbf16>
+    %27 = stablehlo.broadcast_in_dim %arg7, dims = [0, 1, 2] : (tensor<{e}x{d}x{fg}xbf16>) -> tensor<{e}x{d}x{fg}x{gs}xbf16>
+    %28 = stablehlo.reshape %27 : (tensor<{e}x{d}x{fg}x{gs}xbf16>) -> tensor<{e}x{d}x{f}xbf16>
+    %29 = stablehlo.multiply %26, %28 : tensor<{e}x{d}x{f}xbf16>
+    %30 = stablehlo.dot_general %25, %29, batching_dims = [0] x [0], contracting_dims = [2] x [2] : (tensor<{e}x{t}x{f}xbf16>, tensor<{e}x{d}x{f}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %31 = stablehlo.convert %11 : (tensor<{t}x{e}xf32>) -> tensor<{t}x{e}xbf16>
+    %32 = stablehlo.broadcast_in_dim %31, dims = [1, 0] : (tensor<{t}x{e}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %33 = stablehlo.multiply %30, %32 : tensor<{e}x{t}x{d}xbf16>
+    %34 = stablehlo.reduce(%33 init: %cst_0) applies stablehlo.add across dimensions = [0] : (tensor<{e}x{t}x{d}xbf16>, tensor<bf16>) -> tensor<{t}x{d}xbf16>
+    return %34 : tensor<{t}x{d}xbf16>
+  }}
+}}
+"""
+
+
+def moe_inputs(t=6, d=64, e=4, f=64, gs=32, seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn((t, d), generator=g) * 0.5).to(torch.bfloat16)
+    logits = torch.randn((t, e), generator=g)
+
+    def pack(n, kk):
+        codes = torch.randint(-8, 8, (e, n, kk), generator=g, dtype=torch.int8)
+        scales = (torch.rand((e, n, kk // gs), generator=g) * 0.02 + 0.01).to(torch.bfloat16)
+        return codes, scales
+
+    cg, sg = pack(f, d)
+    cu, su = pack(f, d)
+    cd, sd = pack(d, f)
+    return [a.to(device) for a in (x, logits, cg, sg, cu, su, cd, sd)]

@@ -78,3 +78,13 @@ def test_loop_with_carried_weights_fuses_every_iteration():
     from programs import WHILE_LOOP, while_loop_inputs
     it = _gate(WHILE_LOOP, while_loop_inputs(seed=9, device=DEV), expect_fused=3)
     assert it._qmm.matches[0].arg_indices == (1, 2, 3)
+
+
+def test_dense_moe_layer_becomes_the_gathered_block():
+    """Every expert for every token, nulled by a top-2 router, against the gathered block: same
+    result within the reference's gate (the gathered sum has K terms, the dense one E)."""
+    from programs import moe_inputs, moe_program
+    for t, d, e, f in ((6, 64, 4, 64), (40, 128, 8, 256)):
+        it = _gate(moe_program(t, d, e, f), moe_inputs(t, d, e, f, seed=t, device=DEV))
+        st = it._qmm
+        assert len(st.moe) == 1 and st.moe[0].verified and all(m.absorbed for m in st.matches)
