@@ -10,7 +10,8 @@ whole-job TFLOP/s with inputs resident in HBM; `e2e` is the same metric through 
 call with pinned host buffers copied in and out inside the timed region; `roofline` compares
 the kernel with the measured bf16 tensor peak; `cpu_baseline` is the CPU restatement of the
 reference's fused dequantize-and-dot loop timed on the host cores on a bounded sample; `also`
-carries the decode (M=1) configuration against the measured HBM bandwidth.
+carries the decode (M=1) configuration against the measured HBM bandwidth and the tokens/s of
+whole Llama-3-8B-shaped decode steps (batch 1, 16, 64; weights sharded on N over the ranks).
 
 With N > 1 (one process per GPU under torch.distributed.run) every rank runs the same
 workload on its own token batch against replicated weights -- the path shards over
@@ -590,7 +591,7 @@ def main():
 
     if not args.no_also and name == DEFAULT:
         # the decode-step tokens/s at this N (weights sharded on N: strong scaling), all ranks
-        for side_name in ("decode_llama3_8b_b1", "decode_llama3_8b_b16"):
+        for side_name in ("decode_llama3_8b_b1", "decode_llama3_8b_b16", "decode_llama3_8b_b64"):
             side_line = decode_step_line(side_name, args, torch, dist, device, world, pk)
             line.setdefault("also", []).append(
                 {key: side_line[key] for key in ("metric", "value", "unit", "n_gpus", "ms_per_step", "scaling",
