@@ -362,7 +362,7 @@ def measure_decode_step(batch, steps, warmup, torch, dist, device):
     esteps = max(3, min(steps, 20))
     ems = time_device(e2e_step, esteps, 3, torch, dist)
     res = {"ms_per_step": ms / steps, "e2e_ms_per_step": ems / esteps, "launches_per_step": per_step,
-           "h2d": batch * 8, "d2h": batch * 8, "steps": steps}
+           "h2d": batch * 8, "d2h": batch * 8, "steps": steps, "gather": step.gather_mode}
     del step
     torch.cuda.empty_cache()
     return res
@@ -413,7 +413,8 @@ def decode_step_line(name, args, torch, dist, device, world, pk, clk_fn=None):
                    "context": 2048, "group_size": 64, "bits": 4,
                    "l2": f"one step streams {wb / 2**20:.0f} MiB of weights per GPU (> L2)",
                    "parallelism": f"tp{world}: every weight sharded on its output rows, all-gather after each linear"
-                                  + ("" if world == 1 else " (one-shot peer-store kernel over NVLink; QMM_DECODE_GATHER=nccl for NCCL)"),
+                                  + {"none": "", "peer": " (one-shot peer-store kernel over NVLink)",
+                                     "nccl": " (NCCL)", "skip": " (exchange left out: timing experiment)"}[res["gather"]],
                    "timed": "cuda graph replay of the whole step"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],

@@ -203,20 +203,28 @@ class DecodeStep:
         self._sites_per_step = 4 * sh.layers
         if self.gather_mode == "peer":
             # one symmetric allocation per rank: 24 flag words, then three gather slots; every
-            # rank maps every other rank's allocation (CUDA IPC under torch's symmetric memory)
-            import torch.distributed._symmetric_memory as symm_mem
-            self._slot_bytes = -(-widest * 2 // 256) * 256
-            self._symm = symm_mem.empty((256 + 3 * self._slot_bytes,), dtype=torch.uint8, device=dev)
-            self._symm.zero_()
-            self._symm_hdl = symm_mem.rendezvous(self._symm, group if group is not None else dist.group.WORLD)
-            ptrs = [int(p_) for p_ in self._symm_hdl.buffer_ptrs]
-            self._peer_flags = (ctypes.c_void_p * g)(*ptrs)
-            self._peer_bufs = (ctypes.c_void_p * g)(*[p_ + 256 for p_ in ptrs])
-            self._ag_state = torch.zeros((16,), device=dev, dtype=torch.int32)
-            self._slots = [self._symm[256 + i * self._slot_bytes: 256 + (i + 1) * self._slot_bytes].view(torch.bfloat16)
-                           for i in range(3)]
+            # rank maps every other rank's allocation (CUDA IPC under torch's symmetric memory).
+            # If any rank cannot set that up, every rank uses NCCL's all-gather instead.
+            ok = torch.ones((), device=dev, dtype=torch.int32)
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                self._slot_bytes = -(-widest * 2 // 256) * 256
+                self._symm = symm_mem.empty((256 + 3 * self._slot_bytes,), dtype=torch.uint8, device=dev)
+                self._symm.zero_()
+                self._symm_hdl = symm_mem.rendezvous(self._symm, group if group is not None else dist.group.WORLD)
+                ptrs = [int(p_) for p_ in self._symm_hdl.buffer_ptrs]
+                self._peer_flags = (ctypes.c_void_p * g)(*ptrs)
+                self._peer_bufs = (ctypes.c_void_p * g)(*[p_ + 256 for p_ in ptrs])
+                self._ag_state = torch.zeros((16,), device=dev, dtype=torch.int32)
+                self._slots = [self._symm[256 + i * self._slot_bytes: 256 + (i + 1) * self._slot_bytes].view(torch.bfloat16)
+                               for i in range(3)]
+            except Exception as exc:                              # noqa: BLE001 -- any setup failure
+                self._peer_error = repr(exc)
+                ok.zero_()
             torch.cuda.synchronize(dev)
-            dist.barrier(group)                                   # every rank's flags are zero before any call
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)   # also: every rank's flags are zero now
+            if int(ok.item()) == 0:
+                self.gather_mode = "nccl"
         self.graph = None
         self.tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
         self.next_tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
