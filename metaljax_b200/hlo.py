@@ -409,9 +409,12 @@ def _convert(op, x):
 def _broadcast(op, x):
     shape = op.results[0].type.shape
     dims = op.attrs["dims"]
+    order = sorted(range(len(dims)), key=lambda i: dims[i])       # operand axes in result order
+    if order != list(range(len(dims))):
+        x = x.permute(*order)
     view = [1] * len(shape)
-    for i, d in enumerate(dims):
-        view[d] = x.shape[i]
+    for i in order:
+        view[dims[i]] = x.shape[order.index(i)]
     return x.reshape(view).expand(shape)
 
 

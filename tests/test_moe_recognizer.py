@@ -58,3 +58,19 @@ def test_a_router_that_is_not_top_k_is_rejected():
     st.moe[0].router.t_axis, st.moe[0].router.e_axis = 1, 0
     assert recognizer.prologue(it, moe_inputs(seed=2)) is True
     assert st.moe[0].disabled and len(st.roots) == 3 and not any(m.absorbed for m in st.matches)
+
+
+def test_literal_evaluation_of_the_layer_matches_einsum():
+    """The front end's literal evaluator is the ground truth of the fused-vs-literal gates, so
+    it is pinned here against a direct einsum formulation (including the transposing
+    broadcast_in_dim of the routing matrix)."""
+    args = moe_inputs(seed=6)
+    x, logits, cg, sg, cu, su, cd, sd = args
+    got = hlo.evaluate(hlo.parse(moe_program()), args)[0].float()
+    wg, wu, wd = (c.float() * s.float().repeat_interleave(32, -1) for c, s in ((cg, sg), (cu, su), (cd, sd)))
+    v, i = torch.topk(logits, 2)
+    S = torch.zeros(6, 4).scatter_add_(1, i, torch.softmax(v, -1))
+    g, u = torch.einsum("td,efd->tef", x.float(), wg), torch.einsum("td,efd->tef", x.float(), wu)
+    y = torch.einsum("tef,edf->etd", torch.nn.functional.silu(g) * u, wd)
+    want = (y * S.T[:, :, None]).sum(0)
+    assert (got - want).abs().max() <= 3e-2 * want.abs().max()
