@@ -445,6 +445,42 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   // the same, the lanes of row 0 keep it. `xoff` is the pass's first K element in `xs`.
   auto sum_x = [&](int xoff, int jlo, int jhi) {
     if constexpr (QK != kMx4) {
+      if (p.M <= 2) {
+        // One or two tokens: plain float32 sums, four lanes per (token, group), instead of
+        // MMAs that would be seven-eighths empty.
+        constexpr int kPer = kGroupK / 4;                      // elements per lane: 8, 16 or 32
+        const int ng = (jhi - jlo) * kGroupsPerBox;
+        const int g_first = xoff / kGroupK + jlo * kGroupsPerBox;
+        const int items = static_cast<int>(p.M) * ng;
+        const int quad = lane >> 2, ql = lane & 3;
+        for (int it0 = 0; it0 < items; it0 += 8) {
+          const int item = it0 + quad;
+          const int m = item >= ng ? 1 : 0;
+          const int gi = g_first + (item - m * ng);
+          float acc = 0.0f;
+          if (item < items) {
+            const AT* src = xs + m * xrow + gi * kGroupK + ql * kPer;
+#pragma unroll
+            for (int c = 0; c < kPer / 8; ++c) {
+              const uint4 v = *reinterpret_cast<const uint4*>(src + c * 8);
+              const uint32_t u4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                if constexpr (std::is_same<AT, __nv_bfloat16>::value) {
+                  acc += __uint_as_float(u4[i] << 16) + __uint_as_float(u4[i] & 0xffff0000u);
+                } else {
+                  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u4[i]));
+                  acc += f.x + f.y;
+                }
+              }
+            }
+          }
+          acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+          acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+          if (item < items && ql == 0) sumx[gi * kSumTok + m] = acc;
+        }
+        return;
+      }
       const uint32_t one4[4] = {Ops::kOnes, Ops::kOnes, Ops::kOnes, Ops::kOnes};
       for (int j = jlo; j < jhi; ++j) {
 #pragma unroll
