@@ -522,7 +522,12 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
       asm volatile("griddepcontrol.wait;" ::: "memory");
       if (xres) stage_x(0, static_cast<int>(p.K), p.xk);
       else stage_x(kbase, kc, nb * kBoxK);
-      consumer_barrier();
+      table_store(tbl, kbase, cgroups, tg0, frs, frb);       // requested at kernel entry
+      for (int g0 = tg0 + 16 * kTU; g0 < tgroups; g0 += 16 * kTU) {
+        table_load(static_cast<int>(blockIdx.x), kbase, cgroups, g0, frs, frb);
+        table_store(tbl, kbase, cgroups, g0, frs, frb);
+      }
+      consumer_barrier();                                    // activations and tables are staged
       if (tracing) tr_t[3] += clock64() - ts0;
       const long long tp0 = tracing ? clock64() : 0;
       if (xres) {                                            // every pass's sums, once
@@ -534,12 +539,7 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
       } else {
         sum_x(0, jlo, jhi);
       }
-      table_store(tbl, kbase, cgroups, tg0, frs, frb);       // requested long ago: in flight meanwhile
-      for (int g0 = tg0 + 16 * kTU; g0 < tgroups; g0 += 16 * kTU) {
-        table_load(static_cast<int>(blockIdx.x), kbase, cgroups, g0, frs, frb);
-        table_store(tbl, kbase, cgroups, g0, frs, frb);
-      }
-      consumer_barrier();
+      __syncwarp();                                          // a warp reads only its own sums
       first = false;
       if (tracing) tr_t[6] += clock64() - tp0;
     } else if (!xres) {
@@ -549,6 +549,7 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
       stage_x(kbase, kc, nb * kBoxK);
       consumer_barrier();
       sum_x(0, jlo, jhi);
+      __syncwarp();
     }
 
     int tl = 0;                                             // index of the tile among this CTA's tiles
