@@ -76,6 +76,12 @@ typedef enum {
   QMM_ERR_TOO_LARGE = 10   /* a static capacity was exceeded */
 } qmm_status;
 
+/* Codes a kernel can leave in the device status word (qmm_poll_status): 1..99 name the wait
+ * of a compute kernel that ran out, 100 + r the rank an exchange never heard from, and
+ * QMM_DEVICE_BAD_INDEX a gather index outside [0, E) / [0, T): that pair was computed with
+ * index 0 instead of reading out of bounds. */
+#define QMM_DEVICE_BAD_INDEX 200
+
 typedef enum { QMM_MODE_AFFINE = 0, QMM_MODE_MXFP4 = 1 } qmm_mode;
 
 /* Element types of the raw-pointer entry points. */
@@ -93,7 +99,9 @@ typedef enum {
   QMM_ROUTE_NONE = 0,
   QMM_ROUTE_GEMV = 1,       /* decode: M <= 16, weight streaming */
   QMM_ROUTE_GEMM_TC = 2,    /* prefill: tcgen05 tensor-core kernel */
-  QMM_ROUTE_SIMT = 3        /* float32 activations / shapes the others decline */
+  QMM_ROUTE_SIMT = 3,       /* float32 activations / shapes the others decline */
+  QMM_ROUTE_GEMV_FMMA = 4   /* only as an override: the decode family's floating-point mma.sync
+                             * kernel also where the single-row integer kernel would be chosen */
 } qmm_route_id;
 
 /* ---- library ---------------------------------------------------------------- */
@@ -181,7 +189,8 @@ int qmm_dequantize(const qmm_tensor* w, const qmm_tensor* scales, const qmm_tens
  *   - Nothing in the block has to be cleared between calls. Its last 256 bytes hold the status
  *     word of the calls made through this entry point; it is zero when the library is loaded
  *     and becomes non-zero only if a bounded device-side wait runs out (the output of that
- *     call is then undefined). `qmm_poll_status` does not report this word. */
+ *     call is then undefined). `qmm_poll_status_static` reads and clears it without
+ *     allocating; `qmm_poll_status` reports it too. */
 int qmm_quantized_matmul_static(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* scales,
                                 const qmm_tensor* biases, qmm_tensor* y, int transpose,
                                 int group_size, int bits, int mode, void* stream);
@@ -219,6 +228,9 @@ typedef struct {
   /* ragged (NULL otherwise): int32 [batch] on the device; M is then the total row
    * count of x and y, `batch` the number of experts. */
   const int32_t* group_sizes;
+  /* gather: batches of x behind `x` (T), so that a bad lhs_idx can be caught on the device;
+   * 0 = unknown, lhs_idx is then only checked for being non-negative. */
+  int64_t x_batches;
 } qmm_problem;
 
 /* Same computation as the three tensor entry points above, from raw pointers. */
@@ -248,9 +260,25 @@ int qmm_set_route_override(int route);
  * reference, whose MLX calls are synchronous from Python's point of view. */
 int qmm_poll_status(int* status_out);
 
+/* The same for the status word of `qmm_quantized_matmul_static` alone, on the current device:
+ * waits for the device, copies the word out of the library's static block, clears it if set.
+ * Allocates nothing. No counterpart in the reference. */
+int qmm_poll_status_static(int* status_out);
+
+/* Test hook: how many SM clocks the bounded waits of the exchange kernels (qmm_decode.h) may
+ * last before they give up and report through the status word (default 4e9, about two
+ * seconds; at least 1000). Process-wide. No counterpart in the reference. */
+int qmm_set_wait_limit(long long clocks);
+
 /* Number of kernels this library has launched on the calling process since load
  * (monotonic; used by benchmarks to report their launch count). */
 uint64_t qmm_launch_count(void);
+
+/* Number of device-memory allocations (cudaMalloc / cudaMallocAsync) the library itself has
+ * made since load: the per-device status word on first use, and the float32 partial-sum
+ * scratch of a split tensor-core product. `qmm_quantized_matmul_static` never raises it once
+ * the device has been used. No counterpart in the reference. */
+uint64_t qmm_alloc_count(void);
 
 #ifdef __cplusplus
 }

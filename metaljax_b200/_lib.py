@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libqmm.so")
 
 MODE = {"affine": 0, "mxfp4": 1}
-ROUTES = {0: "none", 1: "gemv", 2: "gemm_tc", 3: "simt"}
+ROUTES = {0: "none", 1: "gemv", 2: "gemm_tc", 3: "simt", 4: "gemv_fmma"}
 ELEM = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2, torch.uint8: 3,
         torch.uint32: 4, torch.int32: 5}
 
@@ -45,6 +45,7 @@ class Problem(ctypes.Structure):
         ("y_batch_stride", ctypes.c_int64),
         ("lhs_idx", ctypes.c_void_p), ("rhs_idx", ctypes.c_void_p),
         ("group_sizes", ctypes.c_void_p),
+        ("x_batches", ctypes.c_int64),
     ]
 
 
@@ -58,7 +59,10 @@ _SIGNATURES = {
     "qmm_version": (ctypes.c_int, []),
     "qmm_last_error": (ctypes.c_char_p, []),
     "qmm_launch_count": (ctypes.c_uint64, []),
+    "qmm_alloc_count": (ctypes.c_uint64, []),
     "qmm_poll_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "qmm_poll_status_static": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "qmm_set_wait_limit": (ctypes.c_int, [ctypes.c_longlong]),
     "qmm_set_route_override": (ctypes.c_int, [ctypes.c_int]),
     "qmm_quantized_matmul": (ctypes.c_int, [_T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
                                             ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
@@ -143,7 +147,8 @@ def stream_ptr(t) -> int:
 
 class force_route:
     """Context manager for tests: every launch inside goes to one kernel family
-    ("gemv", "gemm_tc", "simt") or fails with status 7 if that family declines it."""
+    ("gemv", "gemm_tc", "simt"; "gemv_fmma" = the decode family's floating-point mma.sync kernel
+    even for a single row) or fails with status 7 if that family declines it."""
 
     def __init__(self, name: str):
         self.route = {v: k for k, v in ROUTES.items()}[name]
@@ -164,5 +169,17 @@ def poll_status() -> int:
     return int(st.value)
 
 
+def poll_status_static() -> int:
+    """The same for the status word of `qmm_quantized_matmul_static` alone (allocates nothing)."""
+    st = ctypes.c_int(0)
+    check(lib().qmm_poll_status_static(ctypes.byref(st)))
+    return int(st.value)
+
+
 def launch_count() -> int:
     return int(lib().qmm_launch_count())
+
+
+def alloc_count() -> int:
+    """Device-memory allocations libqmm itself has made since it was loaded."""
+    return int(lib().qmm_alloc_count())

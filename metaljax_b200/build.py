@@ -42,7 +42,7 @@ def stale() -> bool:
         return True
     t = os.path.getmtime(LIB)
     deps = sources() + glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
-    deps.append(os.path.join(HERE, "..", "include", "qmm.h"))
+    deps += glob.glob(os.path.join(HERE, "..", "include", "*.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 
 

@@ -48,8 +48,8 @@ add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* res
                    const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* residual_out, int64_t dim, float eps) {   // residual_out may be residual_in
   pdl_enter();
-  extern __shared__ uint4 row_cache[];               // the row as bf16, dim / 8 pieces
-  __shared__ float partial[kNormThreads / 32];
+  extern __shared__ uint4 row_cache[];               // the row as bf16, dim / 8 pieces, then 8 partial sums
+  float* partial = reinterpret_cast<float*>(row_cache + dim / 8);
   const int64_t row = blockIdx.x;
   const int pieces = static_cast<int>(dim / 8);
   float ss = 0.0f;
@@ -105,7 +105,9 @@ __global__ void rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloa
     const float hi = __bfloat162float(qkv[row + head * head_dim + j + half]);
     if (head < heads + kv_heads) {
       float s, c;
-      const float freq = __powf(theta, -2.0f * static_cast<float>(j) / static_cast<float>(head_dim));
+      // full-precision power: the angle is pos * freq, so a relative error of freq is multiplied
+      // by positions of up to 10^5
+      const float freq = exp2f(-2.0f * static_cast<float>(j) / static_cast<float>(head_dim) * log2f(theta));
       sincosf(static_cast<float>(pos) * freq, &s, &c);
       const float rlo = lo * c - hi * s, rhi = hi * c + lo * s;
       if (head < heads) {
@@ -156,7 +158,6 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_
 // slot (slots 0..2), [4] CTAs finished in the current call, [8 + r] CTAs that finished copying
 // to rank r in the current call.
 constexpr int kAgThreads = 256;
-constexpr long long kAgSpinLimit = 2000000000LL;
 
 struct AllGatherParams {
   const uint8_t* local;
@@ -165,6 +166,7 @@ struct AllGatherParams {
   uint32_t* state;
   int* status;
   int64_t rows, slice_bytes, slot_bytes;
+  long long spin_limit;          // SM clocks the wait for the peers may last
   int rank, world, slot;
 };
 
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(kAgThreads) allgather_push_kernel(const AllGat
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
         if (static_cast<int32_t>(v - seq) >= 0) break;
-        if (clock64() - t0 > kAgSpinLimit) {
+        if (clock64() - t0 > p.spin_limit) {
           atomicCAS(p.status, 0, 100 + static_cast<int>(threadIdx.x));   // which rank never arrived
           break;
         }
@@ -253,8 +255,17 @@ extern "C" int qmm_decode_add_rmsnorm(const void* x, const void* residual_in, co
   if (!aligned16(x) || !aligned16(weight) || !aligned16(y) || !aligned16(residual_in) || !aligned16(residual_out))
     return fail(QMM_ERR_LAYOUT, "add_rmsnorm: pointers must be 16-byte aligned");
   if (rows == 0) return QMM_OK;
+  const size_t smem = static_cast<size_t>(dim) * 2 + kNormThreads / 32 * sizeof(float);
+  static bool configured[kMaxDevices] = {};     // more than the default 48 KiB at the largest dim
+  const int dev = current_device();
+  if (dev < 0) return QMM_ERR_DEVICE;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 24576 * 2 + 64);
+    if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured[dev] = true;
+  }
   return launch_pdl("add_rmsnorm_kernel", add_rmsnorm_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads),
-                    static_cast<size_t>(dim) * 2, static_cast<cudaStream_t>(stream),
+                    smem, static_cast<cudaStream_t>(stream),
                     static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual_in),
                     static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(y),
                     static_cast<__nv_bfloat16*>(residual_out), dim, eps);
@@ -308,6 +319,7 @@ extern "C" int qmm_decode_allgather(const void* local, void* const* peer_bufs, v
   p.status = device_status_word();
   if (!p.status) return fail(QMM_ERR_CUDA, "could not allocate the device status word");
   p.rows = rows; p.slice_bytes = slice_bytes; p.slot_bytes = slot_bytes;
+  p.spin_limit = wait_limit_clocks();
   p.rank = rank; p.world = world; p.slot = slot;
   int64_t parts = (rows * slice_bytes + 32767) / 32768;
   if (parts > 16) parts = 16;

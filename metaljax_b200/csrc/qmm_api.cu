@@ -12,6 +12,7 @@ namespace qmm {
 namespace {
 thread_local char g_error[512] = "";
 std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_allocs{0};
 std::atomic<int> g_route_override{QMM_ROUTE_NONE};
 }  // namespace
 
@@ -24,6 +25,9 @@ int fail(int code, const char* fmt, ...) {
 }
 
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+void count_alloc(int n) { g_allocs.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+
+int route_override() { return g_route_override.load(std::memory_order_relaxed); }
 
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
@@ -179,7 +183,7 @@ int validate_problem(const qmm_problem& p, bool pointers) {
 int route_of(const qmm_problem& p) {
   if (p.batch == 0 || p.M == 0 || p.N == 0) return QMM_ROUTE_NONE;
   const int forced = g_route_override.load(std::memory_order_relaxed);
-  if (forced == QMM_ROUTE_GEMV) return gemv_supports(p) ? forced : -QMM_ERR_UNSUPPORTED;
+  if (forced == QMM_ROUTE_GEMV || forced == QMM_ROUTE_GEMV_FMMA) return gemv_supports(p) ? QMM_ROUTE_GEMV : -QMM_ERR_UNSUPPORTED;
   if (forced == QMM_ROUTE_GEMM_TC) return gemm_tc_supports(p) ? forced : -QMM_ERR_UNSUPPORTED;
   if (forced == QMM_ROUTE_SIMT) return forced;
   // More than 8 rows against a long K (the activations no longer fit next to the decode
@@ -284,23 +288,35 @@ namespace {
 // hold the status word of the calls made through this entry point (zero at load, like the
 // whole block; nothing else in the block has to start at any particular value: every partial
 // sum is written before it is read).
+void* g_static_base[qmm::kMaxDevices] = {};     // the block's address on each device, once looked up
+
 int static_scratch(qmm::ScratchBlock* out) {
-  constexpr int kMaxDevices = 64;
-  static void* base[kMaxDevices] = {};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return qmm::fail(QMM_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
-  if (dev < 0 || dev >= kMaxDevices) return qmm::fail(QMM_ERR_DEVICE, "device ordinal %d is out of range", dev);
-  if (!base[dev]) {
+  const int dev = qmm::current_device();
+  if (dev < 0) return QMM_ERR_DEVICE;
+  if (!g_static_base[dev]) {
     void* ptr = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
     if (e != cudaSuccess || !ptr)
       return qmm::fail(QMM_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
-    base[dev] = ptr;
+    g_static_base[dev] = ptr;
   }
-  out->ptr = base[dev];
+  out->ptr = g_static_base[dev];
   out->bytes = kStaticScratchBytes - 256;
-  out->status = reinterpret_cast<int*>(static_cast<unsigned char*>(base[dev]) + kStaticScratchBytes - 256);
+  out->status = reinterpret_cast<int*>(static_cast<unsigned char*>(g_static_base[dev]) + kStaticScratchBytes - 256);
+  return QMM_OK;
+}
+
+// Reads, and clears if set, the status word in the static block of the current device. Zero
+// when the block has never been used there. A plain cudaMemcpy from the block: no allocation.
+int read_static_status(int* out) {
+  *out = 0;
+  const int dev = qmm::current_device();
+  if (dev < 0) return QMM_ERR_DEVICE;
+  if (!g_static_base[dev]) return QMM_OK;
+  int* word = reinterpret_cast<int*>(static_cast<unsigned char*>(g_static_base[dev]) + kStaticScratchBytes - 256);
+  cudaError_t e = cudaMemcpy(out, word, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return qmm::fail(QMM_ERR_CUDA, "cudaMemcpy(static status): %s", cudaGetErrorString(e));
+  if (*out) cudaMemset(word, 0, sizeof(int));
   return QMM_OK;
 }
 
@@ -333,23 +349,45 @@ int qmm_version(void) { return QMM_VERSION; }
 const char* qmm_last_error(void) { return g_error; }
 
 int qmm_set_route_override(int route) {
-  if (route < QMM_ROUTE_NONE || route > QMM_ROUTE_SIMT) return fail(QMM_ERR_UNSUPPORTED, "unknown route %d", route);
+  if (route < QMM_ROUTE_NONE || route > QMM_ROUTE_GEMV_FMMA) return fail(QMM_ERR_UNSUPPORTED, "unknown route %d", route);
   g_route_override.store(route, std::memory_order_relaxed);
   return QMM_OK;
 }
 
 int qmm_poll_status(int* status_out) {
-  int st = 0;
+  int st = 0, st_static = 0;
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
-  int rc = gemm_tc_status(&st);
+  int rc = read_status_word(&st);
   if (rc) return rc;
+  if ((rc = read_static_status(&st_static))) return rc;
+  if (!st) st = st_static;
   if (status_out) *status_out = st;
+  if (st == QMM_DEVICE_BAD_INDEX) return fail(QMM_ERR_SHAPE, "a gather index was out of range (that pair used index 0)");
   if (st) return fail(QMM_ERR_TIMEOUT, "a device-side wait ran out (code %d)", st);
   return QMM_OK;
 }
 
+int qmm_poll_status_static(int* status_out) {
+  int st = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+  int rc = read_static_status(&st);
+  if (rc) return rc;
+  if (status_out) *status_out = st;
+  if (st) return fail(QMM_ERR_TIMEOUT, "a device-side wait of qmm_quantized_matmul_static ran out (code %d)", st);
+  return QMM_OK;
+}
+
+int qmm_set_wait_limit(long long clocks) {
+  if (clocks < 1000) return fail(QMM_ERR_UNSUPPORTED, "wait limit of %lld clocks is too short", clocks);
+  set_wait_limit_clocks(clocks);
+  return QMM_OK;
+}
+
 uint64_t qmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+uint64_t qmm_alloc_count(void) { return g_allocs.load(std::memory_order_relaxed); }
 
 int qmm_launch(const qmm_problem* problem, void* stream) {
   if (!problem) return fail(QMM_ERR_NULL, "problem is NULL");
@@ -422,6 +460,7 @@ int qmm_gather_qmm(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* s
   p.scales = data_of(scales); p.biases = biases ? data_of(biases) : nullptr; p.y = data_of(y);
   p.x_batch_stride = M * K; p.y_batch_stride = M * N; p.w_batch_stride = N;
   p.num_weights = static_cast<int32_t>(w->shape[0]);
+  p.x_batches = x->shape[0];
   p.lhs_idx = static_cast<const int32_t*>(data_of(lhs_idx));
   p.rhs_idx = static_cast<const int32_t*>(data_of(rhs_idx));
   if ((rc = validate_problem(p, true))) return rc;

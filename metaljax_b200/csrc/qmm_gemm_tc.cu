@@ -43,6 +43,9 @@ constexpr int kTeams = 4;        // dequant/epilogue teams of four warps (one pe
 constexpr int kThreads = (2 + 4 * kTeams) * 32;
 constexpr int kMaxSegments = 256;
 constexpr long long kSpinLimit = 4000000000LL;  // SM clocks (~2 s)
+#ifndef QMM_TC_TRACING
+#define QMM_TC_TRACING 0        // development builds: cycles per wait site (-DQMM_TC_TRACING=1)
+#endif
 
 enum { kAff4 = 0, kAff8 = 1, kMx4 = 2 };
 
@@ -462,7 +465,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
 
   // Waits go through here so that a development build can account the cycles per wait site.
   long long waited[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  const bool tracing = p.trace != nullptr;
+  const bool tracing = QMM_TC_TRACING && p.trace != nullptr;
   long long trace_c0 = 0, trace_n0 = 0;
   if (tracing && threadIdx.x == 0) {
     trace_c0 = clock64();
@@ -738,16 +741,7 @@ int* status_word() {
   return device_status_word();
 }
 
-int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
+int sm_count() { return device_sm_count(); }
 
 // Sums the float32 partial tiles of a split product in split order and casts to y's type.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ y, int y_dtype,
@@ -805,6 +799,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   TcParams tp;
   tp.scales = p.scales; tp.biases = p.biases; tp.y = p.y; tp.group_sizes = p.group_sizes;
   tp.status = scratch_override() ? scratch_override()->status : status_word();
+#if QMM_TC_TRACING
   static long long* trace_buf = nullptr;
   static const bool trace_on = getenv("QMM_TC_TRACE") != nullptr;
   if (trace_on && !trace_buf) {
@@ -812,6 +807,9 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   }
   if (trace_on) cudaMemsetAsync(trace_buf, 0, sizeof(long long) * 16 * 1024, stream);
   tp.trace = trace_on ? trace_buf : nullptr;
+#else
+  tp.trace = nullptr;
+#endif
   if (!tp.status) return fail(QMM_ERR_CUDA, "could not allocate the device status word");
   tp.M = p.M; tp.K = p.K; tp.N = p.N;
   tp.segments = p.batch;
@@ -820,15 +818,17 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   tp.splits = 1;
   tp.partial = nullptr;
 
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};     // the attribute is per device
+  const int dev = current_device();
+  if (dev < 0) return QMM_ERR_DEVICE;
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(qmm_gemm_tc_kernel<QK, XT, BT, false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmem);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(qmm_gemm_tc_kernel<QK, XT, BT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                P::kSmem);
     if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    configured = true;
+    configured[dev] = true;
   }
   const int64_t ftiles = (p.N + kBF - 1) / kBF;
   int64_t max_tiles = ragged ? ((p.M + BT - 1) / BT + p.batch) * ftiles
@@ -850,6 +850,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
     } else {
       void* ptr = nullptr;
       if (cudaMallocAsync(&ptr, need, stream) == cudaSuccess) {
+        count_alloc();
         tp.partial = static_cast<float*>(ptr);
         scratch_async = true;
       } else {
@@ -873,6 +874,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
     count_launch();
     if (scratch_async) cudaFreeAsync(tp.partial, stream);
   }
+#if QMM_TC_TRACING
   if (trace_on) {   // development aid: average cycles per wait site over the CTAs
     cudaStreamSynchronize(stream);
     static long long host[16 * 1024];
@@ -886,6 +888,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
             " dequant.st %.0f dequant.full %.0f dequant.a_empty %.0f dequant.d_full %.0f\n",
             avg[1], avg[8], avg[8 + 2], avg[8 + 3], avg[8 + 4], avg[0], avg[5], avg[6], avg[7]);
   }
+#endif
   return check_launch("qmm_gemm_tc_kernel");
 }
 
@@ -923,15 +926,6 @@ int launch_gemm_tc(const qmm_problem& p, cudaStream_t stream) {
   if (p.mode == QMM_MODE_MXFP4) return launch_xt<kMx4>(p, stream);
   if (p.bits == 8) return launch_xt<kAff8>(p, stream);
   return launch_xt<kAff4>(p, stream);
-}
-
-int gemm_tc_status(int* out) {
-  int* w = status_word();
-  if (!w) return fail(QMM_ERR_CUDA, "no status word");
-  cudaError_t e = cudaMemcpy(out, w, sizeof(int), cudaMemcpyDeviceToHost);
-  if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaMemcpy(status): %s", cudaGetErrorString(e));
-  if (*out) cudaMemset(w, 0, sizeof(int));
-  return QMM_OK;
 }
 
 }  // namespace qmm

@@ -75,6 +75,7 @@ struct GemvParams {
   int* status;
   int64_t M, K, N, batch;
   int64_t x_batch_stride, y_batch_stride, w_batch_rows;
+  int64_t num_weights, x_batches;   // gather: valid ranges of rhs_idx / lhs_idx (x_batches 0 = unknown)
   int group_size, table_dtype, y_dtype;
   int kc;          // K elements per pass: the tile's tables are staged pass by pass (a multiple
                    // of the box width)
@@ -241,8 +242,15 @@ qmm_gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvParams p) {
   const int64_t seg = blockIdx.y;
   int64_t x_off, wb;
   if (p.lhs_idx) {
-    x_off = static_cast<int64_t>(p.lhs_idx[seg]) * p.x_batch_stride;
-    wb = p.rhs_idx[seg];
+    // (this launch is serialized in the ordinary way, see launch_kernel: the indices are final)
+    int64_t li = p.lhs_idx[seg], ri = p.rhs_idx[seg];
+    if (ri < 0 || ri >= p.num_weights || li < 0 || (p.x_batches > 0 && li >= p.x_batches)) {
+      if (threadIdx.x == 0) atomicCAS(p.status, 0, QMM_DEVICE_BAD_INDEX);
+      if (ri < 0 || ri >= p.num_weights) ri = 0;
+      if (li < 0 || (p.x_batches > 0 && li >= p.x_batches)) li = 0;
+    }
+    x_off = li * p.x_batch_stride;
+    wb = ri;
   } else {
     x_off = seg * p.x_batch_stride;
     wb = p.w_batch_rows ? seg : 0;
@@ -756,11 +764,13 @@ int launch_kernel(const CUtensorMap& wm, const GemvParams& gp, cudaStream_t stre
   // Persistent CTAs share the machine's segments; a CTA walks tiles with a grid stride.
   const int64_t per_seg = gp.grid;
   auto kernel = qmm_gemv_kernel<QK, XT, NT, SPG>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};     // the attribute is per device
+  const int dev = current_device();
+  if (dev < 0) return QMM_ERR_DEVICE;
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudgetOne);
     if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    configured = true;
+    configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(per_seg), static_cast<unsigned>(gp.batch));
@@ -771,7 +781,10 @@ int launch_kernel(const CUtensorMap& wm, const GemvParams& gp, cudaStream_t stre
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl() ? 1 : 0;
+  // A gather reads its index arrays before `griddepcontrol.wait` (they decide which weight the
+  // first boxes come from), and those are usually the previous kernel's output: such a launch
+  // is serialized in the ordinary way.
+  cfg.numAttrs = (use_pdl() && !gp.lhs_idx) ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, wm, gp);
   if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "qmm_gemv_kernel launch: %s", cudaGetErrorString(e));
   count_launch();
@@ -810,6 +823,7 @@ bool gemv_supports(const qmm_problem& p) {
 }
 
 int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
+  if (route_override() != QMM_ROUTE_GEMV_FMMA && gemv_imma_supports(p)) return launch_gemv_imma(p, stream);
   GemvParams gp;
   gp.x = p.x; gp.scales = p.scales; gp.biases = p.biases; gp.y = p.y;
   gp.lhs_idx = p.lhs_idx; gp.rhs_idx = p.rhs_idx;
@@ -818,6 +832,8 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   gp.M = p.M; gp.K = p.K; gp.N = p.N; gp.batch = p.batch;
   gp.x_batch_stride = p.x_batch_stride; gp.y_batch_stride = p.y_batch_stride;
   gp.w_batch_rows = p.rhs_idx ? p.N : p.w_batch_stride;
+  gp.num_weights = p.num_weights > 0 ? p.num_weights : 1;
+  gp.x_batches = p.x_batches;
   gp.group_size = p.group_size; gp.table_dtype = p.table_dtype; gp.y_dtype = p.y_dtype;
   gp.tiles = static_cast<int>((p.N + kRowsPerCta - 1) / kRowsPerCta);
   const bool mx = p.mode == QMM_MODE_MXFP4;
@@ -857,11 +873,15 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   }
   for (int kc = kc_res; !done && kc >= boxk; kc -= boxk) done = configure(kc, kc, 1, 1) <= kSmemBudgetOne;
   if (!done) return fail(QMM_ERR_UNSUPPORTED, "decode kernel: no staging plan fits shared memory");
+#if QMM_GEMV_TRACING
   static long long* trace_buf = nullptr;
   static const bool trace_on = getenv("QMM_GEMV_TRACE") != nullptr;
   if (trace_on && !trace_buf) cudaMalloc(&trace_buf, sizeof(long long) * 8 * 1024);
   if (trace_on) cudaMemsetAsync(trace_buf, 0, sizeof(long long) * 8 * 1024, stream);
   gp.trace = trace_on ? trace_buf : nullptr;
+#else
+  gp.trace = nullptr;
+#endif
   int pieces = gp.xk / 8, xs = 5;
   while ((1 << xs) < pieces) ++xs;
   gp.xshift = xs;
@@ -877,6 +897,7 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   if (p.mode == QMM_MODE_MXFP4) rc = launch_xt<kMx4>(wm, gp, p.x_dtype, stream);
   else if (p.bits == 8) rc = launch_xt<kAff8>(wm, gp, p.x_dtype, stream);
   else rc = launch_xt<kAff4>(wm, gp, p.x_dtype, stream);
+#if QMM_GEMV_TRACING
   if (trace_on && rc == 0) {   // development aid: average cycles per phase over the CTAs
     cudaStreamSynchronize(stream);
     static long long host[8 * 1024];
@@ -890,6 +911,7 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
             "compute %.0f | sum-x %.0f | total %.0f | table prefetch %.0f | tiles/CTA %.2f\n",
             avg[0], avg[1], avg[2], avg[3], avg[4], avg[6], avg[5], avg[7], static_cast<double>(gp.tiles) / grid);
   }
+#endif
   return rc;
 }
 

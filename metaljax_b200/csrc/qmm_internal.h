@@ -14,6 +14,17 @@ int fail(int code, const char* fmt, ...);
 // Bumps the process-wide launch counter reported by qmm_launch_count().
 void count_launch(int n = 1);
 
+// Bumps the counter of device-memory allocations made by the library (qmm_alloc_count()).
+void count_alloc(int n = 1);
+
+// Per-device facts are cached by device ordinal: a process may drive several GPUs.
+constexpr int kMaxDevices = 64;
+// The calling thread's current device ordinal, or -1 (with the error recorded).
+int current_device();
+
+// The kernel family forced by qmm_set_route_override (a qmm_route_id; QMM_ROUTE_NONE = automatic).
+int route_override();
+
 // Checks the CUDA runtime's sticky/launch error after a launch.
 int check_launch(const char* what);
 
@@ -31,10 +42,13 @@ void set_scratch_override(const ScratchBlock* block);
 
 int launch_gemv(const qmm_problem& p, cudaStream_t stream);
 bool gemv_supports(const qmm_problem& p);
+// The single-row (M = 1) integer tensor-core decode kernel; launch_gemv hands it what it takes.
+int launch_gemv_imma(const qmm_problem& p, cudaStream_t stream);
+bool gemv_imma_supports(const qmm_problem& p);
 int launch_gemm_tc(const qmm_problem& p, cudaStream_t stream);
 bool gemm_tc_supports(const qmm_problem& p);
-// Reads (and clears) the tensor-core kernel's device status word; synchronizes the device.
-int gemm_tc_status(int* out);
+// Reads (and clears) the current device's status word.
+int read_status_word(int* out);
 
 // Encodes a 2-D TMA descriptor (a CUtensorMap, 128 bytes at `map_out`): `inner` x `outer`
 // elements of kind `elem_kind` (a qmm_elem; QMM_U8 for raw bytes), rows `row_bytes` apart,
@@ -42,8 +56,13 @@ int gemm_tc_status(int* out);
 int tensor_map_2d(void* map_out, int elem_kind, const void* base, uint64_t inner, uint64_t outer,
                   uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle128);
 
-// The process-wide device word in which kernels record a bounded wait that ran out.
+// The current device's word in which kernels record a bounded wait that ran out (one word per
+// device, allocated on first use and kept), or NULL.
 int* device_status_word();
+
+// SM clocks a bounded device-side wait may last (qmm_set_wait_limit; default about 2 s).
+long long wait_limit_clocks();
+void set_wait_limit_clocks(long long clocks);
 
 int device_sm_count();
 

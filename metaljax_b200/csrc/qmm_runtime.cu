@@ -2,6 +2,9 @@
 // entry point (no link-time dependency on libcuda), the device status word, device facts.
 #include <cuda.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "qmm_internal.h"
 
 namespace qmm {
@@ -45,25 +48,64 @@ int tensor_map_2d(void* map_out, int elem_kind, const void* base, uint64_t inner
   return QMM_OK;
 }
 
-int* device_status_word() {
-  static int* ptr = nullptr;  // one word per process, allocated on first use and kept
-  if (!ptr) {
-    if (cudaMalloc(&ptr, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(ptr, 0, sizeof(int));
+int current_device() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    fail(QMM_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    return -1;
   }
-  return ptr;
+  if (dev < 0 || dev >= kMaxDevices) {
+    fail(QMM_ERR_DEVICE, "device ordinal %d is out of range", dev);
+    return -1;
+  }
+  return dev;
+}
+
+namespace {
+std::mutex g_device_mutex;
+int* g_status_word[kMaxDevices] = {};
+int g_sm_count[kMaxDevices] = {};
+std::atomic<long long> g_wait_limit{4000000000LL};
+}  // namespace
+
+int* device_status_word() {
+  const int dev = current_device();
+  if (dev < 0) return nullptr;
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  if (!g_status_word[dev]) {
+    int* ptr = nullptr;
+    if (cudaMalloc(&ptr, sizeof(int)) != cudaSuccess) return nullptr;
+    count_alloc();
+    cudaMemset(ptr, 0, sizeof(int));
+    g_status_word[dev] = ptr;
+  }
+  return g_status_word[dev];
+}
+
+int read_status_word(int* out) {
+  int* w = device_status_word();
+  if (!w) return fail(QMM_ERR_CUDA, "no status word");
+  cudaError_t e = cudaMemcpy(out, w, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaMemcpy(status): %s", cudaGetErrorString(e));
+  if (*out) cudaMemset(w, 0, sizeof(int));
+  return QMM_OK;
 }
 
 int device_sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
+  const int dev = current_device();
+  if (dev < 0) return 148;
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  if (!g_sm_count[dev]) {
+    int n = 0;
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
+    g_sm_count[dev] = n > 0 ? n : 148;
   }
-  return n;
+  return g_sm_count[dev];
 }
+
+long long wait_limit_clocks() { return g_wait_limit.load(std::memory_order_relaxed); }
+void set_wait_limit_clocks(long long clocks) { g_wait_limit.store(clocks, std::memory_order_relaxed); }
 
 namespace {
 thread_local const ScratchBlock* t_scratch = nullptr;

@@ -33,6 +33,8 @@ struct SimtParams {
   const int32_t* group_sizes;
   int64_t M, K, N, batch;
   int64_t x_batch_stride, y_batch_stride, w_batch_rows;
+  int64_t num_weights, x_batches;   // gather: valid ranges of rhs_idx / lhs_idx (x_batches 0 = unknown)
+  int* status;
   int group_size, table_dtype, y_dtype;
 };
 
@@ -135,9 +137,15 @@ qmm_simt_kernel(const SimtParams p) {
       x_off = lo * p.K; y_off = lo * p.N; wb = seg;
     } else if (p.lhs_idx) {
       m_count = p.M;
-      x_off = static_cast<int64_t>(p.lhs_idx[seg]) * p.x_batch_stride;
+      int64_t li = p.lhs_idx[seg], ri = p.rhs_idx[seg];
+      if (ri < 0 || ri >= p.num_weights || li < 0 || (p.x_batches > 0 && li >= p.x_batches)) {
+        if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, QMM_DEVICE_BAD_INDEX);
+        if (ri < 0 || ri >= p.num_weights) ri = 0;
+        if (li < 0 || (p.x_batches > 0 && li >= p.x_batches)) li = 0;
+      }
+      x_off = li * p.x_batch_stride;
       y_off = seg * p.y_batch_stride;
-      wb = p.rhs_idx[seg];
+      wb = ri;
     } else {
       m_count = p.M;
       x_off = seg * p.x_batch_stride;
@@ -251,6 +259,9 @@ int launch_simt(const qmm_problem& p, cudaStream_t stream) {
   sp.M = p.M; sp.K = p.K; sp.N = p.N; sp.batch = p.batch;
   sp.x_batch_stride = p.x_batch_stride; sp.y_batch_stride = p.y_batch_stride;
   sp.w_batch_rows = (p.group_sizes || p.rhs_idx) ? p.N : p.w_batch_stride;
+  sp.num_weights = p.num_weights > 0 ? p.num_weights : 1;
+  sp.x_batches = p.x_batches;
+  sp.status = p.lhs_idx ? device_status_word() : nullptr;
   sp.group_size = p.group_size; sp.table_dtype = p.table_dtype; sp.y_dtype = p.y_dtype;
   if (p.M == 0 || p.N == 0 || p.batch == 0) return QMM_OK;
 

@@ -436,18 +436,23 @@ def test_config1_decode_gemv_full_size():
     _gate(to_numpy(y).astype(np.float32), exact, "bf16", lit)
 
 
-@pytest.mark.parametrize("bits,gs,n,k", [(4, 64, 14336, 4096), (8, 128, 4096, 14336)])
+@pytest.mark.parametrize("bits,gs,n,k", [(4, 64, 14336, 4096), (4, 64, 4096, 14336), (8, 128, 14336, 4096),
+                                         (8, 128, 4096, 14336)])
 def test_config2_prefill_full_size_sampled_rows_and_linearity(bits, gs, n, k):
-    """M=2048 at Llama-3-8B MLP shapes: sampled token rows against the oracle, agreement of
-    the tensor-core and SIMT routes on a row block, and linearity y(2x) == 2 y(x) bit for bit
-    (a power-of-two scaling commutes with every rounding)."""
+    """M=2048 at Llama-3-8B MLP shapes (up/gate and down, 4- and 8-bit): token rows sampled from
+    every 256-row token tile (first, last and interior rows of each: 72 rows) against the
+    oracle, agreement of the tensor-core and SIMT routes on a row block, and linearity
+    y(2x) == 2 y(x) bit for bit (a power-of-two scaling commutes with every rounding)."""
     rng = np.random.default_rng(2)
     m = 2048
-    _, w, s, b = affine_case(rng, n, k, gs, bits, "bf16", scale_lo=0.002)
+    w = rng.integers(0, 1 << 32, size=(n, k * bits // 32), dtype=np.uint64).astype(np.uint32)   # uniform codes
+    s = rng.uniform(0.002, 0.02, size=(n, k // gs)).astype(BF16)
+    b = (-float(1 << (bits - 1)) * s.astype(np.float32)).astype(BF16)
     x = activations(rng, (m, k))
     tx, tw, ts, tb = (to_torch(a, DEV) for a in (x, w, s, b))
     y = qmm.quantized_matmul(tx, tw, ts, tb, group_size=gs, bits=bits)
-    rows = np.array([0, 1, 127, 128, 255, 256, 1000, 2047])
+    rows = np.unique(np.concatenate([t0 + np.array([0, 1, 31, 32, 100, 127, 128, 200, 255]) for t0 in range(0, m, 256)]))
+    assert len(rows) >= 64
     exact = clib.qmm(x[rows], w, s, b, len(rows), k, n, gs, bits, out_f32=True).astype(np.float64)
     _gate(to_numpy(y[torch.from_numpy(rows).to(DEV)]).astype(np.float32), exact, "bf16")
     with _lib.force_route("simt"):
@@ -469,3 +474,63 @@ def test_config3_mxfp4_full_size(m):
     rows = np.unique(np.array([0, m // 2, m - 1]))
     exact = clib.qmm(x[rows], w, sb, None, len(rows), k, n, 32, 4, "mxfp4", out_f32=True).astype(np.float64)
     _gate(to_numpy(y[torch.from_numpy(rows).to(DEV)]).astype(np.float32), exact, "bf16")
+
+
+# ---- config 5 at full size: the grouped ragged kernel and the expert block ------------------
+
+
+def _boundary_rows(offsets, total):
+    """First and last row of every expert, and the rows either side of every boundary."""
+    rows = set()
+    for lo, hi in zip(offsets[:-1], offsets[1:]):
+        if hi > lo:
+            rows.update({lo, min(lo + 1, hi - 1), (lo + hi) // 2, max(hi - 2, lo), hi - 1})
+    return np.array(sorted(r for r in rows if 0 <= r < total))
+
+
+def test_config5_moe_full_size_ragged_rows_and_expert_block():
+    """Mixtral-8x7B expert shape: 4096 tokens, top-2 of 8, d 4096, ffn 14336, int4 group 64.
+    The grouped ragged product at that size (about 1024 rows per expert, 256-row token tiles
+    straddling expert boundaries) is checked on the rows at and around every expert boundary,
+    the whole expert block on sampled tokens, both against the oracle."""
+    rng = np.random.default_rng(5)
+    t, e, kk, d, f, gs = 4096, 8, 2, 4096, 14336, 64
+    x = activations(rng, (t, d))
+    logits = rng.standard_normal((t, e)).astype(np.float32)
+    idx, wts = O.topk_router(logits, kk)
+
+    def pack(n, k):
+        w = rng.integers(0, 1 << 32, size=(e, n, k // 8), dtype=np.uint64).astype(np.uint32)
+        s = rng.uniform(0.002, 0.01, size=(e, n, k // gs)).astype(BF16)
+        return w, s, (-8.0 * s.astype(np.float32)).astype(BF16)
+
+    w1, w3, w2 = pack(f, d), pack(f, d), pack(d, f)
+    dev = [tuple(to_torch(a, DEV) for a in p) for p in (w1, w3, w2)]
+    tx, tidx = to_torch(x, DEV), torch.from_numpy(idx).to(DEV)
+    # (1) the ragged product of the gate projection on the sorted pairs
+    order, tok, gsz = moe.sort_pairs(tidx, e)
+    xs = tx.index_select(0, tok)
+    gate = moe.ragged_dot(xs, *dev[0], gsz, group_size=gs, bits=4)
+    sizes = to_numpy(gsz)
+    assert int(sizes.sum()) == t * kk
+    offs = np.concatenate([[0], np.cumsum(sizes)])
+    rows = _boundary_rows(offs, t * kk)
+    xs_np = to_numpy(xs)
+    expert_of = np.searchsorted(offs, rows, side="right") - 1
+    want = np.stack([clib.qmm(xs_np[r:r + 1], w1[0][ex], w1[1][ex], w1[2][ex], 1, d, f, gs, 4, out_f32=True)[0]
+                     for r, ex in zip(rows, expert_of)]).astype(np.float64)
+    _gate(to_numpy(gate[torch.from_numpy(rows).to(DEV)]).astype(np.float32), want, "bf16")
+    # (2) the expert block on sampled tokens
+    y = moe.moe_experts(tx, tidx, torch.from_numpy(wts).to(DEV), dev[0], dev[1], dev[2], group_size=gs, bits=4)
+    toks = np.array([0, 1, 255, 256, 1023, 2048, 3000, 4095])
+    out = np.zeros((len(toks), d))
+    for i, tk in enumerate(toks):
+        for j in range(kk):
+            ex = idx[tk, j]
+            g_ = clib.qmm(x[tk:tk + 1], w1[0][ex], w1[1][ex], w1[2][ex], 1, d, f, gs, 4, out_f32=True)[0].astype(np.float64)
+            u_ = clib.qmm(x[tk:tk + 1], w3[0][ex], w3[1][ex], w3[2][ex], 1, d, f, gs, 4, out_f32=True)[0].astype(np.float64)
+            act = (g_ / (1 + np.exp(-g_)) * u_).astype(np.float32)[None, :]
+            dn = clib.qmm(act, w2[0][ex], w2[1][ex], w2[2][ex], 1, f, d, gs, 4, out_f32=True)[0].astype(np.float64)
+            out[i] += wts[tk, j] * dn
+    got = to_numpy(y[torch.from_numpy(toks).to(DEV)]).astype(np.float32)
+    assert O.rel_err(got, out) <= 2e-2                     # two bf16 hand-offs inside the block

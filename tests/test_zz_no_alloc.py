@@ -28,18 +28,35 @@ def _call(fn, x, w, s, b, y):
 
 
 def test_static_entry_matches_the_ordinary_one_twice():
+    """Same bits as the ordinary entry point, within the parity gate of the oracle, and -- the
+    property it exists for -- no device-memory allocation by the library during the call, while
+    the ordinary entry point allocates the split product's scratch every time."""
+    import numpy as np
+    from helpers import to_numpy
     from metaljax_b200 import _lib
+    from oracle import clib
+    from oracle import qmm_oracle as O
     lib = _lib.lib()
+    assert _lib.poll_status() == 0          # (the device's status word exists from here on)
     for call in range(2):                                         # two calls in a row
         for m, k, n in ((64, 4096, 1024), (40, 2048, 512), (300, 1024, 256)):
             x, w, s, b = _problem(m, k, n, seed=10 * call + m)
             want = torch.empty((m, n), device=DEV, dtype=torch.bfloat16)
             got = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+            split = m <= 64                                       # these two shapes share K among CTAs
             with _lib.force_route("gemm_tc"):
+                a0 = _lib.alloc_count()
                 _lib.check(_call(lib.qmm_quantized_matmul, x, w, s, b, want))
+                assert _lib.alloc_count() - a0 == (1 if split else 0), (m, k, n)
+            a0 = _lib.alloc_count()
             _lib.check(_call(lib.qmm_quantized_matmul_static, x, w, s, b, got))
+            assert _lib.alloc_count() == a0, "the static entry point allocated"
             torch.cuda.synchronize()
             assert torch.equal(got, want), (call, m, k, n)
+            exact = clib.qmm(to_numpy(x), to_numpy(w), to_numpy(s), to_numpy(b), m, k, n, 64, 4,
+                             out_f32=True).astype(np.float64)
+            assert O.rel_err(to_numpy(got).astype(np.float32), exact) <= 1e-2
+    assert _lib.poll_status_static() == 0                          # no bounded wait ran out
 
 
 def test_static_entry_refuses_what_does_not_fit():
