@@ -1,22 +1,24 @@
-"""Benchmark of the fused quantized matmul on B200.
+"""Benchmark of the fused quantized matmul and its decode-step caller on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 
-One JSON line on stdout (rank 0). A step is one pass of the hot path over one batch of
-synthetic input: by default the prefill configuration, an int4 group-64 quantized matmul of
-x[2048, 4096] (bf16, N(0,1)) against W[14336, 4096] (codes uniform 0..15, scales
-U(0.002, 0.02), bias = -8*scale), bf16 output, float32 accumulation. `value` is the
-whole-job TFLOP/s with inputs resident in HBM; `e2e` is the same metric through the public
-call with pinned host buffers copied in and out inside the timed region; `roofline` compares
-the kernel with the measured bf16 tensor peak; `cpu_baseline` is the CPU restatement of the
-reference's fused dequantize-and-dot loop timed on the host cores on a bounded sample; `also`
-carries the decode (M=1) configuration against the measured HBM bandwidth and the tokens/s of
-whole Llama-3-8B-shaped decode steps (batch 1, 16, 64; weights sharded on N over the ranks).
+One JSON line on stdout (rank 0). The default workload is the path that shards over GPUs: one
+decode step of a Llama-3-8B-shaped model (32 layers, d 4096, 32/8 heads, ffn 14336, vocabulary
+128256, every linear an int4 group-64 quantized matmul, bf16 KV cache of 2048 positions) at
+batch 64, the linears sharded on their output rows over the N ranks (q/k/v by head, so the KV
+cache and attention stay local) with the slices exchanged over NVLink. `value` is tokens/s of
+the whole job with everything resident in HBM, the step replayed from one CUDA graph; `e2e` is
+the same through the public call with token ids copied in from pinned host memory and the next
+ids copied back inside the timed region; `roofline` is this rank's packed weights + tables + KV
+cache per step against the measured HBM bandwidth; `cpu_baseline` is the CPU restatement of the
+reference's fused dequantize-and-dot loop timed on the host cores on a bounded sample.
 
-With N > 1 (one process per GPU under torch.distributed.run) every rank runs the same
-workload on its own token batch against replicated weights -- the path shards over
-independent rows of x with no data-path collective -- so scaling is weak and `value` is the
-sum over ranks divided by the slowest rank's time.
+`also` carries, at N = 1, every other configuration of the path -- the single quantized matmul
+at M = 1 (GB/s of weight bytes) and M = 2048 (TFLOP/s) in int4 / int8 at both Llama MLP shapes,
+MXFP4 at M = 1 / 512 / 4096, the Mixtral-shaped expert block, the decode step at batch 1 and 16
+-- each with its own roofline; at N > 1 the decode step at the other batches, the
+expert-parallel expert block (token all-to-all), and `parity`: the sharded decode step and the
+expert-parallel block checked at small shapes against their references before anything is timed.
 """
 
 from __future__ import annotations
@@ -40,27 +42,25 @@ WORKLOADS = {
     "prefill_int4_g64_m2048_14336x4096": (2048, 4096, 14336, 64, 4, "affine"),
     "prefill_int4_g64_m2048_4096x14336": (2048, 14336, 4096, 64, 4, "affine"),
     "prefill_int8_g128_m2048_14336x4096": (2048, 4096, 14336, 128, 8, "affine"),
+    "prefill_int8_g128_m2048_4096x14336": (2048, 14336, 4096, 128, 8, "affine"),
+    "prefill_mxfp4_m512_5760x2880": (512, 2880, 5760, 32, 4, "mxfp4"),
     "prefill_mxfp4_m4096_5760x2880": (4096, 2880, 5760, 32, 4, "mxfp4"),
     "decode_int4_g64_m1_4096x4096": (1, 4096, 4096, 64, 4, "affine"),
     "decode_mxfp4_m1_5760x2880": (1, 2880, 5760, 32, 4, "mxfp4"),
 }
-DEFAULT = "prefill_int4_g64_m2048_14336x4096"
-DECODE = "decode_int4_g64_m1_4096x4096"
 L2_BYTES = 126 * 1024 * 1024
-# Whole decode steps of a Llama-3-8B-shaped model (32 layers, d 4096, 32/8 heads, ffn 14336,
-# vocabulary 128256, int4 group-64 linears, bf16 KV cache of 2048 positions): name -> batch.
-# The weights are sharded on N over the ranks, so these scale strongly.
+# Whole decode steps of the Llama-3-8B-shaped model: name -> batch. The weights are sharded on N
+# over the ranks, so these scale strongly.
 DECODE_STEPS = {"decode_llama3_8b_b1": 1, "decode_llama3_8b_b16": 16, "decode_llama3_8b_b64": 64}
+DEFAULT = "decode_llama3_8b_b64"
 # The expert block of a Mixtral-8x7B-shaped mixture-of-experts layer: 4096 tokens, top-2 of 8
 # experts, d 4096, ffn 14336, int4 group-64 expert weights; three grouped ragged products over
-# 8192 (token, expert) pairs plus the routed weighted sum.
+# 8192 (token, expert) pairs plus the routed weighted sum. Over N ranks: experts split, tokens
+# split, pairs exchanged by all-to-all.
 MOE_BLOCKS = {"moe_mixtral_t4096": (4096, 2, 8, 4096, 14336)}
-# DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures
-# summarized under profiles/ (qmm_gemm_tc_int4_g64_m2048.md, qmm_gemv_int4_g64_m1_4096x4096.md).
-MEASURED_TRAFFIC = {
-    "prefill_int4_g64_m2048_14336x4096": 56048384 + 27941888,    # read + write; part of y is still in L2
-    "decode_int4_g64_m1_4096x4096": 9480000,                      # every weight byte read once
-}
+ALSO_AT_ONE = ["decode_int4_g64_m1_4096x4096", "prefill_int4_g64_m2048_14336x4096", "prefill_int4_g64_m2048_4096x14336",
+               "prefill_int8_g128_m2048_14336x4096", "prefill_int8_g128_m2048_4096x14336", "decode_mxfp4_m1_5760x2880",
+               "prefill_mxfp4_m512_5760x2880", "prefill_mxfp4_m4096_5760x2880", "moe_mixtral_t4096"]
 
 
 def peaks():
@@ -74,6 +74,17 @@ def peaks():
             "source": "fallback"}
 
 
+def measured_traffic(name):
+    """DRAM bytes (read + write) of one launch of the workload's dominant kernel, from the ncu
+    capture recorded next to the profile summaries; None when no capture has been recorded."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        entry = json.load(f).get(name)
+    return None if entry is None else entry["bytes_per_launch"]
+
+
 def work_of(name):
     """Algorithmic flops and bytes of one call (weights + tables + activations + output)."""
     m, k, n, gs, bits, mode = WORKLOADS[name]
@@ -82,6 +93,32 @@ def work_of(name):
     weight_bytes = n * k * bits // 8 + tables
     total_bytes = weight_bytes + m * k * 2 + m * n * 2
     return flops, weight_bytes, total_bytes
+
+
+def config_of(name, world):
+    """What the workload is; both arms print exactly this."""
+    if name in DECODE_STEPS:
+        return {"workload": name, "batch": DECODE_STEPS[name], "layers": 32, "d_model": 4096, "heads": 32, "kv_heads": 8,
+                "ffn": 14336, "vocab": 128256, "context": 2048, "group_size": 64, "bits": 4,
+                "weights": "N(0, 0.02) quantized per group of 64: scale = (max - min)/15, zero = round(-min/scale)",
+                "parallelism": f"tp{world}: every linear sharded on its output rows, slices exchanged after it",
+                "l2": "one step streams this rank's packed weights (4.2 GB / N) and KV cache: far more than L2"}
+    if name in MOE_BLOCKS:
+        t, k, e, d, f = MOE_BLOCKS[name]
+        return {"workload": name, "tokens": t, "top_k": k, "experts": e, "d_model": d, "ffn": f, "group_size": 64, "bits": 4,
+                "parallelism": f"ep{world}: experts and tokens split over the ranks, pairs exchanged by all-to-all"
+                if world > 1 else "ep1",
+                "l2": f"{3 * e * d * f // 2 >> 20} MiB of expert weights per step (> L2)"}
+    m, k, n, gs, bits, mode = WORKLOADS[name]
+    _, _, total = work_of(name)
+    sets = rotation_sets(total)
+    return {"workload": name, "M": m, "K": k, "N": n, "group_size": gs, "bits": bits, "mode": mode,
+            "parallelism": f"dp{world}: rows of x sharded, weights replicated, no collective",
+            "l2": f"inputs rotate through {sets} sets ({sets * total >> 20} MiB > 2x L2)"}
+
+
+def rotation_sets(total_bytes):
+    return min(64, max(2, int(2 * L2_BYTES // total_bytes) + 1))
 
 
 def make_inputs(name, seed, torch, device, sets):
@@ -184,11 +221,20 @@ def time_device(fn, steps, warmup, torch, dist=None):
     return start.elapsed_time(stop)
 
 
-def cpu_baseline(name, budget_rows=None):
+def max_over_ranks(values, torch, dist, device):
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+# ---- the CPU legs ----------------------------------------------------------------------------
+
+
+def cpu_qmm_sample(name, budget_rows=None):
     """The CPU restatement of the fused dequantize-and-dot, all host threads, on a bounded
     sample: the first `rows` rows of x against the whole weight."""
     from oracle import clib
-    from oracle import qmm_oracle as O
     import ml_dtypes
     m, k, n, gs, bits, mode = WORKLOADS[name]
     clib.use_all_cores()
@@ -210,180 +256,23 @@ def cpu_baseline(name, budget_rows=None):
         dt = time.perf_counter() - t0
         if dt > 3.0 or reps >= 200:
             break
-    per_call = dt / reps
-    return {"seconds_per_sample": per_call, "rows": rows, "cores": clib.num_threads(),
+    return {"seconds_per_sample": dt / reps, "rows": rows, "cores": clib.num_threads(),
             "flops": 2.0 * rows * k * n, "reps": reps}
 
 
-def run_reference(args, rank):
-    """The reference arm: the reference's CPU path for this op (its fused dequantize-and-dot,
-    restated in oracle/qmm_oracle.c because the reference itself needs jax + mlx, which are
-    not installed) on the host cores, same workload and metric, bounded sample per step."""
-    if rank != 0:
-        return
-    name = args.workload
+def cpu_baseline_of(name):
+    """`cpu_baseline` object of one workload (value in the workload's own unit)."""
     if name in DECODE_STEPS:
-        vals = [decode_step_cpu(DECODE_STEPS[name]) for _ in range(args.warmup + args.steps)][args.warmup:]
-        value = statistics.mean(v["value"] for v in vals)
-        cb = dict(vals[-1], value=value)
-        print(json.dumps({
-            "impl": "reference", "metric": "decode_tok_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": DECODE_STEPS[name] / value * 1e3,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": name, "batch": DECODE_STEPS[name]}, "cpu_baseline": cb,
-            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}), flush=True)
-        return
-    m, k, n, gs, bits, mode = WORKLOADS[name]
-    flops, weight_bytes, _ = work_of(name)
-    res = None
-    per = []
-    for i in range(args.warmup + args.steps):
-        res = cpu_baseline(name)
-        if i >= args.warmup:
-            per.append(res["seconds_per_sample"])
-    sec = statistics.mean(per)
-    if m > 1:
-        value, unit = res["flops"] / sec / 1e12, "TFLOP/s"
-    else:
-        value, unit = weight_bytes / sec / 1e9, "GB/s"
-    sample = f"first {res['rows']} of {m} rows of x against the whole weight, {res['reps']} calls per step"
-    line = {
-        "impl": "reference", "metric": metric_name(name), "value": value, "unit": unit,
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": sec * 1e3 * (m / res["rows"]), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": name, "M": m, "K": k, "N": n, "group_size": gs, "bits": bits,
-                   "mode": mode},
-        "cpu_baseline": {"value": value, "unit": unit, "cores": res["cores"], "kind": "port",
-                         "sample": sample},
-        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
-    print(json.dumps(line), flush=True)
-
-
-def metric_name(name):
+        return decode_step_cpu(DECODE_STEPS[name])
+    if name in MOE_BLOCKS:
+        return moe_block_cpu(name)
     m = WORKLOADS[name][0]
-    return "qmm_tflops_m%d" % m if m > 1 else "qmm_weight_gbs_m1"
-
-
-def measure(name, args, torch, qmm, _lib, dist, device):
-    """Device-resident and end-to-end timing of one workload on this rank."""
-    m, k, n, gs, bits, mode = WORKLOADS[name]
-    flops, weight_bytes, total_bytes = work_of(name)
-    per_set = total_bytes
-    sets = max(2, int(2 * L2_BYTES // per_set) + 1)                   # rotate through > 2x L2
-    sets = min(sets, 64)
-    data = make_inputs(name, 1234 + int(os.environ.get("RANK", "0")), torch, device, sets)
-    kw = dict(group_size=gs, bits=bits, mode=mode)
-
-    def step(i):
-        x, w, s, b, y = data[i % sets]
-        qmm.quantized_matmul(x, w, s, b, out=y, **kw)
-
-    steps = args.steps if m > 1 else args.steps * 50
-    warm = max(args.warmup, 3)
-    n0 = _lib.launch_count()
-    ms = time_device(step, steps, warm, torch, dist)
-    launches = _lib.launch_count() - n0 - warm
-    if m > 1:
-        # The same K steps replayed from one CUDA graph: with several ranks on one host the
-        # per-call Python time of eight processes can exceed a 0.26 ms step and starve the GPU,
-        # which measures the host, not the path. The smaller of the two times is reported.
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(steps):
-                    step(warm + i)
-        torch.cuda.current_stream().wait_stream(side)
-        gms = time_device(lambda i: graph.replay(), 1, 3, torch, dist)
-        timed = "stream launches"
-        if gms < ms:
-            ms, timed = gms, "cuda graph replay of the K steps"
-    else:
-        timed = "stream launches"
-    res = {"ms_total": ms, "steps": steps, "ms_per_step": ms / steps, "launches": launches, "timed": timed,
-           "sets": sets, "flops": flops, "weight_bytes": weight_bytes, "total_bytes": total_bytes}
-
-    # decode calls are launch-latency sized: also time them replayed from one CUDA graph,
-    # every node on a different weight set
-    if m == 1:
-        gsteps = sets
-        stream = torch.cuda.Stream()
-        with torch.cuda.stream(stream):
-            for i in range(3):
-                step(i)
-            stream.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                for i in range(gsteps):
-                    step(i)
-        torch.cuda.synchronize()
-        reps = max(5, steps // gsteps)
-        gms = time_device(lambda i: graph.replay(), reps, 3, torch, dist)
-        res["graph_ms_per_step"] = gms / (reps * gsteps)
-
-    # end to end: pinned host x in, y out, through the public call
-    x, w, s, b, y = data[0]
-    hx = [torch.empty_like(x, device="cpu").pin_memory().copy_(data[i % sets][0]) for i in range(2)]
-    hy = torch.empty_like(y, device="cpu").pin_memory()
-    dx = torch.empty_like(x)
-
-    def e2e_step(i):
-        dx.copy_(hx[i % 2], non_blocking=True)
-        xx, ww, ss, bb, yy = data[i % sets]
-        qmm.quantized_matmul(dx, ww, ss, bb, out=yy, **kw)
-        hy.copy_(yy, non_blocking=True)
-        torch.cuda.current_stream().synchronize()                     # the caller reads y
-
-    esteps = max(3, min(steps, 20))
-    ems = time_device(e2e_step, esteps, 3, torch, dist)
-    res["e2e_ms_per_step"] = ems / esteps
-    res["h2d"] = x.numel() * x.element_size()
-    res["d2h"] = y.numel() * y.element_size()
-    return res
-
-
-def decode_step_bytes(batch, world):
-    """Algorithmic HBM bytes one rank touches per decode step: its shard of the packed weights
-    and tables, and its heads' KV cache of `batch` sequences."""
-    from metaljax_b200 import llama
-    sh = llama.LLAMA3_8B
-    kv = 2 * sh.layers * batch * sh.kv_heads * sh.ctx * sh.head_dim * 2
-    return sh.weight_bytes() / world, kv / world
-
-
-def measure_decode_step(batch, steps, warmup, torch, dist, device):
-    """One Llama-3-8B-shaped decode step per timed step, replayed from a CUDA graph: device
-    time (tokens resident) and end to end (token ids from pinned host memory, next ids back)."""
-    from metaljax_b200 import _lib, llama
-    n0 = _lib.launch_count()
-    step = llama.DecodeStep(llama.LLAMA3_8B, batch, device, seed=7)
-    n1 = _lib.launch_count()
-    step.capture(warmup=max(warmup, 3))
-    per_step = (_lib.launch_count() - n1) // (max(warmup, 3) + 1)
-    del n0
-    ms = time_device(lambda i: step.replay(), steps, 3, torch, dist)
-    host_in = torch.zeros((batch,), dtype=torch.int64).pin_memory()
-    host_out = torch.zeros((batch,), dtype=torch.int64).pin_memory()
-
-    def e2e_step(i):
-        host_in.fill_(i % 1000)
-        step.tokens.copy_(host_in, non_blocking=True)
-        step.replay()
-        host_out.copy_(step.next_tokens, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    esteps = max(3, min(steps, 20))
-    ems = time_device(e2e_step, esteps, 3, torch, dist)
-    res = {"ms_per_step": ms / steps, "e2e_ms_per_step": ems / esteps, "launches_per_step": per_step,
-           "h2d": batch * 8, "d2h": batch * 8, "steps": steps, "gather": step.gather_mode}
-    del step
-    torch.cuda.empty_cache()
-    return res
+    _, weight_bytes, _ = work_of(name)
+    cb = cpu_qmm_sample(name)
+    val = cb["flops"] / cb["seconds_per_sample"] / 1e12 if m > 1 else weight_bytes / cb["seconds_per_sample"] / 1e9
+    return {"value": val, "unit": "TFLOP/s" if m > 1 else "GB/s", "cores": cb["cores"], "kind": "port",
+            "sample": f"first {cb['rows']} of {m} rows of x against the whole weight, "
+                      f"{cb['reps']} calls in {cb['seconds_per_sample'] * cb['reps']:.1f} s"}
 
 
 def decode_step_cpu(batch):
@@ -414,26 +303,221 @@ def decode_step_cpu(batch):
                       f"({sec:.2f} s), extrapolated to the step by parameter count; attention and glue not counted"}
 
 
-def decode_step_line(name, args, torch, dist, device, world, pk, clk_fn=None):
+def moe_block_cpu(name):
+    """The CPU port on 16 of the block's 8192 pair rows through one expert's three projections."""
+    from oracle import clib
+    import ml_dtypes
+    t, k, e, d, f = MOE_BLOCKS[name]
+    clib.use_all_cores()
+    rng = np.random.default_rng(0)
+    rows, sec = 16, 0.0
+    for n, kk in ((f, d), (f, d), (d, f)):
+        w = rng.integers(0, 1 << 32, size=(n, kk // 8), dtype=np.uint64).astype(np.uint32)
+        s = rng.uniform(0.002, 0.02, size=(n, kk // 64)).astype(ml_dtypes.bfloat16)
+        b = (-8.0 * s.astype(np.float32)).astype(ml_dtypes.bfloat16)
+        x = rng.standard_normal((rows, kk)).astype(np.float32).astype(ml_dtypes.bfloat16)
+        clib.qmm(x[:1], w, s, b, 1, kk, n, 64, 4, "affine")
+        t0 = time.perf_counter()
+        clib.qmm(x, w, s, b, rows, kk, n, 64, 4, "affine")
+        sec += time.perf_counter() - t0
+    flops = 2.0 * rows * 3 * d * f
+    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": clib.num_threads(), "kind": "port",
+            "sample": f"{rows} of {t * k} pair rows through one expert's three projections ({sec:.2f} s)"}
+
+
+def metric_of(name):
+    if name in DECODE_STEPS:
+        return "decode_tok_s", "tok/s"
+    if name in MOE_BLOCKS:
+        return "moe_block_tflops", "TFLOP/s"
+    m = WORKLOADS[name][0]
+    return ("qmm_tflops_m%d" % m, "TFLOP/s") if m > 1 else ("qmm_weight_gbs_m1", "GB/s")
+
+
+def run_reference(args, rank):
+    """The reference arm: the reference's CPU path for this workload (its fused
+    dequantize-and-dot, restated in oracle/qmm_oracle.c because the reference itself needs jax +
+    mlx, which are not installed) on the host cores, same workload and metric, a bounded sample
+    per step."""
+    if rank != 0:
+        return
+    name = args.workload
+    metric, unit = metric_of(name)
+    vals = []
+    cb = None
+    for i in range(args.warmup + args.steps):
+        cb = cpu_baseline_of(name)
+        if i >= args.warmup:
+            vals.append(cb["value"])
+    value = statistics.mean(vals)
+    if name in DECODE_STEPS:
+        ms = DECODE_STEPS[name] / value * 1e3
+    elif name in MOE_BLOCKS:
+        t, k, e, d, f = MOE_BLOCKS[name]
+        ms = 2.0 * t * k * 3 * d * f / (value * 1e12) * 1e3
+    else:
+        flops, wb, _ = work_of(name)
+        ms = (flops / (value * 1e12) if WORKLOADS[name][0] > 1 else wb / (value * 1e9)) * 1e3
+    print(json.dumps({
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong" if name in DECODE_STEPS or name in MOE_BLOCKS else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": config_of(name, args.gpus),
+        "cpu_baseline": dict(cb, value=value),
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}), flush=True)
+
+
+# ---- the single quantized matmul ---------------------------------------------------------------
+
+
+def measure_qmm(name, args, torch, qmm, _lib, dist, device):
+    """Device-resident and end-to-end timing of one quantized-matmul workload on this rank."""
+    m, k, n, gs, bits, mode = WORKLOADS[name]
+    flops, weight_bytes, total_bytes = work_of(name)
+    sets = rotation_sets(total_bytes)
+    data = make_inputs(name, 1234 + int(os.environ.get("RANK", "0")), torch, device, sets)
+    kw = dict(group_size=gs, bits=bits, mode=mode)
+
+    def step(i):
+        x, w, s, b, y = data[i % sets]
+        qmm.quantized_matmul(x, w, s, b, out=y, **kw)
+
+    steps = args.steps if m > 1 else args.steps * 50
+    warm = max(args.warmup, 3)
+    n0 = _lib.launch_count()
+    ms = time_device(step, steps, warm, torch, dist)
+    launches = _lib.launch_count() - n0 - warm
+    # The same calls replayed from one CUDA graph (every node on a different weight set): a
+    # decode call is launch-latency sized, and with several ranks on one host the per-call
+    # Python time of eight processes can exceed a 0.26 ms step. The smaller time is reported.
+    gsteps = steps if m > 1 else sets
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(gsteps):
+                step(warm + i)
+    torch.cuda.current_stream().wait_stream(side)
+    reps = 1 if m > 1 else max(5, steps // gsteps)
+    gms = time_device(lambda i: graph.replay(), reps, 3, torch, dist) / (reps * gsteps)
+    timed = "stream launches"
+    ms_step = ms / steps
+    if gms < ms_step:
+        ms_step, timed = gms, "cuda graph replay"
+    res = {"steps": steps, "ms_per_step": ms_step, "launches": launches, "timed": timed, "sets": sets,
+           "flops": flops, "weight_bytes": weight_bytes, "total_bytes": total_bytes}
+    del graph
+
+    # end to end: pinned host x in, y out, through the public call
+    x, w, s, b, y = data[0]
+    hx = [torch.empty_like(x, device="cpu").pin_memory().copy_(data[i % sets][0]) for i in range(2)]
+    hy = torch.empty_like(y, device="cpu").pin_memory()
+    dx = torch.empty_like(x)
+
+    def e2e_step(i):
+        dx.copy_(hx[i % 2], non_blocking=True)
+        xx, ww, ss, bb, yy = data[i % sets]
+        qmm.quantized_matmul(dx, ww, ss, bb, out=yy, **kw)
+        hy.copy_(yy, non_blocking=True)
+        torch.cuda.current_stream().synchronize()                     # the caller reads y
+
+    esteps = max(3, min(steps, 20))
+    ems = time_device(e2e_step, esteps, 3, torch, dist)
+    res["e2e_ms_per_step"] = ems / esteps
+    res["h2d"] = x.numel() * x.element_size()
+    res["d2h"] = y.numel() * y.element_size()
+    return res
+
+
+def qmm_line(name, args, torch, dist, device, world, pk):
+    from metaljax_b200 import _lib, qmm
+    m, k, n, gs, bits, mode = WORKLOADS[name]
+    res = measure_qmm(name, args, torch, qmm, _lib, dist, device)
+    ms_step, e2e_ms = max_over_ranks([res["ms_per_step"], res["e2e_ms_per_step"]], torch, dist, device)
+    flops, weight_bytes, total_bytes = res["flops"], res["weight_bytes"], res["total_bytes"]
+    metric, unit = metric_of(name)
+    if m > 1:
+        value = world * flops / (ms_step * 1e-3) / 1e12
+        e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
+        achieved = flops / (res["ms_per_step"] * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": unit,
+                "frac": achieved / pk["bf16_tflops"], "traffic": measured_traffic(name),
+                "peak_source": pk["source"], "frac_of_nominal_2250": achieved / 2250.0}
+    else:
+        value = world * weight_bytes / (ms_step * 1e-3) / 1e9
+        e2e_value = world * weight_bytes / (e2e_ms * 1e-3) / 1e9
+        achieved = total_bytes / (res["ms_per_step"] * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": unit,
+                "frac": achieved / pk["hbm_gbs"], "traffic": measured_traffic(name),
+                "peak_source": pk["source"], "frac_of_nominal_8000": achieved / 8000.0,
+                "us_per_call": res["ms_per_step"] * 1e3}
+    return {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world,
+        "steps": res["steps"], "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_of(name, world),
+        "how": {"route": qmm.route(m, k, n, gs, bits, mode), "timed": res["timed"]},
+        "roofline": roof,
+        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": res["h2d"],
+                "d2h_bytes_per_step": res["d2h"], "ms_per_step": e2e_ms},
+        "gpu_launches": int(res["launches"]),
+    }
+
+
+# ---- the decode step ------------------------------------------------------------------------------
+
+
+def decode_step_bytes(batch, world):
+    """Algorithmic HBM bytes one rank touches per decode step: its shard of the packed weights
+    and tables, and its heads' KV cache of `batch` sequences."""
+    from metaljax_b200 import llama
+    sh = llama.LLAMA3_8B
+    kv = 2 * sh.layers * batch * sh.kv_heads * sh.ctx * sh.head_dim * 2
+    return sh.weight_bytes() / world, kv / world
+
+
+def measure_decode_step(batch, steps, warmup, torch, dist, device):
+    """One Llama-3-8B-shaped decode step per timed step, replayed from a CUDA graph: device
+    time (tokens resident) and end to end (token ids from pinned host memory, next ids back)."""
+    from metaljax_b200 import _lib, llama
+    step = llama.DecodeStep(llama.LLAMA3_8B, batch, device, seed=7, weights="normal")
+    n1 = _lib.launch_count()
+    step.capture(warmup=max(warmup, 3))
+    per_step = (_lib.launch_count() - n1) // (max(warmup, 3) + 1)
+    ms = time_device(lambda i: step.replay(), steps, 3, torch, dist)
+    host_in = torch.zeros((batch,), dtype=torch.int64).pin_memory()
+    host_out = torch.zeros((batch,), dtype=torch.int64).pin_memory()
+
+    def e2e_step(i):
+        host_in.fill_(i % 1000)
+        step.tokens.copy_(host_in, non_blocking=True)
+        step.replay()
+        host_out.copy_(step.next_tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    esteps = max(3, min(steps, 20))
+    ems = time_device(e2e_step, esteps, 3, torch, dist)
+    res = {"ms_per_step": ms / steps, "e2e_ms_per_step": ems / esteps, "launches_per_step": per_step,
+           "h2d": batch * 8, "d2h": batch * 8, "steps": steps, "exchange": step.exchange_description()}
+    del step
+    torch.cuda.empty_cache()
+    return res
+
+
+def decode_step_line(name, args, torch, dist, device, world, pk):
     batch = DECODE_STEPS[name]
     res = measure_decode_step(batch, args.steps, args.warmup, torch, dist, device)
-    t = torch.tensor([res["ms_per_step"], res["e2e_ms_per_step"]], device=device, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step, e2e_ms = float(t[0]), float(t[1])
+    ms_step, e2e_ms = max_over_ranks([res["ms_per_step"], res["e2e_ms_per_step"]], torch, dist, device)
     wb, kvb = decode_step_bytes(batch, world)
     achieved = (wb + kvb) / (res["ms_per_step"] * 1e-3) / 1e9
     return {
         "metric": "decode_tok_s", "value": batch / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": res["steps"], "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": name, "batch": batch, "layers": 32, "d_model": 4096, "ffn": 14336, "vocab": 128256,
-                   "context": 2048, "group_size": 64, "bits": 4,
-                   "l2": f"one step streams {wb / 2**20:.0f} MiB of weights per GPU (> L2)",
-                   "parallelism": f"tp{world}: every weight sharded on its output rows, all-gather after each linear"
-                                  + {"none": "", "peer": " (one-shot peer-store kernel over NVLink)",
-                                     "nccl": " (NCCL)", "skip": " (exchange left out: timing experiment)"}[res["gather"]],
-                   "timed": "cuda graph replay of the whole step"},
+        "config": config_of(name, world),
+        "how": {"timed": "cuda graph replay of the whole step", "exchange": res["exchange"]},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
                      "bytes": "this rank's packed weights + tables and its KV cache, read once per step"},
@@ -443,60 +527,133 @@ def decode_step_line(name, args, torch, dist, device, world, pk, clk_fn=None):
     }
 
 
-def moe_line(name, args, torch, dist, device, world, pk):
-    """One step = the whole expert block (`moe.moe_experts`) on this rank's own tokens."""
-    from metaljax_b200 import _lib, moe
-    t, k, e, d, f = MOE_BLOCKS[name]
-    g = torch.Generator(device=device).manual_seed(11 + int(os.environ.get("RANK", "0")))
+# ---- the expert block -------------------------------------------------------------------------------
 
-    def pack(n, kk):
-        w = torch.randint(-(1 << 31), (1 << 31) - 1, (e, n, kk // 8), generator=g, device=device,
-                          dtype=torch.int64).to(torch.int32).view(torch.uint32)
-        s = (torch.rand((e, n, kk // 64), generator=g, device=device) * 0.018 + 0.002).to(torch.bfloat16)
+
+def moe_line(name, args, torch, dist, device, world, pk):
+    """One step = the whole expert block: at N = 1 `moe.moe_experts` on all tokens, at N > 1
+    `parallel.ExpertParallelMoE` with the tokens and the experts split over the ranks."""
+    from metaljax_b200 import _lib, moe, parallel
+    t, k, e, d, f = MOE_BLOCKS[name]
+    rank = int(os.environ.get("RANK", "0"))
+    g = torch.Generator(device=device).manual_seed(11)                     # the same experts on every rank
+    gl = torch.Generator(device=device).manual_seed(100 + rank)            # this rank's tokens
+    el = e // world if world > 1 else e
+
+    def pack(n, kk):                                                        # this rank's experts only
+        ws = []
+        for ex in range(e):
+            w = torch.randint(-(1 << 31), (1 << 31) - 1, (n, kk // 8), generator=g, device=device,
+                              dtype=torch.int64).to(torch.int32).view(torch.uint32)
+            s = (torch.rand((n, kk // 64), generator=g, device=device) * 0.018 + 0.002).to(torch.bfloat16)
+            if world == 1 or ex // el == rank:
+                ws.append((w, s))
+        w = torch.stack([a for a, _ in ws])
+        s = torch.stack([b_ for _, b_ in ws])
         return w, s, (-8.0 * s.float()).to(torch.bfloat16)
 
     w1, w3, w2 = pack(f, d), pack(f, d), pack(d, f)
+    tl = t // world
     sets = 3
-    xs = [(torch.randn((t, d), generator=g, device=device) * 0.5).to(torch.bfloat16) for _ in range(sets)]
-    logits = torch.randn((t, e), generator=g, device=device)
+    xs = [(torch.randn((tl, d), generator=gl, device=device) * 0.5).to(torch.bfloat16) for _ in range(sets)]
+    logits = torch.randn((tl, e), generator=gl, device=device)
     wts, idx = torch.topk(torch.softmax(logits, -1), k, dim=-1)
     wts = (wts / wts.sum(-1, keepdim=True)).float()
-    flops = 2.0 * t * k * (3 * d * f)
+    if world > 1:
+        block = parallel.ExpertParallelMoE(w1, w3, w2, group=None, local_experts=True)
+        run = lambda x: block(x, idx, wts)                                  # noqa: E731
+    else:
+        run = lambda x: moe.moe_experts(x, idx, wts, w1, w3, w2)            # noqa: E731
+    flops = 2.0 * t * k * (3 * d * f)                                       # whole job
+    warm = max(args.warmup, 3)
     n0 = _lib.launch_count()
-    ms = time_device(lambda i: moe.moe_experts(xs[i % sets], idx, wts, w1, w3, w2), args.steps, max(args.warmup, 3),
-                     torch, dist)
-    launches = (_lib.launch_count() - n0) * args.steps // (args.steps + max(args.warmup, 3))
+    ms = time_device(lambda i: run(xs[i % sets]), args.steps, warm, torch, dist)
+    launches = (_lib.launch_count() - n0) * args.steps // (args.steps + warm)
     hx = torch.empty_like(xs[0], device="cpu").pin_memory().copy_(xs[0])
     hy = torch.empty_like(xs[0], device="cpu").pin_memory()
     dx = torch.empty_like(xs[0])
 
     def e2e_step(i):
         dx.copy_(hx, non_blocking=True)
-        y = moe.moe_experts(dx, idx, wts, w1, w3, w2)
+        y = run(dx)
         hy.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     esteps = max(3, min(args.steps, 10))
     ems = time_device(e2e_step, esteps, 3, torch, dist)
-    tt = torch.tensor([ms / args.steps, ems / esteps], device=device, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    ms_step, e2e_ms = float(tt[0]), float(tt[1])
-    achieved = flops / (ms / args.steps * 1e-3) / 1e12
+    ms_step, e2e_ms = max_over_ranks([ms / args.steps, ems / esteps], torch, dist, device)
+    achieved = flops / world / (ms / args.steps * 1e-3) / 1e12               # this rank's share
     return {
-        "metric": "moe_block_tflops", "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": name, "tokens": t, "top_k": k, "experts": e, "d_model": d, "ffn": f, "group_size": 64,
-                   "bits": 4, "l2": f"{3 * e * d * f // 2 >> 20} MiB of expert weights per step (> L2)",
-                   "parallelism": f"dp{world}: every rank routes its own tokens against replicated experts",
-                   "includes": "pair sort, 3 grouped ragged products, SwiGLU, routed weighted sum"},
+        "metric": "moe_block_tflops", "value": flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_of(name, world),
+        "how": {"includes": "pair sort, token exchange, 3 grouped ragged products, SwiGLU, routed weighted sum",
+                "timed": "stream launches"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": achieved / pk["bf16_tflops"], "traffic": None, "peak_source": pk["source"]},
-        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "h2d_bytes_per_step": t * d * 2, "d2h_bytes_per_step": t * d * 2, "ms_per_step": e2e_ms},
+        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": tl * d * 2, "d2h_bytes_per_step": tl * d * 2, "ms_per_step": e2e_ms},
         "gpu_launches": int(launches),
     }
+
+
+# ---- parity of the sharded forms, checked before anything is timed (N > 1) ---------------------------
+
+
+def parity_check(torch, dist, device, world, rank):
+    """The N-sharded decode step against its float reference and the expert-parallel block
+    against the oracle, at small shapes; returns the two relative errors (max over ranks)."""
+    from metaljax_b200 import llama, parallel
+    from oracle import qmm_oracle as O
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import activations, affine_case, to_numpy, to_torch
+    shape = llama.Shape(layers=2, d_model=1024, heads=8, kv_heads=8, head_dim=64, ffn=2048, vocab=4096, ctx=64)
+    errs = []
+    for batch in (1, 5):
+        fw = llama.random_full_weights(shape, batch, device, seed=3)                # identical on every rank
+        step = llama.DecodeStep(shape, batch, device, full_weights=fw)
+        tokens = torch.arange(batch, device=device) * 11 % shape.vocab
+        step.tokens.copy_(tokens)
+        first = step.step().clone()
+        got = step.logits()
+        want = llama.reference_logits(fw, shape, tokens, batch)
+        errs.append((got - want).abs().max().item() / want.abs().max().item())
+        for _ in range(3):                                                          # slots and flags cycle
+            if not torch.equal(step.step(), first):
+                errs.append(float("inf"))
+        del step
+    rng = np.random.default_rng(0)
+    e, kk, d, f, t = 8, 2, 256, 512, 64 + 8 * rank
+    packs = [affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:], affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:],
+             affine_case(rng, d, f, 64, 4, "bf16", lead=(e,))[1:]]
+    block = parallel.ExpertParallelMoE(*[tuple(to_torch(a, device) for a in p) for p in packs])
+    rr = np.random.default_rng(100 + rank)
+    x = activations(rr, (t, d), "bf16", 0.5)
+    idx, wts = O.topk_router(rr.standard_normal((t, e)).astype(np.float32), kk)
+    y = block(to_torch(x, device), torch.from_numpy(idx).to(device), torch.from_numpy(wts).to(device))
+    tidx, eidx = np.repeat(np.arange(t), kk), idx.reshape(-1)
+    gate = O.gather_qmm_exact(x[:, None, :], *packs[0], tidx, eidx)[:, 0]
+    up = O.gather_qmm_exact(x[:, None, :], *packs[1], tidx, eidx)[:, 0]
+    act = (gate / (1 + np.exp(-gate))) * up
+    down = O.gather_qmm_exact(act[:, None, :], *packs[2], np.arange(len(tidx)), eidx)[:, 0]
+    moe_err = O.rel_err(to_numpy(y).astype(np.float32), O.moe_combine_exact(down, wts))
+    step_err, moe_err = max_over_ranks([max(errs), moe_err], torch, dist, device)
+    return {"decode_step": step_err, "ep_moe": moe_err, "bounds": {"decode_step": 3e-2, "ep_moe": 2e-2},
+            "what": "sharded decode step (2 layers, d 1024, batch 1 and 5) vs the float32 step on the dequantized "
+                    "weights; expert-parallel SwiGLU block (8 experts, top-2) vs the oracle's pair-space product"}
+
+
+def line_of(name, args, torch, dist, device, world, pk):
+    if name in DECODE_STEPS:
+        return decode_step_line(name, args, torch, dist, device, world, pk)
+    if name in MOE_BLOCKS:
+        return moe_line(name, args, torch, dist, device, world, pk)
+    return qmm_line(name, args, torch, dist, device, world, pk)
+
+
+ALSO_KEYS = ("metric", "value", "unit", "n_gpus", "ms_per_step", "scaling", "config", "how", "roofline", "e2e",
+             "gpu_launches")
 
 
 def main():
@@ -507,7 +664,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS) + sorted(DECODE_STEPS) + sorted(MOE_BLOCKS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-also", action="store_true", help="skip the decode side measurement")
+    ap.add_argument("--no-also", action="store_true", help="only the headline workload")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -518,7 +675,7 @@ def main():
         return
 
     import torch
-    from metaljax_b200 import _lib, qmm
+    from metaljax_b200 import _lib
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the fused op has no CPU path")
     _lib.lib()
@@ -532,102 +689,26 @@ def main():
 
     name = args.workload
     pk = peaks()
-    if name in DECODE_STEPS or name in MOE_BLOCKS:
-        with ClockSampler(local) as clocks:
-            line = (decode_step_line if name in DECODE_STEPS else moe_line)(name, args, torch, dist, device, world, pk)
-        line["clocks"] = clocks.summary()
-        _lib.poll_status()
-        if rank == 0 and not args.no_cpu and name in DECODE_STEPS:
-            line["cpu_baseline"] = decode_step_cpu(DECODE_STEPS[name])
-        if rank == 0:
-            print(json.dumps(line), flush=True)
-        if dist is not None:
-            dist.barrier()
-            dist.destroy_process_group()
-        return
-    m, k, n, gs, bits, mode = WORKLOADS[name]
+    parity = parity_check(torch, dist, device, world, rank) if world > 1 else None
     with ClockSampler(local) as clocks:
-        res = measure(name, args, torch, qmm, _lib, dist, device)
-    clk = clocks.summary()
+        line = line_of(name, args, torch, dist, device, world, pk)
+    line["clocks"] = clocks.summary()
     _lib.poll_status()
-
-    # max over ranks of the timed region; work summed over ranks
-    t = torch.tensor([res["ms_per_step"], res["e2e_ms_per_step"]], device=device, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step, e2e_ms = float(t[0]), float(t[1])
-    flops, weight_bytes, total_bytes = res["flops"], res["weight_bytes"], res["total_bytes"]
-    if m > 1:
-        unit = "TFLOP/s"
-        value = world * flops / (ms_step * 1e-3) / 1e12
-        e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
-        achieved = flops / (res["ms_per_step"] * 1e-3) / 1e12
-        roof = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": unit,
-                "frac": achieved / pk["bf16_tflops"], "traffic": MEASURED_TRAFFIC.get(name),
-                "peak_source": pk["source"],
-                "frac_of_nominal_2250": achieved / 2250.0}
-    else:
-        unit = "GB/s"
-        value = world * weight_bytes / (ms_step * 1e-3) / 1e9
-        e2e_value = world * weight_bytes / (e2e_ms * 1e-3) / 1e9
-        best = min(res["ms_per_step"], res.get("graph_ms_per_step", 1e9))
-        achieved = total_bytes / (best * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": unit,
-                "frac": achieved / pk["hbm_gbs"], "traffic": MEASURED_TRAFFIC.get(name),
-                "peak_source": pk["source"], "frac_of_nominal_8000": achieved / 8000.0,
-                "timed": "cuda graph replay" if best != res["ms_per_step"] else "stream launches"}
-
-    line = {
-        "metric": metric_name(name), "value": value, "unit": unit, "n_gpus": world,
-        "steps": res["steps"], "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": name, "M": m, "K": k, "N": n, "group_size": gs, "bits": bits,
-                   "mode": mode, "route": qmm.route(m, k, n, gs, bits, mode),
-                   "l2": f"inputs rotate through {res['sets']} sets ({res['sets'] * total_bytes >> 20} MiB > 2x L2)",
-                   "parallelism": f"dp{world}: rows of x sharded, weights replicated, no collective",
-                   "timed": res.get("timed", "stream launches")},
-        "roofline": roof,
-        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": res["h2d"],
-                "d2h_bytes_per_step": res["d2h"], "ms_per_step": e2e_ms},
-        "gpu_launches": int(res["launches"]),
-        "clocks": clk,
-    }
-
-    if rank == 0 and not args.no_also and name == DEFAULT and world == 1:
-        side = measure(DECODE, args, torch, qmm, _lib, None, device)
-        _, wb, tb = work_of(DECODE)
-        best = min(side["ms_per_step"], side.get("graph_ms_per_step", 1e9))
-        line["also"] = [{
-            "workload": DECODE, "metric": "qmm_weight_gbs_m1",
-            "value": wb / (best * 1e-3) / 1e9, "unit": "GB/s",
-            "us_per_call_stream": side["ms_per_step"] * 1e3,
-            "us_per_call_graph": side.get("graph_ms_per_step", float("nan")) * 1e3,
-            "route": qmm.route(1, 4096, 4096),
-            "roofline": {"bound": "hbm", "achieved": tb / (best * 1e-3) / 1e9, "peak": pk["hbm_gbs"],
-                         "unit": "GB/s", "frac": tb / (best * 1e-3) / 1e9 / pk["hbm_gbs"],
-                         "traffic": MEASURED_TRAFFIC.get(DECODE), "peak_source": pk["source"]},
-        }]
+    if parity is not None:
+        line["parity"] = parity
 
     if not args.no_also and name == DEFAULT:
-        # the decode-step tokens/s at this N (weights sharded on N: strong scaling), all ranks
-        for side_name in ("decode_llama3_8b_b1", "decode_llama3_8b_b16", "decode_llama3_8b_b64"):
-            side_line = decode_step_line(side_name, args, torch, dist, device, world, pk)
-            line.setdefault("also", []).append(
-                {key: side_line[key] for key in ("metric", "value", "unit", "n_gpus", "ms_per_step", "scaling",
-                                                 "config", "roofline", "e2e", "gpu_launches")})
-
-    if rank == 0 and not args.no_cpu and world >= 1:
-        cb = cpu_baseline(name)
-        if m > 1:
-            cval = cb["flops"] / cb["seconds_per_sample"] / 1e12
+        if world == 1:
+            sides = [w for w in ALSO_AT_ONE] + [w for w in sorted(DECODE_STEPS, key=DECODE_STEPS.get) if w != name]
         else:
-            cval = weight_bytes / cb["seconds_per_sample"] / 1e9
-        line["cpu_baseline"] = {
-            "value": cval, "unit": unit, "cores": cb["cores"], "kind": "port",
-            "sample": f"first {cb['rows']} of {m} rows of x against the whole weight, "
-                      f"{cb['reps']} calls in {cb['seconds_per_sample'] * cb['reps']:.1f} s"}
+            sides = [w for w in sorted(DECODE_STEPS, key=DECODE_STEPS.get) if w != name] + sorted(MOE_BLOCKS)
+        for side_name in sides:
+            side = line_of(side_name, args, torch, dist, device, world, pk)
+            line.setdefault("also", []).append({key: side[key] for key in ALSO_KEYS})
+        _lib.poll_status()
 
+    if rank == 0 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline_of(name)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:

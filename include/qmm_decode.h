@@ -14,6 +14,8 @@
 
 #include <stdint.h>
 
+#include "qmm.h"
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -51,6 +53,73 @@ int qmm_decode_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t ff
 int qmm_decode_allgather(const void* local, void* const* peer_bufs, void* const* peer_flags, void* state,
                          int rank, int world, int slot, int64_t rows, int64_t slice_bytes,
                          int64_t slot_bytes, void* stream);
+
+/* ---- the exchange folded into the kernels (single-row decode) ------------------------------
+ *
+ * With the weights sharded on their output rows, every linear's slice has to reach every rank
+ * before the next kernel reads the whole row. Instead of a separate all-gather kernel, the
+ * producing kernel stores its slice straight into every rank's gather slot (plain peer stores
+ * over NVLink) and its last CTA raises this rank's flag on every rank; the consuming kernel
+ * requests its weights first and then waits, bounded, for all ranks' flags before it reads the
+ * row. No counterpart in the reference, which is single-device.
+ *
+ * Flags carry (epoch << 10) | (site + 1): `epoch` counts decode steps (qmm_decode_step_begin
+ * advances it on the device, so a step captured in a CUDA graph can be replayed), `site` numbers
+ * the exchanges of one step (< 1023). Every rank makes the same sequence of calls. A slot may be
+ * reused by the exchange after the next one (three slots rotating are always safe). */
+typedef struct {
+  void* const* peer_bufs;   /* [world] every rank's gather area (`slot_bytes` per slot), mapped here */
+  void* const* peer_flags;  /* [world] every rank's flag words: uint32 [slots][8], zeroed once */
+  void* epoch;              /* this rank's step counter: one uint32 of device memory, zeroed once */
+  void* done;               /* this rank's finished-CTA counter: one uint32 of device memory, zeroed once */
+  int64_t slot_bytes;
+  int32_t rank, world;      /* world <= 8 */
+} qmm_exchange;
+
+typedef enum { QMM_PROLOGUE_NONE = 0, QMM_PROLOGUE_ADD_RMSNORM = 1, QMM_PROLOGUE_SWIGLU = 2 } qmm_prologue;
+
+typedef struct {
+  int32_t prologue;         /* qmm_prologue: what the linear's activation row is made from
+                             *   NONE         x as it stands, [1, K]
+                             *   ADD_RMSNORM  h = x (+ residual_in); residual_out = h (written once, by one CTA;
+                             *                must not be the buffer residual_in points to); row = rmsnorm(h) * norm_weight
+                             *   SWIGLU       x holds `world` blocks of [gate | up], each half K / world wide;
+                             *                row = silu(gate) * up, block after block */
+  int32_t wait_slot;        /* >= 0: x is gather slot `wait_slot` of this rank, complete when every rank's flag */
+  int32_t wait_site;        /*       of exchange `wait_site` has risen; < 0: x is problem->x */
+  int32_t push_slot;        /* >= 0: y (this rank's N columns of a row of world * N) also goes to slot `push_slot` */
+  int32_t push_site;        /*       of every rank, as exchange `push_site`; problem->y may then be NULL */
+  const void* residual_in;
+  void* residual_out;
+  const void* norm_weight;  /* [K] bf16 */
+  float eps;
+} qmm_decode_fusion;
+
+/* Advances this rank's step counter: once at the start of every decode step, on the step's
+ * stream, before the step's first exchange. */
+int qmm_decode_step_begin(const qmm_exchange* ex, void* stream);
+
+/* One sharded linear of a single-row decode step: `qmm_launch(problem)` with the activation row
+ * produced, and the output row exchanged, inside the kernel as `fusion` says. M = 1, bf16
+ * activations, bf16 (affine) or E8M0 (mxfp4) tables; QMM_ERR_UNSUPPORTED otherwise (the caller
+ * then runs the unfused sequence). `ex` may be NULL when fusion->wait_slot and push_slot are < 0. */
+int qmm_decode_linear(const qmm_problem* problem, const qmm_decode_fusion* fusion, const qmm_exchange* ex,
+                      void* stream);
+
+/* Rotary embedding + cache append + grouped-query attention of one decode position, one kernel:
+ * what qmm_decode_rope_kv followed by softmax(q k^T / sqrt(head_dim)) v over positions 0..pos
+ * computes. qkv as for qmm_decode_rope_kv; out [batch, heads * head_dim] bf16 (query head i
+ * attends through key/value head i / (heads / kv_heads)), or NULL when the row is only pushed.
+ * head_dim 64 or 128; heads / kv_heads 1, 2, 4 or 8. The context is cut into slices that run as
+ * separate CTAs; their partial results meet in `scratch`, device memory the caller provides:
+ * qmm_decode_attention_scratch_bytes(...) bytes, zeroed once before the first call, not shared
+ * by calls that can overlap. With push_slot >= 0 the row also goes to every rank's gather slot
+ * (this rank's heads are a column block of the gathered row) as exchange `push_site` of `ex`. */
+int64_t qmm_decode_attention_scratch_bytes(int64_t batch, int heads, int kv_heads, int head_dim, int64_t ctx);
+int qmm_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, void* scratch,
+                         int64_t scratch_bytes, int64_t batch, int heads, int kv_heads, int head_dim,
+                         int64_t ctx, int64_t pos, float theta, int push_slot, int push_site,
+                         const qmm_exchange* ex, void* stream);
 
 #ifdef __cplusplus
 }

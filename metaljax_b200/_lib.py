@@ -49,6 +49,23 @@ class Problem(ctypes.Structure):
     ]
 
 
+class Exchange(ctypes.Structure):
+    """`qmm_exchange` of include/qmm_decode.h."""
+
+    _fields_ = [("peer_bufs", ctypes.POINTER(ctypes.c_void_p)), ("peer_flags", ctypes.POINTER(ctypes.c_void_p)),
+                ("epoch", ctypes.c_void_p), ("done", ctypes.c_void_p), ("slot_bytes", ctypes.c_int64),
+                ("rank", ctypes.c_int32), ("world", ctypes.c_int32)]
+
+
+class DecodeFusion(ctypes.Structure):
+    """`qmm_decode_fusion` of include/qmm_decode.h."""
+
+    _fields_ = [("prologue", ctypes.c_int32), ("wait_slot", ctypes.c_int32), ("wait_site", ctypes.c_int32),
+                ("push_slot", ctypes.c_int32), ("push_site", ctypes.c_int32),
+                ("residual_in", ctypes.c_void_p), ("residual_out", ctypes.c_void_p),
+                ("norm_weight", ctypes.c_void_p), ("eps", ctypes.c_float)]
+
+
 _lib = None
 
 ctypes.pythonapi.PyCapsule_GetPointer.restype = ctypes.c_void_p
@@ -90,6 +107,15 @@ _SIGNATURES = {
                                             ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_int,
                                             ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
                                             ctypes.c_int64, ctypes.c_void_p]),
+    "qmm_decode_step_begin": (ctypes.c_int, [ctypes.POINTER(Exchange), ctypes.c_void_p]),
+    "qmm_decode_linear": (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.POINTER(DecodeFusion),
+                                         ctypes.POINTER(Exchange), ctypes.c_void_p]),
+    "qmm_decode_attention_scratch_bytes": (ctypes.c_int64, [ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                            ctypes.c_int64]),
+    "qmm_decode_attention": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
+                                                                   ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_float,
+                                                                   ctypes.c_int, ctypes.c_int, ctypes.POINTER(Exchange),
+                                                                   ctypes.c_void_p]),
     "qmm_route": (ctypes.c_int, [ctypes.POINTER(Problem)]),
 }
 

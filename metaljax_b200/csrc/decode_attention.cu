@@ -1,0 +1,388 @@
+// Attention of one decode position over the key/value cache, with the rotary embedding and the
+// cache append folded in, and -- with the weights sharded over GPUs -- the exchange of its
+// output row folded into its epilogue. The reference reaches this arithmetic through its generic
+// handlers and its fused-attention recognizer (src/metaljax/sdpa.py), which are outside the
+// quantized-matmul path; this kernel exists because a decode step is a chain of launches between
+// the weight streams, and at a few rows every launch that is not a weight stream is pure latency.
+//
+// One CTA per (batch row, key/value head, slice of the context): the query heads that share the
+// key/value head (grouped-query attention) are rotated once and kept in shared memory; the
+// slice's scores are taken thread-per-position, the softmax statistics per chunk of 128
+// positions, the value sum thread-per-(8 dimensions, position subgroup). Every slice writes
+// (max, sum, weighted values) to scratch memory the caller provides; the last CTA of a
+// (row, head) to finish combines the slices and writes the row. The slice that contains the
+// decode position appends the rotated key and the value to the cache; that position is always
+// taken from shared memory, never read back.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/qmm_decode.h"
+#include "qmm_internal.h"
+
+namespace qmm {
+namespace {
+
+constexpr int kAttnThreads = 128;
+
+struct AttnParams {
+  const __nv_bfloat16* qkv;      // [batch, (heads + 2 kv_heads) * HD]: q heads | k heads | v heads
+  __nv_bfloat16* k_cache;        // [batch, kv_heads, ctx, HD]
+  __nv_bfloat16* v_cache;
+  __nv_bfloat16* out;            // [batch, heads * HD], or NULL
+  float* part;                   // scratch: [batch, kv_heads, splits, REP, HD + 2]
+  uint32_t* counters;            // scratch: [batch * kv_heads + 1], zero between calls
+  int heads, kv_heads, splits;
+  int64_t ctx, pos;
+  float theta;
+  // exchange (push_world == 0: none): the row also goes to every rank's gather slot
+  int push_world, push_site;
+  uint8_t* push_dst[8];          // every rank's slot + this rank's column block
+  int64_t push_row_bytes;        // bytes between batch rows of the gathered matrix
+  uint32_t* push_flag[8];
+  const uint32_t* epoch;
+};
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(u[i] << 16);
+    f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+
+// Largest / sum over the CTA's 128 threads of REP values at once (all threads get the results).
+template <int REP, bool MAX>
+__device__ __forceinline__ void block_reduce(float (&v)[REP], float (*scratch)[4]) {
+#pragma unroll
+  for (int h = 0; h < REP; ++h)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[h], o);
+      v[h] = MAX ? fmaxf(v[h], other) : v[h] + other;
+    }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0)
+#pragma unroll
+    for (int h = 0; h < REP; ++h) scratch[h][threadIdx.x >> 5] = v[h];
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < REP; ++h)
+    v[h] = MAX ? fmaxf(fmaxf(scratch[h][0], scratch[h][1]), fmaxf(scratch[h][2], scratch[h][3]))
+               : (scratch[h][0] + scratch[h][1]) + (scratch[h][2] + scratch[h][3]);
+}
+
+template <int HD, int REP>
+__global__ void __launch_bounds__(kAttnThreads)
+decode_attention_kernel(const AttnParams p) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  constexpr int kPieces = HD / 8;                   // 16-byte pieces per row
+  constexpr int kSubs = kAttnThreads / kPieces;     // position subgroups of the value sum
+  constexpr int kStat = HD + 2;
+  __shared__ __align__(16) float q_s[REP][HD];      // rotated queries, scaled by 1/sqrt(HD)
+  __shared__ __align__(16) float knew[HD], vnew[HD];
+  __shared__ __align__(16) float prob[REP][kAttnThreads];
+  __shared__ __align__(16) float accs[kSubs][REP][HD];
+  __shared__ float red4[REP][4];
+  __shared__ float wsplit[REP][64];                 // combine: the weight of every slice
+  __shared__ float denom[REP];
+  __shared__ int is_last;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x;
+  const int total_heads = p.heads + 2 * p.kv_heads;
+  const __nv_bfloat16* row = p.qkv + static_cast<int64_t>(b) * total_heads * HD;
+  const int64_t len = p.pos + 1;                                   // positions 0 .. pos
+  const int64_t per = (len + p.splits - 1) / p.splits;
+  const int64_t lo = split * per, hi = (lo + per < len) ? lo + per : len;
+  __nv_bfloat16* kc = p.k_cache + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.ctx * HD;
+  __nv_bfloat16* vc = p.v_cache + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.ctx * HD;
+
+  // ---- rotary embedding of this head group's queries and key (rotate-half pairing), the value ----
+  constexpr int kHalf = HD / 2;
+  const float inv_sqrt = rsqrtf(static_cast<float>(HD));
+  for (int i = tid; i < (REP + 1) * kHalf; i += kAttnThreads) {
+    const int h = i / kHalf, j = i - h * kHalf;
+    const __nv_bfloat16* src = h < REP ? row + (kvh * REP + h) * HD : row + (p.heads + kvh) * HD;
+    const float a = __bfloat162float(src[j]), c = __bfloat162float(src[j + kHalf]);
+    float sn, cs;
+    const float freq = exp2f(-2.0f * static_cast<float>(j) / static_cast<float>(HD) * log2f(p.theta));
+    sincosf(static_cast<float>(p.pos) * freq, &sn, &cs);
+    const float rlo = bf16_round(a * cs - c * sn), rhi = bf16_round(c * cs + a * sn);
+    if (h < REP) {
+      q_s[h][j] = rlo * inv_sqrt;
+      q_s[h][j + kHalf] = rhi * inv_sqrt;
+    } else {
+      knew[j] = rlo;
+      knew[j + kHalf] = rhi;
+    }
+  }
+  for (int i = tid; i < HD; i += kAttnThreads) vnew[i] = __bfloat162float(row[(p.heads + p.kv_heads + kvh) * HD + i]);
+  __syncthreads();
+  if (p.pos >= lo && p.pos < hi) {                 // this slice owns the decode position: append
+    for (int i = tid; i < HD; i += kAttnThreads) {
+      kc[p.pos * HD + i] = __float2bfloat16_rn(knew[i]);
+      vc[p.pos * HD + i] = __float2bfloat16_rn(vnew[i]);
+    }
+  }
+
+  // ---- the slice, in chunks of 128 positions ----
+  float m_run[REP], l_run[REP], acc[REP][8];
+#pragma unroll
+  for (int h = 0; h < REP; ++h) {
+    m_run[h] = -INFINITY;
+    l_run[h] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[h][e] = 0.0f;
+  }
+  const int piece = tid % kPieces, sub = tid / kPieces;
+  for (int64_t c0 = lo; c0 < hi; c0 += kAttnThreads) {
+    // scores: thread <-> position
+    const int64_t pp = c0 + tid;
+    float s[REP];
+#pragma unroll
+    for (int h = 0; h < REP; ++h) s[h] = 0.0f;
+    if (pp < hi) {
+#pragma unroll 4
+      for (int d8 = 0; d8 < kPieces; ++d8) {
+        float kf[8];
+        if (pp == p.pos) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) kf[e] = knew[d8 * 8 + e];
+        } else {
+          unpack8(__ldg(reinterpret_cast<const uint4*>(kc + pp * HD) + d8), kf);
+        }
+#pragma unroll
+        for (int h = 0; h < REP; ++h) {
+          const float4 q0 = *reinterpret_cast<const float4*>(&q_s[h][d8 * 8]);
+          const float4 q1 = *reinterpret_cast<const float4*>(&q_s[h][d8 * 8 + 4]);
+          s[h] = fmaf(q0.x, kf[0], s[h]); s[h] = fmaf(q0.y, kf[1], s[h]); s[h] = fmaf(q0.z, kf[2], s[h]); s[h] = fmaf(q0.w, kf[3], s[h]);
+          s[h] = fmaf(q1.x, kf[4], s[h]); s[h] = fmaf(q1.y, kf[5], s[h]); s[h] = fmaf(q1.z, kf[6], s[h]); s[h] = fmaf(q1.w, kf[7], s[h]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < REP; ++h) s[h] = -INFINITY;
+    }
+    // softmax statistics of the chunk, running rescale
+    float scale_old[REP], cmax[REP], csum[REP];
+#pragma unroll
+    for (int h = 0; h < REP; ++h) cmax[h] = s[h];
+    block_reduce<REP, true>(cmax, red4);
+#pragma unroll
+    for (int h = 0; h < REP; ++h) {
+      const float m_new = fmaxf(m_run[h], cmax[h]);
+      csum[h] = (pp < hi) ? __expf(s[h] - m_new) : 0.0f;
+      prob[h][tid] = csum[h];
+      scale_old[h] = (m_run[h] == -INFINITY) ? 0.0f : __expf(m_run[h] - m_new);
+      m_run[h] = m_new;
+    }
+    block_reduce<REP, false>(csum, red4);            // (its barriers also make prob complete)
+#pragma unroll
+    for (int h = 0; h < REP; ++h) l_run[h] = l_run[h] * scale_old[h] + csum[h];
+    // weighted values: thread <-> (8 dimensions, position subgroup)
+#pragma unroll
+    for (int h = 0; h < REP; ++h)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[h][e] *= scale_old[h];
+    const int chunk_len = static_cast<int>((hi - c0 < kAttnThreads) ? hi - c0 : kAttnThreads);
+    for (int i = sub; i < chunk_len; i += kSubs) {
+      const int64_t vp = c0 + i;
+      float vf[8];
+      if (vp == p.pos) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vf[e] = bf16_round(vnew[piece * 8 + e]);
+      } else {
+        unpack8(__ldg(reinterpret_cast<const uint4*>(vc + vp * HD) + piece), vf);
+      }
+#pragma unroll
+      for (int h = 0; h < REP; ++h) {
+        const float pr = prob[h][i];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(pr, vf[e], acc[h][e]);
+      }
+    }
+    __syncthreads();                               // prob may be overwritten
+  }
+
+  // ---- this slice's (max, sum, weighted values) to scratch ----
+#pragma unroll
+  for (int h = 0; h < REP; ++h)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) accs[sub][h][piece * 8 + e] = acc[h][e];
+  __syncthreads();
+  float* mine = p.part + ((static_cast<int64_t>(b) * p.kv_heads + kvh) * p.splits + split) * REP * kStat;
+  for (int i = tid; i < REP * HD; i += kAttnThreads) {
+    const int h = i / HD, d = i - h * HD;
+    float v = 0.0f;
+#pragma unroll
+    for (int sb = 0; sb < kSubs; ++sb) v += accs[sb][h][d];
+    mine[h * kStat + d] = v;
+  }
+  if (tid < REP) {
+    mine[tid * kStat + HD] = m_run[tid];
+    mine[tid * kStat + HD + 1] = l_run[tid];
+  }
+  __threadfence();
+  __syncthreads();
+  uint32_t* counter = p.counters + b * p.kv_heads + kvh;
+  if (tid == 0) {
+    const bool last = atomicAdd(counter, 1u) == static_cast<uint32_t>(p.splits - 1);
+    if (last) *counter = 0;
+    is_last = last;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+
+  // ---- the last slice of this (row, head) to finish combines them all ----
+  const float* all = p.part + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.splits * REP * kStat;
+  {
+    // per head: one warp takes the slices' maxima and sums (lane <-> slice), leaves every slice's
+    // weight exp(max_s - max) and the common denominator in shared memory
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int h = warp; h < REP; h += kAttnThreads / 32) {
+      float ms[2], ls[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int sp = lane + 32 * u;
+        ms[u] = sp < p.splits ? __ldcg(all + (sp * REP + h) * kStat + HD) : -INFINITY;
+        ls[u] = sp < p.splits ? __ldcg(all + (sp * REP + h) * kStat + HD + 1) : 0.0f;
+      }
+      float mx = fmaxf(ms[0], ms[1]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float den = 0.0f;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const float w = (ms[u] == -INFINITY) ? 0.0f : __expf(ms[u] - mx);
+        wsplit[h][lane + 32 * u] = w;
+        den = fmaf(w, ls[u], den);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+      if (lane == 0) denom[h] = den;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < REP * HD; i += kAttnThreads) {
+    const int h = i / HD, d = i - h * HD;
+    float num = 0.0f;
+#pragma unroll 8
+    for (int sp = 0; sp < p.splits; ++sp) num = fmaf(wsplit[h][sp], __ldcg(all + (sp * REP + h) * kStat + d), num);
+    const __nv_bfloat16 o = __float2bfloat16_rn(num / denom[h]);
+    const int64_t col = static_cast<int64_t>(kvh * REP + h) * HD + d;
+    if (p.out) p.out[static_cast<int64_t>(b) * p.heads * HD + col] = o;
+    for (int r = 0; r < p.push_world; ++r)
+      reinterpret_cast<__nv_bfloat16*>(p.push_dst[r] + b * p.push_row_bytes)[col] = o;
+  }
+  if (p.push_world > 0) {
+    // the last (row, head) of the grid raises this rank's flag on every rank
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t* done = p.counters + gridDim.z * p.kv_heads;
+      if (atomicAdd(done, 1u) == gridDim.z * gridDim.y - 1) {
+        *done = 0;
+        __threadfence_system();
+        const uint32_t seq = (*reinterpret_cast<const volatile uint32_t*>(p.epoch) << 10) | static_cast<uint32_t>(p.push_site + 1);
+        for (int r = 0; r < p.push_world; ++r)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r]), "r"(seq) : "memory");
+      }
+    }
+  }
+}
+
+template <int HD, int REP>
+int launch_attention(const AttnParams& p, int64_t batch, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.splits), static_cast<unsigned>(p.kv_heads), static_cast<unsigned>(batch));
+  cfg.blockDim = dim3(kAttnThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attention_kernel<HD, REP>, p);
+  if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "decode_attention_kernel launch: %s", cudaGetErrorString(e));
+  count_launch();
+  return check_launch("decode_attention_kernel");
+}
+
+template <int HD>
+int launch_rep(const AttnParams& p, int rep, int64_t batch, cudaStream_t stream) {
+  switch (rep) {
+    case 1: return launch_attention<HD, 1>(p, batch, stream);
+    case 2: return launch_attention<HD, 2>(p, batch, stream);
+    case 4: return launch_attention<HD, 4>(p, batch, stream);
+    case 8: return launch_attention<HD, 8>(p, batch, stream);
+  }
+  return fail(QMM_ERR_UNSUPPORTED, "decode_attention: %d query heads per key/value head (1, 2, 4 or 8)", rep);
+}
+
+}  // namespace
+}  // namespace qmm
+
+using namespace qmm;
+
+extern "C" int64_t qmm_decode_attention_scratch_bytes(int64_t batch, int heads, int kv_heads, int head_dim, int64_t ctx) {
+  if (batch < 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || ctx <= 0) return 0;
+  const int64_t splits = 64;                                     // the most a call ever uses
+  return batch * kv_heads * splits * (heads / kv_heads) * (head_dim + 2) * 4 + (batch * kv_heads + 1) * 4 + 256;
+}
+
+extern "C" int qmm_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, void* scratch,
+                                    int64_t scratch_bytes, int64_t batch, int heads, int kv_heads, int head_dim,
+                                    int64_t ctx, int64_t pos, float theta, int push_slot, int push_site,
+                                    const qmm_exchange* ex, void* stream) {
+  if (!qkv || !k_cache || !v_cache || !scratch) return fail(QMM_ERR_NULL, "decode_attention: null pointer");
+  if (batch < 0 || batch > 65535 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || kv_heads > 65535 || pos < 0 || pos >= ctx)
+    return fail(QMM_ERR_SHAPE, "decode_attention: bad shape or position");
+  if (head_dim != 64 && head_dim != 128) return fail(QMM_ERR_UNSUPPORTED, "decode_attention: head_dim %d (64 or 128)", head_dim);
+  if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+       reinterpret_cast<uintptr_t>(scratch)) & 15)
+    return fail(QMM_ERR_LAYOUT, "decode_attention: pointers must be 16-byte aligned");
+  if (scratch_bytes < qmm_decode_attention_scratch_bytes(batch, heads, kv_heads, head_dim, ctx))
+    return fail(QMM_ERR_TOO_LARGE, "decode_attention: scratch of %lld bytes is too small", (long long)scratch_bytes);
+  const bool pushes = push_slot >= 0;
+  if (!out && !pushes) return fail(QMM_ERR_NULL, "decode_attention: no output");
+  if (pushes && (!ex || ex->world < 1 || ex->world > 8 || !ex->peer_bufs || !ex->peer_flags || !ex->epoch))
+    return fail(QMM_ERR_NULL, "decode_attention: an exchange is needed to push");
+  if (batch == 0) return QMM_OK;
+  AttnParams p = {};
+  p.qkv = static_cast<const __nv_bfloat16*>(qkv);
+  p.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.heads = heads; p.kv_heads = kv_heads; p.ctx = ctx; p.pos = pos; p.theta = theta;
+  // slices of the context: enough CTAs to give every SM one, at least 128 positions each
+  const int64_t len = pos + 1;
+  int64_t splits = (device_sm_count() + batch * kv_heads - 1) / (batch * kv_heads);
+  if (splits > (len + 127) / 128) splits = (len + 127) / 128;
+  if (splits > 64) splits = 64;
+  if (splits < 1) splits = 1;
+  p.splits = static_cast<int>(splits);
+  const int rep = heads / kv_heads;
+  const int64_t part_bytes = batch * kv_heads * 64 * rep * (head_dim + 2) * 4;
+  p.part = static_cast<float*>(scratch);
+  p.counters = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + ((part_bytes + 255) & ~int64_t(255)));
+  if (pushes) {
+    if (push_site < 0 || push_site >= 1023) return fail(QMM_ERR_SHAPE, "decode_attention: exchange sites are 0..1022");
+    const int64_t slice = static_cast<int64_t>(heads) * head_dim * 2;
+    if (batch * slice * ex->world > ex->slot_bytes) return fail(QMM_ERR_SHAPE, "decode_attention: the gathered rows do not fit a slot");
+    p.push_world = ex->world; p.push_site = push_site;
+    p.push_row_bytes = slice * ex->world;
+    p.epoch = static_cast<const uint32_t*>(ex->epoch);
+    for (int r = 0; r < ex->world; ++r) {
+      if (!ex->peer_bufs[r] || !ex->peer_flags[r]) return fail(QMM_ERR_NULL, "decode_attention: bad peer pointer");
+      p.push_dst[r] = static_cast<uint8_t*>(ex->peer_bufs[r]) + static_cast<int64_t>(push_slot) * ex->slot_bytes + ex->rank * slice;
+      p.push_flag[r] = static_cast<uint32_t*>(ex->peer_flags[r]) + push_slot * 8 + ex->rank;
+    }
+  }
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return head_dim == 128 ? launch_rep<128>(p, rep, batch, st) : launch_rep<64>(p, rep, batch, st);
+}

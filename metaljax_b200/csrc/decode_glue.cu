@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 
 #include "qmm_internal.h"
+#include "../../include/qmm_decode.h"
 
 namespace qmm {
 namespace {
@@ -222,6 +223,11 @@ __global__ void __launch_bounds__(kAgThreads) allgather_push_kernel(const AllGat
   }
 }
 
+__global__ void step_begin_kernel(uint32_t* epoch) {
+  pdl_enter();
+  if (threadIdx.x == 0) *epoch = *epoch + 1u;
+}
+
 template <typename... Args>
 int launch_pdl(const char* what, void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                Args... args) {
@@ -325,4 +331,69 @@ extern "C" int qmm_decode_allgather(const void* local, void* const* peer_bufs, v
   if (parts > 16) parts = 16;
   return launch_pdl("allgather_push_kernel", allgather_push_kernel, dim3(static_cast<unsigned>(world), static_cast<unsigned>(parts)),
                     dim3(kAgThreads), 0, static_cast<cudaStream_t>(stream), p);
+}
+
+
+extern "C" int qmm_decode_step_begin(const qmm_exchange* ex, void* stream) {
+  if (!ex || !ex->epoch) return fail(QMM_ERR_NULL, "step_begin: no exchange");
+  return launch_pdl("step_begin_kernel", step_begin_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<uint32_t*>(ex->epoch));
+}
+
+extern "C" int qmm_decode_linear(const qmm_problem* problem, const qmm_decode_fusion* fusion, const qmm_exchange* ex,
+                                 void* stream) {
+  if (!problem || !fusion) return fail(QMM_ERR_NULL, "decode_linear: problem and fusion are required");
+  qmm_problem p = *problem;
+  const bool waits = fusion->wait_slot >= 0, pushes = fusion->push_slot >= 0;
+  if ((waits || pushes) && !ex) return fail(QMM_ERR_NULL, "decode_linear: an exchange is needed for wait_slot / push_slot");
+  if (ex && (ex->world < 1 || ex->world > 8 || ex->rank < 0 || ex->rank >= ex->world || !ex->peer_bufs || !ex->peer_flags ||
+             !ex->epoch || !ex->done))
+    return fail(QMM_ERR_SHAPE, "decode_linear: bad exchange (world 1..8, all pointers set)");
+  const int world = ex ? ex->world : 1;
+  if (waits) p.x = static_cast<const uint8_t*>(ex->peer_bufs[ex->rank]) + static_cast<int64_t>(fusion->wait_slot) * ex->slot_bytes;
+  alignas(16) static unsigned char dummy_y[16];
+  const bool no_y = !p.y;
+  if (no_y) {
+    if (!pushes) return fail(QMM_ERR_NULL, "decode_linear: y is NULL and nothing is pushed");
+    p.y = dummy_y;                                    // (passes the pointer checks; never written: see below)
+  }
+  int rc = check_problem(p);
+  if (rc) return rc;
+  if (no_y) p.y = nullptr;
+  if (p.M != 1 || p.batch != 1 || !gemv_imma_supports(p))
+    return fail(QMM_ERR_UNSUPPORTED, "decode_linear: only what the single-row decode kernel takes (M = 1, bf16)");
+  if (fusion->prologue < QMM_PROLOGUE_NONE || fusion->prologue > QMM_PROLOGUE_SWIGLU)
+    return fail(QMM_ERR_UNSUPPORTED, "decode_linear: unknown prologue %d", fusion->prologue);
+  if (fusion->prologue == QMM_PROLOGUE_ADD_RMSNORM && (!fusion->norm_weight || fusion->residual_out == fusion->residual_in))
+    return fail(QMM_ERR_NULL, "decode_linear: add + rmsnorm needs norm_weight, and residual_out apart from residual_in");
+  if (fusion->prologue == QMM_PROLOGUE_SWIGLU && (p.K % world || (p.K / world) % 8))
+    return fail(QMM_ERR_SHAPE, "decode_linear: SwiGLU blocks must be multiples of 8 wide");
+  if ((waits && (fusion->wait_site < 0 || fusion->wait_site >= 1023)) || (pushes && (fusion->push_site < 0 || fusion->push_site >= 1023)))
+    return fail(QMM_ERR_SHAPE, "decode_linear: exchange sites are 0..1022");
+  if (pushes && (p.N * 2) % 16) return fail(QMM_ERR_LAYOUT, "decode_linear: a pushed slice must be a multiple of 16 bytes");
+  if ((waits || pushes) && world * p.N * 2 > ex->slot_bytes && pushes)
+    return fail(QMM_ERR_SHAPE, "decode_linear: the gathered row does not fit a slot");
+  DecodeFusion f = {};
+  f.prologue = fusion->prologue;
+  f.residual_in = fusion->residual_in; f.residual_out = fusion->residual_out;
+  f.norm_weight = fusion->norm_weight; f.eps = fusion->eps;
+  f.swiglu_width = static_cast<int>(p.K / world);
+  if (ex) {
+    f.epoch = static_cast<const uint32_t*>(ex->epoch);
+    f.done = static_cast<uint32_t*>(ex->done);
+  }
+  if (waits) {
+    f.wait_world = world; f.wait_site = fusion->wait_site;
+    f.wait_flags = static_cast<const uint32_t*>(ex->peer_flags[ex->rank]) + fusion->wait_slot * 8;
+  }
+  if (pushes) {
+    f.push_world = world; f.push_site = fusion->push_site;
+    for (int r = 0; r < world; ++r) {
+      if (!ex->peer_bufs[r] || !ex->peer_flags[r]) return fail(QMM_ERR_NULL, "decode_linear: bad peer pointer");
+      f.push_dst[r] = static_cast<uint8_t*>(ex->peer_bufs[r]) + static_cast<int64_t>(fusion->push_slot) * ex->slot_bytes +
+                      static_cast<int64_t>(ex->rank) * p.N * 2;
+      f.push_flag[r] = static_cast<uint32_t*>(ex->peer_flags[r]) + fusion->push_slot * 8 + ex->rank;
+    }
+  }
+  return launch_gemv_imma(p, static_cast<cudaStream_t>(stream), &f);
 }

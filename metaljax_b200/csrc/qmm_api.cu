@@ -272,6 +272,10 @@ int build_dense(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* scal
 }  // namespace
 }  // namespace qmm
 
+namespace qmm {
+int check_problem(const qmm_problem& p) { return validate_problem(p, true); }
+}  // namespace qmm
+
 using namespace qmm;
 
 // ---- the entry point that allocates nothing ------------------------------------------------

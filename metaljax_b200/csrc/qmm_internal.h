@@ -42,9 +42,29 @@ void set_scratch_override(const ScratchBlock* block);
 
 int launch_gemv(const qmm_problem& p, cudaStream_t stream);
 bool gemv_supports(const qmm_problem& p);
+// What a decode step fuses into a single-row linear: how its activation row is made from the
+// previous kernels' outputs, and the exchange of its input and output rows over peer memory.
+struct DecodeFusion {
+  int prologue;              // 0 none, 1 residual add + RMS norm, 2 SwiGLU
+  const void* residual_in;
+  void* residual_out;
+  const void* norm_weight;
+  float eps;
+  int swiglu_width;
+  const uint32_t* epoch;     // this rank's step counter
+  const uint32_t* wait_flags;
+  int wait_world, wait_site;
+  int push_world, push_site;
+  uint8_t* push_dst[8];
+  uint32_t* push_flag[8];
+  uint32_t* done;
+};
+
 // The single-row (M = 1) integer tensor-core decode kernel; launch_gemv hands it what it takes.
-int launch_gemv_imma(const qmm_problem& p, cudaStream_t stream);
+int launch_gemv_imma(const qmm_problem& p, cudaStream_t stream, const DecodeFusion* fusion = nullptr);
 bool gemv_imma_supports(const qmm_problem& p);
+// qmm_launch's validation of a raw problem (pointers included).
+int check_problem(const qmm_problem& p);
 int launch_gemm_tc(const qmm_problem& p, cudaStream_t stream);
 bool gemm_tc_supports(const qmm_problem& p);
 // Reads (and clears) the current device's status word.

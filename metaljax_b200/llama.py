@@ -98,6 +98,18 @@ def rope_kv(qkv, q_out, k_cache, v_cache, heads, kv_heads, head_dim, pos, theta)
                                              kv_heads, head_dim, ctx, int(pos), float(theta), _lib.stream_ptr(qkv)))
 
 
+def decode_attention(qkv, k_cache, v_cache, out, scratch, heads, kv_heads, head_dim, pos, theta, push=None, ex=None):
+    """Rotary embedding, cache append and attention of the decode position in one kernel
+    (`qmm_decode_attention`); `push` = (slot, site) sends the row to every rank's gather slot."""
+    batch, ctx = qkv.shape[0], k_cache.shape[2]
+    slot, site = push if push is not None else (-1, 0)
+    _lib.check(_lib.lib().qmm_decode_attention(
+        _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(scratch), scratch.numel() * scratch.element_size(), batch,
+        heads, kv_heads, head_dim, ctx, int(pos), float(theta), slot, site, None if ex is None else ctypes.byref(ex),
+        _lib.stream_ptr(qkv)))
+    return out
+
+
 def silu_mul(gate_up, out):
     rows, two_f = gate_up.shape
     _lib.check(_lib.lib().qmm_decode_silu_mul(_ptr(gate_up), _ptr(out), rows, two_f // 2, _lib.stream_ptr(gate_up)))
@@ -127,6 +139,20 @@ class _Linear:
 
     def dense(self):
         return qmm.dequantize(self.w, self.s, self.b, group_size=self.gs, bits=4)
+
+    def problem(self, x, y):
+        """`qmm_problem` of this weight against one bf16 row `x` (or None: the row comes from a
+        gather slot) into `y` (or None: the result only goes to the other ranks)."""
+        p = _lib.Problem()
+        p.struct_size = ctypes.sizeof(_lib.Problem)
+        p.mode, p.bits, p.group_size = 0, 4, self.gs
+        p.x_dtype = p.table_dtype = p.y_dtype = _lib.ELEM[torch.bfloat16]
+        p.batch, p.M, p.K, p.N = 1, 1, self.w.shape[1] * 8, self.n
+        p.x = None if x is None else x.data_ptr()
+        p.w, p.scales, p.biases = self.w.data_ptr(), self.s.data_ptr(), self.b.data_ptr()
+        p.y = None if y is None else y.data_ptr()
+        p.x_batch_stride, p.y_batch_stride = p.K, p.N
+        return p
 
 
 class DecodeStep:
@@ -225,6 +251,44 @@ class DecodeStep:
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)   # also: every rank's flags are zero now
             if int(ok.item()) == 0:
                 self.gather_mode = "nccl"
+        # A single row takes the fused step: norms, SwiGLU and the exchange of every sharded linear
+        # happen inside the linears' kernels (qmm_decode_linear). QMM_DECODE_FUSED=0 turns it off.
+        self.fused = b == 1 and os.environ.get("QMM_DECODE_FUSED", "1") != "0" and self.gather_mode in ("none", "peer")
+        self._ex = None
+        if self.fused:
+            self.res2 = torch.empty((2, b, sh.d_model), **bf)                 # the residual stream, ping-pong
+            self.emb_row = torch.empty((b, sh.d_model), **bf)
+            self.attn_l = torch.empty((b, self.h_l * hd), **bf)
+            nbytes = _lib.lib().qmm_decode_attention_scratch_bytes(b, self.h_l, self.kv_l, hd, sh.ctx)
+            self.attn_scratch = torch.zeros((nbytes,), device=dev, dtype=torch.uint8)
+            if g > 1:
+                ok = torch.ones((), device=dev, dtype=torch.int32)
+                try:
+                    import torch.distributed._symmetric_memory as symm_mem
+                    self._fslot_bytes = -(-(2 * sh.ffn * 2) // 256) * 256    # the widest gathered row: [gate | up]
+                    self._fsymm = symm_mem.empty((256 + 3 * self._fslot_bytes,), dtype=torch.uint8, device=dev)
+                    self._fsymm.zero_()
+                    hdl = symm_mem.rendezvous(self._fsymm, group if group is not None else dist.group.WORLD)
+                    self._fsymm_hdl = hdl
+                    ptrs = [int(p_) for p_ in hdl.buffer_ptrs]
+                    self._fpeer_flags = (ctypes.c_void_p * g)(*ptrs)
+                    self._fpeer_bufs = (ctypes.c_void_p * g)(*[p_ + 256 for p_ in ptrs])
+                    self._fstate = torch.zeros((8,), device=dev, dtype=torch.int32)       # [0] epoch, [4] CTA counter
+                    ex = _lib.Exchange()
+                    ex.peer_bufs = ctypes.cast(self._fpeer_bufs, ctypes.POINTER(ctypes.c_void_p))
+                    ex.peer_flags = ctypes.cast(self._fpeer_flags, ctypes.POINTER(ctypes.c_void_p))
+                    ex.epoch, ex.done = self._fstate.data_ptr(), self._fstate.data_ptr() + 16
+                    ex.slot_bytes, ex.rank, ex.world = self._fslot_bytes, r, g
+                    self._ex = ex
+                    self._fslots = [self._fsymm[256 + i * self._fslot_bytes: 256 + (i + 1) * self._fslot_bytes].view(torch.bfloat16)
+                                    for i in range(3)]
+                except Exception as exc:                          # noqa: BLE001 -- any setup failure
+                    self._peer_error = repr(exc)
+                    ok.zero_()
+                torch.cuda.synchronize(dev)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+                if int(ok.item()) == 0:
+                    self.fused = False
         self.graph = None
         self.tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
         self.next_tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
@@ -274,10 +338,69 @@ class DecodeStep:
         return full
 
     # ---- the step ----
+    def _fused_linear(self, lin, x, y, prologue=0, wait=None, push=None, residual_in=None, residual_out=None,
+                      norm_weight=None):
+        """One `qmm_decode_linear`: `wait` / `push` are (slot, site) pairs or None."""
+        f = _lib.DecodeFusion()
+        f.prologue = prologue
+        f.wait_slot, f.wait_site = wait if wait is not None else (-1, 0)
+        f.push_slot, f.push_site = push if push is not None else (-1, 0)
+        f.residual_in = None if residual_in is None else residual_in.data_ptr()
+        f.residual_out = None if residual_out is None else residual_out.data_ptr()
+        f.norm_weight = None if norm_weight is None else norm_weight.data_ptr()
+        f.eps = float(self.shape.eps)
+        p = lin.problem(x, y)
+        _lib.check(_lib.lib().qmm_decode_linear(ctypes.byref(p), ctypes.byref(f),
+                                                None if self._ex is None else ctypes.byref(self._ex),
+                                                _lib.stream_ptr(self.res)))
+
+    def _step_fused(self, tok):
+        """The single-row step: five kernels per layer (qkv, attention, o, gate/up, down). Every sharded linear writes its slice into
+        all ranks' gather slots from its own epilogue and the kernel that consumes the row waits for
+        the flags itself; RMS norms and SwiGLU are computed by the consuming linear while it stages
+        its activation row."""
+        sh, hd, g = self.shape, self.shape.head_dim, self.world
+        stream = _lib.stream_ptr(self.res)
+        torch.index_select(self.embedding, 0, tok, out=self.emb_row)
+        if self._ex is not None:
+            _lib.check(_lib.lib().qmm_decode_step_begin(ctypes.byref(self._ex), stream))
+        pos = sh.ctx - 1
+        site = 0                      # exchanges of this step so far; exchange i uses slot i % 3
+        down_wait = None              # (slot, site) of the previous layer's down projection
+        x_in = self.emb_row
+        for li, layer in enumerate(self.layers):
+            # qkv <- rmsnorm(residual + previous down) ; the residual stream moves R0 -> R1
+            self._fused_linear(layer["qkv"], None if down_wait else x_in, self.qkv, prologue=1, wait=down_wait,
+                               residual_in=None if li == 0 else self.res2[0], residual_out=self.res2[1],
+                               norm_weight=layer["ln1"])
+            at_push = (site % 3, site) if g > 1 else None
+            decode_attention(self.qkv, self.k_cache[li], self.v_cache[li], None if g > 1 else self.attn_l, self.attn_scratch,
+                             self.h_l, self.kv_l, hd, pos, sh.theta, push=at_push, ex=self._ex)
+            site += g > 1
+            # o ; gate_up <- rmsnorm(residual + o) ; R1 -> R0 ; down <- silu(gate) * up
+            o_push = (site % 3, site) if g > 1 else None
+            self._fused_linear(layer["o"], None if g > 1 else self.attn_l, None if g > 1 else self.o_l, wait=at_push, push=o_push)
+            site += g > 1
+            gu_push = (site % 3, site) if g > 1 else None
+            self._fused_linear(layer["gate_up"], None if g > 1 else self.o_l, None if g > 1 else self.gate_up, prologue=1,
+                               wait=o_push, push=gu_push, residual_in=self.res2[1], residual_out=self.res2[0],
+                               norm_weight=layer["ln2"])
+            site += g > 1
+            dn_push = (site % 3, site) if g > 1 else None
+            self._fused_linear(layer["down"], None if g > 1 else self.gate_up, None if g > 1 else self.down_l,
+                               prologue=2, wait=gu_push, push=dn_push)
+            site += g > 1
+            down_wait, x_in = dn_push, self.down_l
+        self._fused_linear(self.lm_head, None if down_wait else x_in, self.logits_l, prologue=1, wait=down_wait,
+                           residual_in=self.res2[0], residual_out=self.res2[1], norm_weight=self.final_norm)
+
     def step(self, tokens=None):
         sh, b, hd = self.shape, self.batch, self.shape.head_dim
         tok = self.tokens if tokens is None else tokens
         self._site = 0
+        if self.fused:
+            self._step_fused(tok)
+            return self._finish_step()
         torch.index_select(self.embedding, 0, tok, out=self.res)
         pos = sh.ctx - 1
         add_rmsnorm(self.res, self.layers[0]["ln1"], self.normed, eps=sh.eps)
@@ -298,6 +421,10 @@ class DecodeStep:
             nxt = self.final_norm if last else self.layers[li + 1]["ln1"]
             add_rmsnorm(down_full, nxt, self.normed, residual=self.res, eps=sh.eps)
         self.lm_head(self.normed, self.logits_l)
+        return self._finish_step()
+
+    def _finish_step(self):
+        b = self.batch
         val, idx = torch.max(self.logits_l.float(), dim=-1)
         idx = idx + self.v_lo
         if self.world > 1:
@@ -323,6 +450,15 @@ class DecodeStep:
         dist.all_gather_into_tensor(buf, padded, group=self.group)
         buf = buf.view(self.world, self.batch, widest)
         return torch.cat([buf[r, :, :s] for r, s in enumerate(sizes)], dim=-1)
+
+    def exchange_description(self) -> str:
+        """How the slices of a sharded linear reach the other ranks (for benchmark records)."""
+        if self.fused and self.world > 1:
+            return ("peer stores from the epilogue of each sharded kernel (attention, o, gate/up, down), flags awaited "
+                    "by the kernel that consumes the row")
+        return {"none": "none (one rank)", "peer": "one-shot peer-store kernel over NVLink after each sharded linear",
+                "nccl": "NCCL all-gather after each sharded linear",
+                "skip": "left out (timing experiment)"}[self.gather_mode]
 
     def capture(self, warmup: int = 3):
         """Warm up and capture the step in a CUDA graph; `replay()` then runs it."""

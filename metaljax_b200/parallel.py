@@ -103,19 +103,23 @@ class ExpertParallelMoE:
     `[E, ffn, ...]`, `[E, d, ffn*bits/32]`; each rank keeps experts `[rank*E/g, (rank+1)*E/g)`.
     """
 
-    def __init__(self, w1, w3, w2, group_size=64, bits=4, mode="affine", group=None, ops=None):
+    def __init__(self, w1, w3, w2, group_size=64, bits=4, mode="affine", group=None, ops=None,
+                 local_experts=False):
+        """With `local_experts` the packs already hold only this rank's E/g experts."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.ops = ops or _CudaOps
         self.kw = dict(group_size=group_size, bits=bits, mode=mode)
-        self.e = w1[0].shape[0]
+        self.e = w1[0].shape[0] * (self.world if local_experts else 1)
         if self.e % self.world:
             raise ValueError(f"{self.e} experts do not split over {self.world} ranks")
         self.el = self.e // self.world
         lo = self.rank * self.el
 
         def take(pack):
+            if local_experts:
+                return tuple(pack)
             return tuple(None if a is None else a[lo:lo + self.el].contiguous() for a in pack)
 
         self.w1, self.w3, self.w2 = take(w1), take(w3), take(w2)

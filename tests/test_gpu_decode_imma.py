@@ -30,6 +30,8 @@ def _device_ok():
 
 def _call(x, w, s, b, gs, bits, mode="affine", out=torch.float32, route="gemv"):
     args = (to_torch(x, DEV), to_torch(w, DEV), to_torch(s, DEV), None if b is None else to_torch(b, DEV))
+    if route is None:
+        return to_numpy(qmm.quantized_matmul(*args, group_size=gs, bits=bits, mode=mode, out_dtype=out))
     with _lib.force_route(route):
         return to_numpy(qmm.quantized_matmul(*args, group_size=gs, bits=bits, mode=mode, out_dtype=out))
 
@@ -57,7 +59,7 @@ def test_single_row_against_oracle_and_float_kernel(kind, gs, k, n, xdt):
     exact = O.qmm_exact(x, w, s, b, gs, bits, mode)
     assert O.rel_err(y, exact) <= 2e-5                     # float32 out: only accumulation order differs
     yf = _call(x, w, s, b, gs, bits, mode, route="gemv_fmma")
-    assert O.rel_err(y, yf.astype(np.float64)) <= 2e-5
+    assert O.rel_err(y, yf.astype(np.float64)) <= 1e-4         # (that kernel rounds f16 activations' group sums)
     # and in the activation's type, with the reference's "no worse than the literal chain" rule
     y16 = _call(x, w, s, b, gs, bits, mode, out=TDT[xdt]).astype(np.float32)
     err, err_lit = O.rel_err(y16, exact), O.rel_err(O.qmm_literal(x, w, s, b, gs, bits, mode).astype(np.float32), exact)

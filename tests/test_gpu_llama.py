@@ -79,3 +79,136 @@ def test_glue_kernels():
     assert (kc[:, :, pos].float() - rot(x3[:, heads:heads + kvh])).abs().max() <= 3e-2
     assert torch.equal(vc[:, :, pos], x3[:, heads + kvh:])
     assert kc[:, :, :pos].abs().max() == 0 and kc[:, :, pos + 1:].abs().max() == 0
+
+
+def test_single_row_step_fused_against_unfused(monkeypatch):
+    """Batch 1 takes the fused step (norms, SwiGLU and exchanges inside the linears' kernels);
+    with QMM_DECODE_FUSED=0 the same weights go through the separate glue kernels. Both against
+    the float reference, and against each other."""
+    from metaljax_b200 import _lib, llama
+    shape = llama.Shape(layers=3, d_model=512, heads=8, kv_heads=4, head_dim=64, ffn=1024, vocab=2000, ctx=40)
+    fw = llama.random_full_weights(shape, 1, DEV, seed=11)
+    tokens = torch.tensor([17], device=DEV)
+    want = llama.reference_logits(fw, shape, tokens, 1)
+    outs = {}
+    for fused in ("1", "0"):
+        monkeypatch.setenv("QMM_DECODE_FUSED", fused)
+        step = llama.DecodeStep(shape, 1, DEV, full_weights=fw)
+        assert step.fused == (fused == "1")
+        step.tokens.copy_(tokens)
+        step.step()
+        outs[fused] = step.logits().clone()
+        err = (outs[fused] - want).abs().max().item() / want.abs().max().item()
+        assert err <= 3e-2, (fused, err)
+        step.capture()
+        for _ in range(3):
+            step.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(step.logits(), outs[fused])
+    assert (outs["1"] - outs["0"]).abs().max().item() <= 2e-2 * want.abs().max().item()
+    assert _lib.poll_status() == 0
+
+
+def test_decode_linear_prologues_and_self_exchange():
+    """`qmm_decode_linear` against the unfused sequence: SwiGLU prologue bit for bit (the same
+    bf16 row reaches the same kernel), add + RMS-norm within a bf16 rounding of the row; and the
+    exchange protocol on one GPU as a world of one: a linear pushes its row into its own gather
+    slot, the next one waits for the flag and reads the row from the slot, over several steps."""
+    import ctypes
+    from metaljax_b200 import _lib, llama, qmm
+    g = torch.Generator(device=DEV).manual_seed(5)
+    d, f = 512, 1024
+
+    def lin(n, k):
+        return llama._Linear(n, k, DEV, g, 64, "normal")
+
+    up, down, nxt = lin(2 * f, d), lin(d, f), lin(384, d)
+    x = torch.randn((1, d), generator=g, device=DEV).to(torch.bfloat16)
+    res = torch.randn((1, d), generator=g, device=DEV).to(torch.bfloat16)
+    wn = (1 + 0.1 * torch.randn(d, generator=g, device=DEV)).to(torch.bfloat16)
+    lib = _lib.lib()
+    stream = _lib.stream_ptr(x)
+
+    def call(linear, xin, y, ex=None, **kw):
+        fz = _lib.DecodeFusion()
+        fz.prologue = kw.get("prologue", 0)
+        fz.wait_slot, fz.wait_site = kw.get("wait", (-1, 0))
+        fz.push_slot, fz.push_site = kw.get("push", (-1, 0))
+        for name in ("residual_in", "residual_out", "norm_weight"):
+            t = kw.get(name)
+            setattr(fz, name, None if t is None else t.data_ptr())
+        fz.eps = 1e-5
+        p = linear.problem(xin, y)
+        _lib.check(lib.qmm_decode_linear(ctypes.byref(p), ctypes.byref(fz), None if ex is None else ctypes.byref(ex), stream))
+
+    # unfused: h = x + res; normed; gate_up; act; down
+    normed, h = torch.empty_like(x), res.clone()
+    llama.add_rmsnorm(x, wn, normed, residual=h, eps=1e-5)
+    gu_ref = torch.empty((1, 2 * f), device=DEV, dtype=torch.bfloat16)
+    up(normed, gu_ref)
+    act = torch.empty((1, f), device=DEV, dtype=torch.bfloat16)
+    llama.silu_mul(gu_ref, act)
+    dn_ref = torch.empty((1, d), device=DEV, dtype=torch.bfloat16)
+    down(act, dn_ref)
+    # fused, plain buffers
+    gu, dn, h2 = torch.empty_like(gu_ref), torch.empty_like(dn_ref), torch.empty_like(x)
+    call(up, x, gu, prologue=1, residual_in=res, residual_out=h2, norm_weight=wn)
+    assert torch.equal(h2, h)
+    assert (gu.float() - gu_ref.float()).abs().max() <= 2e-2 * gu_ref.float().abs().max()
+    call(down, gu_ref, dn, prologue=2)
+    assert torch.equal(dn, dn_ref)
+    # the same chain through a gather slot of a world of one, three steps in a row
+    slot_bytes = 2 * f * 2
+    area = torch.zeros((3 * slot_bytes,), device=DEV, dtype=torch.uint8)
+    flags = torch.zeros((24,), device=DEV, dtype=torch.int32)
+    state = torch.zeros((8,), device=DEV, dtype=torch.int32)
+    ex = _lib.Exchange()
+    bufs, flg = (ctypes.c_void_p * 1)(area.data_ptr()), (ctypes.c_void_p * 1)(flags.data_ptr())
+    ex.peer_bufs = ctypes.cast(bufs, ctypes.POINTER(ctypes.c_void_p))
+    ex.peer_flags = ctypes.cast(flg, ctypes.POINTER(ctypes.c_void_p))
+    ex.epoch, ex.done, ex.slot_bytes, ex.rank, ex.world = state.data_ptr(), state.data_ptr() + 16, slot_bytes, 0, 1
+    out = torch.empty((1, 384), device=DEV, dtype=torch.bfloat16)
+    want = torch.empty_like(out)
+    h3 = torch.empty_like(x)
+    nxt_in = torch.empty_like(x)
+    llama.add_rmsnorm(dn_ref, wn, nxt_in, residual=h.clone(), eps=1e-5)
+    nxt(nxt_in, want)
+    for step in range(3):
+        _lib.check(lib.qmm_decode_step_begin(ctypes.byref(ex), stream))
+        call(up, x, None, ex, prologue=1, residual_in=res, residual_out=h2, norm_weight=wn, push=(0, 0))
+        call(down, None, None, ex, prologue=2, wait=(0, 0), push=(1, 1))
+        call(nxt, None, out, ex, prologue=1, wait=(1, 1), residual_in=h2, residual_out=h3, norm_weight=wn)
+        torch.cuda.synchronize()
+        assert int(state[0]) == step + 1 and int(state[4]) == 0
+        assert int(flags[0]) == ((step + 1) << 10) | 1 and int(flags[8]) == ((step + 1) << 10) | 2
+        assert (out.float() - want.float()).abs().max() <= 3e-2 * want.float().abs().max()
+    assert _lib.poll_status() == 0
+
+
+@pytest.mark.parametrize("batch,heads,kvh,hd,ctx,pos", [
+    (1, 8, 2, 128, 2048, 2047), (1, 4, 4, 64, 48, 47), (3, 4, 2, 64, 300, 150), (2, 8, 1, 128, 1000, 0),
+    (64, 4, 1, 128, 2048, 2047), (5, 16, 2, 64, 513, 512), (1, 32, 8, 128, 2048, 1000),
+])
+def test_decode_attention_against_rope_and_sdpa(batch, heads, kvh, hd, ctx, pos):
+    """The one-kernel rotary + append + attention against the rotary kernel followed by torch's
+    scaled_dot_product_attention over positions 0..pos, cache contents included."""
+    import torch.nn.functional as F
+    from metaljax_b200 import _lib, llama
+    g = torch.Generator(device=DEV).manual_seed(batch * 100 + heads)
+    qkv = torch.randn((batch, (heads + 2 * kvh) * hd), generator=g, device=DEV).to(torch.bfloat16)
+    kc = (torch.randn((batch, kvh, ctx, hd), generator=g, device=DEV) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn((batch, kvh, ctx, hd), generator=g, device=DEV) * 0.5).to(torch.bfloat16)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q = torch.empty((batch, heads, 1, hd), device=DEV, dtype=torch.bfloat16)
+    llama.rope_kv(qkv, q, kc, vc, heads, kvh, hd, pos, 500000.0)
+    want = F.scaled_dot_product_attention(q.float(), kc[:, :, : pos + 1].float(), vc[:, :, : pos + 1].float(), enable_gqa=True)
+    want = want.reshape(batch, heads * hd)
+    nbytes = _lib.lib().qmm_decode_attention_scratch_bytes(batch, heads, kvh, hd, ctx)
+    scratch = torch.zeros((nbytes,), device=DEV, dtype=torch.uint8)
+    out = torch.empty((batch, heads * hd), device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):                                   # the scratch counters reset themselves
+        out.zero_()
+        llama.decode_attention(qkv, kc2, vc2, out, scratch, heads, kvh, hd, pos, 500000.0)
+        assert (out.float() - want).abs().max().item() <= 2e-2 * max(want.abs().max().item(), 1e-3)
+    assert torch.equal(kc2, kc) and torch.equal(vc2, vc)     # the same append
+    assert _lib.poll_status() == 0
