@@ -58,21 +58,22 @@ int qmm_decode_allgather(const void* local, void* const* peer_bufs, void* const*
  *
  * With the weights sharded on their output rows, every linear's slice has to reach every rank
  * before the next kernel reads the whole row. Instead of a separate all-gather kernel, the
- * producing kernel stores its slice straight into every rank's gather slot (plain peer stores
- * over NVLink) and its last CTA raises this rank's flag on every rank; the consuming kernel
- * requests its weights first and then waits, bounded, for all ranks' flags before it reads the
- * row. No counterpart in the reference, which is single-device.
+ * producing kernel stores its slice straight into every rank's gather slot from its epilogue
+ * (plain peer stores over NVLink) and the consuming kernel, which requests its weights first,
+ * reads the row as it arrives. No counterpart in the reference, which is single-device.
  *
- * Flags carry (epoch << 10) | (site + 1): `epoch` counts decode steps (qmm_decode_step_begin
- * advances it on the device, so a step captured in a CUDA graph can be replayed), `site` numbers
- * the exchanges of one step (< 1023). Every rank makes the same sequence of calls. A slot may be
- * reused by the exchange after the next one (three slots rotating are always safe). */
+ * A gathered row travels as 8-byte units {two bf16 values, 32-bit stamp}; the stamp is
+ * (epoch << 10) | (site + 1), where `epoch` counts decode steps (qmm_decode_step_begin advances
+ * it on the device, so a step captured in a CUDA graph can be replayed) and `site` numbers the
+ * exchanges of one step (< 1023). A reader takes a unit when it carries the stamp it expects
+ * (a bounded wait; a timeout is reported by qmm_poll_status as 100): data and "it has arrived"
+ * cross the link in one store, so there is no separate flag, fence or counter. A slot therefore
+ * holds 4 bytes per value. Every rank makes the same sequence of calls; consecutive exchanges
+ * must use different slots (two slots alternating are enough, any rotation works). */
 typedef struct {
-  void* const* peer_bufs;   /* [world] every rank's gather area (`slot_bytes` per slot), mapped here */
-  void* const* peer_flags;  /* [world] every rank's flag words: uint32 [slots][8], zeroed once */
+  void* const* peer_bufs;   /* [world] every rank's gather area (`slot_bytes` per slot, zeroed once), mapped here */
   void* epoch;              /* this rank's step counter: one uint32 of device memory, zeroed once */
-  void* done;               /* this rank's finished-CTA counter: one uint32 of device memory, zeroed once */
-  int64_t slot_bytes;
+  int64_t slot_bytes;       /* multiple of 16 */
   int32_t rank, world;      /* world <= 8 */
 } qmm_exchange;
 
@@ -85,8 +86,8 @@ typedef struct {
                              *                must not be the buffer residual_in points to); row = rmsnorm(h) * norm_weight
                              *   SWIGLU       x holds `world` blocks of [gate | up], each half K / world wide;
                              *                row = silu(gate) * up, block after block */
-  int32_t wait_slot;        /* >= 0: x is gather slot `wait_slot` of this rank, complete when every rank's flag */
-  int32_t wait_site;        /*       of exchange `wait_site` has risen; < 0: x is problem->x */
+  int32_t wait_slot;        /* >= 0: x is the stamped row in gather slot `wait_slot` of this rank, */
+  int32_t wait_site;        /*       written by exchange `wait_site`; < 0: x is problem->x */
   int32_t push_slot;        /* >= 0: y (this rank's N columns of a row of world * N) also goes to slot `push_slot` */
   int32_t push_site;        /*       of every rank, as exchange `push_site`; problem->y may then be NULL */
   const void* residual_in;

@@ -52,9 +52,8 @@ class Problem(ctypes.Structure):
 class Exchange(ctypes.Structure):
     """`qmm_exchange` of include/qmm_decode.h."""
 
-    _fields_ = [("peer_bufs", ctypes.POINTER(ctypes.c_void_p)), ("peer_flags", ctypes.POINTER(ctypes.c_void_p)),
-                ("epoch", ctypes.c_void_p), ("done", ctypes.c_void_p), ("slot_bytes", ctypes.c_int64),
-                ("rank", ctypes.c_int32), ("world", ctypes.c_int32)]
+    _fields_ = [("peer_bufs", ctypes.POINTER(ctypes.c_void_p)), ("epoch", ctypes.c_void_p),
+                ("slot_bytes", ctypes.c_int64), ("rank", ctypes.c_int32), ("world", ctypes.c_int32)]
 
 
 class DecodeFusion(ctypes.Structure):

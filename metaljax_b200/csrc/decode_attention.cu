@@ -30,15 +30,14 @@ struct AttnParams {
   __nv_bfloat16* v_cache;
   __nv_bfloat16* out;            // [batch, heads * HD], or NULL
   float* part;                   // scratch: [batch, kv_heads, splits, REP, HD + 2]
-  uint32_t* counters;            // scratch: [batch * kv_heads + 1], zero between calls
+  uint32_t* counters;            // scratch: [batch * kv_heads], zero between calls
   int heads, kv_heads, splits;
   int64_t ctx, pos;
   float theta;
   // exchange (push_world == 0: none): the row also goes to every rank's gather slot
   int push_world, push_site;
-  uint8_t* push_dst[8];          // every rank's slot + this rank's column block
+  uint8_t* push_dst[8];          // every rank's slot + this rank's column block (stamped units: 4 bytes per value)
   int64_t push_row_bytes;        // bytes between batch rows of the gathered matrix
-  uint32_t* push_flag[8];
   const uint32_t* epoch;
 };
 
@@ -142,18 +141,34 @@ decode_attention_kernel(const AttnParams p) {
   for (int64_t c0 = lo; c0 < hi; c0 += kAttnThreads) {
     // scores: thread <-> position
     const int64_t pp = c0 + tid;
+    const int chunk_len = static_cast<int>((hi - c0 < kAttnThreads) ? hi - c0 : kAttnThreads);
+    // this thread's value rows of the chunk are requested now, with its key row: they do not
+    // depend on the scores, and one round trip to memory then serves both
+    uint4 vr[kPieces];
+#pragma unroll
+    for (int u = 0; u < kPieces; ++u) {
+      const int i = sub + u * kSubs;
+      vr[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < chunk_len && c0 + i != p.pos) vr[u] = __ldg(reinterpret_cast<const uint4*>(vc + (c0 + i) * HD) + piece);
+    }
     float s[REP];
 #pragma unroll
     for (int h = 0; h < REP; ++h) s[h] = 0.0f;
     if (pp < hi) {
-#pragma unroll 4
+      // the whole key row is requested before the first product (one round trip, not sixteen)
+      uint4 kr[kPieces];
+      if (pp != p.pos) {
+#pragma unroll
+        for (int d8 = 0; d8 < kPieces; ++d8) kr[d8] = __ldg(reinterpret_cast<const uint4*>(kc + pp * HD) + d8);
+      }
+#pragma unroll
       for (int d8 = 0; d8 < kPieces; ++d8) {
         float kf[8];
         if (pp == p.pos) {
 #pragma unroll
           for (int e = 0; e < 8; ++e) kf[e] = knew[d8 * 8 + e];
         } else {
-          unpack8(__ldg(reinterpret_cast<const uint4*>(kc + pp * HD) + d8), kf);
+          unpack8(kr[d8], kf);
         }
 #pragma unroll
         for (int h = 0; h < REP; ++h) {
@@ -188,21 +203,23 @@ decode_attention_kernel(const AttnParams p) {
     for (int h = 0; h < REP; ++h)
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[h][e] *= scale_old[h];
-    const int chunk_len = static_cast<int>((hi - c0 < kAttnThreads) ? hi - c0 : kAttnThreads);
-    for (int i = sub; i < chunk_len; i += kSubs) {
-      const int64_t vp = c0 + i;
-      float vf[8];
-      if (vp == p.pos) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) vf[e] = bf16_round(vnew[piece * 8 + e]);
-      } else {
-        unpack8(__ldg(reinterpret_cast<const uint4*>(vc + vp * HD) + piece), vf);
-      }
+    for (int u = 0; u < kPieces; ++u) {
+      const int i = sub + u * kSubs;
+      if (i < chunk_len) {
+        float vf[8];
+        if (c0 + i == p.pos) {
 #pragma unroll
-      for (int h = 0; h < REP; ++h) {
-        const float pr = prob[h][i];
+          for (int e = 0; e < 8; ++e) vf[e] = vnew[piece * 8 + e];
+        } else {
+          unpack8(vr[u], vf);
+        }
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(pr, vf[e], acc[h][e]);
+        for (int h = 0; h < REP; ++h) {
+          const float pr = prob[h][i];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(pr, vf[e], acc[h][e]);
+        }
       }
     }
     __syncthreads();                               // prob may be overwritten
@@ -268,29 +285,37 @@ decode_attention_kernel(const AttnParams p) {
     }
   }
   __syncthreads();
-  for (int i = tid; i < REP * HD; i += kAttnThreads) {
-    const int h = i / HD, d = i - h * HD;
-    float num = 0.0f;
-#pragma unroll 8
-    for (int sp = 0; sp < p.splits; ++sp) num = fmaf(wsplit[h][sp], __ldcg(all + (sp * REP + h) * kStat + d), num);
-    const __nv_bfloat16 o = __float2bfloat16_rn(num / denom[h]);
-    const int64_t col = static_cast<int64_t>(kvh * REP + h) * HD + d;
-    if (p.out) p.out[static_cast<int64_t>(b) * p.heads * HD + col] = o;
-    for (int r = 0; r < p.push_world; ++r)
-      reinterpret_cast<__nv_bfloat16*>(p.push_dst[r] + b * p.push_row_bytes)[col] = o;
-  }
-  if (p.push_world > 0) {
-    // the last (row, head) of the grid raises this rank's flag on every rank
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) {
-      uint32_t* done = p.counters + gridDim.z * p.kv_heads;
-      if (atomicAdd(done, 1u) == gridDim.z * gridDim.y - 1) {
-        *done = 0;
-        __threadfence_system();
-        const uint32_t seq = (*reinterpret_cast<const volatile uint32_t*>(p.epoch) << 10) | static_cast<uint32_t>(p.push_site + 1);
-        for (int r = 0; r < p.push_world; ++r)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r]), "r"(seq) : "memory");
+  for (int i = tid; i < REP * HD / 8; i += kAttnThreads) {        // thread <-> 8 consecutive dimensions
+    const int h = i / (HD / 8), d0 = (i - h * (HD / 8)) * 8;
+    float num[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+    for (int sp = 0; sp < p.splits; ++sp) {
+      const float* ps = all + (sp * REP + h) * kStat + d0;      // (kStat is even: 8-byte aligned)
+      const float w = wsplit[h][sp];
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(ps + e));
+        num[e] = fmaf(w, v.x, num[e]);
+        num[e + 1] = fmaf(w, v.y, num[e + 1]);
+      }
+    }
+    const float inv = 1.0f / denom[h];
+    uint32_t packed[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 v = __floats2bfloat162_rn(num[2 * e] * inv, num[2 * e + 1] * inv);
+      packed[e] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+    const uint4 o = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    const int64_t col = static_cast<int64_t>(kvh * REP + h) * HD + d0;
+    if (p.out) *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(b) * p.heads * HD + col) = o;
+    if (p.push_world > 0) {
+      // to every rank as stamped units {pair, stamp}: data and arrival in one store
+      const uint32_t stamp = (*reinterpret_cast<const volatile uint32_t*>(p.epoch) << 10) | static_cast<uint32_t>(p.push_site + 1);
+      for (int r = 0; r < p.push_world; ++r) {
+        uint4* dst = reinterpret_cast<uint4*>(p.push_dst[r] + b * p.push_row_bytes + col * 4);
+        dst[0] = make_uint4(o.x, stamp, o.y, stamp);
+        dst[1] = make_uint4(o.z, stamp, o.w, stamp);
       }
     }
   }
@@ -350,7 +375,7 @@ extern "C" int qmm_decode_attention(const void* qkv, void* k_cache, void* v_cach
     return fail(QMM_ERR_TOO_LARGE, "decode_attention: scratch of %lld bytes is too small", (long long)scratch_bytes);
   const bool pushes = push_slot >= 0;
   if (!out && !pushes) return fail(QMM_ERR_NULL, "decode_attention: no output");
-  if (pushes && (!ex || ex->world < 1 || ex->world > 8 || !ex->peer_bufs || !ex->peer_flags || !ex->epoch))
+  if (pushes && (!ex || ex->world < 1 || ex->world > 8 || !ex->peer_bufs || !ex->epoch))
     return fail(QMM_ERR_NULL, "decode_attention: an exchange is needed to push");
   if (batch == 0) return QMM_OK;
   AttnParams p = {};
@@ -372,15 +397,14 @@ extern "C" int qmm_decode_attention(const void* qkv, void* k_cache, void* v_cach
   p.counters = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + ((part_bytes + 255) & ~int64_t(255)));
   if (pushes) {
     if (push_site < 0 || push_site >= 1023) return fail(QMM_ERR_SHAPE, "decode_attention: exchange sites are 0..1022");
-    const int64_t slice = static_cast<int64_t>(heads) * head_dim * 2;
+    const int64_t slice = static_cast<int64_t>(heads) * head_dim * 4;      // stamped units: 4 bytes per value
     if (batch * slice * ex->world > ex->slot_bytes) return fail(QMM_ERR_SHAPE, "decode_attention: the gathered rows do not fit a slot");
     p.push_world = ex->world; p.push_site = push_site;
     p.push_row_bytes = slice * ex->world;
     p.epoch = static_cast<const uint32_t*>(ex->epoch);
     for (int r = 0; r < ex->world; ++r) {
-      if (!ex->peer_bufs[r] || !ex->peer_flags[r]) return fail(QMM_ERR_NULL, "decode_attention: bad peer pointer");
+      if (!ex->peer_bufs[r]) return fail(QMM_ERR_NULL, "decode_attention: bad peer pointer");
       p.push_dst[r] = static_cast<uint8_t*>(ex->peer_bufs[r]) + static_cast<int64_t>(push_slot) * ex->slot_bytes + ex->rank * slice;
-      p.push_flag[r] = static_cast<uint32_t*>(ex->peer_flags[r]) + push_slot * 8 + ex->rank;
     }
   }
   const cudaStream_t st = static_cast<cudaStream_t>(stream);

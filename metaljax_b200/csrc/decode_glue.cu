@@ -346,8 +346,7 @@ extern "C" int qmm_decode_linear(const qmm_problem* problem, const qmm_decode_fu
   qmm_problem p = *problem;
   const bool waits = fusion->wait_slot >= 0, pushes = fusion->push_slot >= 0;
   if ((waits || pushes) && !ex) return fail(QMM_ERR_NULL, "decode_linear: an exchange is needed for wait_slot / push_slot");
-  if (ex && (ex->world < 1 || ex->world > 8 || ex->rank < 0 || ex->rank >= ex->world || !ex->peer_bufs || !ex->peer_flags ||
-             !ex->epoch || !ex->done))
+  if (ex && (ex->world < 1 || ex->world > 8 || ex->rank < 0 || ex->rank >= ex->world || !ex->peer_bufs || !ex->epoch))
     return fail(QMM_ERR_SHAPE, "decode_linear: bad exchange (world 1..8, all pointers set)");
   const int world = ex ? ex->world : 1;
   if (waits) p.x = static_cast<const uint8_t*>(ex->peer_bufs[ex->rank]) + static_cast<int64_t>(fusion->wait_slot) * ex->slot_bytes;
@@ -370,29 +369,26 @@ extern "C" int qmm_decode_linear(const qmm_problem* problem, const qmm_decode_fu
     return fail(QMM_ERR_SHAPE, "decode_linear: SwiGLU blocks must be multiples of 8 wide");
   if ((waits && (fusion->wait_site < 0 || fusion->wait_site >= 1023)) || (pushes && (fusion->push_site < 0 || fusion->push_site >= 1023)))
     return fail(QMM_ERR_SHAPE, "decode_linear: exchange sites are 0..1022");
-  if (pushes && (p.N * 2) % 16) return fail(QMM_ERR_LAYOUT, "decode_linear: a pushed slice must be a multiple of 16 bytes");
-  if ((waits || pushes) && world * p.N * 2 > ex->slot_bytes && pushes)
+  if (pushes && p.N % 8) return fail(QMM_ERR_LAYOUT, "decode_linear: a pushed slice must be a multiple of 8 values");
+  if (pushes && world * p.N * 4 > ex->slot_bytes)           // (a stamped row takes 4 bytes per value)
     return fail(QMM_ERR_SHAPE, "decode_linear: the gathered row does not fit a slot");
+  if (waits && p.K * (fusion->prologue == QMM_PROLOGUE_SWIGLU ? 2 : 1) * 4 > ex->slot_bytes)
+    return fail(QMM_ERR_SHAPE, "decode_linear: the awaited row does not fit a slot");
   DecodeFusion f = {};
   f.prologue = fusion->prologue;
   f.residual_in = fusion->residual_in; f.residual_out = fusion->residual_out;
   f.norm_weight = fusion->norm_weight; f.eps = fusion->eps;
   f.swiglu_width = static_cast<int>(p.K / world);
-  if (ex) {
-    f.epoch = static_cast<const uint32_t*>(ex->epoch);
-    f.done = static_cast<uint32_t*>(ex->done);
-  }
+  if (ex) f.epoch = static_cast<const uint32_t*>(ex->epoch);
   if (waits) {
     f.wait_world = world; f.wait_site = fusion->wait_site;
-    f.wait_flags = static_cast<const uint32_t*>(ex->peer_flags[ex->rank]) + fusion->wait_slot * 8;
   }
   if (pushes) {
     f.push_world = world; f.push_site = fusion->push_site;
     for (int r = 0; r < world; ++r) {
-      if (!ex->peer_bufs[r] || !ex->peer_flags[r]) return fail(QMM_ERR_NULL, "decode_linear: bad peer pointer");
+      if (!ex->peer_bufs[r]) return fail(QMM_ERR_NULL, "decode_linear: bad peer pointer");
       f.push_dst[r] = static_cast<uint8_t*>(ex->peer_bufs[r]) + static_cast<int64_t>(fusion->push_slot) * ex->slot_bytes +
-                      static_cast<int64_t>(ex->rank) * p.N * 2;
-      f.push_flag[r] = static_cast<uint32_t*>(ex->peer_flags[r]) + fusion->push_slot * 8 + ex->rank;
+                      static_cast<int64_t>(ex->rank) * p.N * 4;
     }
   }
   return launch_gemv_imma(p, static_cast<cudaStream_t>(stream), &f);

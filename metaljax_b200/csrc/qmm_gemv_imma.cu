@@ -79,16 +79,16 @@ struct ImmaParams {
   const void* norm_weight;
   float eps;
   int swiglu_width;         // kProSwiglu: x holds blocks of [gate | up], each half this wide
-  // ---- exchange over peer memory (world == 1: none) ----
+  // ---- exchange over peer memory (none when wait_world == push_world == 0) ----
+  // A gathered row travels as 8-byte units {two bf16 values, stamp}: a unit is valid when its
+  // stamp is (epoch, site) of the exchange, so data and "it has arrived" cross NVLink in one
+  // store and the reader needs no separate flag, fence or counter.
   const uint32_t* epoch;    // this rank's step counter
-  const uint32_t* wait_flags;   // this rank's flag words of the slot x lives in, one per source rank
-  int wait_world;           // > 0: x is complete once every flag has reached (epoch, wait_site)
+  int wait_world;           // > 0: x is such a row in this rank's gather slot, stamped (epoch, wait_site)
   int wait_site;
-  int push_world;           // > 0: y also goes to every rank (this rank's column block of its slot) ...
-  int push_site;            // ... and, when this kernel's last CTA is done, the flags rise to (epoch, push_site)
+  int push_world;           // > 0: y also goes, stamped (epoch, push_site), to this rank's column block
+  int push_site;            //      of every rank's slot
   uint8_t* push_dst[8];
-  uint32_t* push_flag[8];
-  uint32_t* done;           // this rank's finished-CTA counter (zero between kernels)
   long long spin_limit;
 };
 
@@ -96,8 +96,27 @@ enum { kProNone = 0, kProAddNorm = 1, kProSwiglu = 2 };
 
 __device__ __forceinline__ uint32_t exchange_seq(uint32_t epoch, int site) { return (epoch << 10) | static_cast<uint32_t>(site + 1); }
 
-// Eight 16-bit activations read past the L1 cache: the row may have been written by other GPUs.
-__device__ __forceinline__ uint4 ld_x(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+// Eight bf16 values of a stamped row (four 8-byte units {pair, stamp}): read until every unit
+// carries `stamp` (bounded; a timeout is recorded in *status and whatever is there is returned).
+__device__ __forceinline__ uint4 ld_stamped8(const uint8_t* p, uint32_t stamp, long long limit, int* status) {
+  uint4 a, b;
+  long long t0 = 0;
+  int spins = 0;
+  for (;;) {
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p) : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p + 16) : "memory");
+    if (a.y == stamp && a.w == stamp && b.y == stamp && b.w == stamp) break;
+    if (++spins >= 32) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) break;            // someone already gave up: do not wait again
+      if (t0 == 0) t0 = clock64();
+      else if (clock64() - t0 > limit) {
+        atomicCAS(status, 0, 100);
+        break;
+      }
+    }
+  }
+  return make_uint4(a.x, a.z, b.x, b.z);
+}
 
 __device__ __forceinline__ uint4 pack8_bf16(const float (&f)[8]) {
   uint32_t u[4];
@@ -214,6 +233,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   uint32_t* zeros = reinterpret_cast<uint32_t*>(full_all + NW * kMaxRing);   // 64 zero bytes
   uint32_t* amax_w = zeros + 16;                     // [2][NW]: largest magnitude, sum of squares
   volatile int* abort_flag = reinterpret_cast<volatile int*>(amax_w + 2 * NW);
+  __nv_bfloat16* ypush = reinterpret_cast<__nv_bfloat16*>(amax_w + 2 * NW + 4);   // [2][kTileRows]: a finished tile on its way to the other ranks
 
   // ---- barriers, then this warp's first boxes: before anything else ----
   uint64_t* full = full_all + warp * kMaxRing;
@@ -264,25 +284,13 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   // ---- the activation row: after everything the previous kernel wrote is visible ----
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t epoch = (p.wait_world > 0 || p.push_world > 0) ? *reinterpret_cast<const volatile uint32_t*>(p.epoch) : 0u;
-  if (p.wait_world > 0) {
-    // the row lives in a gather slot that every rank fills: wait (bounded) for all their flags
-    if (threadIdx.x < p.wait_world && *reinterpret_cast<volatile int*>(p.status) == 0) {
-      const uint32_t want = exchange_seq(epoch, p.wait_site);
-      const uint32_t* flag = p.wait_flags + threadIdx.x;
-      const long long t0 = clock64();
-      for (;;) {
-        uint32_t v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-        if (static_cast<int32_t>(v - want) >= 0) break;
-        if (clock64() - t0 > p.spin_limit) {
-          atomicCAS(p.status, 0, 100 + static_cast<int>(threadIdx.x));     // which rank never arrived
-          break;
-        }
-      }
-    }
-    __syncthreads();
-  }
-  const XT* xg = static_cast<const XT*>(p.x);
+  const uint32_t wait_stamp = exchange_seq(epoch, p.wait_site);
+  // Eight consecutive elements of x starting at element `i` (a multiple of 8): plain memory, or a
+  // stamped row of this rank's gather slot that the other ranks are still filling.
+  auto ld_x = [&](int64_t i) -> uint4 {
+    if (p.wait_world > 0) return ld_stamped8(static_cast<const uint8_t*>(p.x) + i * 4, wait_stamp, p.spin_limit, p.status);
+    return __ldcg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.x) + i * sizeof(XT)));
+  };
   const int vpieces = p.K / 8, ppieces = nchunks * kBoxCodes / 8;
   const int iters = (ppieces + kThreads - 1) / kThreads;
   // Piece pc of the row before its last step: the activations themselves, silu(gate) * up, or
@@ -292,17 +300,17 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
     if (p.prologue == kProSwiglu) {
       const int k = pc * 8, blk = k / p.swiglu_width, i = k - blk * p.swiglu_width;
       float gt[8], up[8];
-      unpack8<__nv_bfloat16>(ld_x(reinterpret_cast<const __nv_bfloat16*>(p.x) + static_cast<int64_t>(blk) * 2 * p.swiglu_width + i), gt);
-      unpack8<__nv_bfloat16>(ld_x(reinterpret_cast<const __nv_bfloat16*>(p.x) + static_cast<int64_t>(blk) * 2 * p.swiglu_width + p.swiglu_width + i), up);
+      unpack8<__nv_bfloat16>(ld_x(static_cast<int64_t>(blk) * 2 * p.swiglu_width + i), gt);
+      unpack8<__nv_bfloat16>(ld_x(static_cast<int64_t>(blk) * 2 * p.swiglu_width + p.swiglu_width + i), up);
 #pragma unroll
       for (int e = 0; e < 8; ++e) gt[e] = gt[e] / (1.0f + __expf(-gt[e])) * up[e];
       return pack8_bf16(gt);
     }
-    uint4 raw = ld_x(xg + pc * 8);
+    uint4 raw = ld_x(static_cast<int64_t>(pc) * 8);
     if (p.prologue == kProAddNorm && p.residual_in) {
       float a[8], r[8];
       unpack8<__nv_bfloat16>(raw, a);
-      unpack8<__nv_bfloat16>(ld_x(reinterpret_cast<const __nv_bfloat16*>(p.residual_in) + pc * 8), r);
+      unpack8<__nv_bfloat16>(__ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.residual_in) + pc * 8)), r);
 #pragma unroll
       for (int e = 0; e < 8; ++e) a[e] += r[e];
       raw = pack8_bf16(a);             // the sum as it is stored: bf16
@@ -433,9 +441,23 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   const int magic4[4] = {static_cast<int>(kMagicBits), static_cast<int>(kMagicBits), static_cast<int>(kMagicBits),
                          static_cast<int>(kMagicBits)};
 
-  int cslot = 0, rbuf = 0;
+  int cslot = 0, rbuf = 0, prev_tile = -1;
   uint32_t cphase = 0;
   bool ok = true;
+  // A finished tile goes to every rank as stamped units (this rank's rows are a column block of
+  // the row every rank gathers): plain 16-byte peer stores of {pair, stamp, pair, stamp};
+  // lane <-> (rank, 8 rows); made by the last warp.
+  const uint32_t push_stamp = exchange_seq(epoch, p.push_site);
+  auto push_tile = [&](int tl, int buf) {
+    const int peer = lane / R, v = lane % R;
+    const int n8 = tl * kTileRows + v * 8;
+    if (peer < p.push_world && n8 < p.N) {
+      const uint4 d = *reinterpret_cast<const uint4*>(ypush + buf * kTileRows + v * 8);
+      uint4* dst = reinterpret_cast<uint4*>(p.push_dst[peer] + static_cast<int64_t>(n8) * 4);
+      dst[0] = make_uint4(d.x, push_stamp, d.y, push_stamp);
+      dst[1] = make_uint4(d.z, push_stamp, d.w, push_stamp);
+    }
+  };
   for (int tile = blockIdx.x; tile < ntiles; tile += tstride) {
     float ylo[R][2], yhi[R][2];
     uint32_t rowoff[R][2];           // byte offsets of the scale-table rows behind this lane's two MMA
@@ -588,6 +610,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
       if (threadIdx.x == 0) atomicCAS(p.status, 0, *abort_flag);
       return;
     }
+    if (p.push_world > 0 && prev_tile >= 0 && warp == NW - 1) push_tile(prev_tile, rbuf ^ 1);   // (complete since this barrier)
     // ---- rows x NW threads: the warps' shares (fixed order) plus the bias term ----
     if (frow < kTileRows) {
       const int n = tile * kTileRows + frow;
@@ -613,32 +636,21 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
 #pragma unroll
       for (int o = 1; o < NW; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
       if (nonfinite) s = __uint_as_float(0x7fc00000u);
-      if (fslice == 0 && n < p.N) {
-        if (p.y) {
+      if (fslice == 0) {
+        if (p.y && n < p.N) {
           if (p.y_dtype == QMM_BF16) static_cast<__nv_bfloat16*>(p.y)[n] = __float2bfloat16_rn(s);
           else if (p.y_dtype == QMM_F16) static_cast<__half*>(p.y)[n] = __float2half_rn(s);
           else static_cast<float*>(p.y)[n] = s;
         }
-        // this rank's rows are a column block of the row every rank gathers: plain peer stores
-        for (int r = 0; r < p.push_world; ++r) reinterpret_cast<__nv_bfloat16*>(p.push_dst[r])[n] = __float2bfloat16_rn(s);
+        if (p.push_world > 0) ypush[rbuf * kTileRows + frow] = __float2bfloat16_rn(s);
       }
     }
     rbuf ^= 1;
+    prev_tile = tile;
   }
   if (p.push_world > 0) {
-    // every store of this CTA is ordered before its count; the last CTA of the grid raises this
-    // rank's flag on every rank
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      if (atomicAdd(p.done, 1u) == gridDim.x - 1) {
-        *p.done = 0;
-        __threadfence_system();
-        const uint32_t seq = exchange_seq(epoch, p.push_site);
-        for (int r = 0; r < p.push_world; ++r)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r]), "r"(seq) : "memory");
-      }
-    }
+    __syncthreads();                 // the last tile's rows are in shared memory
+    if (warp == NW - 1 && prev_tile >= 0) push_tile(prev_tile, rbuf ^ 1);
   }
 }
 
@@ -654,7 +666,7 @@ size_t imma_smem(int r, int nw, int ring, int plane_bytes, int groups, bool mx) 
   const size_t xsum_words = mx ? 4 * static_cast<size_t>((groups + 7) & ~7) : static_cast<size_t>((groups + 7) & ~7);
   return 1024 + static_cast<size_t>(nw) * ring * r * 8 * kBoxBytes + 2 * static_cast<size_t>(plane_bytes) +
          xsum_words * 4 + static_cast<size_t>(2) * nw * 8 * r * 4 + static_cast<size_t>(nw) * kMaxRing * 8 +
-         64 + nw * 8 + 16;
+         64 + nw * 8 + 16 + 2 * 8 * r * 2;
 }
 
 int env_int(const char* name, int fallback) {
@@ -764,11 +776,10 @@ int launch_gemv_imma(const qmm_problem& p, cudaStream_t stream, const DecodeFusi
     ip.prologue = fusion->prologue;
     ip.residual_in = fusion->residual_in; ip.residual_out = fusion->residual_out;
     ip.norm_weight = fusion->norm_weight; ip.eps = fusion->eps; ip.swiglu_width = fusion->swiglu_width;
-    ip.epoch = fusion->epoch; ip.wait_flags = fusion->wait_flags;
+    ip.epoch = fusion->epoch;
     ip.wait_world = fusion->wait_world; ip.wait_site = fusion->wait_site;
     ip.push_world = fusion->push_world; ip.push_site = fusion->push_site;
-    for (int r = 0; r < 8; ++r) { ip.push_dst[r] = fusion->push_dst[r]; ip.push_flag[r] = fusion->push_flag[r]; }
-    ip.done = fusion->done;
+    for (int r = 0; r < 8; ++r) ip.push_dst[r] = fusion->push_dst[r];
     ip.spin_limit = wait_limit_clocks();
   }
   ip.x = p.x; ip.scales = p.scales; ip.biases = p.biases; ip.y = p.y;

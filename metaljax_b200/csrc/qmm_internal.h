@@ -52,12 +52,9 @@ struct DecodeFusion {
   float eps;
   int swiglu_width;
   const uint32_t* epoch;     // this rank's step counter
-  const uint32_t* wait_flags;
-  int wait_world, wait_site;
-  int push_world, push_site;
+  int wait_world, wait_site; // x is a stamped row in this rank's gather slot
+  int push_world, push_site; // y also goes, stamped, to every rank's slot
   uint8_t* push_dst[8];
-  uint32_t* push_flag[8];
-  uint32_t* done;
 };
 
 // The single-row (M = 1) integer tensor-core decode kernel; launch_gemv hands it what it takes.

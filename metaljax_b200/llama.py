@@ -265,23 +265,19 @@ class DecodeStep:
                 ok = torch.ones((), device=dev, dtype=torch.int32)
                 try:
                     import torch.distributed._symmetric_memory as symm_mem
-                    self._fslot_bytes = -(-(2 * sh.ffn * 2) // 256) * 256    # the widest gathered row: [gate | up]
-                    self._fsymm = symm_mem.empty((256 + 3 * self._fslot_bytes,), dtype=torch.uint8, device=dev)
+                    # two gather slots of the widest row, [gate | up], as stamped units (4 bytes per value)
+                    self._fslot_bytes = -(-(2 * sh.ffn * 4) // 256) * 256
+                    self._fsymm = symm_mem.empty((2 * self._fslot_bytes,), dtype=torch.uint8, device=dev)
                     self._fsymm.zero_()
                     hdl = symm_mem.rendezvous(self._fsymm, group if group is not None else dist.group.WORLD)
                     self._fsymm_hdl = hdl
-                    ptrs = [int(p_) for p_ in hdl.buffer_ptrs]
-                    self._fpeer_flags = (ctypes.c_void_p * g)(*ptrs)
-                    self._fpeer_bufs = (ctypes.c_void_p * g)(*[p_ + 256 for p_ in ptrs])
-                    self._fstate = torch.zeros((8,), device=dev, dtype=torch.int32)       # [0] epoch, [4] CTA counter
+                    self._fpeer_bufs = (ctypes.c_void_p * g)(*[int(p_) for p_ in hdl.buffer_ptrs])
+                    self._fstate = torch.zeros((8,), device=dev, dtype=torch.int32)       # [0] the step counter
                     ex = _lib.Exchange()
                     ex.peer_bufs = ctypes.cast(self._fpeer_bufs, ctypes.POINTER(ctypes.c_void_p))
-                    ex.peer_flags = ctypes.cast(self._fpeer_flags, ctypes.POINTER(ctypes.c_void_p))
-                    ex.epoch, ex.done = self._fstate.data_ptr(), self._fstate.data_ptr() + 16
+                    ex.epoch = self._fstate.data_ptr()
                     ex.slot_bytes, ex.rank, ex.world = self._fslot_bytes, r, g
                     self._ex = ex
-                    self._fslots = [self._fsymm[256 + i * self._fslot_bytes: 256 + (i + 1) * self._fslot_bytes].view(torch.bfloat16)
-                                    for i in range(3)]
                 except Exception as exc:                          # noqa: BLE001 -- any setup failure
                     self._peer_error = repr(exc)
                     ok.zero_()
@@ -365,7 +361,7 @@ class DecodeStep:
         if self._ex is not None:
             _lib.check(_lib.lib().qmm_decode_step_begin(ctypes.byref(self._ex), stream))
         pos = sh.ctx - 1
-        site = 0                      # exchanges of this step so far; exchange i uses slot i % 3
+        site = 0                      # exchanges of this step so far; exchange i uses slot i % 2
         down_wait = None              # (slot, site) of the previous layer's down projection
         x_in = self.emb_row
         for li, layer in enumerate(self.layers):
@@ -373,20 +369,20 @@ class DecodeStep:
             self._fused_linear(layer["qkv"], None if down_wait else x_in, self.qkv, prologue=1, wait=down_wait,
                                residual_in=None if li == 0 else self.res2[0], residual_out=self.res2[1],
                                norm_weight=layer["ln1"])
-            at_push = (site % 3, site) if g > 1 else None
+            at_push = (site % 2, site) if g > 1 else None
             decode_attention(self.qkv, self.k_cache[li], self.v_cache[li], None if g > 1 else self.attn_l, self.attn_scratch,
                              self.h_l, self.kv_l, hd, pos, sh.theta, push=at_push, ex=self._ex)
             site += g > 1
             # o ; gate_up <- rmsnorm(residual + o) ; R1 -> R0 ; down <- silu(gate) * up
-            o_push = (site % 3, site) if g > 1 else None
+            o_push = (site % 2, site) if g > 1 else None
             self._fused_linear(layer["o"], None if g > 1 else self.attn_l, None if g > 1 else self.o_l, wait=at_push, push=o_push)
             site += g > 1
-            gu_push = (site % 3, site) if g > 1 else None
+            gu_push = (site % 2, site) if g > 1 else None
             self._fused_linear(layer["gate_up"], None if g > 1 else self.o_l, None if g > 1 else self.gate_up, prologue=1,
                                wait=o_push, push=gu_push, residual_in=self.res2[1], residual_out=self.res2[0],
                                norm_weight=layer["ln2"])
             site += g > 1
-            dn_push = (site % 3, site) if g > 1 else None
+            dn_push = (site % 2, site) if g > 1 else None
             self._fused_linear(layer["down"], None if g > 1 else self.gate_up, None if g > 1 else self.down_l,
                                prologue=2, wait=gu_push, push=dn_push)
             site += g > 1
@@ -454,8 +450,8 @@ class DecodeStep:
     def exchange_description(self) -> str:
         """How the slices of a sharded linear reach the other ranks (for benchmark records)."""
         if self.fused and self.world > 1:
-            return ("peer stores from the epilogue of each sharded kernel (attention, o, gate/up, down), flags awaited "
-                    "by the kernel that consumes the row")
+            return ("stamped peer stores from the epilogue of each sharded kernel (attention, o, gate/up, down), read "
+                    "as they arrive by the kernel that consumes the row")
         return {"none": "none (one rank)", "peer": "one-shot peer-store kernel over NVLink after each sharded linear",
                 "nccl": "NCCL all-gather after each sharded linear",
                 "skip": "left out (timing experiment)"}[self.gather_mode]

@@ -124,11 +124,20 @@ def match_router(S) -> Router:
 
 def verify_router(r: Router, device=None, draws=VERIFY_DRAWS) -> bool:
     """Evaluate the router tail on synthetic logits and compare S, exactly, with `w` scattered at
-    `indices` (src/metaljax/moe.py:1112-1160). Fails the match closed if an axis was misread."""
+    `indices`, a few draws (src/metaljax/moe.py:1112-1153). The draws are the reference's: one
+    generator seeded 20260803, standard normal `[T, E]`; every draw after the first is rounded to
+    halves, because exact ties are where a top-k and a hand-rolled scatter would most easily
+    disagree (`:1128-1131`). A token with more than K nonzero routing weights also fails the
+    match (`:1144-1152`). Fails closed: an axis misread, an op the evaluator lacks -> False."""
+    import numpy as np
     logits = r.top_k.operands[0]
-    for d in range(draws):
-        g = torch.Generator().manual_seed(1234 + d)
-        draw = torch.randn(logits.type.shape, generator=g).to(logits.type.dtype).to(device)
+    rng = np.random.default_rng(20260803)
+    k = r.indices.type.shape[-1]
+    for d in range(max(1, draws)):
+        raw = rng.standard_normal(tuple(logits.type.shape)).astype(np.float32)
+        if d:
+            raw = np.round(raw * 2.0) / 2.0
+        draw = torch.from_numpy(raw).to(logits.type.dtype).to(device)
         env = {logits: draw}
         try:
             S = hlo.evaluate_value(r.S, env)
@@ -136,10 +145,14 @@ def verify_router(r: Router, device=None, draws=VERIFY_DRAWS) -> bool:
             w = hlo.evaluate_value(r.weights, env)
         except (KeyError, NotImplementedError):
             return False
-        want = torch.zeros((r.T, r.E), dtype=torch.float64, device=S.device)
-        want.scatter_add_(1, idx, w.to(torch.float64))
         got = S if r.t_axis < r.e_axis else S.transpose(0, 1)
-        if not torch.equal(got.to(torch.float64), want.to(S.dtype).to(torch.float64)):
+        if tuple(got.shape) != (r.T, r.E):
+            return False
+        want = torch.zeros((r.T, r.E), dtype=got.dtype, device=S.device)
+        want.index_put_((torch.arange(r.T, device=S.device)[:, None].expand_as(idx), idx), w.to(got.dtype), accumulate=True)
+        if not torch.equal(got, want):
+            return False
+        if int((got != 0).sum(dim=1).max().item()) > k:
             return False
     STATS["verified"] += 1
     return True

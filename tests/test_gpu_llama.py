@@ -112,8 +112,8 @@ def test_single_row_step_fused_against_unfused(monkeypatch):
 def test_decode_linear_prologues_and_self_exchange():
     """`qmm_decode_linear` against the unfused sequence: SwiGLU prologue bit for bit (the same
     bf16 row reaches the same kernel), add + RMS-norm within a bf16 rounding of the row; and the
-    exchange protocol on one GPU as a world of one: a linear pushes its row into its own gather
-    slot, the next one waits for the flag and reads the row from the slot, over several steps."""
+    exchange protocol on one GPU as a world of one: a linear pushes its row, as stamped units, into
+    its own gather slot, the next one reads the row from the slot as it arrives, over several steps."""
     import ctypes
     from metaljax_b200 import _lib, llama, qmm
     g = torch.Generator(device=DEV).manual_seed(5)
@@ -158,15 +158,13 @@ def test_decode_linear_prologues_and_self_exchange():
     call(down, gu_ref, dn, prologue=2)
     assert torch.equal(dn, dn_ref)
     # the same chain through a gather slot of a world of one, three steps in a row
-    slot_bytes = 2 * f * 2
-    area = torch.zeros((3 * slot_bytes,), device=DEV, dtype=torch.uint8)
-    flags = torch.zeros((24,), device=DEV, dtype=torch.int32)
+    slot_bytes = 2 * f * 4                               # a stamped row: 4 bytes per value
+    area = torch.zeros((2 * slot_bytes,), device=DEV, dtype=torch.uint8)
     state = torch.zeros((8,), device=DEV, dtype=torch.int32)
     ex = _lib.Exchange()
-    bufs, flg = (ctypes.c_void_p * 1)(area.data_ptr()), (ctypes.c_void_p * 1)(flags.data_ptr())
+    bufs = (ctypes.c_void_p * 1)(area.data_ptr())
     ex.peer_bufs = ctypes.cast(bufs, ctypes.POINTER(ctypes.c_void_p))
-    ex.peer_flags = ctypes.cast(flg, ctypes.POINTER(ctypes.c_void_p))
-    ex.epoch, ex.done, ex.slot_bytes, ex.rank, ex.world = state.data_ptr(), state.data_ptr() + 16, slot_bytes, 0, 1
+    ex.epoch, ex.slot_bytes, ex.rank, ex.world = state.data_ptr(), slot_bytes, 0, 1
     out = torch.empty((1, 384), device=DEV, dtype=torch.bfloat16)
     want = torch.empty_like(out)
     h3 = torch.empty_like(x)
@@ -179,8 +177,10 @@ def test_decode_linear_prologues_and_self_exchange():
         call(down, None, None, ex, prologue=2, wait=(0, 0), push=(1, 1))
         call(nxt, None, out, ex, prologue=1, wait=(1, 1), residual_in=h2, residual_out=h3, norm_weight=wn)
         torch.cuda.synchronize()
-        assert int(state[0]) == step + 1 and int(state[4]) == 0
-        assert int(flags[0]) == ((step + 1) << 10) | 1 and int(flags[8]) == ((step + 1) << 10) | 2
+        assert int(state[0]) == step + 1
+        units = area.view(torch.int32)                    # {pair, stamp} units: every stamp of a row is the exchange's
+        assert bool((units[1: 2 * f: 2] == (((step + 1) << 10) | 1)).all())
+        assert bool((units[slot_bytes // 4 + 1: slot_bytes // 4 + d: 2] == (((step + 1) << 10) | 2)).all())
         assert (out.float() - want.float()).abs().max() <= 3e-2 * want.float().abs().max()
     assert _lib.poll_status() == 0
 

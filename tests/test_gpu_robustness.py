@@ -173,3 +173,36 @@ def test_two_devices_in_one_process():
                                          group_size=64, bits=4)
                 assert O.rel_err(to_numpy(y).astype(np.float32), O.qmm_exact(x, w, s, b, 64, 4)) <= 1e-2
                 assert _lib.poll_status() == 0
+
+
+def test_stamped_row_that_never_arrives():
+    """A fused decode linear whose activation row is a gather slot nobody fills: the bounded wait
+    of the consuming kernel runs out (limit about a millisecond), the status word reports 100,
+    the call returns, and the library works afterwards."""
+    g = torch.Generator(device=DEV).manual_seed(4)
+    lin = llama._Linear(64, 256, DEV, g, 64, "normal")
+    area = torch.zeros((2 * 256 * 4,), device=DEV, dtype=torch.uint8)
+    state = torch.ones((8,), device=DEV, dtype=torch.int32)
+    ex = _lib.Exchange()
+    bufs = (ctypes.c_void_p * 1)(area.data_ptr())
+    ex.peer_bufs = ctypes.cast(bufs, ctypes.POINTER(ctypes.c_void_p))
+    ex.epoch, ex.slot_bytes, ex.rank, ex.world = state.data_ptr(), 256 * 4, 0, 1
+    fz = _lib.DecodeFusion()
+    fz.wait_slot, fz.wait_site, fz.push_slot = 0, 5, -1
+    y = torch.zeros((1, 64), device=DEV, dtype=torch.bfloat16)
+    p = lin.problem(None, y)
+    lib = _lib.lib()
+    _lib.check(lib.qmm_set_wait_limit(2_000_000))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    _lib.check(lib.qmm_decode_linear(ctypes.byref(p), ctypes.byref(fz), ctypes.byref(ex), _lib.stream_ptr(y)))
+    stop.record()
+    torch.cuda.synchronize()
+    assert start.elapsed_time(stop) < 200.0
+    st = ctypes.c_int(0)
+    assert lib.qmm_poll_status(ctypes.byref(st)) == 9 and st.value == 100        # QMM_ERR_TIMEOUT
+    assert _lib.poll_status() == 0
+    x = torch.randn((1, 256), generator=g, device=DEV).to(torch.bfloat16)
+    want = (x.float() @ lin.dense().float().T)
+    lin(x, y)
+    assert float((y.float() - want).abs().max()) <= 2e-2 * float(want.abs().max())

@@ -74,3 +74,38 @@ def test_literal_evaluation_of_the_layer_matches_einsum():
     y = torch.einsum("tef,edf->etd", torch.nn.functional.silu(g) * u, wd)
     want = (y * S.T[:, :, None]).sum(0)
     assert (got - want).abs().max() <= 3e-2 * want.abs().max()
+
+
+def test_router_verification_forces_ties_and_counts_nonzeros():
+    """A hand-rolled router that keeps every logit >= the k-th largest agrees with top-k until two
+    logits tie at the k-th place: then it routes a token to K + 1 experts. The reference's
+    verification rounds its later draws to halves exactly to provoke that
+    (src/metaljax/moe.py:1128-1131) and counts the nonzeros per token (`:1144-1152`); a
+    verification on the first, continuous draw alone would have accepted this router."""
+    from metaljax_b200 import hlo
+    from metaljax_b200 import moe_recognizer as M
+    text = """
+module @threshold_router {
+  func.func public @main(%arg0: tensor<64x8xf32>) -> (tensor<64x8xf32>) {
+    %0:2 = chlo.top_k(%arg0, k = 2) : tensor<64x8xf32> -> (tensor<64x2xf32>, tensor<64x2xi32>)
+    %1 = stablehlo.slice %0#0 [0:64, 1:2] : (tensor<64x2xf32>) -> tensor<64x1xf32>
+    %2 = stablehlo.reshape %1 : (tensor<64x1xf32>) -> tensor<64xf32>
+    %3 = stablehlo.broadcast_in_dim %2, dims = [0] : (tensor<64xf32>) -> tensor<64x8xf32>
+    %4 = stablehlo.compare GE, %arg0, %3 : (tensor<64x8xf32>, tensor<64x8xf32>) -> tensor<64x8xi1>
+    %cst = stablehlo.constant dense<0.000000e+00> : tensor<64x8xf32>
+    %5 = stablehlo.select %4, %arg0, %cst : tensor<64x8xi1>, tensor<64x8xf32>
+    return %5 : tensor<64x8xf32>
+  }
+}
+"""
+    fn = hlo.parse(text)
+    ops = {o.name: o for o in fn.walk()}
+    r = M.Router()
+    r.top_k = ops["chlo.top_k"]
+    r.indices, r.weights = r.top_k.results[1], r.top_k.results[0]
+    r.S = ops["stablehlo.select"].results[0]
+    r.T, r.K, r.E, r.t_axis, r.e_axis = 64, 2, 8, 0, 1
+    before = M.STATS["verified"]
+    assert M.verify_router(r, draws=1)                  # continuous logits: no ties, looks like top-2
+    assert not M.verify_router(r, draws=3)              # halves: ties at the second place give it away
+    assert M.STATS["verified"] == before + 1
