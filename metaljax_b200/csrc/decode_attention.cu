@@ -29,7 +29,7 @@ struct AttnParams {
   __nv_bfloat16* k_cache;        // [batch, kv_heads, ctx, HD]
   __nv_bfloat16* v_cache;
   __nv_bfloat16* out;            // [batch, heads * HD], or NULL
-  float* part;                   // scratch: [batch, kv_heads, splits, REP, HD + 2]
+  float* part;                   // scratch: [batch, kv_heads, splits, REP, HD + 4]
   uint32_t* counters;            // scratch: [batch * kv_heads], zero between calls
   int heads, kv_heads, splits;
   int64_t ctx, pos;
@@ -39,6 +39,9 @@ struct AttnParams {
   uint8_t* push_dst[8];          // every rank's slot + this rank's column block (stamped units: 4 bytes per value)
   int64_t push_row_bytes;        // bytes between batch rows of the gathered matrix
   const uint32_t* epoch;
+#if QMM_STEP_TRACING
+  unsigned long long* trace;
+#endif
 };
 
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
@@ -76,11 +79,17 @@ __device__ __forceinline__ void block_reduce(float (&v)[REP], float (*scratch)[4
 template <int HD, int REP>
 __global__ void __launch_bounds__(kAttnThreads)
 decode_attention_kernel(const AttnParams p) {
+#if QMM_STEP_TRACING
+  unsigned long long* const trace = p.trace;
+#else
+  unsigned long long* const trace = nullptr;
+  (void)trace;
+#endif
+  QMM_TRACE(trace, 0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int kPieces = HD / 8;                   // 16-byte pieces per row
   constexpr int kSubs = kAttnThreads / kPieces;     // position subgroups of the value sum
-  constexpr int kStat = HD + 2;
+  constexpr int kStat = HD + 4;                     // (max, sum) after the values; rows stay 16-byte aligned
   __shared__ __align__(16) float q_s[REP][HD];      // rotated queries, scaled by 1/sqrt(HD)
   __shared__ __align__(16) float knew[HD], vnew[HD];
   __shared__ __align__(16) float prob[REP][kAttnThreads];
@@ -99,6 +108,29 @@ decode_attention_kernel(const AttnParams p) {
   const int64_t lo = split * per, hi = (lo + per < len) ? lo + per : len;
   __nv_bfloat16* kc = p.k_cache + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.ctx * HD;
   __nv_bfloat16* vc = p.v_cache + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.ctx * HD;
+
+  // The first chunk's key and value rows are requested before this kernel waits for the one
+  // that writes the query row: the cache holds earlier positions only (the decode position's
+  // own row is never read back), so the trip to memory runs under the predecessor's tail.
+  const int piece = tid % kPieces, sub = tid / kPieces;
+  uint4 kr[kPieces], vr[kPieces];
+  auto request = [&](int64_t c0) {
+    const int64_t pp = c0 + tid;
+    const int chunk_len = static_cast<int>((hi - c0 < kAttnThreads) ? hi - c0 : kAttnThreads);
+#pragma unroll
+    for (int u = 0; u < kPieces; ++u) {
+      const int i = sub + u * kSubs;
+      vr[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < chunk_len && c0 + i != p.pos) vr[u] = __ldg(reinterpret_cast<const uint4*>(vc + (c0 + i) * HD) + piece);
+    }
+    if (pp < hi && pp != p.pos) {
+#pragma unroll
+      for (int d8 = 0; d8 < kPieces; ++d8) kr[d8] = __ldg(reinterpret_cast<const uint4*>(kc + pp * HD) + d8);
+    }
+  };
+  if (lo < hi) request(lo);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  QMM_TRACE(trace, 1);
 
   // ---- rotary embedding of this head group's queries and key (rotate-half pairing), the value ----
   constexpr int kHalf = HD / 2;
@@ -128,6 +160,7 @@ decode_attention_kernel(const AttnParams p) {
     }
   }
 
+  QMM_TRACE(trace, 2);               // queries rotated
   // ---- the slice, in chunks of 128 positions ----
   float m_run[REP], l_run[REP], acc[REP][8];
 #pragma unroll
@@ -137,30 +170,16 @@ decode_attention_kernel(const AttnParams p) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[h][e] = 0.0f;
   }
-  const int piece = tid % kPieces, sub = tid / kPieces;
   for (int64_t c0 = lo; c0 < hi; c0 += kAttnThreads) {
-    // scores: thread <-> position
+    // scores: thread <-> position. This thread's key row and value rows of the chunk were
+    // requested together (one round trip to memory serves both; the first chunk's before the wait)
     const int64_t pp = c0 + tid;
     const int chunk_len = static_cast<int>((hi - c0 < kAttnThreads) ? hi - c0 : kAttnThreads);
-    // this thread's value rows of the chunk are requested now, with its key row: they do not
-    // depend on the scores, and one round trip to memory then serves both
-    uint4 vr[kPieces];
-#pragma unroll
-    for (int u = 0; u < kPieces; ++u) {
-      const int i = sub + u * kSubs;
-      vr[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (i < chunk_len && c0 + i != p.pos) vr[u] = __ldg(reinterpret_cast<const uint4*>(vc + (c0 + i) * HD) + piece);
-    }
+    if (c0 != lo) request(c0);
     float s[REP];
 #pragma unroll
     for (int h = 0; h < REP; ++h) s[h] = 0.0f;
     if (pp < hi) {
-      // the whole key row is requested before the first product (one round trip, not sixteen)
-      uint4 kr[kPieces];
-      if (pp != p.pos) {
-#pragma unroll
-        for (int d8 = 0; d8 < kPieces; ++d8) kr[d8] = __ldg(reinterpret_cast<const uint4*>(kc + pp * HD) + d8);
-      }
 #pragma unroll
       for (int d8 = 0; d8 < kPieces; ++d8) {
         float kf[8];
@@ -225,6 +244,7 @@ decode_attention_kernel(const AttnParams p) {
     __syncthreads();                               // prob may be overwritten
   }
 
+  QMM_TRACE(trace, 3);               // the slice is done
   // ---- this slice's (max, sum, weighted values) to scratch ----
 #pragma unroll
   for (int h = 0; h < REP; ++h)
@@ -252,6 +272,7 @@ decode_attention_kernel(const AttnParams p) {
     is_last = last;
   }
   __syncthreads();
+  QMM_TRACE(trace, 4);               // partials published
   if (!is_last) return;
   __threadfence();
 
@@ -285,40 +306,32 @@ decode_attention_kernel(const AttnParams p) {
     }
   }
   __syncthreads();
-  for (int i = tid; i < REP * HD / 8; i += kAttnThreads) {        // thread <-> 8 consecutive dimensions
-    const int h = i / (HD / 8), d0 = (i - h * (HD / 8)) * 8;
-    float num[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 4
+  const uint32_t stamp = p.push_world > 0
+      ? (*reinterpret_cast<const volatile uint32_t*>(p.epoch) << 10) | static_cast<uint32_t>(p.push_site + 1) : 0u;
+  for (int i = tid; i < REP * HD / 4; i += kAttnThreads) {        // thread <-> 4 consecutive dimensions
+    const int h = i / (HD / 4), d0 = (i - h * (HD / 4)) * 4;
+    float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
     for (int sp = 0; sp < p.splits; ++sp) {
-      const float* ps = all + (sp * REP + h) * kStat + d0;      // (kStat is even: 8-byte aligned)
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(all + (sp * REP + h) * kStat + d0));
       const float w = wsplit[h][sp];
-#pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        const float2 v = __ldcg(reinterpret_cast<const float2*>(ps + e));
-        num[e] = fmaf(w, v.x, num[e]);
-        num[e + 1] = fmaf(w, v.y, num[e + 1]);
-      }
+      num.x = fmaf(w, v.x, num.x); num.y = fmaf(w, v.y, num.y);
+      num.z = fmaf(w, v.z, num.z); num.w = fmaf(w, v.w, num.w);
     }
     const float inv = 1.0f / denom[h];
-    uint32_t packed[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const __nv_bfloat162 v = __floats2bfloat162_rn(num[2 * e] * inv, num[2 * e + 1] * inv);
-      packed[e] = *reinterpret_cast<const uint32_t*>(&v);
-    }
-    const uint4 o = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    const __nv_bfloat162 v0 = __floats2bfloat162_rn(num.x * inv, num.y * inv);
+    const __nv_bfloat162 v1 = __floats2bfloat162_rn(num.z * inv, num.w * inv);
+    const uint2 o = make_uint2(*reinterpret_cast<const uint32_t*>(&v0), *reinterpret_cast<const uint32_t*>(&v1));
     const int64_t col = static_cast<int64_t>(kvh * REP + h) * HD + d0;
-    if (p.out) *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(b) * p.heads * HD + col) = o;
+    if (p.out) *reinterpret_cast<uint2*>(p.out + static_cast<int64_t>(b) * p.heads * HD + col) = o;
     if (p.push_world > 0) {
       // to every rank as stamped units {pair, stamp}: data and arrival in one store
-      const uint32_t stamp = (*reinterpret_cast<const volatile uint32_t*>(p.epoch) << 10) | static_cast<uint32_t>(p.push_site + 1);
-      for (int r = 0; r < p.push_world; ++r) {
-        uint4* dst = reinterpret_cast<uint4*>(p.push_dst[r] + b * p.push_row_bytes + col * 4);
-        dst[0] = make_uint4(o.x, stamp, o.y, stamp);
-        dst[1] = make_uint4(o.z, stamp, o.w, stamp);
-      }
+      const uint4 unit = make_uint4(o.x, stamp, o.y, stamp);
+      for (int r = 0; r < p.push_world; ++r)
+        *reinterpret_cast<uint4*>(p.push_dst[r] + b * p.push_row_bytes + col * 4) = unit;
     }
   }
+  QMM_TRACE(trace, 6);               // (the combining CTA only)
 }
 
 template <int HD, int REP>
@@ -332,7 +345,13 @@ int launch_attention(const AttnParams& p, int64_t batch, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+#if QMM_STEP_TRACING
+  AttnParams traced = p;
+  traced.trace = next_trace_block(8);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attention_kernel<HD, REP>, traced);
+#else
   cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attention_kernel<HD, REP>, p);
+#endif
   if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "decode_attention_kernel launch: %s", cudaGetErrorString(e));
   count_launch();
   return check_launch("decode_attention_kernel");
@@ -357,7 +376,7 @@ using namespace qmm;
 extern "C" int64_t qmm_decode_attention_scratch_bytes(int64_t batch, int heads, int kv_heads, int head_dim, int64_t ctx) {
   if (batch < 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || ctx <= 0) return 0;
   const int64_t splits = 64;                                     // the most a call ever uses
-  return batch * kv_heads * splits * (heads / kv_heads) * (head_dim + 2) * 4 + (batch * kv_heads + 1) * 4 + 256;
+  return batch * kv_heads * splits * (heads / kv_heads) * (head_dim + 4) * 4 + (batch * kv_heads + 1) * 4 + 256;
 }
 
 extern "C" int qmm_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, void* scratch,
@@ -392,7 +411,7 @@ extern "C" int qmm_decode_attention(const void* qkv, void* k_cache, void* v_cach
   if (splits < 1) splits = 1;
   p.splits = static_cast<int>(splits);
   const int rep = heads / kv_heads;
-  const int64_t part_bytes = batch * kv_heads * 64 * rep * (head_dim + 2) * 4;
+  const int64_t part_bytes = batch * kv_heads * 64 * rep * (head_dim + 4) * 4;
   p.part = static_cast<float*>(scratch);
   p.counters = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + ((part_bytes + 255) & ~int64_t(255)));
   if (pushes) {

@@ -90,6 +90,9 @@ struct ImmaParams {
   int push_site;            //      of every rank's slot
   uint8_t* push_dst[8];
   long long spin_limit;
+#if QMM_STEP_TRACING
+  unsigned long long* trace;
+#endif
 };
 
 enum { kProNone = 0, kProAddNorm = 1, kProSwiglu = 2 };
@@ -235,6 +238,13 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   volatile int* abort_flag = reinterpret_cast<volatile int*>(amax_w + 2 * NW);
   __nv_bfloat16* ypush = reinterpret_cast<__nv_bfloat16*>(amax_w + 2 * NW + 4);   // [2][kTileRows]: a finished tile on its way to the other ranks
 
+#if QMM_STEP_TRACING
+  unsigned long long* const trace = p.trace;
+#else
+  unsigned long long* const trace = nullptr;
+  (void)trace;
+#endif
+  QMM_TRACE(trace, 0);               // CTA resident
   // ---- barriers, then this warp's first boxes: before anything else ----
   uint64_t* full = full_all + warp * kMaxRing;
   uint8_t* wring = smem + warp * ring * kBoxSmem;
@@ -283,6 +293,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
 
   // ---- the activation row: after everything the previous kernel wrote is visible ----
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  QMM_TRACE(trace, 1);               // predecessor done (or flushed)
   const uint32_t epoch = (p.wait_world > 0 || p.push_world > 0) ? *reinterpret_cast<const volatile uint32_t*>(p.epoch) : 0u;
   const uint32_t wait_stamp = exchange_seq(epoch, p.wait_site);
   // Eight consecutive elements of x starting at element `i` (a multiple of 8): plain memory, or a
@@ -354,6 +365,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   }
   if (lane == 0) { amax_w[warp] = mag; amax_w[NW + warp] = __float_as_uint(ss); }
   __syncthreads();
+  QMM_TRACE(trace, 2);               // the whole row has arrived and been read once
   mag = 0;
   ss = 0.0f;
 #pragma unroll
@@ -431,6 +443,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
     }
   }
   __syncthreads();                   // the staged activations, their sums and the zeros are in place
+  QMM_TRACE(trace, 3);               // digits staged
 
   // what one unit of an accumulator is worth: rows g (digit 2(g&1)) and g + 8 (the next digit)
   const float ps_lo = __uint_as_float((ebits - 29u + 16u * (g & 1) - (QK == kMx4 ? 1u : 0u)) << 23);   // 2^(e - 156 + 8 digit)
@@ -646,12 +659,15 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
       }
     }
     rbuf ^= 1;
+    if (prev_tile < 0) QMM_TRACE(trace, 4);   // first tile done
     prev_tile = tile;
   }
+  QMM_TRACE(trace, 5);               // all tiles done
   if (p.push_world > 0) {
     __syncthreads();                 // the last tile's rows are in shared memory
     if (warp == NW - 1 && prev_tile >= 0) push_tile(prev_tile, rbuf ^ 1);
   }
+  QMM_TRACE(trace, 6);
 }
 
 struct ImmaPlan {
@@ -695,7 +711,13 @@ int launch_r(const CUtensorMap& wm, const ImmaParams& ip, const ImmaPlan& plan, 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+#if QMM_STEP_TRACING
+  ImmaParams traced = ip;
+  traced.trace = next_trace_block(1 + ip.prologue);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, wm, traced);
+#else
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, wm, ip);
+#endif
   if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "qmm_gemv_imma_kernel launch: %s", cudaGetErrorString(e));
   count_launch();
   return check_launch("qmm_gemv_imma_kernel");

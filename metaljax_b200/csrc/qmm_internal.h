@@ -64,6 +64,32 @@ bool gemv_imma_supports(const qmm_problem& p);
 int check_problem(const qmm_problem& p);
 int launch_gemm_tc(const qmm_problem& p, cudaStream_t stream);
 bool gemm_tc_supports(const qmm_problem& p);
+// Development builds (-DQMM_STEP_TRACING=1): every launch of the decode-step kernels takes the
+// next block of a caller-provided buffer and its CTAs stamp %globaltimer at fixed points
+// (8 stamps per CTA, 512 CTAs per block). Off in the product build: no parameter, no code.
+#ifndef QMM_STEP_TRACING
+#define QMM_STEP_TRACING 0
+#endif
+#if QMM_STEP_TRACING
+constexpr int kTraceStamps = 8, kTraceCtas = 512;
+unsigned long long* next_trace_block(int kind);
+#ifdef __CUDACC__
+__device__ __forceinline__ void trace_mark(unsigned long long* t, int slot) {
+  if (t && threadIdx.x == 0) {
+    const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta < kTraceCtas) {
+      unsigned long long g;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+      t[cta * kTraceStamps + slot] = g;
+    }
+  }
+}
+#endif
+#define QMM_TRACE(t, slot) trace_mark(t, slot)
+#else
+#define QMM_TRACE(t, slot) ((void)0)
+#endif
+
 // Reads (and clears) the current device's status word.
 int read_status_word(int* out);
 

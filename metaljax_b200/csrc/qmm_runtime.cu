@@ -115,3 +115,26 @@ const ScratchBlock* scratch_override() { return t_scratch; }
 void set_scratch_override(const ScratchBlock* block) { t_scratch = block; }
 
 }  // namespace qmm
+
+#if QMM_STEP_TRACING
+namespace qmm {
+namespace {
+unsigned long long* g_trace_base = nullptr;
+int64_t g_trace_blocks = 0, g_trace_next = 0;
+int* g_trace_kinds = nullptr;
+}  // namespace
+unsigned long long* next_trace_block(int kind) {
+  if (!g_trace_base || g_trace_next >= g_trace_blocks) return nullptr;
+  if (g_trace_kinds) g_trace_kinds[g_trace_next] = kind;
+  return g_trace_base + (g_trace_next++) * kTraceStamps * kTraceCtas;
+}
+}  // namespace qmm
+// `buf`: device memory of blocks * 8 * 512 uint64, zeroed by the caller; `kinds`: host ints, one per block.
+extern "C" void qmm_debug_set_trace(void* buf, int64_t blocks, int* kinds) {
+  qmm::g_trace_base = static_cast<unsigned long long*>(buf);
+  qmm::g_trace_blocks = blocks;
+  qmm::g_trace_next = 0;
+  qmm::g_trace_kinds = kinds;
+}
+extern "C" int64_t qmm_debug_trace_count() { return qmm::g_trace_next; }
+#endif

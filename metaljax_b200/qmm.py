@@ -518,12 +518,162 @@ def build_pack(m: Match, codes, scale_map, zero_map=None, leaves=()) -> _Pack:
         pack = _Pack(leaves, w, s, b,
                      None if perm is None else torch.as_tensor(perm, device=codes.device),
                      gs, bits, "affine")
+    return _record_pack(m, pack)
+
+
+def _record_pack(m: Match, pack: _Pack) -> _Pack:
+    pack = _share(pack)
     m.gs, m.bits, m.has_perm = pack.gs, pack.bits, pack.perm is not None
     m.nvals = len(pack.arrays())
     m.packs.insert(0, pack)
     del m.packs[_MAX_PACKS:]
     STATS["packs"] += 1
     return pack
+
+
+# Packs that are still alive, grouped by a digest of their contents. jax lowers a decode loop's
+# prefill and its while body as two separate dots over one set of weights, and two programs of
+# one model are handed the same weights in different buffers: without this a model's packed
+# weights would be held once per chain (src/metaljax/qmm.py:1645-1704). Entries are weak.
+_SHARED = {}
+_MAX_SHARED = int(os.environ.get("METALJAX_QMM_SHARE", "512"))
+
+
+def _digest(a: torch.Tensor) -> int:
+    """A cheap content digest of a packed array; it only narrows the search."""
+    u = a.contiguous().reshape(-1)
+    if u.numel() == 0:
+        return 0
+    nbytes = u.numel() * u.element_size()
+    u8 = u.view(torch.uint8)
+    if nbytes % 4:
+        u8 = torch.cat([u8, u8.new_zeros(4 - nbytes % 4)])
+    v = u8.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    idx = torch.arange(v.numel(), device=v.device, dtype=torch.int64)
+    mixed = ((v ^ ((idx * 2654435761) & 0xFFFFFFFF)) * _MIX) & 0xFFFFFFFF
+    mixed = mixed ^ (mixed >> 15)
+    return int(mixed.sum().item()) & 0xFFFFFFFFFFFF
+
+
+def _share(pk: _Pack) -> _Pack:
+    """Alias `pk`'s arrays onto an identical earlier pack's, if one is alive. Content-addressed:
+    nothing is aliased until the arrays compare equal element for element, so two chains that
+    reconstruct the same weight share one copy and two that do not can never be confused."""
+    arrays = pk.arrays()
+    key = (pk.mode, pk.gs, pk.bits, len(arrays), str(arrays[0].device),
+           tuple((tuple(a.shape), a.dtype) for a in arrays), _digest(arrays[0]))
+    bucket = _SHARED.get(key)
+    if bucket is not None:
+        for i, refs in enumerate(bucket):
+            other = [r() for r in refs]
+            if any(o is None for o in other):
+                continue
+            if all(a is b or bool(torch.equal(a, b)) for a, b in zip(arrays, other)):
+                pk.w, pk.scales = other[0], other[1]
+                rest = list(other[2:])
+                if pk.biases is not None:
+                    pk.biases = rest.pop(0)
+                if pk.perm is not None:
+                    pk.perm = rest.pop(0)
+                bucket.insert(0, bucket.pop(i))
+                STATS["shared"] = STATS.get("shared", 0) + 1
+                return pk
+    if len(_SHARED) > _MAX_SHARED:
+        _SHARED.clear()                                  # coarse, and only ever costs a repack
+    bucket = _SHARED.setdefault(key, [])
+    bucket[:] = [refs for refs in bucket if all(r() is not None for r in refs)]
+    bucket.insert(0, [weakref.ref(a) for a in arrays])
+    return pk
+
+
+class BlockedPacker:
+    """`build_pack` for a weight that arrives one block of rows at a time (`add`), so that the
+    reconstruction chain -- several times wider than the weight -- is never alive whole
+    (src/metaljax/qmm.py:1360-1400, 1723-1915). Per block only what the final decisions need is
+    kept: the codes (one byte or two per element until the bit width is known), the first scale
+    and zero of every 32 columns, the running code range. `finish` takes the same decisions as
+    `build_pack` from those and returns an identical pack.
+
+    A block whose maps are not constant within groups of 32 would need the column regrouping,
+    which looks at whole columns: `NeedsWhole` is raised and the caller evaluates whole.
+    """
+
+    class NeedsWhole(Exception):
+        pass
+
+    def __init__(self, m: Match, k: int):
+        self.m, self.k = m, k
+        self.codes, self.scale_heads, self.zero_heads = [], [], []
+        self.lo, self.hi = None, None
+        self.sdt = None
+        if m.mode == "mxfp4" and k % _MXFP4_GROUP:
+            raise _Reject(f"K={k} is not a multiple of 32")
+
+    def add(self, codes, scale_map, zero_map=None):
+        g0 = _GROUP_SIZES[-1]
+        if self.m.mode == "mxfp4":
+            if not _group_const(scale_map, _MXFP4_GROUP):
+                raise _Reject("MXFP4 scales are not constant within groups of 32")
+            self.codes.append(pack_codes(mxfp4_codes(codes), 4))
+            self.scale_heads.append(mxfp4_scale_bytes(_group_heads(scale_map, _MXFP4_GROUP)))
+            return
+        c = codes
+        if c.dtype in _FLOATS and not bool(torch.all(c == torch.round(c)).item()):
+            raise _Reject("codes are not integers")
+        c = c.to(torch.int64)
+        lo, hi = int(c.min().item()), int(c.max().item())
+        self.lo = lo if self.lo is None else min(self.lo, lo)
+        self.hi = hi if self.hi is None else max(self.hi, hi)
+        if self.hi - self.lo + 1 > 256:
+            raise _Reject(f"codes span {self.hi - self.lo + 1} values: more than 8 bits")
+        if lo < -32768 or hi > 32767:
+            raise BlockedPacker.NeedsWhole("codes outside 16 bits")
+        self.codes.append(c.to(torch.int16))
+        if self.k % g0 or not _group_const(scale_map, g0) or (zero_map is not None and not _group_const(zero_map, g0)):
+            raise BlockedPacker.NeedsWhole("maps are not constant within groups of 32 as laid out")
+        self.sdt = scale_map.dtype if scale_map.dtype in _FLOATS else torch.float32
+        self.scale_heads.append(_group_heads(scale_map, g0))
+        if zero_map is not None:
+            self.zero_heads.append(_group_heads(zero_map, g0))
+
+    def finish(self, leaves, prefix) -> _Pack:
+        """`prefix` is the shape in front of the last axis (`[B, N]` or `[N]`)."""
+        m, k = self.m, self.k
+        join = lambda parts: (parts[0] if len(parts) == 1 else torch.cat(parts, 0))
+        fold = lambda t: t.reshape(list(prefix) + [t.shape[-1]])
+        if m.mode == "mxfp4":
+            pack = _Pack(leaves, fold(join(self.codes)), fold(join(self.scale_heads)), None, None, _MXFP4_GROUP, 4, "mxfp4")
+            STATS["mxfp4"] += 1
+            return _record_pack(m, pack)
+        lo, hi = self.lo, self.hi
+        span = hi - lo + 1
+        bits = 4 if span <= 16 else 8
+        half = 1 << (bits - 1)
+        off = half if (lo >= -half and hi < half) else -lo
+        g0 = _GROUP_SIZES[-1]
+        sh = join(self.scale_heads)
+        zh32 = join(self.zero_heads) if self.zero_heads else None
+        gs = _pick_group_heads(k, sh, zh32)
+        if gs is None:
+            raise _Reject("scale/zero maps are not constant within legal groups")
+        step = gs // g0
+        sh = sh[..., ::step].contiguous()
+        zh = None
+        if zh32 is not None:
+            zh = zh32[..., ::step].contiguous().to(torch.float32)
+            if not bool(torch.all(zh == torch.round(zh)).item()):
+                raise _Reject("zero points are not integers")
+            if float(zh.abs().max().item()) > 32768:
+                raise _Reject("zero points out of range")
+            if m.sub_range is not None:
+                zlo, zhi = int(zh.min().item()), int(zh.max().item())
+                if (lo - zhi) < m.sub_range[0] or (hi - zlo) > m.sub_range[1]:
+                    raise _Reject("integer zero-point subtraction can wrap")
+        words = [pack_codes(c.to(torch.int32) + off, bits) for c in self.codes]
+        self.codes = []
+        s, b = _scale_bias(sh, zh, off, self.sdt)
+        pack = _Pack(leaves, fold(join(words)), fold(s), fold(b), None, gs, bits, "affine")
+        return _record_pack(m, pack)
 
 
 # --------------------------------------------------------------------------------------

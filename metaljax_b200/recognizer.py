@@ -29,6 +29,8 @@ literally (`hlo.eval_op`).
 
 from __future__ import annotations
 
+import os
+import re
 import weakref
 
 import torch
@@ -403,7 +405,210 @@ def _cached_build(key, leaves):
     return pack
 
 
+# Weight elements evaluated per block: the reconstruction chain is several times wider than its
+# result, so a block of 2^24 elements keeps the transient within a few hundred MB
+# (src/metaljax/qmm.py:1253-1259).
+_BLOCK_ELEMS = int(os.environ.get("METALJAX_QMM_BLOCK", str(1 << 24)))
+# Ceiling on a value the blocking reads WHOLE for every block (a decode table, a splat): a big
+# one means the blocking misread the graph, and evaluating whole is the honest answer.
+_WHOLE_MAX = 1 << 22
+
+# Ops whose evaluator is a pure function of the arrays it is handed, so that a slice of the
+# leading axis of every operand gives that slice of the result (src/metaljax/qmm.py:1274-1292).
+_ROW_LOCAL = frozenset("""
+    stablehlo.abs stablehlo.add stablehlo.and stablehlo.ceil stablehlo.clamp stablehlo.compare
+    stablehlo.convert stablehlo.divide stablehlo.exponential stablehlo.floor stablehlo.log
+    stablehlo.maximum stablehlo.minimum stablehlo.multiply stablehlo.negate stablehlo.not
+    stablehlo.or stablehlo.power stablehlo.round_nearest_even stablehlo.rsqrt stablehlo.select
+    stablehlo.shift_left stablehlo.shift_right_arithmetic stablehlo.shift_right_logical
+    stablehlo.sign stablehlo.sqrt stablehlo.subtract stablehlo.tanh stablehlo.xor
+    stablehlo.bitcast_convert
+""".split())
+
+
+class _NotBlockable(Exception):
+    """The subtree cannot be evaluated one block of rows at a time. Not a `_Reject`: the weight
+    still packs, from a whole evaluation."""
+
+
+class _RowBlocks:
+    """A match's operand subtrees evaluated one slice of the weight's leading axis at a time
+    (src/metaljax/qmm.py:1360-1631). Every op on the way has to be row-local: the slice of its
+    result must be its result on the slices. That is free for an element-wise op and a rule
+    about the dimension attributes of the others (`_ev`). A value read through a gather (a
+    decode table) or broadcast along the leading axis is wanted whole by every block, and has
+    to be small. Anything else raises `_NotBlockable`."""
+
+    def __init__(self, interp, m, args):
+        self.m = m
+        self.env = dict(zip(interp.func.args, args))
+        self.whole = dict(self.env)                              # memo of the small whole-evaluated values
+        self.lead = int(m.rshape[0]) if m.rshape else 0
+        per = _prod(m.rshape[1:]) if m.rshape else 0
+        self.step = None
+        if m.rshape and list(m.rperm)[:1] == [0] and self.lead > 1 and self.lead * per > _BLOCK_ELEMS:
+            self.step = max(1, _BLOCK_ELEMS // max(per, 1))
+
+    def blocks(self):
+        return [(lo, min(lo + self.step, self.lead)) for lo in range(0, self.lead, self.step)]
+
+    def rows(self, value, lo, hi, memo, like=None):
+        """`value`'s rows of block [lo, hi) as a `[rows, K]` matrix (batch and row axes folded);
+        `like` is the shape the chain broadcasts the value to before the post ops."""
+        m = self.m
+        t = self._ev(value, True, lo, hi, memo)
+        if like is not None and list(t.shape[1:]) != list(like[1:]):
+            t = t.expand([hi - lo] + list(like[1:]))
+        for op in m.post:                                        # reshapes / transposes after the multiply
+            shape = list(op.results[0].type.shape)
+            if not shape or shape[0] != self.lead:
+                raise _NotBlockable(f"{op.name} folds the leading axis")
+            if op.name == "stablehlo.reshape":
+                t = t.reshape([hi - lo] + shape[1:])
+            elif op.name == "stablehlo.transpose":
+                if op.attrs["dims"][0] != 0:
+                    raise _NotBlockable("a transpose moves the leading axis")
+                t = t.permute(*op.attrs["dims"])
+            elif op.name in _ROW_LOCAL and op.name in hlo.EVAL:
+                t = hlo.EVAL[op.name](op, t)
+            else:
+                raise _NotBlockable(op.name)
+        if list(t.shape) != [hi - lo] + list(m.rshape[1:]):
+            raise _NotBlockable(f"a block evaluated to {list(t.shape)}")
+        return t.permute(*m.rperm).reshape(-1, m.K)
+
+    def _whole(self, v):
+        if _prod(v.type.shape) > _WHOLE_MAX:
+            raise _NotBlockable(f"a value of {_prod(v.type.shape)} elements is wanted whole by every block")
+        return hlo.evaluate_value(v, self.whole)
+
+    def _ev(self, v, row, lo, hi, memo):
+        if not row:
+            return self._whole(v)
+        got = memo.get(v)
+        if got is not None:
+            return got
+        shape = list(v.type.shape)
+        if not shape or shape[0] != self.lead:
+            raise _NotBlockable(f"%{v.name} of shape {shape} has no row axis")
+        bshape = [hi - lo] + shape[1:]
+        if v.op is None:
+            t = self.env.get(v)
+            if t is None:
+                outer = hlo.invariant_init(v)
+                if outer is None:
+                    raise _Reject("unbound value in operand subtree")
+                out = self._ev(outer, True, lo, hi, memo)
+            else:
+                out = t[lo:hi]
+            memo[v] = out
+            return out
+        op, n = v.op, v.op.name
+        ev = lambda o, r=True: self._ev(o, r, lo, hi, memo)
+        if n in _ROW_LOCAL and n in hlo.EVAL:
+            out = hlo.EVAL[n](op, *[ev(o) for o in op.operands])
+        elif n == "stablehlo.constant":
+            if re.search(r"dense<\s*[^\[\]<>]+\s*>", op.text):  # a splat: one value however big the type
+                one = hlo._dense(op.text, hlo.TensorType((), v.type.el))
+                dev = next((t.device for t in self.env.values()), None)
+                out = one.to(dev).reshape([1] * len(bshape)).expand(bshape)
+            else:
+                out = self._whole(v)[lo:hi]
+        elif n == "stablehlo.broadcast_in_dim":
+            dims, src = list(op.attrs["dims"]), op.operands[0]
+            sshape = list(src.type.shape)
+            rowwise = 0 in dims and sshape[dims.index(0)] == self.lead
+            if rowwise and dims.index(0) != 0:
+                raise _NotBlockable("a broadcast moves the leading axis")
+            x = ev(src, rowwise)
+            view = [1] * len(bshape)
+            for i, d in enumerate(dims):
+                view[d] = x.shape[i]
+            out = x.reshape(view).expand(bshape)
+        elif n == "stablehlo.reshape":
+            src = op.operands[0]
+            if not src.type.shape or src.type.shape[0] != self.lead:
+                raise _NotBlockable("a reshape folds the leading axis")
+            out = ev(src).reshape(bshape)
+        elif n == "stablehlo.transpose":
+            if op.attrs["dims"][0] != 0:
+                raise _NotBlockable("a transpose moves the leading axis")
+            out = ev(op.operands[0]).permute(*op.attrs["dims"])
+        elif n == "stablehlo.gather":
+            a = op.attrs
+            table, idx = op.operands
+            if a["collapsed_slice_dims"] != [0] or a["start_index_map"] != [0] or a.get("operand_batching_dims") \
+                    or a["slice_sizes"][1:] != list(table.type.shape[1:]):
+                raise _NotBlockable("a gather that is not a row take")
+            tb, ix = ev(table, False), ev(idx)
+            ivd = a["index_vector_dim"]
+            ix = ix.select(ivd, 0) if ivd < ix.dim() else ix
+            out = tb[ix.to(torch.int64).clamp(0, tb.shape[0] - 1)].reshape(bshape)
+        elif n == "stablehlo.concatenate":
+            if op.attrs["dim"] == 0:
+                raise _NotBlockable("a concatenation along the leading axis")
+            out = torch.cat([ev(o) for o in op.operands], dim=op.attrs["dim"])
+        elif n == "stablehlo.slice":
+            sl = op.attrs["slices"]
+            if not sl or tuple(sl[0][:2]) != (0, self.lead) or (len(sl[0]) > 2 and sl[0][2] != 1):
+                raise _NotBlockable("a slice of the leading axis")
+            x = ev(op.operands[0])
+            out = x[(slice(None),) + tuple(slice(*s) for s in sl[1:])]
+        else:
+            raise _NotBlockable(n)
+        if list(out.shape) != bshape:
+            raise _NotBlockable(f"{n} evaluated to {list(out.shape)} for a block of {bshape}")
+        memo[v] = out
+        return out
+
+
+def _build_blocked(src, m, leaves):
+    """The pack from row blocks: the same decisions as `qmm.build_pack`, the same arrays."""
+    packer = qmm.BlockedPacker(m, m.K)
+    like = None
+    if not m.recip and m.required:
+        like = list(m.ops[m.required[0]].results[0].type.shape)
+    inv = None
+    if m.recip:                                                  # one scale per output channel, small
+        s = hlo.evaluate_value(m.scale, src.whole)
+        dims = list(m.bcast_dims)
+        if dims != sorted(dims):
+            order = sorted(range(len(dims)), key=lambda i: dims[i])
+            s, dims = s.permute(*order), sorted(dims)
+        interim = [1] * len(m.nshape)
+        for i, d in enumerate(dims):
+            interim[d] = s.shape[i]
+        inv = (1.0 / s.reshape(interim).expand(m.nshape).reshape(m.N, 1).to(torch.float32))
+    rows_per = _prod(m.rshape[1:]) // m.K
+    for lo, hi in src.blocks():
+        memo = {}
+        codes = src.rows(m.codes, lo, hi, memo, None if m.recip else like)
+        if m.recip:
+            if m.bshape:
+                raise _NotBlockable("a batched per-channel weight")
+            packer.add(codes, inv[lo * rows_per: hi * rows_per].expand(-1, m.K), None)
+        else:
+            scale = src.rows(m.scale, lo, hi, memo, like)
+            zero = None if m.zero is None else src.rows(m.zero, lo, hi, memo, like)
+            packer.add(codes, scale, zero)
+        del memo
+    qmm.STATS["blocked"] = qmm.STATS.get("blocked", 0) + 1
+    return packer.finish(leaves, [m.B, m.N] if m.bshape else [m.N])
+
+
 def _build(interp, m, args, leaves):
+    src = _RowBlocks(interp, m, args)
+    if src.step is not None:
+        try:
+            return _build_blocked(src, m, leaves)
+        except (_NotBlockable, qmm.BlockedPacker.NeedsWhole, NotImplementedError) as why:
+            qmm.STATS["unblocked"] = qmm.STATS.get("unblocked", 0) + 1
+            if qmm._DEBUG:
+                print(f"[metaljax] qmm: {m.name} packs from a whole evaluation ({why})", flush=True)
+    return _build_whole(interp, m, args, leaves)
+
+
+def _build_whole(interp, m, args, leaves):
     fn = interp.func
     env = dict(zip(fn.args, args))
     shape = m.codes.type.shape if not m.post else None
@@ -491,6 +696,166 @@ def prologue(interp, args) -> bool:
         st.rebuild()
     st.values = vals
     return changed
+
+
+# ---------------------------------------------------------------------------------------
+# what a host that traces / compiles blocks asks the recognizer
+# ---------------------------------------------------------------------------------------
+
+_UNKNOWN_TRIP = 1024            # a loop whose bound is not static is charged this many bodies
+
+
+def _scalar_constant(v):
+    if v is None or v.op is None or v.op.name != "stablehlo.constant" or _prod(v.type.shape) != 1:
+        return None
+    try:
+        return int(hlo._dense(v.op.text, v.type).reshape(()).item())
+    except Exception:
+        return None
+
+
+def static_trip(loop):
+    """Iterations of a counted `stablehlo.while` (carry i starts at a constant, the condition is
+    `carry_i < constant`, the body returns `carry_i + 1`), or None (src/metaljax/ops/control.py:289-301)."""
+    if loop.name != "stablehlo.while" or len(loop.regions) != 2:
+        return None
+    cond, body = loop.regions
+    if len(cond.returns) != 1 or cond.returns[0].op is None:
+        return None
+    cmp_ = cond.returns[0].op
+    if cmp_.name != "stablehlo.compare" or cmp_.attrs.get("direction") != "LT":
+        return None
+    counter, bound = cmp_.operands
+    end = _scalar_constant(bound)
+    if end is None or counter.op is not None or counter not in cond.args:
+        return None
+    i = cond.args.index(counter)
+    start = _scalar_constant(loop.operands[i])
+    nxt = body.returns[i].op if i < len(body.returns) else None
+    if start is None or nxt is None or nxt.name != "stablehlo.add":
+        return None
+    a, b = nxt.operands
+    step = _scalar_constant(b) if a is body.args[i] else _scalar_constant(a) if b is body.args[i] else None
+    if step != 1:
+        return None
+    return max(end - start, 1)
+
+
+def _state_of(interp):
+    st = analyze(interp)
+    return st if st is not None and st.matches else None
+
+
+def block_cost(interp, block) -> int:
+    """Approximate op count of `block` when it is traced with loops unrolled: an op the rewrite
+    absorbed costs nothing (it never runs), a fused root costs 2 units (one kernel plus the
+    activation reshuffle), a loop its body times the trip count -- 1024 when the bound is not
+    static, so that an unknown loop can never look cheap (src/metaljax/ops/control.py:251-312)."""
+    st = _state_of(interp)
+    cost = 0
+    for op in block.ops:
+        if st is not None:
+            if id(op) in st.roots:
+                cost += 2
+                continue
+            if id(op) in st.skip:
+                continue
+        cost += 1
+        if op.name == "stablehlo.while" and len(op.regions) == 2:
+            trip = static_trip(op)
+            cost += (trip if trip is not None else _UNKNOWN_TRIP) * block_cost(interp, op.regions[1])
+        else:
+            for region in op.regions:
+                cost += block_cost(interp, region)
+    return cost
+
+
+def value_bytes(v) -> int:
+    t = v.type
+    bits = 8 if t.el == "i1" else int(re.sub(r"\D", "", t.el) or 8)
+    return (_prod(t.shape) * bits + 7) // 8
+
+
+def op_bytes(op) -> int:
+    """Declared result bytes; a splat constant is one element however big its type says
+    (src/metaljax/interpreter.py:162-199)."""
+    if op.name == "stablehlo.constant" and re.search(r"dense<\s*[-+0-9.eE xa-fA-Fin]+\s*>", op.text):
+        return sum((value_bytes(r) // max(_prod(r.type.shape), 1)) or 1 for r in op.results)
+    return sum(value_bytes(r) for r in op.results)
+
+
+def block_bytes(interp, block) -> int:
+    """Approximate device bytes materialized when `block` is traced: the same walk as
+    `block_cost`, absorbed ops charged nothing, a fused root its result plus what the emission
+    builds in the chain's place (`emit_bytes`: one copy of the activation; for an expert block
+    the pair-space intermediates), loops unrolled (src/metaljax/ops/control.py:317-423)."""
+    st = _state_of(interp)
+    total = 0
+    for op in block.ops:
+        if st is not None:
+            root = st.roots.get(id(op))
+            if root is not None:
+                total += op_bytes(op)
+                try:
+                    total += qmm.emit_bytes(root)
+                except Exception:                                # an unsizable plan must not zero the block
+                    pass
+                continue
+            if id(op) in st.skip:
+                continue
+        total += op_bytes(op)
+        if op.name == "stablehlo.while" and len(op.regions) == 2:
+            trip = static_trip(op)
+            total += (trip if trip is not None else _UNKNOWN_TRIP) * block_bytes(interp, op.regions[1])
+        else:
+            for region in op.regions:
+                total += block_bytes(interp, region)
+    return total
+
+
+def free_values(block):
+    """Values `block` reads but neither defines nor takes as arguments, in first-use order
+    (what a compiled body must be handed explicitly)."""
+    own = set(block.args)
+    free, seen = [], set()
+
+    def rec(b):
+        for op in b.ops:
+            for v in op.operands:
+                if v not in own and v not in seen:
+                    seen.add(v)
+                    free.append(v)
+            for region in op.regions:
+                own.update(region.args)
+                rec(region)
+            own.update(op.results)
+    rec(block)
+    return free
+
+
+def captures(interp, env, free):
+    """The buffers a compiled body takes besides its carries: its free values, then the packed
+    arrays of every live rewrite -- those travel as explicit inputs so that a repack reaches a
+    body that was already compiled. A free value the rewrite absorbed in the enclosing block has
+    no buffer; nothing in the body can read it (its consumers are absorbed too), so a stand-in
+    keeps the body's arity stable (src/metaljax/ops/control.py:700-725)."""
+    st = interp._qmm
+    skipped = set()
+    if st is not None and st.matches:
+        skipped = st.skip
+    caps = []
+    for v in free:
+        t = env.get(v)
+        if t is None and v.op is not None and id(v.op) in skipped:
+            t = _ABSORBED
+        elif t is None:
+            t = env[v]                                           # missing for another reason: raise
+        caps.append(t)
+    caps.extend(qmm.values(interp))
+    return caps
+
+
+_ABSORBED = torch.zeros((), dtype=torch.uint8)
 
 
 # ---------------------------------------------------------------------------------------

@@ -67,6 +67,41 @@ module @jit_dense_mxfp4 {{
 }}
 """
 
+def mxfp4_expert_program(e, m, k, n):
+    """The MXFP4 chain of `MXFP4` over a stack of `e` expert weights `[e, n, k]` (one code per
+    byte, one E8M0 byte per 32), contracted with `[e, m, k]` activations expert by expert."""
+    g = k // 32
+    return f"""
+module @jit_expert_mxfp4 {{
+  func.func public @main(%arg0: tensor<{e}x{m}x{k}xbf16>, %arg1: tensor<{e}x{n}x{k}xui8>, %arg2: tensor<{e}x{n}x{g}xui8>) -> (tensor<{e}x{m}x{n}xbf16>) {{
+    %cst = stablehlo.constant dense<[{_VTABLE}]> : tensor<16xbf16>
+    %cst_0 = stablehlo.constant dense<[{_STABLE}]> : tensor<256xf32>
+    %0 = stablehlo.convert %arg1 : (tensor<{e}x{n}x{k}xui8>) -> tensor<{e}x{n}x{k}xi32>
+    %1 = stablehlo.reshape %0 : (tensor<{e}x{n}x{k}xi32>) -> tensor<{e}x{n}x{k}x1xi32>
+    %2 = "stablehlo.gather"(%cst, %1) <{{dimension_numbers = #stablehlo.gather<collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 3>, indices_are_sorted = false, slice_sizes = array<i64: 1>}}> : (tensor<16xbf16>, tensor<{e}x{n}x{k}x1xi32>) -> tensor<{e}x{n}x{k}xbf16>
+    %3 = stablehlo.convert %arg2 : (tensor<{e}x{n}x{g}xui8>) -> tensor<{e}x{n}x{g}xi32>
+    %4 = stablehlo.reshape %3 : (tensor<{e}x{n}x{g}xi32>) -> tensor<{e}x{n}x{g}x1xi32>
+    %5 = "stablehlo.gather"(%cst_0, %4) <{{dimension_numbers = #stablehlo.gather<collapsed_slice_dims = [0], start_index_map = [0], index_vector_dim = 3>, indices_are_sorted = false, slice_sizes = array<i64: 1>}}> : (tensor<256xf32>, tensor<{e}x{n}x{g}x1xi32>) -> tensor<{e}x{n}x{g}xf32>
+    %6 = stablehlo.convert %5 : (tensor<{e}x{n}x{g}xf32>) -> tensor<{e}x{n}x{g}xbf16>
+    %7 = stablehlo.reshape %2 : (tensor<{e}x{n}x{k}xbf16>) -> tensor<{e}x{n}x{g}x32xbf16>
+    %8 = stablehlo.broadcast_in_dim %6, dims = [0, 1, 2] : (tensor<{e}x{n}x{g}xbf16>) -> tensor<{e}x{n}x{g}x32xbf16>
+    %9 = stablehlo.multiply %7, %8 : tensor<{e}x{n}x{g}x32xbf16>
+    %10 = stablehlo.reshape %9 : (tensor<{e}x{n}x{g}x32xbf16>) -> tensor<{e}x{n}x{k}xbf16>
+    %11 = stablehlo.dot_general %arg0, %10, batching_dims = [0] x [0], contracting_dims = [2] x [2] : (tensor<{e}x{m}x{k}xbf16>, tensor<{e}x{n}x{k}xbf16>) -> tensor<{e}x{m}x{n}xbf16>
+    return %11 : tensor<{e}x{m}x{n}xbf16>
+  }}
+}}
+"""
+
+
+def mxfp4_expert_inputs(e, m, k, n, seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((e, m, k), generator=g).to(torch.bfloat16).to(device)
+    codes = torch.randint(0, 16, (e, n, k), generator=g, dtype=torch.uint8).to(device)
+    scales = torch.randint(118, 126, (e, n, k // 32), generator=g, dtype=torch.uint8).to(device)
+    return [x, codes, scales]
+
+
 RMS_NORM = """
 module @jit_embed_norm_dot {
   func.func public @main(%arg0: tensor<3x64xf32>, %arg1: tensor<4x1xi32>, %arg2: tensor<100x64xf32>, %arg3: tensor<4xf32>) -> (tensor<3x4xf32>) {

@@ -88,3 +88,42 @@ def test_dense_moe_layer_becomes_the_gathered_block():
         it = _gate(moe_program(t, d, e, f), moe_inputs(t, d, e, f, seed=t, device=DEV))
         st = it._qmm
         assert len(st.moe) == 1 and st.moe[0].verified and all(m.absorbed for m in st.matches)
+
+
+def test_expert_stack_packs_in_row_blocks_within_a_memory_bound():
+    """A [32, 5760, 2880] MXFP4 expert weight (the shape the reference's pack-transient notes
+    measure, notes/qmm-pack-transient-2026-08.md:100-109): its reconstruction chain evaluated
+    whole holds tens of GB; evaluated one block of rows at a time the transient stays a small
+    multiple of one block, and the pack is the same."""
+    from metaljax_b200 import _lib, qmm, recognizer
+    from programs import mxfp4_expert_inputs, mxfp4_expert_program
+    e, m, k, n = 32, 4, 2880, 5760
+    args = mxfp4_expert_inputs(e, m, k, n, seed=11, device=DEV)
+    it = recognizer.Interpreter(mxfp4_expert_program(e, m, k, n))
+    qmm.reset_stats()
+    recognizer._BUILD_CACHE.clear()
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    recognizer.prologue(it, args)
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated() - base
+    mt = recognizer.analyze(it).matches[0]
+    assert not mt.disabled and qmm.stats()["blocked"] == 1, it.rejections
+    pk = mt.packs[0]
+    packed_bytes = sum(a.numel() * a.element_size() for a in pk.arrays())
+    assert packed_bytes == e * n * k // 2 + e * n * k // 32
+    # the whole chain would hold > 16 bytes per weight element (8.5 GB here) before the packer's own
+    # 64-bit temporaries; a block is 1/32 of that
+    assert peak < packed_bytes + (3 << 30), peak
+    for ex in (0, 17, e - 1):                                    # the pack itself, expert by expert
+        assert torch.equal(pk.w[ex], qmm.pack_codes(args[1][ex], 4))
+        assert torch.equal(pk.scales[ex], args[2][ex])
+    out = it.execute(args)[0]
+    assert it.fused_calls == 1 and _lib.poll_status() == 0
+    table = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0] + [-0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], device=DEV, dtype=torch.float64)
+    ex = e - 1
+    w = table[args[1][ex].long()] * torch.exp2(args[2][ex].double() - 127).repeat_interleave(32, dim=1)
+    want = args[0][ex].double() @ w.T
+    err = (out[ex].double() - want).abs().max().item() / want.abs().max().item()
+    assert err <= 1e-2, err

@@ -133,3 +133,168 @@ def test_weights_carried_through_a_loop():
         want = (want.to(torch.bfloat16).float() @ w.to(torch.bfloat16).float().T)
     assert torch.allclose(lit.float(), want.to(torch.bfloat16).float(), rtol=5e-2, atol=5e-2 * float(want.abs().max()))
     assert recognizer.prologue(it, args) is False and not m.disabled and (m.gs, m.bits) == (64, 4)
+
+
+def test_block_cost_bytes_and_captures():
+    """What a tracing host asks of the recognizer (the reference's ops/control.py:251-283,
+    317-401, 700-725): an absorbed op costs nothing, a fused root 2 units; loops are unrolled;
+    the packed arrays travel with a body's captures."""
+    it = recognizer.Interpreter(WHILE_LOOP)
+    fn = it.func
+    loop = next(o for o in fn.ops if o.name == "stablehlo.while")
+    body = loop.regions[1]
+    assert recognizer.static_trip(loop) == 3
+    # body: 7 reconstruction ops absorbed, the dot = 2 units, the counter's add = 1
+    assert recognizer.block_cost(it, body) == 3
+    # @main: three constants, the while itself, three bodies
+    assert recognizer.block_cost(it, fn) == 3 + 1 + 3 * 3
+    lit = recognizer.Interpreter(WHILE_LOOP)
+    lit._qmm = qmm.State()                                       # a program with no rewrite: every op counts
+    assert recognizer.block_cost(lit, lit.func.ops[3].regions[1]) == 9
+    # bytes: the body materializes the dot's result (5x256 bf16), one activation copy, the counter
+    assert recognizer.block_bytes(it, body) == 5 * 256 * 2 + 5 * 256 * 2 + 4
+    literal_body = recognizer.block_bytes(lit, lit.func.ops[3].regions[1])
+    assert literal_body > 7 * 256 * 256 * 2 // 2                 # the dequantize chain at full weight size
+    whole = recognizer.block_bytes(it, fn)
+    assert whole == 3 * 4 + (4 + 256 * 256 + 2 * 256 * 4 * 2 + 5 * 256 * 2) + 3 * recognizer.block_bytes(it, body)
+    # captures: free values of the body in first-use order, then the packed arrays
+    free = recognizer.free_values(body)
+    assert [v.name for v in free] == [fn.ops[2].results[0].name]           # only the constant 1
+    args = while_loop_inputs(seed=4)
+    recognizer.prologue(it, args)
+    env = {fn.ops[2].results[0]: torch.tensor(1, dtype=torch.int32)}
+    caps = recognizer.captures(it, env, free)
+    assert caps[0] is env[free[0]] and len(caps) == 1 + len(qmm.values(it)) and len(qmm.values(it)) == 3
+    assert all(a is b for a, b in zip(caps[1:], qmm.values(it)))
+
+
+def test_captures_stand_in_for_an_absorbed_value():
+    """A reconstruction op hoisted out of the loop is skipped in the enclosing block, so it has
+    no buffer; the body's capture list keeps its arity with a stand-in."""
+    it = recognizer.Interpreter(SUB_CHANNEL)
+    st = recognizer.analyze(it)
+    absorbed = next(o for o in it.func.ops if id(o) in st.skip)
+    caps = recognizer.captures(it, {}, [absorbed.results[0]])
+    assert caps[0].numel() == 1 and caps[0].dtype == torch.uint8
+    live = it.func.ops[-1].results[0]                            # not absorbed and not in env: an error, as before
+    try:
+        recognizer.captures(it, {}, [live])
+    except KeyError:
+        pass
+    else:
+        raise AssertionError("a missing live capture must raise")
+
+
+def test_unknown_trip_count_is_pessimistic():
+    text = WHILE_LOOP.replace("%1 = stablehlo.compare LT, %iterArg, %c_0, SIGNED", "%1 = stablehlo.compare NE, %iterArg, %c_0, SIGNED")
+    it = recognizer.Interpreter(text)
+    loop = next(o for o in it.func.ops if o.name == "stablehlo.while")
+    assert recognizer.static_trip(loop) is None
+    assert recognizer.block_cost(it, it.func) == 3 + 1 + 1024 * recognizer.block_cost(it, loop.regions[1])
+
+
+def test_real_jax_lowering_recognizes_nothing():
+    """The one program text in the reference's tree that jax itself printed (a shrunk qwen3
+    prefill, bf16 weights, a scan over layers, private callees): it parses, and an ordinary
+    float graph matches nothing -- no quantized dot, no expert block. Read from the reference
+    checkout where that exists; the file is not redistributed."""
+    import os
+    import pytest
+    path = os.path.join(os.environ.get("METALJAX_REFERENCE", "/root/reference"), "tests", "data", "qwen3_prefill_shrunk.mlir")
+    if not os.path.exists(path):
+        pytest.skip("no reference checkout on this machine")
+    it = recognizer.Interpreter(open(path).read())
+    fn = it.func
+    names = [o.name for o in fn.walk()]
+    assert fn.name == "main" and len(fn.args) > 8
+    assert names.count("stablehlo.while") == 1 and names.count("stablehlo.dot_general") >= 2 and "func.call" in names
+    loop = next(o for o in fn.ops if o.name == "stablehlo.while")
+    assert len(loop.regions) == 2 and recognizer.static_trip(loop) == 8          # one trip per layer
+    st = recognizer.analyze(it)
+    assert st.matches == [] and not st.roots and not st.skip
+    # with nothing absorbed the cost walk charges every op: 8 unrolled bodies dominate
+    body_cost = recognizer.block_cost(it, loop.regions[1])
+    assert body_cost >= len(loop.regions[1].ops)
+    assert recognizer.block_cost(it, fn) >= 8 * body_cost
+
+
+def _packs_equal(a, b):
+    xa, xb = a.arrays(), b.arrays()
+    return (a.gs, a.bits, a.mode, len(xa)) == (b.gs, b.bits, b.mode, len(xb)) and all(
+        p.dtype == q.dtype and p.shape == q.shape and torch.equal(p, q) for p, q in zip(xa, xb))
+
+
+def _build_both(text, args, block_elems, monkeypatch):
+    """The pack of every match from row blocks of `block_elems` weight elements and from one
+    whole evaluation; sharing off so that each build keeps its own arrays."""
+    out = []
+    for elems in (block_elems, 1 << 40):
+        monkeypatch.setattr(recognizer, "_BLOCK_ELEMS", elems)
+        monkeypatch.setattr(qmm, "_SHARED", {})
+        recognizer._BUILD_CACHE.clear()
+        qmm.reset_stats()
+        it = recognizer.Interpreter(text)
+        recognizer.prologue(it, args)
+        ms = [m for m in recognizer.analyze(it).matches]
+        assert ms and not any(m.disabled for m in ms), it.rejections
+        out.append(([m.packs[0] for m in ms], dict(qmm.stats())))
+    return out
+
+
+def test_row_blocked_build_equals_whole(monkeypatch):
+    """Packing from blocks of rows (the reference's `_Source`, src/metaljax/qmm.py:1360-1631)
+    takes the same decisions and gives the same arrays as packing from the whole maps."""
+    from programs import moe_inputs, moe_program, per_channel_inputs, sub_channel_inputs_at, sub_channel_program
+    cases = [
+        (sub_channel_program(4, 256, 96, gs=64), sub_channel_inputs_at(4, 256, 96, gs=64, seed=3), 256 * 10),
+        (MXFP4, mxfp4_inputs(seed=2), 64 * 3),
+        (WHILE_LOOP, while_loop_inputs(seed=5), 256 * 100),
+        (PER_CHANNEL, per_channel_inputs(seed=7), 0),
+        (moe_program(t=6, d=64, e=4, f=64, gs=32, k=2), moe_inputs(t=6, d=64, e=4, f=64, gs=32, seed=1), 64 * 64),
+    ]
+    for text, args, elems in cases:
+        if not elems:                                            # too small a weight to cut: sized below
+            w = next(a for a in args if a.dtype == torch.int8)
+            elems = w.shape[-1] * max(w.shape[0] // 3, 1)
+        (blocked, bstats), (whole, wstats) = _build_both(text, args, elems, monkeypatch)
+        if text is PER_CHANNEL:                                   # stored [K, N]: the leading axis is not the row axis
+            assert not bstats.get("blocked")
+        else:
+            assert bstats.get("blocked", 0) == len(blocked) and not bstats.get("unblocked"), bstats
+        assert not wstats.get("blocked")
+        assert len(blocked) == len(whole) and all(_packs_equal(a, b) for a, b in zip(blocked, whole))
+
+
+def test_row_blocked_build_rejects_like_whole(monkeypatch):
+    """A bad value in the LAST block is still found: codes off the integer grid reject."""
+    args = mxfp4_inputs(seed=2)
+    bad = args[1].clone()
+    monkeypatch.setattr(recognizer, "_BLOCK_ELEMS", 64 * 3)
+    recognizer._BUILD_CACHE.clear()
+    it = recognizer.Interpreter(MXFP4)
+    scales = args[2].clone()
+    scales[-1, -1] = 255                                          # E8M0 byte 255 decodes to NaN in the table: not a power of two
+    recognizer.prologue(it, [args[0], bad, scales])
+    assert recognizer.analyze(it).matches[0].disabled and it.rejections
+
+
+def test_share_aliases_equal_packs(monkeypatch):
+    """Two chains that reconstruct the same weight from different buffers hold one packed copy
+    (content-addressed: equal arrays, not equal graphs; src/metaljax/qmm.py:1652-1704)."""
+    monkeypatch.setattr(qmm, "_SHARED", {})
+    recognizer._BUILD_CACHE.clear()
+    qmm.reset_stats()
+    args = sub_channel_inputs(seed=6)
+    it1, it2 = recognizer.Interpreter(SUB_CHANNEL), recognizer.Interpreter(SUB_CHANNEL)
+    recognizer.prologue(it1, args)
+    copy = [a.clone() for a in args]                               # other buffers, same contents
+    recognizer.prologue(it2, copy)
+    p1, p2 = recognizer.analyze(it1).matches[0].packs[0], recognizer.analyze(it2).matches[0].packs[0]
+    assert p1 is not p2 and p1.w is p2.w and p1.scales is p2.scales and p1.biases is p2.biases
+    assert qmm.stats().get("shared") == 1
+    other = [a.clone() for a in args]
+    other[1][0, 0] = (other[1][0, 0] + 1) if int(other[1][0, 0]) < 7 else (other[1][0, 0] - 1)        # one code differs
+    it3 = recognizer.Interpreter(SUB_CHANNEL)
+    recognizer.prologue(it3, other)
+    p3 = recognizer.analyze(it3).matches[0].packs[0]
+    assert p3.w is not p1.w and not torch.equal(p3.w, p1.w) and qmm.stats().get("shared") == 1
