@@ -46,6 +46,8 @@ WORKLOADS = {
     "prefill_mxfp4_m512_5760x2880": (512, 2880, 5760, 32, 4, "mxfp4"),
     "prefill_mxfp4_m4096_5760x2880": (4096, 2880, 5760, 32, 4, "mxfp4"),
     "decode_int4_g64_m1_4096x4096": (1, 4096, 4096, 64, 4, "affine"),
+    "decode_int4_g64_m1_28672x4096": (1, 4096, 28672, 64, 4, "affine"),
+    "decode_int4_g64_m1_65536x4096": (1, 4096, 65536, 64, 4, "affine"),
     "decode_mxfp4_m1_5760x2880": (1, 2880, 5760, 32, 4, "mxfp4"),
 }
 L2_BYTES = 126 * 1024 * 1024
@@ -58,7 +60,7 @@ DEFAULT = "decode_llama3_8b_b64"
 # 8192 (token, expert) pairs plus the routed weighted sum. Over N ranks: experts split, tokens
 # split, pairs exchanged by all-to-all.
 MOE_BLOCKS = {"moe_mixtral_t4096": (4096, 2, 8, 4096, 14336)}
-ALSO_AT_ONE = ["decode_int4_g64_m1_4096x4096", "prefill_int4_g64_m2048_14336x4096", "prefill_int4_g64_m2048_4096x14336",
+ALSO_AT_ONE = ["decode_int4_g64_m1_4096x4096", "decode_int4_g64_m1_65536x4096", "prefill_int4_g64_m2048_14336x4096", "prefill_int4_g64_m2048_4096x14336",
                "prefill_int8_g128_m2048_14336x4096", "prefill_int8_g128_m2048_4096x14336", "decode_mxfp4_m1_5760x2880",
                "prefill_mxfp4_m512_5760x2880", "prefill_mxfp4_m4096_5760x2880", "moe_mixtral_t4096"]
 
@@ -201,6 +203,9 @@ class ClockSampler:
         return out
 
 
+PROFILE_WINDOW = False
+
+
 def time_device(fn, steps, warmup, torch, dist=None):
     """`steps` calls of `fn(i)` between CUDA events on the current stream; ms total."""
     for i in range(warmup):
@@ -210,11 +215,15 @@ def time_device(fn, steps, warmup, torch, dist=None):
         dist.barrier()
         torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if PROFILE_WINDOW:                 # a profiler started with --profile-from-start off sees the timed steps only
+        torch.cuda.profiler.start()
     start.record()
     for i in range(steps):
         fn(warmup + i)
     stop.record()
     torch.cuda.synchronize()
+    if PROFILE_WINDOW:
+        torch.cuda.profiler.stop()
     if dist is not None:
         dist.barrier()
         torch.cuda.synchronize()
@@ -665,7 +674,11 @@ def main():
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS) + sorted(DECODE_STEPS) + sorted(MOE_BLOCKS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-also", action="store_true", help="only the headline workload")
+    ap.add_argument("--profile-window", action="store_true",
+                    help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
+    global PROFILE_WINDOW
+    PROFILE_WINDOW = args.profile_window
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

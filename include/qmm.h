@@ -159,6 +159,22 @@ int qmm_ragged_dot(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* s
                    const qmm_tensor* biases, const qmm_tensor* group_sizes, qmm_tensor* y,
                    int group_size, int bits, int mode, void* stream);
 
+/* The two element-wise steps of a gathered expert block, raw pointers (dtype: QMM_BF16 |
+ * QMM_F16; 16-byte aligned). The reference runs them as generic pair-space ops after its
+ * gathered dots (src/metaljax/moe.py:1425-1461).
+ *
+ * qmm_moe_silu_mul: out[i] = silu(gate[i]) * up[i] over `elements` values (a multiple of 8),
+ * silu rounded to the storage type before the product, as the two-op form rounds it.
+ *
+ * qmm_moe_routed_sum: out[t, :] = sum over k of weights[t, k] * rows[row_of_pair[t*K + k], :]
+ * in float32 (product rounded, then added, k ascending), cast to the storage type; rows is
+ * [total_rows, width] (pairs sorted by expert), row_of_pair int64 [tokens * K] maps a pair in
+ * router order to its sorted row, weights float32 [tokens, K], width a multiple of 8. An index
+ * outside [0, total_rows) is clamped and reported (QMM_ERR_SHAPE from qmm_poll_status). */
+int qmm_moe_silu_mul(const void* gate, const void* up, void* out, int64_t elements, int dtype, void* stream);
+int qmm_moe_routed_sum(const void* rows, const int64_t* row_of_pair, const float* weights, void* out,
+                       int64_t tokens, int k, int64_t width, int64_t total_rows, int dtype, void* stream);
+
 /* Replaces `mx.dequantize(w, scales, biases, group_size, bits[, mode])`, which the
  * reference uses to pin the packed layout (tests/test_qmm.py:121,
  * tests/test_qmm_mxfp4.py:192): out [.., N, K] bf16 | f16 | f32, each element one

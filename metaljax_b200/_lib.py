@@ -93,6 +93,11 @@ _SIGNATURES = {
     "qmm_dequantize": (ctypes.c_int, [_T, _T, _T, _T, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_void_p]),
     "qmm_pack_codes": (ctypes.c_int, [_T, _T, ctypes.c_int, ctypes.c_void_p]),
+    "qmm_moe_silu_mul": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                        ctypes.c_int, ctypes.c_void_p]),
+    "qmm_moe_routed_sum": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_int64, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+                                          ctypes.c_void_p]),
     "qmm_launch": (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.c_void_p]),
     # include/qmm_decode.h
     "qmm_decode_add_rmsnorm": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.c_int64, ctypes.c_int64,

@@ -7,8 +7,10 @@
 //
 // One CTA per (batch row, key/value head, slice of the context): the query heads that share the
 // key/value head (grouped-query attention) are rotated once and kept in shared memory; the
-// slice's scores are taken thread-per-position, the softmax statistics per chunk of 128
-// positions, the value sum thread-per-(8 dimensions, position subgroup). Every slice writes
+// slice is walked in chunks of 128 positions by 512 threads (256 for eight query heads per
+// key/value head): scores by four (two) threads per position, each over an interleaved quarter
+// (half) of the head dimension, the softmax statistics per chunk, the value sum
+// thread-per-(8 dimensions, position subgroup). Every slice writes
 // (max, sum, weighted values) to scratch memory the caller provides; the last CTA of a
 // (row, head) to finish combines the slices and writes the row. The slice that contains the
 // decode position appends the rotated key and the value to the cache; that position is always
@@ -22,7 +24,7 @@
 namespace qmm {
 namespace {
 
-constexpr int kAttnThreads = 128;
+constexpr int kChunk = 128;                      // positions per chunk
 
 struct AttnParams {
   const __nv_bfloat16* qkv;      // [batch, (heads + 2 kv_heads) * HD]: q heads | k heads | v heads
@@ -55,9 +57,9 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   }
 }
 
-// Largest / sum over the CTA's 128 threads of REP values at once (all threads get the results).
-template <int REP, bool MAX>
-__device__ __forceinline__ void block_reduce(float (&v)[REP], float (*scratch)[4]) {
+// Largest / sum over the CTA's threads of REP values at once (all threads get the results).
+template <int REP, int WARPS, bool MAX>
+__device__ __forceinline__ void block_reduce(float (&v)[REP], float (*scratch)[WARPS]) {
 #pragma unroll
   for (int h = 0; h < REP; ++h)
 #pragma unroll
@@ -71,14 +73,20 @@ __device__ __forceinline__ void block_reduce(float (&v)[REP], float (*scratch)[4
     for (int h = 0; h < REP; ++h) scratch[h][threadIdx.x >> 5] = v[h];
   __syncthreads();
 #pragma unroll
-  for (int h = 0; h < REP; ++h)
-    v[h] = MAX ? fmaxf(fmaxf(scratch[h][0], scratch[h][1]), fmaxf(scratch[h][2], scratch[h][3]))
-               : (scratch[h][0] + scratch[h][1]) + (scratch[h][2] + scratch[h][3]);
+  for (int h = 0; h < REP; ++h) {
+    float r = scratch[h][0];
+#pragma unroll
+    for (int w = 1; w < WARPS; ++w) r = MAX ? fmaxf(r, scratch[h][w]) : r + scratch[h][w];
+    v[h] = r;
+  }
 }
 
 template <int HD, int REP>
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(REP <= 4 ? 512 : 256)
 decode_attention_kernel(const AttnParams p) {
+  constexpr int kAttnThreads = REP <= 4 ? 512 : 256;
+  constexpr int kWarps = kAttnThreads / 32;
+  constexpr int kTPP = kAttnThreads / kChunk;       // threads per position in the score phase
 #if QMM_STEP_TRACING
   unsigned long long* const trace = p.trace;
 #else
@@ -89,12 +97,14 @@ decode_attention_kernel(const AttnParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int kPieces = HD / 8;                   // 16-byte pieces per row
   constexpr int kSubs = kAttnThreads / kPieces;     // position subgroups of the value sum
+  constexpr int kMine = kPieces / kTPP;             // key pieces per thread in the score phase
+  constexpr int kVals = kChunk / kSubs;             // value rows per thread and chunk
   constexpr int kStat = HD + 4;                     // (max, sum) after the values; rows stay 16-byte aligned
   __shared__ __align__(16) float q_s[REP][HD];      // rotated queries, scaled by 1/sqrt(HD)
   __shared__ __align__(16) float knew[HD], vnew[HD];
-  __shared__ __align__(16) float prob[REP][kAttnThreads];
-  __shared__ __align__(16) float accs[kSubs][REP][HD];
-  __shared__ float red4[REP][4];
+  __shared__ __align__(16) float prob[REP][kChunk];
+  __shared__ __align__(16) float accs[kWarps][REP][HD];
+  __shared__ float red4[REP][kWarps];
   __shared__ float wsplit[REP][64];                 // combine: the weight of every slice
   __shared__ float denom[REP];
   __shared__ int is_last;
@@ -113,19 +123,21 @@ decode_attention_kernel(const AttnParams p) {
   // that writes the query row: the cache holds earlier positions only (the decode position's
   // own row is never read back), so the trip to memory runs under the predecessor's tail.
   const int piece = tid % kPieces, sub = tid / kPieces;
-  uint4 kr[kPieces], vr[kPieces];
+  const int spos = tid / kTPP, part = tid % kTPP;    // score phase: position within the chunk, share of its row
+  uint4 kr[kMine], vr[kVals];
   auto request = [&](int64_t c0) {
-    const int64_t pp = c0 + tid;
-    const int chunk_len = static_cast<int>((hi - c0 < kAttnThreads) ? hi - c0 : kAttnThreads);
+    const int64_t pp = c0 + spos;
+    const int chunk_len = static_cast<int>((hi - c0 < kChunk) ? hi - c0 : kChunk);
 #pragma unroll
-    for (int u = 0; u < kPieces; ++u) {
+    for (int u = 0; u < kVals; ++u) {
       const int i = sub + u * kSubs;
       vr[u] = make_uint4(0u, 0u, 0u, 0u);
       if (i < chunk_len && c0 + i != p.pos) vr[u] = __ldg(reinterpret_cast<const uint4*>(vc + (c0 + i) * HD) + piece);
     }
-    if (pp < hi && pp != p.pos) {
 #pragma unroll
-      for (int d8 = 0; d8 < kPieces; ++d8) kr[d8] = __ldg(reinterpret_cast<const uint4*>(kc + pp * HD) + d8);
+    for (int u = 0; u < kMine; ++u) {
+      kr[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (pp < hi && pp != p.pos) kr[u] = __ldg(reinterpret_cast<const uint4*>(kc + pp * HD) + u * kTPP + part);
     }
   };
   if (lo < hi) request(lo);
@@ -170,34 +182,45 @@ decode_attention_kernel(const AttnParams p) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[h][e] = 0.0f;
   }
-  for (int64_t c0 = lo; c0 < hi; c0 += kAttnThreads) {
-    // scores: thread <-> position. This thread's key row and value rows of the chunk were
-    // requested together (one round trip to memory serves both; the first chunk's before the wait)
-    const int64_t pp = c0 + tid;
-    const int chunk_len = static_cast<int>((hi - c0 < kAttnThreads) ? hi - c0 : kAttnThreads);
+  for (int64_t c0 = lo; c0 < hi; c0 += kChunk) {
+    // scores: kTPP threads <-> position. This thread's share of its key row and its value rows of
+    // the chunk were requested together (one round trip to memory serves both; the first chunk's
+    // before the wait)
+    const int64_t pp = c0 + spos;
+    const int chunk_len = static_cast<int>((hi - c0 < kChunk) ? hi - c0 : kChunk);
     if (c0 != lo) request(c0);
     float s[REP];
 #pragma unroll
     for (int h = 0; h < REP; ++h) s[h] = 0.0f;
     if (pp < hi) {
 #pragma unroll
-      for (int d8 = 0; d8 < kPieces; ++d8) {
+      for (int u = 0; u < kMine; ++u) {
+        const int d8 = u * kTPP + part;
         float kf[8];
         if (pp == p.pos) {
 #pragma unroll
           for (int e = 0; e < 8; ++e) kf[e] = knew[d8 * 8 + e];
         } else {
-          unpack8(kr[d8], kf);
+          unpack8(kr[u], kf);
         }
 #pragma unroll
         for (int h = 0; h < REP; ++h) {
           const float4 q0 = *reinterpret_cast<const float4*>(&q_s[h][d8 * 8]);
           const float4 q1 = *reinterpret_cast<const float4*>(&q_s[h][d8 * 8 + 4]);
-          s[h] = fmaf(q0.x, kf[0], s[h]); s[h] = fmaf(q0.y, kf[1], s[h]); s[h] = fmaf(q0.z, kf[2], s[h]); s[h] = fmaf(q0.w, kf[3], s[h]);
-          s[h] = fmaf(q1.x, kf[4], s[h]); s[h] = fmaf(q1.y, kf[5], s[h]); s[h] = fmaf(q1.z, kf[6], s[h]); s[h] = fmaf(q1.w, kf[7], s[h]);
+          float sa = q0.x * kf[0], sb = q0.y * kf[1];
+          sa = fmaf(q0.z, kf[2], sa); sb = fmaf(q0.w, kf[3], sb);
+          sa = fmaf(q1.x, kf[4], sa); sb = fmaf(q1.y, kf[5], sb);
+          sa = fmaf(q1.z, kf[6], sa); sb = fmaf(q1.w, kf[7], sb);
+          s[h] += sa + sb;
         }
       }
-    } else {
+    }
+    // the position's kTPP shares (adjacent lanes)
+#pragma unroll
+    for (int h = 0; h < REP; ++h)
+#pragma unroll
+      for (int o = 1; o < kTPP; o <<= 1) s[h] += __shfl_xor_sync(0xffffffffu, s[h], o);
+    if (pp >= hi) {
 #pragma unroll
       for (int h = 0; h < REP; ++h) s[h] = -INFINITY;
     }
@@ -205,16 +228,17 @@ decode_attention_kernel(const AttnParams p) {
     float scale_old[REP], cmax[REP], csum[REP];
 #pragma unroll
     for (int h = 0; h < REP; ++h) cmax[h] = s[h];
-    block_reduce<REP, true>(cmax, red4);
+    block_reduce<REP, kWarps, true>(cmax, red4);
 #pragma unroll
     for (int h = 0; h < REP; ++h) {
       const float m_new = fmaxf(m_run[h], cmax[h]);
-      csum[h] = (pp < hi) ? __expf(s[h] - m_new) : 0.0f;
-      prob[h][tid] = csum[h];
+      const float pr = (pp < hi) ? __expf(s[h] - m_new) : 0.0f;
+      csum[h] = part == 0 ? pr : 0.0f;              // one of the position's threads counts it
+      if (part == 0) prob[h][spos] = pr;
       scale_old[h] = (m_run[h] == -INFINITY) ? 0.0f : __expf(m_run[h] - m_new);
       m_run[h] = m_new;
     }
-    block_reduce<REP, false>(csum, red4);            // (its barriers also make prob complete)
+    block_reduce<REP, kWarps, false>(csum, red4);     // (its barriers also make prob complete)
 #pragma unroll
     for (int h = 0; h < REP; ++h) l_run[h] = l_run[h] * scale_old[h] + csum[h];
     // weighted values: thread <-> (8 dimensions, position subgroup)
@@ -223,7 +247,7 @@ decode_attention_kernel(const AttnParams p) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[h][e] *= scale_old[h];
 #pragma unroll
-    for (int u = 0; u < kPieces; ++u) {
+    for (int u = 0; u < kVals; ++u) {
       const int i = sub + u * kSubs;
       if (i < chunk_len) {
         float vf[8];
@@ -246,17 +270,26 @@ decode_attention_kernel(const AttnParams p) {
 
   QMM_TRACE(trace, 3);               // the slice is done
   // ---- this slice's (max, sum, weighted values) to scratch ----
+  // the subgroups that share a warp first (lanes piece, piece + kPieces, ...), then the warps
 #pragma unroll
   for (int h = 0; h < REP; ++h)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) accs[sub][h][piece * 8 + e] = acc[h][e];
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+      for (int o = kPieces; o < 32; o <<= 1) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], o);
+  if ((tid & 31) < kPieces) {
+#pragma unroll
+    for (int h = 0; h < REP; ++h)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) accs[tid >> 5][h][piece * 8 + e] = acc[h][e];
+  }
   __syncthreads();
   float* mine = p.part + ((static_cast<int64_t>(b) * p.kv_heads + kvh) * p.splits + split) * REP * kStat;
   for (int i = tid; i < REP * HD; i += kAttnThreads) {
     const int h = i / HD, d = i - h * HD;
     float v = 0.0f;
 #pragma unroll
-    for (int sb = 0; sb < kSubs; ++sb) v += accs[sb][h][d];
+    for (int w = 0; w < kWarps; ++w) v += accs[w][h][d];
     mine[h * kStat + d] = v;
   }
   if (tid < REP) {
@@ -338,7 +371,7 @@ template <int HD, int REP>
 int launch_attention(const AttnParams& p, int64_t batch, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(p.splits), static_cast<unsigned>(p.kv_heads), static_cast<unsigned>(batch));
-  cfg.blockDim = dim3(kAttnThreads);
+  cfg.blockDim = dim3(REP <= 4 ? 512 : 256);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

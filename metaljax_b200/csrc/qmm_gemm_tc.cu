@@ -63,6 +63,9 @@ struct TcParams {
   int group_size, table_dtype, y_dtype;
   int splits;                  // > 1: the K blocks of a tile are divided among `splits` CTAs, each
   float* partial;              // of which writes its float32 partial tile to partial[split][M][N]
+  int64_t item0, item_end;     // the work items [item0, item_end) of the persistent walk are this launch's
+  int64_t tail_tile0;          // >= 0: this launch splits only the tiles from here on, and partial is
+  int64_t tail_tiles;          //       compact: partial[split][tile - tail_tile0][BT][128]
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -367,6 +370,7 @@ struct Plan {
 struct TileInfo {
   int split, kb_lo, kb_hi;   // this work item's share of the tile's K blocks
   int seg;
+  int64_t tile;      // index in the walk
   int64_t row0;      // first x / y row of this tile
   int rows;          // valid rows in the tile (<= BT)
   int64_t f0;        // first feature
@@ -387,6 +391,7 @@ __device__ __forceinline__ bool tile_at(int64_t item, const int64_t* seg_tile0, 
     out->split = static_cast<int>(item - t * splits);
   }
   if (t >= seg_tile0[nseg]) return false;
+  out->tile = t;
   out->kb_lo = static_cast<int>(static_cast<int64_t>(out->split) * num_kb / splits);
   out->kb_hi = static_cast<int>(static_cast<int64_t>(out->split + 1) * num_kb / splits);
   int s = 0;
@@ -485,7 +490,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       uint32_t it = 0;
       TileInfo ti;
       bool ok = true;
-      for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
+      for (int64_t t = p.item0 + blockIdx.x; ok && t < p.item_end && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
            t += gridDim.x) {
         const int64_t wrow = ti.seg * p.w_seg_rows + ti.f0;
         for (int kb = ti.kb_lo; kb < ti.kb_hi; ++kb, ++it) {
@@ -508,7 +513,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
     int s = 0;
     TileInfo ti;
     bool ok = true;
-    for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
+    for (int64_t t = p.item0 + blockIdx.x; ok && t < p.item_end && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
          t += gridDim.x, ++tile_n) {
       if (!(ok = twait(d_empty, (tile_n & 1) ^ 1, abort_flag, 2))) break;
       tc_fence_after();
@@ -545,7 +550,7 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
     uint32_t it = 0, tile_n = 0;
     TileInfo ti;
     bool ok = true;
-    for (int64_t t = blockIdx.x; ok && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
+    for (int64_t t = p.item0 + blockIdx.x; ok && t < p.item_end && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
          t += gridDim.x, ++tile_n) {
       int64_t feat = ti.f0 + frow;
       const bool feat_ok = feat < p.N;
@@ -649,7 +654,11 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
         uint32_t r[32];
         tmem_ld32(tmem_base + lane_addr + c0, r);
         tmem_wait_ld();
-        if (SPLIT && feat_ok) {                    // a share of the tile's K: float32 partial sums
+        if (SPLIT && p.tail_tile0 >= 0) {          // the last partial wave only: compact partial tiles
+          float* part = p.partial + ((static_cast<int64_t>(ti.split) * p.tail_tiles + (ti.tile - p.tail_tile0)) * BT + c0) * kBF + frow;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) part[j * kBF] = __uint_as_float(r[j]);
+        } else if (SPLIT && feat_ok) {             // a share of the tile's K: float32 partial sums
           float* part = p.partial + static_cast<int64_t>(ti.split) * p.M * p.N;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
@@ -767,10 +776,37 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
   }
 }
 
+// The same for a split last wave: partial[split][tile][BT][128] -> the tiles' places in y
+// (one dense segment; tile t of the walk is token tile t / ftiles, feature tile t % ftiles).
+__global__ void splitk_tail_reduce_kernel(const float* __restrict__ partial, void* __restrict__ y, int y_dtype,
+                                          int64_t M, int64_t N, int64_t ftiles, int64_t tile0, int64_t tiles,
+                                          int bt, int splits) {
+  const int64_t per_tile = static_cast<int64_t>(bt) * kBF, total = tiles * per_tile;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t tl = i / per_tile, in = i - tl * per_tile;
+    const int64_t r = in / kBF, c = in - r * kBF;
+    const int64_t t = tile0 + tl;
+    const int64_t row = (t / ftiles) * bt + r, col = (t % ftiles) * kBF + c;
+    if (row >= M || col >= N) continue;
+    float acc = partial[i];
+    for (int s = 1; s < splits; ++s) acc += partial[static_cast<int64_t>(s) * total + i];
+    const int64_t o = row * N + col;
+    if (y_dtype == QMM_BF16) static_cast<__nv_bfloat16*>(y)[o] = __float2bfloat16_rn(acc);
+    else if (y_dtype == QMM_F16) static_cast<__half*>(y)[o] = __float2half_rn(acc);
+    else static_cast<float*>(y)[o] = acc;
+  }
+}
+
 // How many CTAs share one tile's K blocks. A short row run against a narrow weight leaves most
 // SMs without a tile while each busy CTA walks all of K alone; dividing K among CTAs fills the
 // machine. Only for one dense segment, N a multiple of 4 (the reduce kernel's vectors), and
 // never fewer than 8 K blocks per share.
+bool tail_split_enabled() {
+  static const bool on = [] { const char* e = getenv("QMM_TC_TAIL_SPLIT"); return !(e && *e == '0'); }();
+  return on;
+}
+
 int choose_splits(const qmm_problem& p, int64_t tiles, int num_kb) {
   if (p.group_sizes || p.batch != 1 || (p.N & 3)) return 1;
   int64_t s = sm_count() / (tiles < 1 ? 1 : tiles);
@@ -817,6 +853,10 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   tp.group_size = p.group_size; tp.table_dtype = p.table_dtype; tp.y_dtype = p.y_dtype;
   tp.splits = 1;
   tp.partial = nullptr;
+  tp.item0 = 0;
+  tp.item_end = INT64_MAX;
+  tp.tail_tile0 = -1;
+  tp.tail_tiles = 0;
 
   static bool configured[kMaxDevices] = {};     // the attribute is per device
   const int dev = current_device();
@@ -863,6 +903,53 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   int64_t items = max_tiles * splits;
   int grid = sm_count();
   if (items < grid) grid = static_cast<int>(items < 1 ? 1 : items);
+  // Several waves of tiles whose last wave fills under half of the SMs: the full waves run
+  // unsplit, and the leftover tiles' K blocks are divided among the SMs (compact float32 partial
+  // tiles, a small reduce) instead of a few CTAs walking all of K while the rest idle.
+  if (splits == 1 && !ragged && p.batch == 1 && max_tiles > grid && tail_split_enabled()) {
+    const int64_t rem = max_tiles % grid;
+    int64_t s = rem ? grid / rem : 0;
+    if (s > num_kb / 8) s = num_kb / 8;
+    if (s > 8) s = 8;
+    if (rem > 0 && s >= 2) {
+      const size_t need = static_cast<size_t>(s) * rem * BT * kBF * sizeof(float);
+      const ScratchBlock* block = scratch_override();
+      float* part = nullptr;
+      bool part_async = false;
+      if (block) {
+        if (need <= block->bytes) part = static_cast<float*>(block->ptr);
+      } else {
+        void* ptr = nullptr;
+        if (cudaMallocAsync(&ptr, need, stream) == cudaSuccess) {
+          count_alloc();
+          part = static_cast<float*>(ptr);
+          part_async = true;
+        } else {
+          cudaGetLastError();
+        }
+      }
+      if (part) {
+        TcParams head = tp, tail = tp;
+        head.item_end = max_tiles - rem;
+        qmm_gemm_tc_kernel<QK, XT, BT, false><<<grid, kThreads, P::kSmem, stream>>>(xm, wm, head);
+        tail.splits = static_cast<int>(s);
+        tail.partial = part;
+        tail.tail_tile0 = max_tiles - rem;
+        tail.tail_tiles = rem;
+        tail.item0 = (max_tiles - rem) * s;
+        tail.item_end = max_tiles * s;
+        qmm_gemm_tc_kernel<QK, XT, BT, true><<<static_cast<unsigned>(rem * s), kThreads, P::kSmem, stream>>>(xm, wm, tail);
+        const int64_t total = rem * BT * kBF;
+        int64_t blocks = (total + 255) / 256;
+        if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+        splitk_tail_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(part, p.y, p.y_dtype, p.M, p.N, ftiles,
+                                                                                    max_tiles - rem, rem, BT, static_cast<int>(s));
+        count_launch(3);
+        if (part_async) cudaFreeAsync(part, stream);
+        return check_launch("qmm_gemm_tc_kernel");
+      }
+    }
+  }
   if (splits > 1) qmm_gemm_tc_kernel<QK, XT, BT, true><<<grid, kThreads, P::kSmem, stream>>>(xm, wm, tp);
   else qmm_gemm_tc_kernel<QK, XT, BT, false><<<grid, kThreads, P::kSmem, stream>>>(xm, wm, tp);
   count_launch();

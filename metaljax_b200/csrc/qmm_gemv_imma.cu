@@ -101,7 +101,7 @@ __device__ __forceinline__ uint32_t exchange_seq(uint32_t epoch, int site) { ret
 
 // Eight bf16 values of a stamped row (four 8-byte units {pair, stamp}): read until every unit
 // carries `stamp` (bounded; a timeout is recorded in *status and whatever is there is returned).
-__device__ __forceinline__ uint4 ld_stamped8(const uint8_t* p, uint32_t stamp, long long limit, int* status) {
+__device__ __noinline__ uint4 ld_stamped8(const uint8_t* p, uint32_t stamp, long long limit, int* status) {
   uint4 a, b;
   long long t0 = 0;
   int spins = 0;
@@ -161,6 +161,65 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   }
 }
 
+// How the activation row is made (a by-value subset of the launch parameters).
+struct RowSource {
+  const void* x;
+  const void* residual_in;
+  int* status;
+  long long spin_limit;
+  int K, prologue, swiglu_width, wait_world;
+};
+
+// Where piece pc (8 elements) of the row starts in x: for SwiGLU the gate part (the up part is
+// swiglu_width further on).
+__device__ __forceinline__ int64_t x_index_of(int prologue, int swiglu_width, int pc) {
+  if (prologue != kProSwiglu) return static_cast<int64_t>(pc) * 8;
+  const int k = pc * 8, blk = k / swiglu_width;
+  return static_cast<int64_t>(blk) * 2 * swiglu_width + (k - blk * swiglu_width);
+}
+
+// Piece of the row before its last step, from its parts: the activations themselves,
+// silu(gate) * up, or h = x + residual (whose normalisation needs the whole row first).
+__device__ __forceinline__ uint4 compose_piece(int prologue, bool has_residual, const uint4& x0, const uint4& x1, const uint4& res) {
+  if (prologue == kProSwiglu) {
+    float gt[8], up[8];
+    unpack8<__nv_bfloat16>(x0, gt);
+    unpack8<__nv_bfloat16>(x1, up);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) gt[e] = gt[e] / (1.0f + __expf(-gt[e])) * up[e];
+    return pack8_bf16(gt);
+  }
+  if (prologue == kProAddNorm && has_residual) {
+    float a[8], r[8];
+    unpack8<__nv_bfloat16>(x0, a);
+    unpack8<__nv_bfloat16>(res, r);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] += r[e];
+    return pack8_bf16(a);              // the sum as it is stored: bf16
+  }
+  return x0;
+}
+
+// The same piece read from memory on the spot (rows longer than a thread's registers hold; out
+// of line: it runs rarely and the kernel's prologue is paid for by its size).
+template <typename XT>
+__device__ __noinline__ uint4 load_piece_slow(const RowSource src, int pc, uint32_t wait_stamp) {
+  if (pc >= src.K / 8) return make_uint4(0u, 0u, 0u, 0u);
+  const int64_t xi = x_index_of(src.prologue, src.swiglu_width, pc);
+  const uint8_t* xb = static_cast<const uint8_t*>(src.x);
+  uint4 x0, x1 = make_uint4(0u, 0u, 0u, 0u), res = make_uint4(0u, 0u, 0u, 0u);
+  if (src.wait_world > 0) {
+    x0 = ld_stamped8(xb + xi * 4, wait_stamp, src.spin_limit, src.status);
+    if (src.prologue == kProSwiglu) x1 = ld_stamped8(xb + (xi + src.swiglu_width) * 4, wait_stamp, src.spin_limit, src.status);
+  } else {
+    x0 = __ldcg(reinterpret_cast<const uint4*>(xb + xi * sizeof(XT)));
+    if (src.prologue == kProSwiglu) x1 = __ldcg(reinterpret_cast<const uint4*>(xb + (xi + src.swiglu_width) * sizeof(XT)));
+  }
+  if (src.prologue == kProAddNorm && src.residual_in)
+    res = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src.residual_in) + pc * 8));
+  return compose_piece(src.prologue, src.residual_in != nullptr, x0, x1, res);
+}
+
 // Largest 15-bit magnitude pattern among the eight 16-bit floats of `v` (for both bf16 and f16
 // the patterns order like the magnitudes).
 __device__ __forceinline__ uint32_t max_mag16(const uint4& v, uint32_t m) {
@@ -208,9 +267,15 @@ __device__ __forceinline__ void reduce_over_g(float (&v)[NV], int lane) {
 }
 
 // QK: quantization kind. XT: activation type in memory. R: 8-row blocks per tile. NW: warps.
-template <int QK, typename XT, int R, int NW>
+// FUSED: the decode-step form (a prologue PRO, stamped exchange rows, pushes); the plain product is a
+// separate instantiation without any of that code -- a launch runs its prologue once, from a cold
+// instruction cache, and pays for every byte of it.
+template <int QK, typename XT, int R, int NW, bool FUSED, int PRO>
 __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1)
 qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams p) {
+  constexpr int pro = PRO;           // how the activation row is made (compile-time: see FUSED)
+  const int wait_world = FUSED ? p.wait_world : 0;
+  const int push_world = FUSED ? p.push_world : 0;
   constexpr int kThreads = NW * 32;
   constexpr int BITS = (QK == kAff8) ? 8 : 4;
   constexpr int kBoxCodes = kBoxBytes * 8 / BITS;    // 256 or 128 codes per row and box
@@ -291,42 +356,58 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   }
   const uint8_t* sc8 = static_cast<const uint8_t*>(p.scales);
 
+  // ---- what does not depend on the previous kernel: requested before the wait ----
+  const int vpieces = p.K / 8, ppieces = nchunks * kBoxCodes / 8;
+  const int iters = (ppieces + kThreads - 1) / kThreads;
+  // (lines of the norm weight, of the first tile's scale rows and of its bias rows into L1: the
+  // loads that want them later then cost a cache hit instead of a trip to L2)
+  {
+    auto prefetch_l1 = [](const void* q) { asm volatile("prefetch.global.L1 [%0];" ::"l"(q)); };
+    if (pro == kProAddNorm)
+      for (int ln = threadIdx.x; ln * 128 < p.K * 2; ln += kThreads) prefetch_l1(static_cast<const uint8_t*>(p.norm_weight) + ln * 128);
+    const int row_bytes = p.groups * kTS, lines_per_row = (row_bytes + 127) / 128;
+    const int first_row = blockIdx.x * kTileRows;
+    for (int ln = threadIdx.x; ln < kTileRows * lines_per_row; ln += kThreads) {
+      const int r = min(first_row + ln / lines_per_row, p.N - 1), o = (ln % lines_per_row) * 128;
+      if (static_cast<int>(blockIdx.x) < ntiles && o < row_bytes) {
+        prefetch_l1(sc8 + static_cast<int64_t>(r) * row_bytes + o);
+        if (QK != kMx4) prefetch_l1(static_cast<const uint8_t*>(p.biases) + static_cast<int64_t>(r) * row_bytes + o);
+      }
+    }
+  }
+
   // ---- the activation row: after everything the previous kernel wrote is visible ----
   asm volatile("griddepcontrol.wait;" ::: "memory");
   QMM_TRACE(trace, 1);               // predecessor done (or flushed)
-  const uint32_t epoch = (p.wait_world > 0 || p.push_world > 0) ? *reinterpret_cast<const volatile uint32_t*>(p.epoch) : 0u;
+  const uint32_t epoch = (wait_world > 0 || push_world > 0) ? *reinterpret_cast<const volatile uint32_t*>(p.epoch) : 0u;
   const uint32_t wait_stamp = exchange_seq(epoch, p.wait_site);
+  if (wait_stamp != 0xffffffffu) QMM_TRACE(trace, 8);    // the epoch has arrived
+  const bool stamped = wait_world > 0;
+  const uint8_t* xbytes = static_cast<const uint8_t*>(p.x);
   // Eight consecutive elements of x starting at element `i` (a multiple of 8): plain memory, or a
-  // stamped row of this rank's gather slot that the other ranks are still filling.
-  auto ld_x = [&](int64_t i) -> uint4 {
-    if (p.wait_world > 0) return ld_stamped8(static_cast<const uint8_t*>(p.x) + i * 4, wait_stamp, p.spin_limit, p.status);
-    return __ldcg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.x) + i * sizeof(XT)));
+  // stamped row of this rank's gather slot that the other ranks are still filling. `request`
+  // only reads (both halves of a stamped piece, unchecked); `settle` checks the stamps and falls
+  // back to the bounded re-reading loop. All of a thread's requests go out before its first
+  // check, so the row costs one trip to memory, not one per piece.
+  auto request = [&](int64_t i, uint4& a, uint4& b) {
+    if (stamped) {
+      // weak loads served by L2 (where the peers' stores land): they pipeline, which the
+      // volatile loads of the re-reading loop do not -- those complete one after the other
+      const uint8_t* q = xbytes + i * 4;
+      asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(q));
+      asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(q + 16));
+    } else {
+      a = __ldcg(reinterpret_cast<const uint4*>(xbytes + i * sizeof(XT)));
+    }
   };
-  const int vpieces = p.K / 8, ppieces = nchunks * kBoxCodes / 8;
-  const int iters = (ppieces + kThreads - 1) / kThreads;
-  // Piece pc of the row before its last step: the activations themselves, silu(gate) * up, or
-  // h = x + residual (whose normalisation needs the whole row first).
+  auto settle = [&](int64_t i, const uint4& a, const uint4& b) -> uint4 {
+    if (!stamped) return a;
+    if (a.y == wait_stamp && a.w == wait_stamp && b.y == wait_stamp && b.w == wait_stamp) return make_uint4(a.x, a.z, b.x, b.z);
+    return ld_stamped8(xbytes + i * 4, wait_stamp, p.spin_limit, p.status);
+  };
   auto load_piece = [&](int pc) -> uint4 {
-    if (pc >= vpieces) return make_uint4(0u, 0u, 0u, 0u);
-    if (p.prologue == kProSwiglu) {
-      const int k = pc * 8, blk = k / p.swiglu_width, i = k - blk * p.swiglu_width;
-      float gt[8], up[8];
-      unpack8<__nv_bfloat16>(ld_x(static_cast<int64_t>(blk) * 2 * p.swiglu_width + i), gt);
-      unpack8<__nv_bfloat16>(ld_x(static_cast<int64_t>(blk) * 2 * p.swiglu_width + p.swiglu_width + i), up);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) gt[e] = gt[e] / (1.0f + __expf(-gt[e])) * up[e];
-      return pack8_bf16(gt);
-    }
-    uint4 raw = ld_x(static_cast<int64_t>(pc) * 8);
-    if (p.prologue == kProAddNorm && p.residual_in) {
-      float a[8], r[8];
-      unpack8<__nv_bfloat16>(raw, a);
-      unpack8<__nv_bfloat16>(__ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.residual_in) + pc * 8)), r);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) a[e] += r[e];
-      raw = pack8_bf16(a);             // the sum as it is stored: bf16
-    }
-    return raw;
+    const RowSource src = {p.x, p.residual_in, p.status, p.spin_limit, p.K, pro, p.swiglu_width, wait_world};
+    return load_piece_slow<XT>(src, pc, wait_stamp);
   };
   // |f| as an unsigned pattern orders like the magnitude, NaNs above infinity above everything
   auto mag_of = [&](const float (&f)[8], uint32_t m) -> uint32_t {
@@ -334,36 +415,81 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
     for (int e = 0; e < 8; ++e) m = max(m, __float_as_uint(f[e]) & 0x7fffffffu);
     return m;
   };
+  // Register arrays are only ever indexed by unrolled constants; the loops that do the work stay
+  // rolled (this code runs once per CTA from a cold instruction cache: its size is its cost).
+  auto pick = [&](const uint4 (&arr)[kXCache], int i) -> uint4 {
+    uint4 v = arr[0];
+#pragma unroll
+    for (int c = 1; c < kXCache; ++c)
+      if (c == i) v = arr[c];
+    return v;
+  };
   uint4 xcache[kXCache];
   uint32_t mag = 0;
   float ss = 0.0f;
-  for (int i = 0; i < iters; ++i) {
-    const int pc = threadIdx.x + i * kThreads;
-    const uint4 raw = load_piece(pc);
-    if (i < kXCache) {
-#pragma unroll
-      for (int c = 0; c < kXCache; ++c)
-        if (c == i) xcache[c] = raw;
-    }
+  // first pass over the row: its largest magnitude (and the sum of squares of h)
+  auto scan_piece = [&](int pc, const uint4& raw, const uint4& nwraw) {
     float f[8];
     unpack8<XT>(raw, f);
-    if (p.prologue == kProAddNorm) {
-      if (pc < vpieces) {
-        if (blockIdx.x == 0 && p.residual_out) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.residual_out) + pc * 8) = raw;
-        float w8[8];
-        unpack8<__nv_bfloat16>(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + pc * 8)), w8);
+    if (pro == kProAddNorm && pc < vpieces) {
+      if (blockIdx.x == 0 && p.residual_out) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.residual_out) + pc * 8) = raw;
+      float w8[8];
+      unpack8<__nv_bfloat16>(nwraw, w8);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { ss = fmaf(f[e], f[e], ss); f[e] *= w8[e]; }
-      }
+      for (int e = 0; e < 8; ++e) { ss = fmaf(f[e], f[e], ss); f[e] *= w8[e]; }
     }
     mag = mag_of(f, mag);
+  };
+  auto norm_piece = [&](int pc) -> uint4 {
+    if (pro != kProAddNorm || pc >= vpieces) return make_uint4(0u, 0u, 0u, 0u);
+    return __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + pc * 8));
+  };
+  {
+    // every request of the first kXCache pieces goes out before the first check
+    uint4 qa[kXCache], qb[kXCache], ua[kXCache], ub[kXCache];      // (ua doubles as the residual piece: never both)
+#pragma unroll
+    for (int c = 0; c < kXCache; ++c) {
+      const int pc = threadIdx.x + c * kThreads;
+      qa[c] = qb[c] = ua[c] = ub[c] = make_uint4(0u, 0u, 0u, 0u);
+      if (c < iters && pc < vpieces) {
+        const int64_t xi = x_index_of(pro, p.swiglu_width, pc);
+        request(xi, qa[c], qb[c]);
+        if (pro == kProSwiglu) request(xi + p.swiglu_width, ua[c], ub[c]);
+        if (pro == kProAddNorm && p.residual_in)
+          ua[c] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.residual_in) + pc * 8));
+      }
+    }
+    QMM_TRACE(trace, 9);             // requests issued
+    for (int i = 0; i < iters; ++i) {
+      const int pc = threadIdx.x + i * kThreads;
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (i < kXCache) {
+        if (pc < vpieces) {
+          const int64_t xi = x_index_of(pro, p.swiglu_width, pc);
+          const uint4 u0 = pick(ua, i);
+          const uint4 x0 = settle(xi, pick(qa, i), pick(qb, i));
+          uint4 x1 = make_uint4(0u, 0u, 0u, 0u);
+          if (pro == kProSwiglu) x1 = settle(xi + p.swiglu_width, u0, pick(ub, i));
+          raw = compose_piece(pro, p.residual_in != nullptr, x0, x1, u0);
+          if (raw.x != 0x12345677u && i == 0) QMM_TRACE(trace, 10);   // thread 0's first piece settled
+        }
+#pragma unroll
+        for (int c = 0; c < kXCache; ++c)
+          if (c == i) xcache[c] = raw;
+        scan_piece(pc, raw, norm_piece(pc));
+      } else {
+        scan_piece(pc, load_piece(pc), norm_piece(pc));
+      }
+    }
   }
+  if (mag != 0xffffffffu) QMM_TRACE(trace, 11);   // thread 0 has scanned its pieces
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     mag = max(mag, __shfl_xor_sync(0xffffffffu, mag, o));
     ss += __shfl_xor_sync(0xffffffffu, ss, o);
   }
   if (lane == 0) { amax_w[warp] = mag; amax_w[NW + warp] = __float_as_uint(ss); }
+  QMM_TRACE(trace, 12);
   __syncthreads();
   QMM_TRACE(trace, 2);               // the whole row has arrived and been read once
   mag = 0;
@@ -372,7 +498,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   for (int i = 0; i < NW; ++i) { mag = max(mag, amax_w[i]); ss += __uint_as_float(amax_w[NW + i]); }
   float inv_rms = 1.0f;
   bool nonfinite = mag >= 0x7f800000u;
-  if (p.prologue == kProAddNorm) {
+  if (pro == kProAddNorm) {
     inv_rms = rsqrtf(ss / static_cast<float>(p.K) + p.eps);
     // the row's largest magnitude is at most this (a bf16 rounding above max |h w| / rms)
     const float bound = __uint_as_float(mag) * inv_rms * 1.0079f;
@@ -385,21 +511,13 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   const float to_fixed = __uint_as_float((283u - ebits) << 23);      // 2^(156 - e): |x| * this <= 2^30
   {
     const int lanes_per_group = p.group_size / 8;
-    for (int i = 0; i < iters; ++i) {
-      const int pc = threadIdx.x + i * kThreads;
-      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-      if (i < kXCache) {
-#pragma unroll
-        for (int c = 0; c < kXCache; ++c)
-          if (c == i) raw = xcache[c];
-      } else {
-        raw = load_piece(pc);
-      }
+    // second pass: the digits of piece pc into the planes, the per-group sums
+    auto stage_piece = [&](int pc, const uint4& raw, const uint4& nwraw) {
       float f[8];
       unpack8<XT>(raw, f);
-      if (p.prologue == kProAddNorm && pc < vpieces) {
+      if (pro == kProAddNorm && pc < vpieces) {
         float w8[8];
-        unpack8<__nv_bfloat16>(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.norm_weight) + pc * 8)), w8);
+        unpack8<__nv_bfloat16>(nwraw, w8);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] = f[e] * inv_rms * w8[e];
         unpack8<__nv_bfloat16>(pack8_bf16(f), f);          // the normalised row as a glue kernel would store it: bf16
@@ -434,14 +552,20 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
         if ((lane & 3) == 0 && grp < p.groups) *reinterpret_cast<int4*>(reinterpret_cast<int*>(xsum) + grp * 4) = make_int4(ds[0], ds[1], ds[2], ds[3]);
       } else {
         // per group: the sum of x itself, for the bias term (in units of 2^(e-156))
-        float s = fmaf(static_cast<float>(ds[3]), 16777216.0f, fmaf(static_cast<float>(ds[2]), 65536.0f,
-                       fmaf(static_cast<float>(ds[1]), 256.0f, static_cast<float>(ds[0]))));
-        for (int o = 1; o < lanes_per_group; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        float sx = fmaf(static_cast<float>(ds[3]), 16777216.0f, fmaf(static_cast<float>(ds[2]), 65536.0f,
+                        fmaf(static_cast<float>(ds[1]), 256.0f, static_cast<float>(ds[0]))));
+        for (int o = 1; o < lanes_per_group; o <<= 1) sx += __shfl_xor_sync(0xffffffffu, sx, o);
         const int grp = pc / lanes_per_group;
-        if ((lane & (lanes_per_group - 1)) == 0 && grp < p.groups) xsum[grp] = s;
+        if ((lane & (lanes_per_group - 1)) == 0 && grp < p.groups) xsum[grp] = sx;
       }
+    };
+    for (int i = 0; i < iters; ++i) {
+      const int pc = threadIdx.x + i * kThreads;
+      if (i < kXCache) stage_piece(pc, pick(xcache, i), norm_piece(pc));
+      else stage_piece(pc, load_piece(pc), norm_piece(pc));
     }
   }
+  QMM_TRACE(trace, 13);              // thread 0 has staged its pieces
   __syncthreads();                   // the staged activations, their sums and the zeros are in place
   QMM_TRACE(trace, 3);               // digits staged
 
@@ -464,7 +588,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   auto push_tile = [&](int tl, int buf) {
     const int peer = lane / R, v = lane % R;
     const int n8 = tl * kTileRows + v * 8;
-    if (peer < p.push_world && n8 < p.N) {
+    if (peer < push_world && n8 < p.N) {
       const uint4 d = *reinterpret_cast<const uint4*>(ypush + buf * kTileRows + v * 8);
       uint4* dst = reinterpret_cast<uint4*>(p.push_dst[peer] + static_cast<int64_t>(n8) * 4);
       dst[0] = make_uint4(d.x, push_stamp, d.y, push_stamp);
@@ -603,6 +727,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
       if (lane == 0 && itile < ntiles) issue_box();
     }
 
+    if (prev_tile < 0) QMM_TRACE(trace, 7);   // first tile: this warp's K loop done
     // ---- this warp's share of K, for its lanes' digit planes and slots: scale, add up ----
     float v[2 * R];
 #pragma unroll
@@ -623,7 +748,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
       if (threadIdx.x == 0) atomicCAS(p.status, 0, *abort_flag);
       return;
     }
-    if (p.push_world > 0 && prev_tile >= 0 && warp == NW - 1) push_tile(prev_tile, rbuf ^ 1);   // (complete since this barrier)
+    if (push_world > 0 && prev_tile >= 0 && warp == NW - 1) push_tile(prev_tile, rbuf ^ 1);   // (complete since this barrier)
     // ---- rows x NW threads: the warps' shares (fixed order) plus the bias term ----
     if (frow < kTileRows) {
       const int n = tile * kTileRows + frow;
@@ -655,7 +780,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
           else if (p.y_dtype == QMM_F16) static_cast<__half*>(p.y)[n] = __float2half_rn(s);
           else static_cast<float*>(p.y)[n] = s;
         }
-        if (p.push_world > 0) ypush[rbuf * kTileRows + frow] = __float2bfloat16_rn(s);
+        if (push_world > 0) ypush[rbuf * kTileRows + frow] = __float2bfloat16_rn(s);
       }
     }
     rbuf ^= 1;
@@ -663,7 +788,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
     prev_tile = tile;
   }
   QMM_TRACE(trace, 5);               // all tiles done
-  if (p.push_world > 0) {
+  if (push_world > 0) {
     __syncthreads();                 // the last tile's rows are in shared memory
     if (warp == NW - 1 && prev_tile >= 0) push_tile(prev_tile, rbuf ^ 1);
   }
@@ -690,9 +815,9 @@ int env_int(const char* name, int fallback) {
   return (e && *e) ? atoi(e) : fallback;
 }
 
-template <int QK, typename XT, int R, int NW>
+template <int QK, typename XT, int R, int NW, bool FUSED, int PRO>
 int launch_r(const CUtensorMap& wm, const ImmaParams& ip, const ImmaPlan& plan, cudaStream_t stream) {
-  auto kernel = qmm_gemv_imma_kernel<QK, XT, R, NW>;
+  auto kernel = qmm_gemv_imma_kernel<QK, XT, R, NW, FUSED, PRO>;
   static bool configured[kMaxDevices] = {};     // the attribute is per device
   const int dev = current_device();
   if (dev < 0) return QMM_ERR_DEVICE;
@@ -726,13 +851,22 @@ int launch_r(const CUtensorMap& wm, const ImmaParams& ip, const ImmaPlan& plan, 
 template <int QK, typename XT>
 int launch_qx(const CUtensorMap& wm, const ImmaParams& ip, const ImmaPlan& plan, cudaStream_t stream) {
   if (plan.nw == 16) {
-    if (plan.r == 4) return launch_r<QK, XT, 4, 16>(wm, ip, plan, stream);
-    if (plan.r == 2) return launch_r<QK, XT, 2, 16>(wm, ip, plan, stream);
-    return launch_r<QK, XT, 1, 16>(wm, ip, plan, stream);
+    if (plan.r == 4) return launch_r<QK, XT, 4, 16, false, kProNone>(wm, ip, plan, stream);
+    if (plan.r == 2) return launch_r<QK, XT, 2, 16, false, kProNone>(wm, ip, plan, stream);
+    return launch_r<QK, XT, 1, 16, false, kProNone>(wm, ip, plan, stream);
   }
-  if (plan.r == 4) return launch_r<QK, XT, 4, 8>(wm, ip, plan, stream);
-  if (plan.r == 2) return launch_r<QK, XT, 2, 8>(wm, ip, plan, stream);
-  return launch_r<QK, XT, 1, 8>(wm, ip, plan, stream);
+  if (plan.r == 4) return launch_r<QK, XT, 4, 8, false, kProNone>(wm, ip, plan, stream);
+  if (plan.r == 2) return launch_r<QK, XT, 2, 8, false, kProNone>(wm, ip, plan, stream);
+  return launch_r<QK, XT, 1, 8, false, kProNone>(wm, ip, plan, stream);
+}
+
+// The decode-step forms: 4-bit affine weights, bf16 activations, sixteen warps (one family of
+// kernels for every linear of a step, so that consecutive launches find their code cached).
+template <int PRO>
+int launch_fused(const CUtensorMap& wm, const ImmaParams& ip, const ImmaPlan& plan, cudaStream_t stream) {
+  if (plan.r == 4) return launch_r<kAff4, __nv_bfloat16, 4, 16, true, PRO>(wm, ip, plan, stream);
+  if (plan.r == 2) return launch_r<kAff4, __nv_bfloat16, 2, 16, true, PRO>(wm, ip, plan, stream);
+  return launch_r<kAff4, __nv_bfloat16, 1, 16, true, PRO>(wm, ip, plan, stream);
 }
 
 // Tile height, warps per CTA, ring depth and grid for one problem, or r = 0 when the staged
@@ -741,14 +875,14 @@ int launch_qx(const CUtensorMap& wm, const ImmaParams& ip, const ImmaPlan& plan,
 // the SMs one. A larger weight is a throughput problem: eight warps and two CTAs per SM when
 // that leaves every warp 8 KiB of boxes in flight (a tile's fixed costs are then paid by eight
 // warps, and the successor's CTAs can become resident early), else sixteen warps in one CTA.
-ImmaPlan make_plan(const qmm_problem& p, int nchunks, int plane_bytes, int groups, bool mx) {
+ImmaPlan make_plan(const qmm_problem& p, int nchunks, int plane_bytes, int groups, bool mx, bool fused) {
   const int sms = device_sm_count();
   const int force_r = env_int("QMM_IMMA_R", 0), force_ring = env_int("QMM_IMMA_RING", 0), force_nw = env_int("QMM_IMMA_NW", 0);
   const size_t kTwoPerSm = 113 * 1024;     // an SM has 228 KiB, of which every resident CTA also takes 1 KiB
   const size_t kOnePerSm = 226 * 1024;
   const bool small = (p.N + 31) / 32 <= sms;
   for (int pass = 0; pass < 2; ++pass) {
-    const int nw = force_nw ? force_nw : ((pass == 0) == small ? 16 : 8);
+    const int nw = fused ? 16 : (force_nw ? force_nw : ((pass == 0) == small ? 16 : 8));
     for (int r = 4; r >= 1; r >>= 1) {
       if (force_r && r != force_r) continue;
       const int64_t tiles = (p.N + 8 * r - 1) / (8 * r);
@@ -813,7 +947,7 @@ int launch_gemv_imma(const qmm_problem& p, cudaStream_t stream, const DecodeFusi
   ip.y_dtype = p.y_dtype;
   ip.nchunks = (ip.K + boxcodes - 1) / boxcodes;
   ip.plane_bytes = plane_bytes_of(ip.nchunks, boxcodes);
-  const ImmaPlan plan = make_plan(p, ip.nchunks, ip.plane_bytes, ip.groups, mx);
+  const ImmaPlan plan = make_plan(p, ip.nchunks, ip.plane_bytes, ip.groups, mx, fusion != nullptr);
   if (!plan.r) return fail(QMM_ERR_UNSUPPORTED, "single-row decode kernel: the activations do not fit shared memory");
   ip.ring = plan.ring;
   ip.ntiles = static_cast<int>((p.N + 8 * plan.r - 1) / (8 * plan.r));
@@ -825,6 +959,12 @@ int launch_gemv_imma(const qmm_problem& p, cudaStream_t stream, const DecodeFusi
   int rc = tensor_map_2d(&wm, QMM_U8, p.w, row_bytes, static_cast<uint64_t>(p.N), row_bytes, kBoxBytes, 8 * plan.r, 1);
   if (rc) return rc;
   const bool bf = p.x_dtype == QMM_BF16;
+  if (fusion) {      // the decode step: bf16 activations (checked above), 4-bit affine weights
+    if (mx || bits != 4) return fail(QMM_ERR_UNSUPPORTED, "fused decode linears take 4-bit affine weights");
+    if (ip.prologue == kProAddNorm) return launch_fused<kProAddNorm>(wm, ip, plan, stream);
+    if (ip.prologue == kProSwiglu) return launch_fused<kProSwiglu>(wm, ip, plan, stream);
+    return launch_fused<kProNone>(wm, ip, plan, stream);
+  }
   if (mx) return bf ? launch_qx<kMx4, __nv_bfloat16>(wm, ip, plan, stream) : launch_qx<kMx4, __half>(wm, ip, plan, stream);
   if (bits == 8) return bf ? launch_qx<kAff8, __nv_bfloat16>(wm, ip, plan, stream) : launch_qx<kAff8, __half>(wm, ip, plan, stream);
   return bf ? launch_qx<kAff4, __nv_bfloat16>(wm, ip, plan, stream) : launch_qx<kAff4, __half>(wm, ip, plan, stream);

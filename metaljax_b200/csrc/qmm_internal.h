@@ -66,12 +66,12 @@ int launch_gemm_tc(const qmm_problem& p, cudaStream_t stream);
 bool gemm_tc_supports(const qmm_problem& p);
 // Development builds (-DQMM_STEP_TRACING=1): every launch of the decode-step kernels takes the
 // next block of a caller-provided buffer and its CTAs stamp %globaltimer at fixed points
-// (8 stamps per CTA, 512 CTAs per block). Off in the product build: no parameter, no code.
+// (16 stamps per CTA, 512 CTAs per block). Off in the product build: no parameter, no code.
 #ifndef QMM_STEP_TRACING
 #define QMM_STEP_TRACING 0
 #endif
 #if QMM_STEP_TRACING
-constexpr int kTraceStamps = 8, kTraceCtas = 512;
+constexpr int kTraceStamps = 16, kTraceCtas = 512;
 unsigned long long* next_trace_block(int kind);
 #ifdef __CUDACC__
 __device__ __forceinline__ void trace_mark(unsigned long long* t, int slot) {

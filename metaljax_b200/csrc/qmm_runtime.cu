@@ -129,7 +129,7 @@ unsigned long long* next_trace_block(int kind) {
   return g_trace_base + (g_trace_next++) * kTraceStamps * kTraceCtas;
 }
 }  // namespace qmm
-// `buf`: device memory of blocks * 8 * 512 uint64, zeroed by the caller; `kinds`: host ints, one per block.
+// `buf`: device memory of blocks * 16 * 512 uint64, zeroed by the caller; `kinds`: host ints, one per block.
 extern "C" void qmm_debug_set_trace(void* buf, int64_t blocks, int* kinds) {
   qmm::g_trace_base = static_cast<unsigned long long*>(buf);
   qmm::g_trace_blocks = blocks;

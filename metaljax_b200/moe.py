@@ -92,13 +92,44 @@ def moe_experts(x, indices, weights, w1, w3, w2, group_size=64, bits=4, mode="af
     kw = dict(group_size=group_size, bits=bits, mode=mode)
     gate = ragged_dot(xs, *w1, group_sizes, **kw)
     up = ragged_dot(xs, *w3, group_sizes, **kw)
-    act = torch.nn.functional.silu(gate) * up
+    act = silu_mul(gate, up)
+    del gate, up
     down = ragged_dot(act, *w2, group_sizes, **kw)
+    if sum_dtype == torch.float32 and down.dtype in _GLUE_DTYPES and down.shape[1] % 8 == 0:
+        return routed_sum(down, order, weights, t, k)
     wsorted = weights.reshape(-1).index_select(0, order).to(sum_dtype)
     contrib = down.to(sum_dtype) * wsorted[:, None]
     out = torch.zeros((t, down.shape[1]), dtype=sum_dtype, device=x.device)
     out.index_add_(0, tok, contrib)
     return out.to(x.dtype)
+
+
+_GLUE_DTYPES = (torch.bfloat16, torch.float16)
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """`silu(gate) * up` in one pass (the SwiGLU between the grouped products)."""
+    if gate.dtype not in _GLUE_DTYPES or gate.numel() % 8 or gate.shape != up.shape:
+        return torch.nn.functional.silu(gate) * up
+    gate, up = gate.contiguous(), up.contiguous()
+    out = torch.empty_like(gate)
+    _lib.check(_lib.lib().qmm_moe_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(),
+                                           _lib.ELEM[gate.dtype], _lib.stream_ptr(gate)))
+    return out
+
+
+def routed_sum(rows: torch.Tensor, order: torch.Tensor, weights: torch.Tensor, tokens: int, k: int) -> torch.Tensor:
+    """Every token's K expert outputs times their routing weights, added in float32 in k order
+    (src/metaljax/moe.py:1446-1453): `rows` are the pair outputs sorted by expert, `order[r]` the
+    pair (router order) on sorted row r."""
+    rows = rows.contiguous()
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel(), device=order.device, dtype=order.dtype)
+    w32 = weights.reshape(tokens, k).to(torch.float32).contiguous()
+    out = torch.empty((tokens, rows.shape[1]), dtype=rows.dtype, device=rows.device)
+    _lib.check(_lib.lib().qmm_moe_routed_sum(rows.data_ptr(), inv.data_ptr(), w32.data_ptr(), out.data_ptr(), tokens, k,
+                                             rows.shape[1], rows.shape[0], _lib.ELEM[rows.dtype], _lib.stream_ptr(rows)))
+    return out
 
 
 # ---- recognizer-facing hooks (metaljax.moe.emit_reads / emit_bytes / emit) ------------------

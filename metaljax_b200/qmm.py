@@ -677,6 +677,69 @@ class BlockedPacker:
 
 
 # --------------------------------------------------------------------------------------
+# on-wire formats: packs straight from what a checkpoint or a quantized keras layer stores
+# --------------------------------------------------------------------------------------
+
+
+def check_scale_range(scale_bytes: torch.Tensor, what: str = ""):
+    """E8M0 bytes 0 (2**-127, a float32 subnormal) and 255 (NaN) are not usable scales
+    (scripts/model_bench/mxfp4_gpt_oss.py:83-87)."""
+    lo, hi = int(scale_bytes.min().item()), int(scale_bytes.max().item())
+    if lo < 1 or hi > 254:
+        raise ValueError(f"{what}: E8M0 bytes span [{lo}, {hi}]; 0 and 255 are not usable scales")
+
+
+def from_hf_mxfp4(blocks: torch.Tensor, scales: torch.Tensor):
+    """A Hugging Face MXFP4 expert weight as the fused op's operands, with no copy:
+    `*_blocks` uint8 `[.., N, K/32, 16]` (byte j of a block holds elements 2j and 2j+1, low
+    nibble first) and `*_scales` uint8 `[.., N, K/32]` (E8M0) -> `(w uint32 [.., N, K/8],
+    scales uint8 [.., N, K/32])` for `mode="mxfp4"`. The byte order is already the packed
+    stream's (scripts/model_bench/mxfp4_gpt_oss.py:216-240, :90-97)."""
+    if blocks.dtype != torch.uint8 or scales.dtype != torch.uint8:
+        raise TypeError("MXFP4 blocks and scales are uint8")
+    if blocks.shape[-1] != 16 or tuple(blocks.shape[:-1]) != tuple(scales.shape):
+        raise ValueError(f"blocks {tuple(blocks.shape)} do not go with scales {tuple(scales.shape)}")
+    check_scale_range(scales, "MXFP4 scales")
+    lead = list(scales.shape[:-1])
+    flat = blocks.contiguous().reshape(lead + [scales.shape[-1] * 16])
+    return flat.view(torch.uint32), scales.contiguous()
+
+
+def unpack_keras_int4(packed: torch.Tensor, columns: int) -> torch.Tensor:
+    """`keras.quantizers.unpack_int4` for the layout packed along the last axis: int8
+    `[rows, ceil(columns/2)]`, byte j of a row = columns 2j (low nibble) and 2j+1 (high), each
+    a 4-bit two's-complement code -> int8 `[rows, columns]` (tests/test_qmm.py:179-190)."""
+    p = packed.to(torch.int16) & 0xFF
+    lo, hi = p & 15, (p >> 4) & 15
+    both = torch.stack([lo, hi], dim=-1).reshape(packed.shape[0], -1)[:, :columns]
+    return ((both ^ 8) - 8).to(torch.int8)
+
+
+def from_keras_int4(packed, scale, zero=None, g_idx=None, columns=None, out_dtype=None):
+    """A keras int4 `Dense` kernel as the fused op's operands (`Dense._int4_call`,
+    tests/test_qmm.py:193-199): `packed` int8 `[K, ceil(N/2)]` (two OUTPUT columns per byte),
+    `scale` / `zero` `[G, N]` per group of input rows, `g_idx[K]` the group of every input row
+    (default: `K/G` consecutive rows per group) -> a `_Pack` with `w [N, K*bits/32]`,
+    `scales`, `biases [N, K/gs]` and, when the groups interleave, the K permutation to apply to
+    the activations. The same checks as the recognizer's pack prologue (`build_pack`)."""
+    k = packed.shape[0]
+    n = int(columns if columns is not None else scale.shape[-1])
+    codes = unpack_keras_int4(packed, n).t().contiguous()                      # [N, K]
+    groups = scale.shape[0]
+    if g_idx is None:
+        if k % groups:
+            raise _Reject(f"{groups} groups do not divide K={k}")
+        g_idx = torch.arange(k, device=packed.device) // (k // groups)
+    g = g_idx.to(torch.int64)
+    scale_map = scale.index_select(0, g).t()                                    # [N, K], a view of [K, N]
+    zero_map = None if zero is None else zero.index_select(0, g).t()
+    m = Match()
+    m.mode, m.N, m.K = "affine", n, k
+    m.out_dtype = out_dtype or (scale.dtype if scale.dtype in _FLOATS else torch.bfloat16)
+    return build_pack(m, codes, scale_map, zero_map, leaves=(packed, scale))
+
+
+# --------------------------------------------------------------------------------------
 # runtime
 # --------------------------------------------------------------------------------------
 

@@ -534,3 +534,32 @@ def test_config5_moe_full_size_ragged_rows_and_expert_block():
             out[i] += wts[tk, j] * dn
     got = to_numpy(y[torch.from_numpy(toks).to(DEV)]).astype(np.float32)
     assert O.rel_err(got, out) <= 2e-2                     # two bf16 hand-offs inside the block
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_moe_glue_kernels_match_the_two_step_forms(dtype):
+    """`silu(gate) * up` and the routed K-sum as single passes against the eager forms they
+    replace (bit for bit: the same roundings in the same order)."""
+    from metaljax_b200 import _lib, moe
+    g = torch.Generator(device=DEV).manual_seed(3)
+    gate = (torch.randn((301, 192), generator=g, device=DEV) * 3).to(dtype)
+    up = torch.randn((301, 192), generator=g, device=DEV).to(dtype)
+    want = torch.nn.functional.silu(gate) * up
+    got = moe.silu_mul(gate, up)
+    # __expf against torch's expf: a unit in the last place of the storage type at most
+    assert (got.float() - want.float()).abs().max() <= 2 ** -7 * want.float().abs().max()
+    assert (got != want).float().mean() < 0.02
+    t, k, e, d = 37, 3, 5, 136
+    idx = torch.stack([torch.randperm(e, generator=g, device=DEV)[:k] for _ in range(t)])
+    weights = torch.rand((t, k), generator=g, device=DEV)
+    order, tok, sizes = moe.sort_pairs(idx, e)
+    rows = torch.randn((t * k, d), generator=g, device=DEV).to(dtype)
+    out = moe.routed_sum(rows, order, weights, t, k)
+    # the same sum pair by pair in router order
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(t * k, device=DEV)
+    acc = torch.zeros((t, d), device=DEV, dtype=torch.float32)
+    for j in range(k):
+        acc = acc + rows[inv.reshape(t, k)[:, j]].float() * weights[:, j:j + 1].float()
+    assert torch.equal(out, acc.to(dtype))
+    assert _lib.poll_status() == 0
