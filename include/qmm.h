@@ -82,7 +82,9 @@ typedef enum {
  * index 0 instead of reading out of bounds. */
 #define QMM_DEVICE_BAD_INDEX 200
 
-typedef enum { QMM_MODE_AFFINE = 0, QMM_MODE_MXFP4 = 1 } qmm_mode;
+/* QMM_MODE_FLOAT: the weight holds values of the activation type, nothing is dequantized; taken
+ * by qmm_ragged_mm only (the other entry points refuse it). */
+typedef enum { QMM_MODE_AFFINE = 0, QMM_MODE_MXFP4 = 1, QMM_MODE_FLOAT = 2 } qmm_mode;
 
 /* Element types of the raw-pointer entry points. */
 typedef enum {
@@ -158,6 +160,15 @@ int qmm_gather_qmm(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* s
 int qmm_ragged_dot(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* scales,
                    const qmm_tensor* biases, const qmm_tensor* group_sizes, qmm_tensor* y,
                    int group_size, int bits, int mode, void* stream);
+
+/* The same grouped product for FLOAT experts: replaces `mx.gather_mm(x, w, lhs_idx, rhs_idx)`
+ * (src/metaljax/moe.py:1324-1336) once the pairs are sorted by expert, through the ragged
+ * tensor-core main loop with the dequantization step bypassed.
+ *   x [Mtot, K] bf16 | f16; w [G, N, K] of x's type; group_sizes int32 [G] on the device;
+ *   y [Mtot, N] bf16 | f16 | f32. K >= 64 and a multiple of 8. Rows past sum(group_sizes) are
+ *   zeroed. QMM_ERR_UNSUPPORTED for anything else (there is no other route for float weights). */
+int qmm_ragged_mm(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* group_sizes,
+                  qmm_tensor* y, void* stream);
 
 /* The two element-wise steps of a gathered expert block, raw pointers (dtype: QMM_BF16 |
  * QMM_F16; 16-byte aligned). The reference runs them as generic pair-space ops after its

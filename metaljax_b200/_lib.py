@@ -90,6 +90,7 @@ _SIGNATURES = {
                                       ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "qmm_ragged_dot": (ctypes.c_int, [_T, _T, _T, _T, _T, _T, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_int, ctypes.c_void_p]),
+    "qmm_ragged_mm": (ctypes.c_int, [_T, _T, _T, _T, ctypes.c_void_p]),
     "qmm_dequantize": (ctypes.c_int, [_T, _T, _T, _T, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_void_p]),
     "qmm_pack_codes": (ctypes.c_int, [_T, _T, ctypes.c_int, ctypes.c_void_p]),

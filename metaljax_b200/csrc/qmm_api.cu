@@ -509,6 +509,46 @@ int qmm_ragged_dot(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* s
   return launch_problem(p, static_cast<cudaStream_t>(stream));
 }
 
+int qmm_ragged_mm(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* group_sizes, qmm_tensor* y,
+                  void* stream) {
+  int rc;
+  if ((rc = check_view(x, "x", 2, 2, true))) return rc;
+  if ((rc = check_view(y, "y", 2, 2, true))) return rc;
+  if ((rc = check_view(w, "w", 3, 3, true))) return rc;
+  if ((rc = check_view(group_sizes, "group_sizes", 1, 1, true))) return rc;
+  if ((rc = check_same_device(x, w, "w")) || (rc = check_same_device(x, y, "y")) ||
+      (rc = check_same_device(x, group_sizes, "group_sizes")))
+    return rc;
+  if (elem_of(group_sizes) != QMM_I32) return fail(QMM_ERR_DTYPE, "group_sizes must be int32");
+  const int xe = elem_of(x), ye = elem_of(y);
+  if ((xe != QMM_BF16 && xe != QMM_F16) || elem_of(w) != xe)
+    return fail(QMM_ERR_DTYPE, "ragged_mm: x and w must both be bf16 or both f16");
+  if (!is_float_elem(ye)) return fail(QMM_ERR_DTYPE, "y must be bf16, f16 or f32");
+  const int64_t K = w->shape[2], N = w->shape[1];
+  if (group_sizes->shape[0] != w->shape[0])
+    return fail(QMM_ERR_SHAPE, "group_sizes has %lld entries for %lld experts", (long long)group_sizes->shape[0],
+                (long long)w->shape[0]);
+  if (x->shape[1] != K) return fail(QMM_ERR_SHAPE, "x has K=%lld, the weight has K=%lld", (long long)x->shape[1], (long long)K);
+  if (y->shape[0] != x->shape[0] || y->shape[1] != N)
+    return fail(QMM_ERR_SHAPE, "y is not [M=%lld, N=%lld]", (long long)x->shape[0], (long long)N);
+  qmm_problem p;
+  init_problem(&p);
+  p.mode = QMM_MODE_FLOAT; p.bits = 16; p.group_size = 64;      // (no groups: the kernel's K block)
+  p.x_dtype = xe; p.table_dtype = xe; p.y_dtype = ye;
+  p.batch = w->shape[0]; p.M = x->shape[0]; p.K = K; p.N = N;
+  p.x = data_of(x); p.w = static_cast<const uint32_t*>(data_of(w)); p.y = data_of(y);
+  p.w_batch_stride = N;
+  p.group_sizes = static_cast<const int32_t*>(data_of(group_sizes));
+  if (p.batch == 0 || p.M == 0 || p.N == 0) return QMM_OK;
+  if (K == 0) return zero_fill(p.y, p.M * p.N * elem_size(ye), static_cast<cudaStream_t>(stream));
+  if ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.w) | reinterpret_cast<uintptr_t>(p.y)) & 15)
+    return fail(QMM_ERR_LAYOUT, "a data pointer is not 16-byte aligned");
+  if (!gemm_tc_supports(p))
+    return fail(QMM_ERR_UNSUPPORTED, "ragged_mm: K=%lld must be at least 64 and a multiple of 8, at most %d experts",
+                (long long)K, 1024);
+  return launch_gemm_tc(p, static_cast<cudaStream_t>(stream));
+}
+
 int qmm_dequantize(const qmm_tensor* w, const qmm_tensor* scales, const qmm_tensor* biases,
                    qmm_tensor* out, int group_size, int bits, int mode, void* stream) {
   int rc;

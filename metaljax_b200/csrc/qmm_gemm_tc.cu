@@ -47,7 +47,7 @@ constexpr long long kSpinLimit = 4000000000LL;  // SM clocks (~2 s)
 #define QMM_TC_TRACING 0        // development builds: cycles per wait site (-DQMM_TC_TRACING=1)
 #endif
 
-enum { kAff4 = 0, kAff8 = 1, kMx4 = 2 };
+enum { kAff4 = 0, kAff8 = 1, kMx4 = 2, kFloat = 3 };    // kFloat: the weight holds values of the activation type (nothing to dequantize)
 
 struct TcParams {
   const void* scales;
@@ -347,8 +347,8 @@ __host__ __device__ constexpr uint32_t instr_desc(int fmt /*0 f16, 1 bf16*/, int
 
 template <int QK, int BT>
 struct Plan {
-  static constexpr int kBits = (QK == kAff8) ? 8 : 4;
-  static constexpr int kWRowBytes = kBK * kBits / 8;          // 32 or 64
+  static constexpr int kBits = (QK == kFloat) ? 16 : ((QK == kAff8) ? 8 : 4);
+  static constexpr int kWRowBytes = kBK * kBits / 8;          // 32, 64 or (float weights) 128
   static constexpr int kXBytes = BT * kBK * 2;                // one activation stage
   static constexpr int kWBytes = kBF * kWRowBytes;            // one packed-weight stage
   static constexpr int kStageBytes = kXBytes + kWBytes;
@@ -594,19 +594,23 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
       const int kb_end = ti.kb_hi;
       float sc[2], bi[2];
       uint32_t e8[2];
-      if (kb < kb_end) fetch_tables(kb, sc, bi, e8);
+      if constexpr (QK == kFloat) { sc[0] = sc[1] = bi[0] = bi[1] = 0.0f; e8[0] = e8[1] = 0u; }
+      if (QK != kFloat && kb < kb_end) fetch_tables(kb, sc, bi, e8);
       for (; kb < kb_end; kb += kTeams) {
         it = it0 + static_cast<uint32_t>(kb - ti.kb_lo);
         const int s = it % P::kStages;
         float nsc[2] = {0.0f, 0.0f}, nbi[2] = {0.0f, 0.0f};
         uint32_t ne8[2] = {0u, 0u};
-        if (kb + kTeams < kb_end) fetch_tables(kb + kTeams, nsc, nbi, ne8);
+        if (QK != kFloat && kb + kTeams < kb_end) fetch_tables(kb + kTeams, nsc, nbi, ne8);
         if (!(ok = twait(&full[s], (it / P::kStages) & 1, abort_flag, 5))) break;
         const uint8_t* wsm = smem + s * P::kStageBytes + P::kXBytes + frow * P::kWRowBytes;
         uint32_t packed[2][kHalfWords];
 #pragma unroll
         for (int i = 0; i < P::kWRowBytes / 16; ++i) {
-          const uint4 v = *reinterpret_cast<const uint4*>(wsm + i * 16);
+          // float weights are 128-byte rows in the TMA unit's 128-byte swizzle (chunk i of row r
+          // sits at chunk i ^ (r & 7)): the lanes of a quarter-warp then read distinct banks
+          const int ci = (QK == kFloat) ? (i ^ (frow & 7)) : i;
+          const uint4 v = *reinterpret_cast<const uint4*>(wsm + ci * 16);
           const uint32_t q4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) packed[(i * 4 + e) / kHalfWords][(i * 4 + e) % kHalfWords] = q4[e];
@@ -616,7 +620,10 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
         uint32_t out[32];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          if constexpr (QK == kAff4) {
+          if constexpr (QK == kFloat) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) out[h * 16 + j] = packed[h][j];
+          } else if constexpr (QK == kAff4) {
             if (twide)
               dequant_aff4_wide<XT, kHalfWords>(packed[h], sc[h], bi[h], &out[h * 16]);
             else
@@ -830,7 +837,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
     return rc;
   const uint64_t wrow_bytes = static_cast<uint64_t>(p.K) * P::kBits / 8;
   if ((rc = make_map(&wm, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.w, wrow_bytes, static_cast<uint64_t>(w_rows),
-                     wrow_bytes, P::kWRowBytes, kBF, CU_TENSOR_MAP_SWIZZLE_NONE)))
+                     wrow_bytes, P::kWRowBytes, kBF, QK == kFloat ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE)))
     return rc;
   TcParams tp;
   tp.scales = p.scales; tp.biases = p.biases; tp.y = p.y; tp.group_sizes = p.group_sizes;
@@ -1001,7 +1008,7 @@ bool gemm_tc_supports(const qmm_problem& p) {
   if (p.x_dtype != QMM_BF16 && p.x_dtype != QMM_F16) return false;
   if (p.lhs_idx || p.rhs_idx) return false;                   // unsorted gathers go elsewhere
   if (p.batch > kMaxSegments) return false;
-  if (p.K < kBK || p.K % 32) return false;
+  if (p.K < kBK || p.K % (p.mode == QMM_MODE_FLOAT ? 8 : 32)) return false;
   if ((p.K * 2) % 16) return false;
   if (!p.group_sizes && p.batch > 1 && p.x_batch_stride != p.M * p.K) return false;
   if (!p.group_sizes && p.batch > 1 && p.y_batch_stride != p.M * p.N) return false;
@@ -1010,6 +1017,7 @@ bool gemm_tc_supports(const qmm_problem& p) {
 }
 
 int launch_gemm_tc(const qmm_problem& p, cudaStream_t stream) {
+  if (p.mode == QMM_MODE_FLOAT) return launch_xt<kFloat>(p, stream);
   if (p.mode == QMM_MODE_MXFP4) return launch_xt<kMx4>(p, stream);
   if (p.bits == 8) return launch_xt<kAff8>(p, stream);
   return launch_xt<kAff4>(p, stream);

@@ -61,6 +61,36 @@ def ragged_dot(x, w, scales, biases, group_sizes, group_size=64, bits=4, mode="a
     return y
 
 
+def ragged_mm(x, w, group_sizes, out_dtype=None):
+    """`ragged_dot` for float experts: `w [G, N, K]` holds values of x's type."""
+    y = torch.empty((x.shape[0], w.shape[-2]), dtype=out_dtype or x.dtype, device=x.device)
+    v = _lib.Views()
+    _lib.check(_lib.lib().qmm_ragged_mm(v(x.contiguous()), v(w.contiguous()), v(group_sizes.to(torch.int32).contiguous()),
+                                        v(y), _lib.stream_ptr(x)))
+    STATS["ragged_dot"] += 1
+    return y
+
+
+def gather_mm(x, w, lhs_idx, rhs_idx, out_dtype=None):
+    """`y[p] = x[lhs_idx[p]] @ w[rhs_idx[p]].T` for float experts: x `[T, M, K]`, w `[E, N, K]`
+    (the reference hands MLX the lazily transposed `[E, K, N]` view of the same array,
+    src/metaljax/moe.py:1324-1336), indices `[P]` -> `[P, M, N]`. The pairs are sorted by expert,
+    the sorted rows go through one grouped product, the result is put back in pair order."""
+    if x.dim() != 3:
+        raise RuntimeError("moe: gather operand is not [batch, M, K]")
+    e, n = w.shape[0], w.shape[1]
+    p, m = lhs_idx.shape[0], x.shape[1]
+    eidx = rhs_idx.reshape(-1).to(torch.int64)
+    order = torch.sort(eidx, stable=True).indices
+    sizes = torch.bincount(eidx, minlength=e).to(torch.int32) * m
+    rows = x.index_select(0, lhs_idx.reshape(-1).to(torch.int64).index_select(0, order)).reshape(p * m, x.shape[2])
+    ys = ragged_mm(rows, w, sizes, out_dtype=out_dtype)
+    y = torch.empty((p, m, n), dtype=ys.dtype, device=x.device)
+    y[order] = ys.reshape(p, m, n)
+    STATS["gather_mm"] += 1
+    return y
+
+
 def sort_pairs(indices: torch.Tensor, num_experts: int):
     """Router output `indices[T, K]` -> the sorted pair layout `ragged_dot` walks.
 
@@ -101,6 +131,22 @@ def moe_experts(x, indices, weights, w1, w3, w2, group_size=64, bits=4, mode="af
     contrib = down.to(sum_dtype) * wsorted[:, None]
     out = torch.zeros((t, down.shape[1]), dtype=sum_dtype, device=x.device)
     out.index_add_(0, tok, contrib)
+    return out.to(x.dtype)
+
+
+def moe_experts_float(x, indices, weights, w1, w3, w2, sum_dtype=torch.float32):
+    """`moe_experts` over FLOAT expert weights `w1, w3 [E, ffn, d]`, `w2 [E, d, ffn]` of x's
+    type: the same pair sort, three grouped products (`ragged_mm`), SwiGLU and routed sum."""
+    t, k = indices.shape
+    order, tok, group_sizes = sort_pairs(indices, w1.shape[0])
+    xs = x.index_select(0, tok)
+    act = silu_mul(ragged_mm(xs, w1, group_sizes), ragged_mm(xs, w3, group_sizes))
+    down = ragged_mm(act, w2, group_sizes)
+    if sum_dtype == torch.float32 and down.dtype in _GLUE_DTYPES and down.shape[1] % 8 == 0:
+        return routed_sum(down, order, weights, t, k)
+    wsorted = weights.reshape(-1).index_select(0, order).to(sum_dtype)
+    out = torch.zeros((t, down.shape[1]), dtype=sum_dtype, device=x.device)
+    out.index_add_(0, tok, down.to(sum_dtype) * wsorted[:, None])
     return out.to(x.dtype)
 
 

@@ -168,8 +168,38 @@ class ExpertBlock(moe.Match):
         self.verified = False
 
 
-def _find_match(st, value, through=("stablehlo.transpose", "stablehlo.reshape", "stablehlo.convert")):
-    """The quantized match whose root produces `value` (looking through shape ops)."""
+def _float_match(st, dot):
+    """A dot whose weight operand is a FLOAT array computed from `@main`'s arguments alone (an
+    unquantized expert weight, possibly converted / transposed on the way): the dimension
+    bookkeeping of a quantized match with nothing to dequantize. The reference plans these onto
+    `mx.gather_mm` (src/metaljax/moe.py:1324-1336). Cached per dot in `st`."""
+    from . import recognizer
+    cache = st.floats
+    if id(dot) in cache:
+        return cache[id(dot)]
+    last = None
+    for qside in (1, 0):
+        m = qmm.Match()
+        m.mode = "float"
+        w = dot.operands[qside]
+        try:
+            if w.type.el not in ("bf16", "f16") or dot.operands[1 - qside].type.el != w.type.el:
+                raise _Reject("float experts are taken in the activations' 16-bit type only")
+            recognizer._finish(st.fn, m, dot, [w], dot, qside=qside)
+            if not m.arg_indices:
+                raise _Reject("the weight operand does not come from an argument")
+        except _Reject as why:
+            last = why
+            continue
+        m.codes = w
+        cache[id(dot)] = m
+        return m
+    raise last or _Reject("no float expert weight under this dot")
+
+
+def _find_match(st, value, through=("stablehlo.transpose", "stablehlo.reshape", "stablehlo.convert"), floats=False):
+    """The quantized match whose root produces `value` (looking through shape ops); with
+    `floats`, a plain dot over a float expert weight counts too."""
     v = value
     while v.op is not None and v.op.name in through:
         v = v.op.operands[0]
@@ -178,13 +208,15 @@ def _find_match(st, value, through=("stablehlo.transpose", "stablehlo.reshape", 
     for m in st.matches:
         if not m.disabled and m.root is v.op:
             return m
+    if floats and v.op.name == "stablehlo.dot_general":
+        return _float_match(st, v.op)
     raise _Reject("expert activations do not come from a recognized quantized dot")
 
 
 def _plan_swiglu(st, Y, r: Router) -> ExpertBlock:
     """Y = down( silu(gate(x)) * up(x) ) on three matches of the quantized recognizer."""
-    down = _find_match(st, Y)
-    if down.bshape != [r.E] or down.M != r.T or down.swapped or down.mode not in ("affine", "mxfp4"):
+    down = _find_match(st, Y, floats=True)
+    if down.bshape != [r.E] or down.M != r.T or down.swapped or down.mode not in ("affine", "mxfp4", "float"):
         raise _Reject("the last expert dot is not batched over the experts with the tokens as rows")
     act = down.lhs
     while act.op is not None and act.op.name in ("stablehlo.transpose", "stablehlo.reshape", "stablehlo.convert"):
@@ -208,7 +240,9 @@ def _plan_swiglu(st, Y, r: Router) -> ExpertBlock:
         g = silu_of(prod.operands[i])
         if g is None:
             continue
-        gate, up = _find_match(st, g), _find_match(st, prod.operands[1 - i])
+        gate, up = _find_match(st, g, floats=True), _find_match(st, prod.operands[1 - i], floats=True)
+        if len({m.mode == "float" for m in (gate, up, down)}) != 1:
+            raise _Reject("float and quantized projections in one expert block")
         for m in (gate, up):
             if m.bshape or m.swapped or m.M != r.T or len(m.nshape) != 2 or m.nshape[0] != r.E:
                 raise _Reject("an expert projection does not lead its output features with the expert axis")
@@ -227,6 +261,7 @@ def analyze(interp, st) -> None:
     """Find dense expert blocks on top of the quantized matches in `st` (the reference chains
     its recognizers the same way, src/metaljax/qmm.py:1085-1091). Never raises."""
     fn = interp.func
+    st.fn = fn
     try:
         for op in fn.walk():
             if op.name != "stablehlo.reduce" or op.attrs.get("applies") != "stablehlo.add":
@@ -340,6 +375,24 @@ def _expert_pack(interp, m, E):
     return stack(w), stack(s), stack(b)
 
 
+def _float_weight(interp, m, env, E):
+    """The float expert weight of `m` as `[E, rows, K]`, contiguous: evaluated from the argument
+    buffers once and kept while those buffers are the same objects (like a pack)."""
+    from . import recognizer
+    fn = interp.func
+    leaves = [env[fn.args[i]] for i in m.arg_indices]
+    for pk in m.packs:
+        if pk.matches(leaves):
+            return pk.w
+    t = hlo.evaluate_value(m.codes, {a: env[a] for a in fn.args if a in env})
+    w = recognizer._to_nk(recognizer._replay(t, m.post), m).contiguous()
+    w = w.reshape(E, -1, w.shape[-1])
+    pk = qmm._Pack(leaves, w, None, None, None, 0, 16, "float")
+    m.packs.insert(0, pk)
+    del m.packs[2:]
+    return w
+
+
 def emit(interp, b: ExpertBlock, env):
     """The gathered expert block in place of the dense region."""
     r = b.router
@@ -349,6 +402,11 @@ def emit(interp, b: ExpertBlock, env):
     if list(b.gate.lperm) != list(range(x.dim())):
         x = x.permute(*b.gate.lperm)
     x = x.reshape(b.T, b.gate.K)
+    if b.gate.mode == "float":
+        y = moe.moe_experts_float(x.to(b.out_dtype) if x.dtype != b.out_dtype else x, idx, wts,
+                                  _float_weight(interp, b.gate, env, b.E), _float_weight(interp, b.up, env, b.E),
+                                  _float_weight(interp, b.down, env, b.E))
+        return [y.reshape(b.out_shape).to(b.out_dtype)]
     kw = dict(group_size=b.gate.gs, bits=b.gate.bits, mode=b.gate.mode)
     if (b.up.gs, b.up.bits, b.down.gs, b.down.bits) != (b.gate.gs, b.gate.bits, b.gate.gs, b.gate.bits):
         raise _Reject("the three projections are packed differently")

@@ -424,11 +424,13 @@ class State:
     """Per-program recognizer state: matches, the skip set, root dispatch and the flat
     list of packed arrays `emit` reads by slot."""
 
-    __slots__ = ("matches", "skip", "roots", "values", "active", "moe")
+    __slots__ = ("matches", "skip", "roots", "values", "active", "moe", "fn", "floats")
 
     def __init__(self):
         self.matches = []
         self.moe = []
+        self.fn = None               # the program (set by the analysis that needs it)
+        self.floats = {}             # dots over float expert weights, by op identity
         self.skip = frozenset()
         self.roots = {}
         self.values = []

@@ -673,7 +673,7 @@ def prologue(interp, args) -> bool:
     `st.values` (`m.slot`, `m.nvals`). Returns True when the set of live rewrites changed
     (a match was disabled), so that a caller that caches a traced program can retrace."""
     st = analyze(interp)
-    if not st.matches:
+    if not st.matches and not st.moe:
         return False
     from . import moe_recognizer
     changed = moe_recognizer.prologue(interp, st, args[0].device if args else None)
@@ -743,7 +743,7 @@ def static_trip(loop):
 
 def _state_of(interp):
     st = analyze(interp)
-    return st if st is not None and st.matches else None
+    return st if st is not None and (st.matches or st.moe) else None
 
 
 def block_cost(interp, block) -> int:
@@ -841,7 +841,7 @@ def captures(interp, env, free):
     keeps the body's arity stable (src/metaljax/ops/control.py:700-725)."""
     st = interp._qmm
     skipped = set()
-    if st is not None and st.matches:
+    if st is not None and (st.matches or st.moe):
         skipped = st.skip
     caps = []
     for v in free:

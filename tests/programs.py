@@ -261,6 +261,53 @@ module @jit_moe {{
 """
 
 
+def moe_program_float(t=6, d=64, e=4, f=64, k=2):
+    """The same dense SwiGLU mixture-of-experts layer with FLOAT (bf16) expert weights: nothing
+    to dequantize, the three dots read their weights straight from the arguments."""
+    return f"""
+module @jit_moe_float {{
+  func.func public @main(%arg0: tensor<{t}x{d}xbf16>, %arg1: tensor<{t}x{e}xf32>, %arg2: tensor<{e}x{f}x{d}xbf16>, %arg3: tensor<{e}x{f}x{d}xbf16>, %arg4: tensor<{e}x{d}x{f}xbf16>) -> (tensor<{t}x{d}xbf16>) {{
+    %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %cst_0 = stablehlo.constant dense<0.000000e+00> : tensor<bf16>
+    %0:2 = chlo.top_k(%arg1, k = {k}) : tensor<{t}x{e}xf32> -> (tensor<{t}x{k}xf32>, tensor<{t}x{k}xi32>)
+    %1 = stablehlo.exponential %0#0 : tensor<{t}x{k}xf32>
+    %2 = stablehlo.reduce(%1 init: %cst) applies stablehlo.add across dimensions = [1] : (tensor<{t}x{k}xf32>, tensor<f32>) -> tensor<{t}xf32>
+    %3 = stablehlo.broadcast_in_dim %2, dims = [0] : (tensor<{t}xf32>) -> tensor<{t}x{k}xf32>
+    %4 = stablehlo.divide %1, %3 : tensor<{t}x{k}xf32>
+    %5 = stablehlo.iota dim = 2 : tensor<{t}x{k}x{e}xi32>
+    %6 = stablehlo.broadcast_in_dim %0#1, dims = [0, 1] : (tensor<{t}x{k}xi32>) -> tensor<{t}x{k}x{e}xi32>
+    %7 = stablehlo.compare EQ, %6, %5, SIGNED : (tensor<{t}x{k}x{e}xi32>, tensor<{t}x{k}x{e}xi32>) -> tensor<{t}x{k}x{e}xi1>
+    %8 = stablehlo.convert %7 : (tensor<{t}x{k}x{e}xi1>) -> tensor<{t}x{k}x{e}xf32>
+    %9 = stablehlo.broadcast_in_dim %4, dims = [0, 1] : (tensor<{t}x{k}xf32>) -> tensor<{t}x{k}x{e}xf32>
+    %10 = stablehlo.multiply %8, %9 : tensor<{t}x{k}x{e}xf32>
+    %11 = stablehlo.reduce(%10 init: %cst) applies stablehlo.add across dimensions = [1] : (tensor<{t}x{k}x{e}xf32>, tensor<f32>) -> tensor<{t}x{e}xf32>
+    %16 = stablehlo.dot_general %arg0, %arg2, contracting_dims = [1] x [2] : (tensor<{t}x{d}xbf16>, tensor<{e}x{f}x{d}xbf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %21 = stablehlo.dot_general %arg0, %arg3, contracting_dims = [1] x [2] : (tensor<{t}x{d}xbf16>, tensor<{e}x{f}x{d}xbf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %22 = stablehlo.logistic %16 : tensor<{t}x{e}x{f}xbf16>
+    %23 = stablehlo.multiply %16, %22 : tensor<{t}x{e}x{f}xbf16>
+    %24 = stablehlo.multiply %23, %21 : tensor<{t}x{e}x{f}xbf16>
+    %25 = stablehlo.transpose %24, dims = [1, 0, 2] : (tensor<{t}x{e}x{f}xbf16>) -> tensor<{e}x{t}x{f}xbf16>
+    %30 = stablehlo.dot_general %25, %arg4, batching_dims = [0] x [0], contracting_dims = [2] x [2] : (tensor<{e}x{t}x{f}xbf16>, tensor<{e}x{d}x{f}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %31 = stablehlo.convert %11 : (tensor<{t}x{e}xf32>) -> tensor<{t}x{e}xbf16>
+    %32 = stablehlo.broadcast_in_dim %31, dims = [1, 0] : (tensor<{t}x{e}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %33 = stablehlo.multiply %30, %32 : tensor<{e}x{t}x{d}xbf16>
+    %34 = stablehlo.reduce(%33 init: %cst_0) applies stablehlo.add across dimensions = [0] : (tensor<{e}x{t}x{d}xbf16>, tensor<bf16>) -> tensor<{t}x{d}xbf16>
+    return %34 : tensor<{t}x{d}xbf16>
+  }}
+}}
+"""
+
+
+def moe_float_inputs(t=6, d=64, e=4, f=64, seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn((t, d), generator=g) * 0.5).to(torch.bfloat16)
+    logits = torch.randn((t, e), generator=g)
+    w1 = (torch.randn((e, f, d), generator=g) * 0.1).to(torch.bfloat16)
+    w3 = (torch.randn((e, f, d), generator=g) * 0.1).to(torch.bfloat16)
+    w2 = (torch.randn((e, d, f), generator=g) * 0.1).to(torch.bfloat16)
+    return [a.to(device) for a in (x, logits, w1, w3, w2)]
+
+
 def moe_inputs(t=6, d=64, e=4, f=64, gs=32, seed=0, device="cpu"):
     g = torch.Generator().manual_seed(seed)
     x = (torch.randn((t, d), generator=g) * 0.5).to(torch.bfloat16)

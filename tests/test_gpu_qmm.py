@@ -563,3 +563,51 @@ def test_moe_glue_kernels_match_the_two_step_forms(dtype):
         acc = acc + rows[inv.reshape(t, k)[:, j]].float() * weights[:, j:j + 1].float()
     assert torch.equal(out, acc.to(dtype))
     assert _lib.poll_status() == 0
+
+
+@pytest.mark.parametrize("dtype,e,n,k,sizes,extra", [
+    (torch.bfloat16, 5, 136, 200, [70, 0, 129, 1, 100], 4),        # an empty expert, a one-row expert, a K tail, rows past the groups
+    (torch.float16, 3, 300, 64, [256, 257, 3], 0),                 # tiles that straddle expert boundaries
+    (torch.bfloat16, 8, 512, 1024, [200] * 8, 0),
+])
+def test_ragged_mm_float_experts(dtype, e, n, k, sizes, extra):
+    """The grouped product over FLOAT expert weights (the reference's `mx.gather_mm` once the
+    pairs are sorted, src/metaljax/moe.py:1324-1336) against float64, with the reference's gate:
+    within 1e-2 of the largest magnitude and no worse than 1.5x the literal bf16/f16 matmul."""
+    g = torch.Generator(device=DEV).manual_seed(e * 1000 + n)
+    rows = sum(sizes) + extra
+    x = torch.randn((rows, k), generator=g, device=DEV).to(dtype)
+    w = (torch.randn((e, n, k), generator=g, device=DEV) * 0.1).to(dtype)
+    gs = torch.tensor(sizes, device=DEV, dtype=torch.int32)
+    y = moe.ragged_mm(x, w, gs)
+    assert y.shape == (rows, n) and y.dtype == dtype
+    exact = torch.zeros((rows, n), device=DEV, dtype=torch.float64)
+    literal = torch.zeros((rows, n), device=DEV, dtype=dtype)
+    lo = 0
+    for ex, sz in enumerate(sizes):
+        exact[lo:lo + sz] = x[lo:lo + sz].double() @ w[ex].double().T
+        literal[lo:lo + sz] = x[lo:lo + sz] @ w[ex].T
+        lo += sz
+    scale = exact.abs().max().item()
+    err = (y.double() - exact).abs().max().item() / scale
+    err_l = (literal.double() - exact).abs().max().item() / scale
+    assert err <= 1e-2 and err <= 1.5 * err_l + 1e-6, (err, err_l)
+    assert bool((y[sum(sizes):] == 0).all())                       # rows past the last group
+    assert _lib.poll_status() == 0
+
+
+def test_gather_mm_float_experts_in_router_order():
+    g = torch.Generator(device=DEV).manual_seed(77)
+    t, m, k, e, n, p = 9, 2, 128, 4, 72, 23
+    x = torch.randn((t, m, k), generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn((e, n, k), generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+    lhs = torch.randint(0, t, (p,), generator=g, device=DEV)
+    rhs = torch.randint(0, e, (p,), generator=g, device=DEV)
+    y = moe.gather_mm(x, w, lhs, rhs)
+    want = torch.einsum("pmk,pnk->pmn", x[lhs].double(), w[rhs].double())
+    assert y.shape == (p, m, n)
+    assert (y.double() - want).abs().max() <= 1e-2 * want.abs().max()
+    with pytest.raises(RuntimeError):
+        moe.gather_mm(x[0], w, lhs, rhs)                             # a 2-D operand has no batch to gather from
+    with pytest.raises(_lib.QmmError):
+        moe.ragged_mm(x.reshape(-1, k)[:, :60].contiguous(), w[:, :, :60].contiguous(), torch.tensor([18, 0, 0, 0], device=DEV, dtype=torch.int32))

@@ -90,6 +90,23 @@ def test_dense_moe_layer_becomes_the_gathered_block():
         assert len(st.moe) == 1 and st.moe[0].verified and all(m.absorbed for m in st.matches)
 
 
+def test_dense_float_moe_layer_becomes_the_gathered_block():
+    """The same layer with unquantized bf16 experts: planned onto the float grouped product
+    (`qmm_ragged_mm`), same gate; the expert weights are laid out once per set of buffers."""
+    from metaljax_b200 import moe
+    from programs import moe_float_inputs, moe_program_float
+    for t, d, e, f in ((6, 64, 4, 64), (40, 128, 8, 256)):
+        moe.reset_stats()
+        args = moe_float_inputs(t, d, e, f, seed=t, device=DEV)
+        it = _gate(moe_program_float(t, d, e, f), args)
+        st = it._qmm
+        assert st.matches == [] and len(st.moe) == 1 and st.moe[0].verified and st.moe[0].gate.mode == "float"
+        assert moe.stats()["ragged_dot"] == 3
+        first = st.moe[0].gate.packs[0].w
+        it.execute(args)
+        assert st.moe[0].gate.packs[0].w is first                  # not rebuilt for the same buffers
+
+
 def test_expert_stack_packs_in_row_blocks_within_a_memory_bound():
     """A [32, 5760, 2880] MXFP4 expert weight (the shape the reference's pack-transient notes
     measure, notes/qmm-pack-transient-2026-08.md:100-109): its reconstruction chain evaluated

@@ -109,3 +109,24 @@ module @threshold_router {
     assert M.verify_router(r, draws=1)                  # continuous logits: no ties, looks like top-2
     assert not M.verify_router(r, draws=3)              # halves: ties at the second place give it away
     assert M.STATS["verified"] == before + 1
+
+
+def test_float_expert_block_is_planned_on_the_float_grouped_product():
+    """Unquantized (bf16) experts: the same router proof and region, the three projections read
+    their weights straight from the arguments and are planned onto the float grouped product
+    (the reference's `mx.gather_mm` branch, src/metaljax/moe.py:1324-1336)."""
+    from programs import moe_program_float
+    it = recognizer.Interpreter(moe_program_float(t=6, d=64, e=4, f=64, k=2))
+    st = recognizer.analyze(it)
+    assert st.matches == [] and len(st.moe) == 1 and st.active
+    b = st.moe[0]
+    assert (b.gate.mode, b.up.mode, b.down.mode) == ("float", "float", "float")
+    assert b.gate.nshape == [4, 64] and b.gate.K == 64 and b.down.bshape == [4] and (b.down.N, b.down.K) == (64, 64)
+    assert b.gate.arg_indices == (2,) and b.up.arg_indices == (3,) and b.down.arg_indices == (4,)
+    names = [o.name for o in it.func.ops if id(o) in st.skip]
+    assert names.count("stablehlo.dot_general") == 3 and "stablehlo.logistic" in names
+    assert "chlo.top_k" not in names                              # the router's own outputs stay
+    # float32 experts keep their literal dots (the fused product takes the activations' 16-bit type)
+    f32 = moe_program_float(t=6, d=64, e=4, f=64, k=2).replace("%arg2: tensor<4x64x64xbf16>", "%arg2: tensor<4x64x64xf32>")
+    f32 = f32.replace("(tensor<6x64xbf16>, tensor<4x64x64xbf16>) -> tensor<6x4x64xbf16>\n    %21", "(tensor<6x64xbf16>, tensor<4x64x64xf32>) -> tensor<6x4x64xbf16>\n    %21")
+    assert recognizer.analyze(recognizer.Interpreter(f32)).moe == []
