@@ -78,6 +78,7 @@ typedef struct {
 } qmm_exchange;
 
 typedef enum { QMM_PROLOGUE_NONE = 0, QMM_PROLOGUE_ADD_RMSNORM = 1, QMM_PROLOGUE_SWIGLU = 2 } qmm_prologue;
+typedef enum { QMM_EPILOGUE_NONE = 0, QMM_EPILOGUE_SWIGLU_PAIRS = 1 } qmm_epilogue;
 
 typedef struct {
   int32_t prologue;         /* qmm_prologue: what the linear's activation row is made from
@@ -94,6 +95,15 @@ typedef struct {
   void* residual_out;
   const void* norm_weight;  /* [K] bf16 */
   float eps;
+  int32_t epilogue;         /* qmm_epilogue: what is pushed
+                             *   NONE          the N outputs
+                             *   SWIGLU_PAIRS  the weight's rows alternate gate_j, up_j (rows 2j, 2j + 1): the
+                             *                 N / 2 values silu(y[2j]) * y[2j + 1], each y rounded to bf16 first
+                             *                 (what a separate SwiGLU of the stored outputs computes); they go to
+                             *                 epilogue_out and / or, with push_slot >= 0, to the gather slots (this
+                             *                 rank's N / 2 columns of a row of world * N / 2); N a multiple of 16;
+                             *                 problem->y, if given, still receives the N plain outputs */
+  void* epilogue_out;       /* [N / 2] bf16, or NULL */
 } qmm_decode_fusion;
 
 /* Advances this rank's step counter: once at the start of every decode step, on the step's

@@ -62,7 +62,7 @@ class DecodeFusion(ctypes.Structure):
     _fields_ = [("prologue", ctypes.c_int32), ("wait_slot", ctypes.c_int32), ("wait_site", ctypes.c_int32),
                 ("push_slot", ctypes.c_int32), ("push_site", ctypes.c_int32),
                 ("residual_in", ctypes.c_void_p), ("residual_out", ctypes.c_void_p),
-                ("norm_weight", ctypes.c_void_p), ("eps", ctypes.c_float)]
+                ("norm_weight", ctypes.c_void_p), ("eps", ctypes.c_float), ("epilogue", ctypes.c_int32), ("epilogue_out", ctypes.c_void_p)]
 
 
 _lib = None

@@ -353,7 +353,8 @@ extern "C" int qmm_decode_linear(const qmm_problem* problem, const qmm_decode_fu
   alignas(16) static unsigned char dummy_y[16];
   const bool no_y = !p.y;
   if (no_y) {
-    if (!pushes) return fail(QMM_ERR_NULL, "decode_linear: y is NULL and nothing is pushed");
+    if (!pushes && !(fusion->epilogue == QMM_EPILOGUE_SWIGLU_PAIRS && fusion->epilogue_out))
+      return fail(QMM_ERR_NULL, "decode_linear: y is NULL and nothing is pushed");
     p.y = dummy_y;                                    // (passes the pointer checks; never written: see below)
   }
   int rc = check_problem(p);
@@ -369,8 +370,16 @@ extern "C" int qmm_decode_linear(const qmm_problem* problem, const qmm_decode_fu
     return fail(QMM_ERR_SHAPE, "decode_linear: SwiGLU blocks must be multiples of 8 wide");
   if ((waits && (fusion->wait_site < 0 || fusion->wait_site >= 1023)) || (pushes && (fusion->push_site < 0 || fusion->push_site >= 1023)))
     return fail(QMM_ERR_SHAPE, "decode_linear: exchange sites are 0..1022");
+  if (fusion->epilogue != QMM_EPILOGUE_NONE && fusion->epilogue != QMM_EPILOGUE_SWIGLU_PAIRS)
+    return fail(QMM_ERR_UNSUPPORTED, "decode_linear: unknown epilogue %d", fusion->epilogue);
+  const bool pairs = fusion->epilogue == QMM_EPILOGUE_SWIGLU_PAIRS;
+  if (pairs && ((!pushes && !fusion->epilogue_out) || p.N % 16))
+    return fail(QMM_ERR_SHAPE, "decode_linear: the SwiGLU epilogue needs somewhere to put its N / 2 values, and N a multiple of 16");
+  if (pairs && (reinterpret_cast<uintptr_t>(fusion->epilogue_out) & 15))
+    return fail(QMM_ERR_LAYOUT, "decode_linear: epilogue_out must be 16-byte aligned");
   if (pushes && p.N % 8) return fail(QMM_ERR_LAYOUT, "decode_linear: a pushed slice must be a multiple of 8 values");
-  if (pushes && world * p.N * 4 > ex->slot_bytes)           // (a stamped row takes 4 bytes per value)
+  const int64_t n_out = pairs ? p.N / 2 : p.N;             // values this rank contributes to the gathered row
+  if (pushes && world * n_out * 4 > ex->slot_bytes)         // (a stamped row takes 4 bytes per value)
     return fail(QMM_ERR_SHAPE, "decode_linear: the gathered row does not fit a slot");
   if (waits && p.K * (fusion->prologue == QMM_PROLOGUE_SWIGLU ? 2 : 1) * 4 > ex->slot_bytes)
     return fail(QMM_ERR_SHAPE, "decode_linear: the awaited row does not fit a slot");
@@ -388,8 +397,10 @@ extern "C" int qmm_decode_linear(const qmm_problem* problem, const qmm_decode_fu
     for (int r = 0; r < world; ++r) {
       if (!ex->peer_bufs[r]) return fail(QMM_ERR_NULL, "decode_linear: bad peer pointer");
       f.push_dst[r] = static_cast<uint8_t*>(ex->peer_bufs[r]) + static_cast<int64_t>(fusion->push_slot) * ex->slot_bytes +
-                      static_cast<int64_t>(ex->rank) * p.N * 4;
+                      static_cast<int64_t>(ex->rank) * n_out * 4;
     }
   }
+  f.epilogue = pairs ? 1 : 0;
+  f.epilogue_out = pairs ? fusion->epilogue_out : nullptr;
   return launch_gemv_imma(p, static_cast<cudaStream_t>(stream), &f);
 }

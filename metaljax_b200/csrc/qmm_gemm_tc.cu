@@ -352,18 +352,22 @@ struct Plan {
   static constexpr int kXBytes = BT * kBK * 2;                // one activation stage
   static constexpr int kWBytes = kBF * kWRowBytes;            // one packed-weight stage
   static constexpr int kStageBytes = kXBytes + kWBytes;
-  // as many stages as fit next to the barriers and the tile tables, at most 8 (the
-  // dequantized-A ring in TMEM has one 32-column slot per stage)
+  // as many stages as fit next to the barriers and the tile tables (the dequantized-A ring in
+  // tensor memory has one 32-column slot per stage)
   static constexpr int kFit = (232448 - 4200 - 2048) / kStageBytes;
   // The depth is a multiple of the number of dequant teams, so that a ring slot is always
   // handled by the same team: a waiter then never lags its barrier by two phases, which a
   // parity wait could not tell from "ready".
-  static constexpr int kStages = kFit >= 8 ? 8 : 4;
+  // Narrow token tiles leave most of tensor memory to the A ring and stage little: twelve
+  // slots instead of eight cover the per-slot latency chain (TMA, one team's dequantization,
+  // MMA, commit) that bounds a CTA's rate at a few dozen rows.
+  static constexpr int kACol0 = (BT <= 64) ? 64 : 256;        // A ring starts here (D is columns [0, BT))
+  static constexpr int kTmemFit = (512 - kACol0) / 32;
+  static constexpr int kStages = (kFit >= 12 && kTmemFit >= 12) ? 12 : (kFit >= 8 ? 8 : 4);
   static_assert(kFit >= 4, "a ring of four stages must fit");
   static constexpr int kBarBytes = 1024;
   static constexpr int kSmem = kStages * kStageBytes + kBarBytes + 1024 /* alignment slack */;
   static constexpr int kDCols = BT;                           // accumulator columns
-  static constexpr int kACol0 = 256;                          // A ring starts here
   static constexpr int kTmemCols = 512;
 };
 

@@ -89,6 +89,8 @@ struct ImmaParams {
   int push_world;           // > 0: y also goes, stamped (epoch, push_site), to this rank's column block
   int push_site;            //      of every rank's slot
   uint8_t* push_dst[8];
+  int epilogue;             // 1: rows alternate gate, up; the pushed values are silu(gate) * up
+  void* epilogue_out;       //    ... also written plainly here ([N / 2] bf16) when not NULL
   long long spin_limit;
 #if QMM_STEP_TRACING
   unsigned long long* trace;
@@ -585,14 +587,29 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
   // the row every rank gathers): plain 16-byte peer stores of {pair, stamp, pair, stamp};
   // lane <-> (rank, 8 rows); made by the last warp.
   const uint32_t push_stamp = exchange_seq(epoch, p.push_site);
+  const bool pairs = FUSED && p.epilogue == 1;
+  const bool tile_out = push_world > 0 || pairs;     // finished tiles pass through shared memory
   auto push_tile = [&](int tl, int buf) {
     const int peer = lane / R, v = lane % R;
     const int n8 = tl * kTileRows + v * 8;
-    if (peer < push_world && n8 < p.N) {
+    const bool plain = pairs && peer == 0 && p.epilogue_out != nullptr;
+    if ((peer < push_world || plain) && n8 < p.N) {
       const uint4 d = *reinterpret_cast<const uint4*>(ypush + buf * kTileRows + v * 8);
-      uint4* dst = reinterpret_cast<uint4*>(p.push_dst[peer] + static_cast<int64_t>(n8) * 4);
-      dst[0] = make_uint4(d.x, push_stamp, d.y, push_stamp);
-      dst[1] = make_uint4(d.z, push_stamp, d.w, push_stamp);
+      if (pairs) {
+        // rows (2j, 2j + 1) = (gate_j, up_j): four values silu(gate) * up, two stamped units
+        float f[8];
+        unpack8<__nv_bfloat16>(d, f);
+        const __nv_bfloat162 o0 = __floats2bfloat162_rn(f[0] / (1.0f + __expf(-f[0])) * f[1], f[2] / (1.0f + __expf(-f[2])) * f[3]);
+        const __nv_bfloat162 o1 = __floats2bfloat162_rn(f[4] / (1.0f + __expf(-f[4])) * f[5], f[6] / (1.0f + __expf(-f[6])) * f[7]);
+        const uint32_t u0 = *reinterpret_cast<const uint32_t*>(&o0), u1 = *reinterpret_cast<const uint32_t*>(&o1);
+        if (plain) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.epilogue_out) + n8 / 2) = make_uint2(u0, u1);
+        if (peer < push_world)
+          *reinterpret_cast<uint4*>(p.push_dst[peer] + static_cast<int64_t>(n8 / 2) * 4) = make_uint4(u0, push_stamp, u1, push_stamp);
+      } else {
+        uint4* dst = reinterpret_cast<uint4*>(p.push_dst[peer] + static_cast<int64_t>(n8) * 4);
+        dst[0] = make_uint4(d.x, push_stamp, d.y, push_stamp);
+        dst[1] = make_uint4(d.z, push_stamp, d.w, push_stamp);
+      }
     }
   };
   for (int tile = blockIdx.x; tile < ntiles; tile += tstride) {
@@ -748,7 +765,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
       if (threadIdx.x == 0) atomicCAS(p.status, 0, *abort_flag);
       return;
     }
-    if (push_world > 0 && prev_tile >= 0 && warp == NW - 1) push_tile(prev_tile, rbuf ^ 1);   // (complete since this barrier)
+    if (tile_out && prev_tile >= 0 && warp == NW - 1) push_tile(prev_tile, rbuf ^ 1);   // (complete since this barrier)
     // ---- rows x NW threads: the warps' shares (fixed order) plus the bias term ----
     if (frow < kTileRows) {
       const int n = tile * kTileRows + frow;
@@ -780,7 +797,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
           else if (p.y_dtype == QMM_F16) static_cast<__half*>(p.y)[n] = __float2half_rn(s);
           else static_cast<float*>(p.y)[n] = s;
         }
-        if (push_world > 0) ypush[rbuf * kTileRows + frow] = __float2bfloat16_rn(s);
+        if (tile_out) ypush[rbuf * kTileRows + frow] = __float2bfloat16_rn(s);
       }
     }
     rbuf ^= 1;
@@ -788,7 +805,7 @@ qmm_gemv_imma_kernel(const __grid_constant__ CUtensorMap w_map, const ImmaParams
     prev_tile = tile;
   }
   QMM_TRACE(trace, 5);               // all tiles done
-  if (push_world > 0) {
+  if (tile_out) {
     __syncthreads();                 // the last tile's rows are in shared memory
     if (warp == NW - 1 && prev_tile >= 0) push_tile(prev_tile, rbuf ^ 1);
   }
@@ -936,6 +953,8 @@ int launch_gemv_imma(const qmm_problem& p, cudaStream_t stream, const DecodeFusi
     ip.wait_world = fusion->wait_world; ip.wait_site = fusion->wait_site;
     ip.push_world = fusion->push_world; ip.push_site = fusion->push_site;
     for (int r = 0; r < 8; ++r) ip.push_dst[r] = fusion->push_dst[r];
+    ip.epilogue = fusion->epilogue;
+    ip.epilogue_out = fusion->epilogue_out;
     ip.spin_limit = wait_limit_clocks();
   }
   ip.x = p.x; ip.scales = p.scales; ip.biases = p.biases; ip.y = p.y;

@@ -55,6 +55,8 @@ struct DecodeFusion {
   int wait_world, wait_site; // x is a stamped row in this rank's gather slot
   int push_world, push_site; // y also goes, stamped, to every rank's slot
   uint8_t* push_dst[8];
+  int epilogue;              // 1: rows alternate gate, up; silu(gate) * up is what is pushed / written
+  void* epilogue_out;        //    ... plainly to here ([N / 2] bf16), when not NULL
 };
 
 // The single-row (M = 1) integer tensor-core decode kernel; launch_gemv hands it what it takes.

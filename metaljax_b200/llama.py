@@ -285,6 +285,14 @@ class DecodeStep:
                 dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
                 if int(ok.item()) == 0:
                     self.fused = False
+        if self.fused:
+            # the fused gate/up kernel applies SwiGLU in its epilogue: its rows alternate gate_j, up_j
+            idx = torch.stack([torch.arange(self.ffn_l, device=dev), torch.arange(self.ffn_l, device=dev) + self.ffn_l],
+                              dim=1).reshape(-1)
+            for layer in self.layers:
+                lin = layer["gate_up"]
+                lin.w = lin.w.view(torch.int32).index_select(0, idx).contiguous().view(torch.uint32)
+                lin.s, lin.b = lin.s.index_select(0, idx).contiguous(), lin.b.index_select(0, idx).contiguous()
         self.graph = None
         self.tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
         self.next_tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
@@ -335,10 +343,13 @@ class DecodeStep:
 
     # ---- the step ----
     def _fused_linear(self, lin, x, y, prologue=0, wait=None, push=None, residual_in=None, residual_out=None,
-                      norm_weight=None):
-        """One `qmm_decode_linear`: `wait` / `push` are (slot, site) pairs or None."""
+                      norm_weight=None, swiglu_out=None, swiglu=False):
+        """One `qmm_decode_linear`: `wait` / `push` are (slot, site) pairs or None; with `swiglu`
+        the weight's rows alternate gate, up and silu(gate) * up is what leaves the kernel."""
         f = _lib.DecodeFusion()
         f.prologue = prologue
+        f.epilogue = 1 if swiglu else 0
+        f.epilogue_out = None if swiglu_out is None else swiglu_out.data_ptr()
         f.wait_slot, f.wait_site = wait if wait is not None else (-1, 0)
         f.push_slot, f.push_site = push if push is not None else (-1, 0)
         f.residual_in = None if residual_in is None else residual_in.data_ptr()
@@ -378,13 +389,14 @@ class DecodeStep:
             self._fused_linear(layer["o"], None if g > 1 else self.attn_l, None if g > 1 else self.o_l, wait=at_push, push=o_push)
             site += g > 1
             gu_push = (site % 2, site) if g > 1 else None
-            self._fused_linear(layer["gate_up"], None if g > 1 else self.o_l, None if g > 1 else self.gate_up, prologue=1,
+            # (gate/up rows are interleaved in the fused layout: SwiGLU happens in that kernel's epilogue)
+            self._fused_linear(layer["gate_up"], None if g > 1 else self.o_l, None, prologue=1,
                                wait=o_push, push=gu_push, residual_in=self.res2[1], residual_out=self.res2[0],
-                               norm_weight=layer["ln2"])
+                               norm_weight=layer["ln2"], swiglu=True, swiglu_out=None if g > 1 else self.act_l)
             site += g > 1
             dn_push = (site % 2, site) if g > 1 else None
-            self._fused_linear(layer["down"], None if g > 1 else self.gate_up, None if g > 1 else self.down_l,
-                               prologue=2, wait=gu_push, push=dn_push)
+            self._fused_linear(layer["down"], None if g > 1 else self.act_l, None if g > 1 else self.down_l,
+                               wait=gu_push, push=dn_push)
             site += g > 1
             down_wait, x_in = dn_push, self.down_l
         self._fused_linear(self.lm_head, None if down_wait else x_in, self.logits_l, prologue=1, wait=down_wait,

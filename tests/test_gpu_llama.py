@@ -212,3 +212,58 @@ def test_decode_attention_against_rope_and_sdpa(batch, heads, kvh, hd, ctx, pos)
         assert (out.float() - want).abs().max().item() <= 2e-2 * max(want.abs().max().item(), 1e-3)
     assert torch.equal(kc2, kc) and torch.equal(vc2, vc)     # the same append
     assert _lib.poll_status() == 0
+
+
+def test_decode_linear_swiglu_epilogue():
+    """Gate and up rows interleaved in one weight, SwiGLU applied where the tile is finished:
+    bit for bit the separate SwiGLU of the stored bf16 outputs, written plainly and / or pushed as
+    stamped units; the down projection that follows reads either."""
+    import ctypes
+    from metaljax_b200 import _lib, llama
+    g = torch.Generator(device=DEV).manual_seed(9)
+    d, f = 512, 1088                                     # 2 f = 2176 rows = 68 tiles of 32: a ragged last wave
+    gate_up, down = llama._Linear(2 * f, d, DEV, g, 64, "normal"), llama._Linear(d, f, DEV, g, 64, "normal")
+    x = torch.randn((1, d), generator=g, device=DEV).to(torch.bfloat16)
+    lib, stream = _lib.lib(), _lib.stream_ptr(x)
+    # reference: [gate | up] halves, stored as bf16, then the glue kernel
+    gu = torch.empty((1, 2 * f), device=DEV, dtype=torch.bfloat16)
+    gate_up(x, gu)
+    act_ref = torch.empty((1, f), device=DEV, dtype=torch.bfloat16)
+    llama.silu_mul(gu, act_ref)
+    dn_ref = torch.empty((1, d), device=DEV, dtype=torch.bfloat16)
+    down(act_ref, dn_ref)
+    # the interleaved layout of the same weight
+    idx = torch.stack([torch.arange(f, device=DEV), torch.arange(f, device=DEV) + f], dim=1).reshape(-1)
+    inter = llama._Linear(2 * f, d, DEV, g, 64, "normal",
+                          pack=(gate_up.w.view(torch.int32)[idx].view(torch.uint32), gate_up.s[idx], gate_up.b[idx]))
+
+    def call(linear, xin, y, ex=None, wait=(-1, 0), push=(-1, 0), swiglu_out=None, swiglu=False):
+        fz = _lib.DecodeFusion()
+        fz.wait_slot, fz.wait_site = wait
+        fz.push_slot, fz.push_site = push
+        fz.epilogue = 1 if swiglu else 0
+        fz.epilogue_out = None if swiglu_out is None else swiglu_out.data_ptr()
+        p = linear.problem(xin, y)
+        _lib.check(lib.qmm_decode_linear(ctypes.byref(p), ctypes.byref(fz), None if ex is None else ctypes.byref(ex), stream))
+
+    act, y_all = torch.zeros_like(act_ref), torch.empty_like(gu)
+    call(inter, x, y_all, swiglu=True, swiglu_out=act)
+    assert torch.equal(y_all.reshape(f, 2).t().reshape(1, 2 * f), gu)          # the plain outputs, de-interleaved
+    assert torch.equal(act, act_ref)
+    # pushed through a world of one and consumed by the down projection
+    slot_bytes = 2 * f * 4
+    area = torch.zeros((2 * slot_bytes,), device=DEV, dtype=torch.uint8)
+    state = torch.zeros((8,), device=DEV, dtype=torch.int32)
+    ex = _lib.Exchange()
+    bufs = (ctypes.c_void_p * 1)(area.data_ptr())
+    ex.peer_bufs = ctypes.cast(bufs, ctypes.POINTER(ctypes.c_void_p))
+    ex.epoch, ex.slot_bytes, ex.rank, ex.world = state.data_ptr(), slot_bytes, 0, 1
+    for step in range(2):
+        _lib.check(lib.qmm_decode_step_begin(ctypes.byref(ex), stream))
+        dn = torch.zeros_like(dn_ref)
+        call(inter, x, None, ex=ex, push=(0, 0), swiglu=True)
+        call(down, None, dn, ex=ex, wait=(0, 0))
+        assert torch.equal(dn, dn_ref)
+    assert _lib.poll_status() == 0
+    with pytest.raises(_lib.QmmError):
+        call(inter, x, y_all, swiglu=True)                                      # nowhere to put the values
