@@ -37,6 +37,16 @@ class _CudaOps:
         from . import moe
         return moe.ragged_dot(*a, **k)
 
+    @staticmethod
+    def silu_mul(gate, up):
+        from . import moe
+        return moe.silu_mul(gate, up)
+
+    @staticmethod
+    def routed_sum(rows, order, weights, tokens, k):
+        from . import moe
+        return moe.routed_sum(rows, order, weights, tokens, k)
+
 
 def shard_rows(n: int, world: int, rank: int, multiple: int = 16):
     """Rows `[lo, hi)` of an N-row weight owned by `rank`: contiguous, sized in multiples of
@@ -152,7 +162,9 @@ class ExpertParallelMoE:
             rows, group_sizes, perm = xs, counts.to(torch.int32), None
         gate = self.ops.ragged_dot(rows, *self.w1, group_sizes, **self.kw)
         up = self.ops.ragged_dot(rows, *self.w3, group_sizes, **self.kw)
-        act = torch.nn.functional.silu(gate) * up
+        silu_mul = getattr(self.ops, "silu_mul", None)
+        act = silu_mul(gate, up) if silu_mul is not None else torch.nn.functional.silu(gate) * up
+        del gate, up
         down = self.ops.ragged_dot(act, *self.w2, group_sizes, **self.kw)
         if self.world > 1:
             back = torch.empty_like(down)
@@ -161,6 +173,10 @@ class ExpertParallelMoE:
             dist.all_to_all_single(ret, back.contiguous(), send_rows, recv_rows, group=self.group)
         else:
             ret = down
+        routed_sum = getattr(self.ops, "routed_sum", None)
+        if routed_sum is not None and sum_dtype == torch.float32 and ret.dtype in (torch.bfloat16, torch.float16) \
+                and ret.shape[1] % 8 == 0:
+            return routed_sum(ret, order, weights, t, k).to(x.dtype)
         wsorted = weights.reshape(-1).index_select(0, order).to(sum_dtype)
         out = torch.zeros((t, ret.shape[1]), dtype=sum_dtype, device=x.device)
         out.index_add_(0, tok, ret.to(sum_dtype) * wsorted[:, None])
