@@ -611,3 +611,20 @@ def test_gather_mm_float_experts_in_router_order():
         moe.gather_mm(x[0], w, lhs, rhs)                             # a 2-D operand has no batch to gather from
     with pytest.raises(_lib.QmmError):
         moe.ragged_mm(x.reshape(-1, k)[:, :60].contiguous(), w[:, :, :60].contiguous(), torch.tensor([18, 0, 0, 0], device=DEV, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("m,k,n,gs,xdt,tdt,ydt", [
+    (64, 4096, 1024, 64, "bf16", "bf16", None),          # few tiles: every tile's K blocks split over CTAs
+    (17, 512, 1000, 32, "bf16", "bf16", None),           # a feature tile that ends inside 32 columns
+    (33, 4096, 6144, 64, "bf16", "bf16", "f32"),
+    (64, 14336, 512, 128, "f16", "f16", None),           # long K
+    (48, 2048, 40000, 64, "bf16", "f32", None),          # more tiles than SMs (persistent walk), wide tables
+    (20, 64, 256, 64, "bf16", "bf16", None),             # a single K block
+])
+def test_few_dozen_rows_take_the_tensor_core_kernel(m, k, n, gs, xdt, tdt, ydt):
+    """17..64 rows (the decode step at a batch of a few dozen): the tensor-core kernel with narrow
+    token tiles and the twelve-slot ring, the usual gate against the oracle."""
+    rng = np.random.default_rng(m * 7 + n)
+    assert qmm.route(m, k, n, gs, 4, "affine", TDT[xdt]) == "gemm_tc"
+    _run_affine(rng, m, k, n, gs, 4, xdt=xdt, tdt=tdt, ydt=ydt, route="gemm_tc")
+    assert _lib.poll_status() == 0
