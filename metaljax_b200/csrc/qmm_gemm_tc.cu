@@ -914,11 +914,13 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
   int64_t items = max_tiles * splits;
   int grid = sm_count();
   if (items < grid) grid = static_cast<int>(items < 1 ? 1 : items);
-  // Several waves of tiles whose last wave fills under half of the SMs: the full waves run
-  // unsplit, and the leftover tiles' K blocks are divided among the SMs (compact float32 partial
-  // tiles, a small reduce) instead of a few CTAs walking all of K while the rest idle.
+  // More tiles than SMs and a last wave that does not fill them: the full waves run unsplit, and
+  // the leftover tiles' K blocks are divided among the SMs (compact float32 partial tiles, a small
+  // reduce) instead of some CTAs walking all of K while the rest idle.
   if (splits == 1 && !ragged && p.batch == 1 && max_tiles > grid && tail_split_enabled()) {
     const int64_t rem = max_tiles % grid;
+    // (only a last wave that fills under half of the SMs: dividing a fuller one was measured and
+    // lost more to the short K shares' pipeline fill than the idle SMs cost)
     int64_t s = rem ? grid / rem : 0;
     if (s > num_kb / 8) s = num_kb / 8;
     if (s > 8) s = 8;
@@ -949,7 +951,8 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
         tail.tail_tiles = rem;
         tail.item0 = (max_tiles - rem) * s;
         tail.item_end = max_tiles * s;
-        qmm_gemm_tc_kernel<QK, XT, BT, true><<<static_cast<unsigned>(rem * s), kThreads, P::kSmem, stream>>>(xm, wm, tail);
+        const int64_t tail_grid = rem * s < grid ? rem * s : grid;
+        qmm_gemm_tc_kernel<QK, XT, BT, true><<<static_cast<unsigned>(tail_grid), kThreads, P::kSmem, stream>>>(xm, wm, tail);
         const int64_t total = rem * BT * kBF;
         int64_t blocks = (total + 255) / 256;
         if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
