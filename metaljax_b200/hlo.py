@@ -218,17 +218,8 @@ def _dense(text, type_):
     return t.to(type_.dtype).expand(type_.shape).contiguous() if t.dim() == 0 else t.to(type_.dtype).reshape(type_.shape)
 
 
-def parse(text: str) -> Func:
-    """The first `func.func ... @main` (or the first function) of a module."""
-    lines = text.splitlines()
-    start = next((i for i, ln in enumerate(lines) if "func.func" in ln and "@main" in ln), None)
-    if start is None:
-        start = next((i for i, ln in enumerate(lines) if "func.func" in ln), None)
-    if start is None:
-        raise ValueError("no func.func in the module")
-    head = lines[start]
-    fn = Func(re.search(r"@([\w.$-]+)", head).group(1))
-    env = {}
+def _signature(head):
+    """`(name, type, attribute text)` of every argument in a `func.func` header line."""
     sig = head[head.index("(") + 1:]
     depth, end = 1, 0
     for end, c in enumerate(sig):
@@ -236,20 +227,65 @@ def parse(text: str) -> Func:
         depth -= c == ")"
         if depth == 0:
             break
-    for i, piece in enumerate(p for p in _top_level_split(sig[:end], ",") if p.strip()):
+    out = []
+    for piece in (p for p in _top_level_split(sig[:end], ",") if p.strip()):
         m = re.match(r"\s*%([\w.$-]+)\s*:\s*(tensor<[^>]*>)(.*)", piece, re.S)
         if not m:
             raise ValueError(f"cannot parse argument {piece!r}")
-        v = Value(m.group(1), parse_type(m.group(2)), None, i)
-        if "tf.aliasing_output" in m.group(3) or "jax.buffer_donor" in m.group(3):
+        out.append((m.group(1), parse_type(m.group(2)), m.group(3)))
+    return out
+
+
+def parse(text: str) -> Func:
+    """The first `func.func ... @main` (or the first function) of a module. Calls of the module's
+    other functions (`func.call @callee(...)`: jax outlines helpers such as `take` and
+    `dynamic_index_in_dim` as private functions) are inlined where they stand, so the recognizer
+    sees one flat graph, as the reference does by following callees (src/metaljax/qmm.py:743-777)."""
+    lines = text.splitlines()
+    heads = [i for i, ln in enumerate(lines) if re.search(r"\bfunc\.func\b", ln)]
+    start = next((i for i in heads if "@main" in lines[i]), None)
+    if start is None:
+        start = heads[0] if heads else None
+    if start is None:
+        raise ValueError("no func.func in the module")
+    funcs = {}
+    for i in heads:
+        if i != start:
+            m = re.search(r"@([\w.$-]+)", lines[i])
+            if m:
+                funcs[m.group(1)] = i
+    head = lines[start]
+    fn = Func(re.search(r"@([\w.$-]+)", head).group(1))
+    env = {}
+    for i, (name, type_, attrs) in enumerate(_signature(head)):
+        v = Value(name, type_, None, i)
+        if "tf.aliasing_output" in attrs or "jax.buffer_donor" in attrs:
             fn.donated.add(i)
         fn.args.append(v)
         env[v.name] = v
-
         v.block = fn
-    counter = [0]
+    counter = [0, funcs, 0]          # next op position, the module's other functions, inlining depth
     _parse_block(lines, start + 1, env, fn, counter)
     return fn
+
+
+def _inline_call(lines, callee_line, operands, block, counter):
+    """The body of the function whose header is `lines[callee_line]`, parsed into `block` with its
+    arguments bound to `operands`; returns the Values it returns."""
+    if counter[2] >= 32:
+        raise ValueError("function calls nest too deeply (recursion?)")
+    sig = _signature(lines[callee_line])
+    if len(sig) != len(operands):
+        raise ValueError(f"call with {len(operands)} operands of a function of {len(sig)}")
+    cenv = {name: v for (name, _, _), v in zip(sig, operands)}
+    tmp = Block(block.owner)
+    counter[2] += 1
+    _parse_block(lines, callee_line + 1, cenv, tmp, counter)
+    counter[2] -= 1
+    block.ops.extend(tmp.ops)
+    for k, v in enumerate(tmp.returns):                            # the callee's return is no use of its own
+        v.uses[:] = [u for u in v.uses if u[0] is not tmp.return_op]
+    return tmp.returns
 
 
 def _parse_block(lines, i, env, block, counter):
@@ -279,6 +315,25 @@ def _parse_block(lines, i, env, block, counter):
         if name == "stablehlo.while":
             i = _parse_while(lines, i, ln, res_name, res_count, rest, env, block, counter, lookup)
             continue
+        if name == "reducer" and not res_name:
+            # the region of the reduce printed on the line before (its multi-result form):
+            # swallowed, and that op stays opaque
+            depth = ln.count("{") - ln.count("}")
+            while depth > 0 and i < len(lines):
+                depth += lines[i].count("{") - lines[i].count("}")
+                i += 1
+            if block.ops:
+                block.ops[-1].opaque = True
+            continue
+        if name in ("func.call", "call") and len(counter) > 1:
+            callee = re.search(r"@([\w.$-]+)", rest)
+            target = counter[1].get(callee.group(1)) if callee else None
+            if target is not None:
+                inside = rest[rest.index("(") + 1: rest.index(")")]
+                outs = _inline_call(lines, target, [lookup(t[1:]) for t in re.findall(r"%[\w.$#-]+", inside)], block, counter)
+                if res_name:
+                    env[res_name[1:]] = list(outs) if res_count else outs[0]
+                continue
         # any other op with regions: swallow lines until its braces balance, keep it opaque
         body = ln
         if ln.endswith("{") or ln.endswith("({"):

@@ -29,6 +29,33 @@ DONATED = _SUB.format(donor=" {jax.buffer_donor = true}", dot=_DOT_RHS, ret="%7"
 LHS_QUANT = _SUB.format(donor="", dot=_DOT_LHS, ret="%7", results="tensor<16x5xbf16>")
 SHARED_WEIGHT = _SUB.format(donor="", dot=_DOT_RHS, ret="%7, %6", results="tensor<5x16xbf16>, tensor<16x256xbf16>")
 
+# The same layer as jax prints it when the dequantization sits in a helper: private functions
+# called from @main (`call` and `func.call` both occur in jax's output).
+OUTLINED = """
+module @jit_dense_outlined {
+  func.func public @main(%arg0: tensor<5x256xbf16>, %arg1: tensor<16x256xi8>, %arg2: tensor<16x4xbf16>, %arg3: tensor<16x4xbf16>) -> (tensor<5x16xbf16>) {
+    %0 = call @dequantize(%arg1, %arg2, %arg3) : (tensor<16x256xi8>, tensor<16x4xbf16>, tensor<16x4xbf16>) -> tensor<16x256xbf16>
+    %1 = stablehlo.dot_general %arg0, %0, contracting_dims = [1] x [1] : (tensor<5x256xbf16>, tensor<16x256xbf16>) -> tensor<5x16xbf16>
+    %2 = func.call @twice(%1) : (tensor<5x16xbf16>) -> tensor<5x16xbf16>
+    return %2 : tensor<5x16xbf16>
+  }
+  func.func private @dequantize(%arg0: tensor<16x256xi8>, %arg1: tensor<16x4xbf16>, %arg2: tensor<16x4xbf16>) -> tensor<16x256xbf16> {
+    %0 = stablehlo.convert %arg0 : (tensor<16x256xi8>) -> tensor<16x256xbf16>
+    %1 = stablehlo.broadcast_in_dim %arg2, dims = [0, 1] : (tensor<16x4xbf16>) -> tensor<16x4x64xbf16>
+    %2 = stablehlo.reshape %1 : (tensor<16x4x64xbf16>) -> tensor<16x256xbf16>
+    %3 = stablehlo.subtract %0, %2 : tensor<16x256xbf16>
+    %4 = stablehlo.broadcast_in_dim %arg1, dims = [0, 1] : (tensor<16x4xbf16>) -> tensor<16x4x64xbf16>
+    %5 = stablehlo.reshape %4 : (tensor<16x4x64xbf16>) -> tensor<16x256xbf16>
+    %6 = stablehlo.multiply %3, %5 : tensor<16x256xbf16>
+    return %6 : tensor<16x256xbf16>
+  }
+  func.func private @twice(%arg0: tensor<5x16xbf16>) -> tensor<5x16xbf16> {
+    %0 = stablehlo.add %arg0, %arg0 : tensor<5x16xbf16>
+    return %0 : tensor<5x16xbf16>
+  }
+}
+"""
+
 PER_CHANNEL = """
 module @jit_dense_perchannel {
   func.func public @main(%arg0: tensor<5x128xbf16>, %arg1: tensor<128x16xi8>, %arg2: tensor<16xbf16>) -> (tensor<5x16xbf16>) {

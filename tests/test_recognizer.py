@@ -207,7 +207,8 @@ def test_real_jax_lowering_recognizes_nothing():
     fn = it.func
     names = [o.name for o in fn.walk()]
     assert fn.name == "main" and len(fn.args) > 8
-    assert names.count("stablehlo.while") == 1 and names.count("stablehlo.dot_general") >= 2 and "func.call" in names
+    # the private callees (dynamic_index_in_dim, the layer body, silu, argmax, ...) are inlined
+    assert names.count("stablehlo.while") == 1 and names.count("stablehlo.dot_general") == 15 and "func.call" not in names
     loop = next(o for o in fn.ops if o.name == "stablehlo.while")
     assert len(loop.regions) == 2 and recognizer.static_trip(loop) == 8          # one trip per layer
     st = recognizer.analyze(it)
@@ -298,3 +299,22 @@ def test_share_aliases_equal_packs(monkeypatch):
     recognizer.prologue(it3, other)
     p3 = recognizer.analyze(it3).matches[0].packs[0]
     assert p3.w is not p1.w and not torch.equal(p3.w, p1.w) and qmm.stats().get("shared") == 1
+
+
+def test_outlined_helpers_are_inlined():
+    """jax outlines helpers as private functions; the dequantization chain inside one is matched
+    through the call, and the packed weight is the one of the flat program."""
+    from programs import OUTLINED
+    it = recognizer.Interpreter(OUTLINED)
+    assert [o.name for o in it.func.ops].count("stablehlo.dot_general") == 1
+    assert not any(o.name in ("call", "func.call") for o in it.func.walk())
+    st = recognizer.analyze(it)
+    assert len(st.matches) == 1 and st.matches[0].arg_indices == (1, 2, 3) and st.matches[0].mode == "affine"
+    args = sub_channel_inputs(seed=3)
+    flat = recognizer.Interpreter(SUB_CHANNEL)
+    assert torch.equal(hlo.evaluate(it.func, args)[0], (hlo.evaluate(flat.func, args)[0].float() * 2).to(torch.bfloat16))
+    recognizer._BUILD_CACHE.clear()
+    recognizer.prologue(it, args)
+    recognizer.prologue(flat, args)
+    a, b = st.matches[0].packs[0], recognizer.analyze(flat).matches[0].packs[0]
+    assert all(torch.equal(x, y) for x, y in zip(a.arrays(), b.arrays()))
