@@ -238,8 +238,9 @@ def _signature(head):
 
 def parse(text: str) -> Func:
     """The first `func.func ... @main` (or the first function) of a module. Calls of the module's
-    other functions (`func.call @callee(...)`: jax outlines helpers such as `take` and
-    `dynamic_index_in_dim` as private functions) are inlined where they stand, so the recognizer
+    other functions (`func.call @callee(...)`, `stablehlo.composite ... {decomposition = @callee}`:
+    jax outlines helpers such as `take` and `dynamic_index_in_dim` as private functions) are
+    inlined where they stand, so the recognizer
     sees one flat graph, as the reference does by following callees (src/metaljax/qmm.py:743-777)."""
     lines = text.splitlines()
     heads = [i for i, ln in enumerate(lines) if re.search(r"\bfunc\.func\b", ln)]
@@ -325,11 +326,13 @@ def _parse_block(lines, i, env, block, counter):
             if block.ops:
                 block.ops[-1].opaque = True
             continue
-        if name in ("func.call", "call") and len(counter) > 1:
-            callee = re.search(r"@([\w.$-]+)", rest)
+        if name in ("func.call", "call", "stablehlo.composite") and len(counter) > 1:
+            # `call @f(%a, %b)`; `stablehlo.composite "name" %a, %b {..., decomposition = @f}`
+            composite = name == "stablehlo.composite"
+            callee = re.search(r"decomposition\s*=\s*@([\w.$-]+)" if composite else r"@([\w.$-]+)", rest)
             target = counter[1].get(callee.group(1)) if callee else None
             if target is not None:
-                inside = rest[rest.index("(") + 1: rest.index(")")]
+                inside = rest.split("{")[0] if composite else rest[rest.index("(") + 1: rest.index(")")]
                 outs = _inline_call(lines, target, [lookup(t[1:]) for t in re.findall(r"%[\w.$#-]+", inside)], block, counter)
                 if res_name:
                     env[res_name[1:]] = list(outs) if res_count else outs[0]

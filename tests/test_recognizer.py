@@ -318,3 +318,12 @@ def test_outlined_helpers_are_inlined():
     recognizer.prologue(flat, args)
     a, b = st.matches[0].packs[0], recognizer.analyze(flat).matches[0].packs[0]
     assert all(torch.equal(x, y) for x, y in zip(a.arrays(), b.arrays()))
+
+
+def test_composite_decomposition_is_inlined():
+    from programs import OUTLINED
+    text = OUTLINED.replace("%0 = call @dequantize(%arg1, %arg2, %arg3) :",
+                            '%0 = stablehlo.composite "my.dequantize" %arg1, %arg2, %arg3 {composite_attributes = {group = 64 : i64}, decomposition = @dequantize} :')
+    it = recognizer.Interpreter(text)
+    assert not any(o.name == "stablehlo.composite" for o in it.func.walk())
+    assert len(recognizer.analyze(it).matches) == 1
