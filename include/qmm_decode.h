@@ -37,6 +37,14 @@ int qmm_decode_rope_kv(const void* qkv, void* q_out, void* k_cache, void* v_cach
 /* gate_up: [rows, 2*ffn] = gate, then up.  out[r, i] = silu(gate[r, i]) * up[r, i]. */
 int qmm_decode_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t ffn, void* stream);
 
+/* Greedy sampling: out_val[r] (float32) = the largest of logits[r, 0..n) (bf16, rows row_stride
+ * elements apart) and out_idx[r] (int64) = its index + index_offset (ties: the smallest index).
+ * `scratch`: qmm_decode_argmax_scratch_bytes(rows) bytes of device memory, 16-byte aligned,
+ * zeroed once before the first call, not shared by calls that can overlap. */
+int64_t qmm_decode_argmax_scratch_bytes(int64_t rows);
+int qmm_decode_argmax(const void* logits, int64_t rows, int64_t n, int64_t row_stride, int64_t index_offset,
+                      void* out_val, void* out_idx, void* scratch, int64_t scratch_bytes, void* stream);
+
 /* One-shot all-gather over peer memory (one call per rank, each on its own GPU): this rank's
  * slice `local` [rows, slice_bytes] is stored into every rank's gather buffer
  * `peer_bufs[r] + slot*slot_bytes` at column offset rank*slice_bytes of rows world*slice_bytes

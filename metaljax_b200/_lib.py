@@ -108,6 +108,9 @@ _SIGNATURES = {
                                                                  ctypes.c_float, ctypes.c_void_p]),
     "qmm_decode_silu_mul": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                            ctypes.c_void_p]),
+    "qmm_decode_argmax_scratch_bytes": (ctypes.c_int64, [ctypes.c_int64]),
+    "qmm_decode_argmax": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]),
     "qmm_decode_allgather": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
                                             ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_int,
                                             ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64,

@@ -228,6 +228,82 @@ __global__ void step_begin_kernel(uint32_t* epoch) {
   if (threadIdx.x == 0) *epoch = *epoch + 1u;
 }
 
+// ---- greedy sampling: the largest logit of every row and its index ---------------------
+// grid (parts, rows): every CTA takes a slice of one row and leaves (value, index) in scratch;
+// the last CTA of a row to finish compares the slices and writes the row's result. Ties go to
+// the smallest index. NaNs never win (a row of NaNs gives index 0).
+constexpr int kArgmaxThreads = 256;
+
+__global__ void argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, int64_t n, int64_t row_stride,
+                                   int64_t index_offset, float* __restrict__ out_val, int64_t* __restrict__ out_idx,
+                                   float* part_val, int64_t* part_idx, uint32_t* counters) {
+  pdl_enter();
+  __shared__ float sval[kArgmaxThreads / 32];
+  __shared__ int64_t sidx[kArgmaxThreads / 32];
+  __shared__ int is_last;
+  const int parts = gridDim.x, part = blockIdx.x;
+  const int64_t row = blockIdx.y;
+  const __nv_bfloat16* x = logits + row * row_stride;
+  const int64_t per = ((n + parts - 1) / parts + 7) & ~int64_t(7);
+  const int64_t lo = part * per, hi = lo + per < n ? lo + per : n;
+  float best = -INFINITY;
+  int64_t where = lo < n ? lo : 0;
+  auto take = [&](float v, int64_t i) {
+    if (v > best || (v == best && i < where)) { best = v; where = i; }
+  };
+  const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  if (vec) {
+    for (int64_t i = lo + threadIdx.x * 8; i < hi; i += kArgmaxThreads * 8) {
+      if (i + 8 <= hi) {
+        float f[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(x + i)), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) take(f[e], i + e);
+      } else {
+        for (int64_t j = i; j < hi; ++j) take(__bfloat162float(x[j]), j);
+      }
+    }
+  } else {
+    for (int64_t i = lo + threadIdx.x; i < hi; i += kArgmaxThreads) take(__bfloat162float(x[i]), i);
+  }
+  auto merge = [&](float ov, int64_t oi) {
+    if (ov > best || (ov == best && oi < where)) { best = ov; where = oi; }
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int64_t oi = __shfl_xor_sync(0xffffffffu, where, o);
+    merge(ov, oi);
+  }
+  if ((threadIdx.x & 31) == 0) { sval[threadIdx.x >> 5] = best; sidx[threadIdx.x >> 5] = where; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kArgmaxThreads / 32; ++w) merge(sval[w], sidx[w]);
+    part_val[row * parts + part] = best;
+    part_idx[row * parts + part] = where;
+    __threadfence();
+    const bool last = atomicAdd(&counters[row], 1u) == static_cast<uint32_t>(parts - 1);
+    if (last) counters[row] = 0;
+    is_last = last;
+  }
+  __syncthreads();
+  if (!is_last || threadIdx.x >= 32) return;
+  __threadfence();
+  best = -INFINITY;
+  where = 0;
+  for (int q = threadIdx.x; q < parts; q += 32) merge(__ldcg(part_val + row * parts + q), __ldcg(part_idx + row * parts + q));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int64_t oi = __shfl_xor_sync(0xffffffffu, where, o);
+    merge(ov, oi);
+  }
+  if (threadIdx.x == 0) {
+    out_val[row] = best;
+    out_idx[row] = where + index_offset;
+  }
+}
+
 template <typename... Args>
 int launch_pdl(const char* what, void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                Args... args) {
@@ -302,6 +378,32 @@ extern "C" int qmm_decode_silu_mul(const void* gate_up, void* out, int64_t rows,
   return launch_pdl("silu_mul_kernel", silu_mul_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0,
                     static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(gate_up),
                     static_cast<__nv_bfloat16*>(out), rows, ffn);
+}
+
+extern "C" int64_t qmm_decode_argmax_scratch_bytes(int64_t rows) {
+  return rows < 0 ? 0 : rows * 64 * 12 + rows * 4 + 64;
+}
+
+extern "C" int qmm_decode_argmax(const void* logits, int64_t rows, int64_t n, int64_t row_stride, int64_t index_offset,
+                                 void* out_val, void* out_idx, void* scratch, int64_t scratch_bytes, void* stream) {
+  if (!logits || !out_val || !out_idx || !scratch) return fail(QMM_ERR_NULL, "argmax: null pointer");
+  if (rows < 0 || rows > 65535 || n < 1 || row_stride < n) return fail(QMM_ERR_SHAPE, "argmax: bad shape");
+  if (scratch_bytes < qmm_decode_argmax_scratch_bytes(rows)) return fail(QMM_ERR_TOO_LARGE, "argmax: scratch is too small");
+  if (reinterpret_cast<uintptr_t>(scratch) & 15)
+    return fail(QMM_ERR_LAYOUT, "argmax: scratch must be 16-byte aligned");
+  if (rows == 0) return QMM_OK;
+  int64_t parts = (n + 4095) / 4096;
+  if (parts > 64) parts = 64;
+  const int64_t fill = (2 * device_sm_count() + rows - 1) / rows;         // no more CTAs than two per SM in all
+  if (parts > fill) parts = fill < 1 ? 1 : fill;
+  uint8_t* sc = static_cast<uint8_t*>(scratch);
+  float* part_val = reinterpret_cast<float*>(sc);
+  int64_t* part_idx = reinterpret_cast<int64_t*>(sc + rows * 64 * 4);
+  uint32_t* counters = reinterpret_cast<uint32_t*>(sc + rows * 64 * 12);
+  return launch_pdl("argmax_rows_kernel", argmax_rows_kernel, dim3(static_cast<unsigned>(parts), static_cast<unsigned>(rows)),
+                    dim3(kArgmaxThreads), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(logits), n,
+                    row_stride, index_offset, static_cast<float*>(out_val), static_cast<int64_t*>(out_idx), part_val, part_idx,
+                    counters);
 }
 
 extern "C" int qmm_decode_allgather(const void* local, void* const* peer_bufs, void* const* peer_flags, void* state,

@@ -293,6 +293,9 @@ class DecodeStep:
                 lin = layer["gate_up"]
                 lin.w = lin.w.view(torch.int32).index_select(0, idx).contiguous().view(torch.uint32)
                 lin.s, lin.b = lin.s.index_select(0, idx).contiguous(), lin.b.index_select(0, idx).contiguous()
+        self._argmax_scratch = torch.zeros((_lib.lib().qmm_decode_argmax_scratch_bytes(b),), device=dev, dtype=torch.uint8)
+        self._argmax_val = torch.empty((b,), device=dev, dtype=torch.float32)
+        self._argmax_idx = torch.empty((b,), device=dev, dtype=torch.int64)
         self.graph = None
         self.tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
         self.next_tokens = torch.zeros((b,), device=dev, dtype=torch.int64)
@@ -433,8 +436,14 @@ class DecodeStep:
 
     def _finish_step(self):
         b = self.batch
-        val, idx = torch.max(self.logits_l.float(), dim=-1)
-        idx = idx + self.v_lo
+        val, idx = self._argmax_val, self._argmax_idx
+        if self.v_l > 0:
+            _lib.check(_lib.lib().qmm_decode_argmax(_ptr(self.logits_l), b, self.v_l, self.logits_l.shape[1], self.v_lo,
+                                                    _ptr(val), _ptr(idx), _ptr(self._argmax_scratch),
+                                                    self._argmax_scratch.numel(), _lib.stream_ptr(self.logits_l)))
+        else:                                                     # a rank without vocabulary rows never wins
+            val.fill_(float("-inf"))
+            idx.zero_()
         if self.world > 1:
             pair = torch.stack([val, idx.float()], dim=-1).contiguous()            # [b, 2]
             allp = torch.empty((self.world,) + tuple(pair.shape), device=self.device, dtype=pair.dtype)

@@ -267,3 +267,27 @@ def test_decode_linear_swiglu_epilogue():
     assert _lib.poll_status() == 0
     with pytest.raises(_lib.QmmError):
         call(inter, x, y_all, swiglu=True)                                      # nowhere to put the values
+
+
+@pytest.mark.parametrize("rows,n,stride", [(1, 128256, 128256), (64, 128256, 128256), (3, 1001, 1008), (2, 7, 16), (5, 16032, 16032)])
+def test_decode_argmax_kernel(rows, n, stride):
+    """The largest logit of every row and its index (ties: the smallest index), offset added."""
+    import ctypes
+    from metaljax_b200 import _lib
+    g = torch.Generator(device=DEV).manual_seed(rows + n)
+    logits = torch.randn((rows, stride), generator=g, device=DEV).to(torch.bfloat16)
+    logits[:, n:] = 100.0                                  # beyond n: must not be looked at
+    if n > 10:
+        logits[0, 5] = logits[0, n - 1] = 50.0             # a tie: the smaller index wins
+    lib = _lib.lib()
+    scratch = torch.zeros((lib.qmm_decode_argmax_scratch_bytes(rows),), device=DEV, dtype=torch.uint8)
+    val = torch.empty((rows,), device=DEV, dtype=torch.float32)
+    idx = torch.empty((rows,), device=DEV, dtype=torch.int64)
+    for _ in range(2):                                     # (the counters return to zero between calls)
+        _lib.check(lib.qmm_decode_argmax(logits.data_ptr(), rows, n, stride, 1000, val.data_ptr(), idx.data_ptr(),
+                                         scratch.data_ptr(), scratch.numel(), _lib.stream_ptr(logits)))
+        ref = logits[:, :n].float()
+        want_val = ref.max(dim=-1).values
+        assert torch.equal(val, want_val)
+        first = (ref == want_val[:, None]).float().argmax(dim=-1)
+        assert torch.equal(idx, first + 1000)
