@@ -881,6 +881,9 @@ int launch_qx(const CUtensorMap& wm, const ImmaParams& ip, const ImmaPlan& plan,
 // kernels for every linear of a step, so that consecutive launches find their code cached).
 template <int PRO>
 int launch_fused(const CUtensorMap& wm, const ImmaParams& ip, const ImmaPlan& plan, cudaStream_t stream) {
+  if (plan.nw == 8) {        // (only the tall form: a weight of many tiles per SM)
+    if (plan.r == 4) return launch_r<kAff4, __nv_bfloat16, 4, 8, true, PRO>(wm, ip, plan, stream);
+  }
   if (plan.r == 4) return launch_r<kAff4, __nv_bfloat16, 4, 16, true, PRO>(wm, ip, plan, stream);
   if (plan.r == 2) return launch_r<kAff4, __nv_bfloat16, 2, 16, true, PRO>(wm, ip, plan, stream);
   return launch_r<kAff4, __nv_bfloat16, 1, 16, true, PRO>(wm, ip, plan, stream);
@@ -899,9 +902,14 @@ ImmaPlan make_plan(const qmm_problem& p, int nchunks, int plane_bytes, int group
   const size_t kOnePerSm = 226 * 1024;
   const bool small = (p.N + 31) / 32 <= sms;
   for (int pass = 0; pass < 2; ++pass) {
-    const int nw = fused ? 16 : (force_nw ? force_nw : ((pass == 0) == small ? 16 : 8));
+    // the decode step's linears: sixteen warps, except a weight of at least `big` rows (many
+    // tiles per SM), which streams better from two eight-warp CTAs per SM
+    static const int big = env_int("QMM_IMMA_FUSED_BIG", 4096);
+    const int nw = fused ? ((p.N >= big && pass == 0) ? 8 : 16)
+                         : (force_nw ? force_nw : ((pass == 0) == small ? 16 : 8));
     for (int r = 4; r >= 1; r >>= 1) {
       if (force_r && r != force_r) continue;
+      if (fused && nw == 8 && r != 4) break;              // (the eight-warp fused form exists for tall tiles only)
       const int64_t tiles = (p.N + 8 * r - 1) / (8 * r);
       if (!force_r && r > 1 && tiles * 2 < sms) continue;
       const size_t budget = nw == 8 ? kTwoPerSm : kOnePerSm;
