@@ -13,7 +13,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libqmm.so")
+LIB_PATH = os.environ.get("QMM_LIBRARY") or os.path.join(_HERE, "libqmm.so")     # (a development build can be named)
 
 MODE = {"affine": 0, "mxfp4": 1}
 ROUTES = {0: "none", 1: "gemv", 2: "gemm_tc", 3: "simt", 4: "gemv_fmma"}

@@ -39,8 +39,18 @@ namespace {
 
 constexpr int kBF = 128;        // features per tile (MMA M, TMEM lanes)
 constexpr int kBK = 64;         // K elements per pipeline stage
-constexpr int kTeams = 4;        // dequant/epilogue teams of four warps (one per TMEM lane quarter)
-constexpr int kThreads = (2 + 4 * kTeams) * 32;
+// Dequant / epilogue teams of four warps (one per TMEM lane quarter): five for wide token tiles,
+// where the dequantization is what the issuer waits for (C2a 965 -> 1009 TFLOP/s, C2b 1106 -> 1199,
+// int8 891 -> 991 against four); four for narrow tiles (five lose there: fewer ring slots fit)
+// and for float weights (whose 16 KB slots leave room for four).
+template <int QK, int BT>
+struct Teams {
+#ifndef QMM_TC_WIDE_TEAMS
+#define QMM_TC_WIDE_TEAMS 5
+#endif
+  static constexpr int kTeams = (BT <= 64 || QK == 3 /* kFloat */) ? 4 : QMM_TC_WIDE_TEAMS;
+  static constexpr int kThreads = (2 + 4 * kTeams) * 32;
+};
 constexpr int kMaxSegments = 256;
 constexpr long long kSpinLimit = 4000000000LL;  // SM clocks (~2 s)
 #ifndef QMM_TC_TRACING
@@ -347,6 +357,8 @@ __host__ __device__ constexpr uint32_t instr_desc(int fmt /*0 f16, 1 bf16*/, int
 
 template <int QK, int BT>
 struct Plan {
+  static constexpr int kTeams = Teams<QK, BT>::kTeams;
+  static constexpr int kThreads = Teams<QK, BT>::kThreads;
   static constexpr int kBits = (QK == kFloat) ? 16 : ((QK == kAff8) ? 8 : 4);
   static constexpr int kWRowBytes = kBK * kBits / 8;          // 32, 64 or (float weights) 128
   static constexpr int kXBytes = BT * kBK * 2;                // one activation stage
@@ -361,10 +373,12 @@ struct Plan {
   // Narrow token tiles leave most of tensor memory to the A ring and stage little: twelve
   // slots instead of eight cover the per-slot latency chain (TMA, one team's dequantization,
   // MMA, commit) that bounds a CTA's rate at a few dozen rows.
-  static constexpr int kACol0 = (BT <= 64) ? 64 : 256;        // A ring starts here (D is columns [0, BT))
+  static constexpr int kACol0 = (BT <= 64) ? 64 : (BT <= 128 ? 128 : 256);   // A ring starts here (D is columns [0, BT))
   static constexpr int kTmemFit = (512 - kACol0) / 32;
-  static constexpr int kStages = (kFit >= 12 && kTmemFit >= 12) ? 12 : (kFit >= 8 ? 8 : 4);
-  static_assert(kFit >= 4, "a ring of four stages must fit");
+  static constexpr int kMost = kFit < kTmemFit ? kFit : kTmemFit;
+  // (at most three rounds of the teams: twelve slots for four teams, five for five at 256 tokens)
+  static constexpr int kStages = (kMost / kTeams >= 3 ? 3 : (kMost / kTeams >= 2 ? 2 : 1)) * kTeams;
+  static_assert(kMost >= kTeams, "one slot per team must fit");
   static constexpr int kBarBytes = 1024;
   static constexpr int kSmem = kStages * kStageBytes + kBarBytes + 1024 /* alignment slack */;
   static constexpr int kDCols = BT;                           // accumulator columns
@@ -415,10 +429,11 @@ __device__ __forceinline__ bool tile_at(int64_t item, const int64_t* seg_tile0, 
 // SPLIT: the K blocks of a tile are shared among p.splits CTAs (float32 partial tiles). A
 // separate instantiation, so that the unsplit kernel keeps compile-time K bounds.
 template <int QK, typename XT, int BT, bool SPLIT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((Teams<QK, BT>::kThreads), 1)
 qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map,
                    const TcParams p) {
   using P = Plan<QK, BT>;
+  constexpr int kTeams = P::kTeams;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* bar_base = smem + P::kStages * P::kStageBytes;
@@ -944,7 +959,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
       if (part) {
         TcParams head = tp, tail = tp;
         head.item_end = max_tiles - rem;
-        qmm_gemm_tc_kernel<QK, XT, BT, false><<<grid, kThreads, P::kSmem, stream>>>(xm, wm, head);
+        qmm_gemm_tc_kernel<QK, XT, BT, false><<<grid, P::kThreads, P::kSmem, stream>>>(xm, wm, head);
         tail.splits = static_cast<int>(s);
         tail.partial = part;
         tail.tail_tile0 = max_tiles - rem;
@@ -952,7 +967,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
         tail.item0 = (max_tiles - rem) * s;
         tail.item_end = max_tiles * s;
         const int64_t tail_grid = rem * s < grid ? rem * s : grid;
-        qmm_gemm_tc_kernel<QK, XT, BT, true><<<static_cast<unsigned>(tail_grid), kThreads, P::kSmem, stream>>>(xm, wm, tail);
+        qmm_gemm_tc_kernel<QK, XT, BT, true><<<static_cast<unsigned>(tail_grid), P::kThreads, P::kSmem, stream>>>(xm, wm, tail);
         const int64_t total = rem * BT * kBF;
         int64_t blocks = (total + 255) / 256;
         if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
@@ -964,8 +979,8 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
       }
     }
   }
-  if (splits > 1) qmm_gemm_tc_kernel<QK, XT, BT, true><<<grid, kThreads, P::kSmem, stream>>>(xm, wm, tp);
-  else qmm_gemm_tc_kernel<QK, XT, BT, false><<<grid, kThreads, P::kSmem, stream>>>(xm, wm, tp);
+  if (splits > 1) qmm_gemm_tc_kernel<QK, XT, BT, true><<<grid, P::kThreads, P::kSmem, stream>>>(xm, wm, tp);
+  else qmm_gemm_tc_kernel<QK, XT, BT, false><<<grid, P::kThreads, P::kSmem, stream>>>(xm, wm, tp);
   count_launch();
   if (splits > 1) {
     const int64_t total = p.M * p.N;
