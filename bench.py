@@ -17,7 +17,7 @@ reference's fused dequantize-and-dot loop timed on the host cores on a bounded s
 at M = 1 (GB/s of weight bytes) and M = 2048 (TFLOP/s) in int4 / int8 at both Llama MLP shapes,
 MXFP4 at M = 1 / 512 / 4096, the Mixtral-shaped expert block, the decode step at batch 1 and 16
 -- each with its own roofline; at N > 1 the decode step at the other batches, the
-expert-parallel expert block (token all-to-all), and `parity`: the sharded decode step and the
+expert-parallel expert block (rows exchanged through peer memory), and `parity`: the sharded decode step and the
 expert-parallel block checked at small shapes against their references before anything is timed.
 """
 
@@ -58,7 +58,7 @@ DEFAULT = "decode_llama3_8b_b64"
 # The expert block of a Mixtral-8x7B-shaped mixture-of-experts layer: 4096 tokens, top-2 of 8
 # experts, d 4096, ffn 14336, int4 group-64 expert weights; three grouped ragged products over
 # 8192 (token, expert) pairs plus the routed weighted sum. Over N ranks: experts split, tokens
-# split, pairs exchanged by all-to-all.
+# split, pairs exchanged through peer memory (QMM_EP_EXCHANGE=nccl: by all-to-all collectives).
 MOE_BLOCKS = {"moe_mixtral_t4096": (4096, 2, 8, 4096, 14336)}
 ALSO_AT_ONE = ["decode_int4_g64_m1_4096x4096", "decode_int4_g64_m1_65536x4096", "prefill_int4_g64_m2048_14336x4096", "prefill_int4_g64_m2048_4096x14336",
                "prefill_int8_g128_m2048_14336x4096", "prefill_int8_g128_m2048_4096x14336", "decode_mxfp4_m1_5760x2880",
@@ -108,7 +108,7 @@ def config_of(name, world):
     if name in MOE_BLOCKS:
         t, k, e, d, f = MOE_BLOCKS[name]
         return {"workload": name, "tokens": t, "top_k": k, "experts": e, "d_model": d, "ffn": f, "group_size": 64, "bits": 4,
-                "parallelism": f"ep{world}: experts and tokens split over the ranks, pairs exchanged by all-to-all"
+                "parallelism": f"ep{world}: experts and tokens split over the ranks, pairs exchanged between them"
                 if world > 1 else "ep1",
                 "l2": f"{3 * e * d * f // 2 >> 20} MiB of expert weights per step (> L2)"}
     m, k, n, gs, bits, mode = WORKLOADS[name]
@@ -569,7 +569,9 @@ def moe_line(name, args, torch, dist, device, world, pk):
     wts, idx = torch.topk(torch.softmax(logits, -1), k, dim=-1)
     wts = (wts / wts.sum(-1, keepdim=True)).float()
     if world > 1:
-        block = parallel.ExpertParallelMoE(w1, w3, w2, group=None, local_experts=True)
+        exchange = os.environ.get("QMM_EP_EXCHANGE", "peer")               # "nccl": all-to-all collectives
+        block = parallel.ExpertParallelMoE(w1, w3, w2, group=None, local_experts=True,
+                                           capacity_pairs=tl * k if exchange == "peer" else None)
         run = lambda x: block(x, idx, wts)                                  # noqa: E731
     else:
         run = lambda x: moe.moe_experts(x, idx, wts, w1, w3, w2)            # noqa: E731
@@ -598,7 +600,8 @@ def moe_line(name, args, torch, dist, device, world, pk):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": config_of(name, world),
         "how": {"includes": "pair sort, token exchange, 3 grouped ragged products, SwiGLU, routed weighted sum",
-                "timed": "stream launches"},
+                "timed": "stream launches",
+                "exchange": None if world == 1 else ("peer memory" if getattr(block, "_peer", None) else "nccl all-to-all")},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": achieved / pk["bf16_tflops"], "traffic": None, "peak_source": pk["source"]},
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -636,7 +639,8 @@ def parity_check(torch, dist, device, world, rank):
     e, kk, d, f, t = 8, 2, 256, 512, 64 + 8 * rank
     packs = [affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:], affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:],
              affine_case(rng, d, f, 64, 4, "bf16", lead=(e,))[1:]]
-    block = parallel.ExpertParallelMoE(*[tuple(to_torch(a, device) for a in p) for p in packs])
+    block = parallel.ExpertParallelMoE(*[tuple(to_torch(a, device) for a in p) for p in packs],
+                                       capacity_pairs=256 if os.environ.get("QMM_EP_EXCHANGE", "peer") == "peer" else None)
     rr = np.random.default_rng(100 + rank)
     x = activations(rr, (t, d), "bf16", 0.5)
     idx, wts = O.topk_router(rr.standard_normal((t, e)).astype(np.float32), kk)

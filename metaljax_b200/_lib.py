@@ -56,6 +56,16 @@ class Exchange(ctypes.Structure):
                 ("slot_bytes", ctypes.c_int64), ("rank", ctypes.c_int32), ("world", ctypes.c_int32)]
 
 
+class EpExchange(ctypes.Structure):
+    """`qmm_ep_exchange` of include/qmm_ep.h."""
+
+    _fields_ = [("peer_counts", ctypes.POINTER(ctypes.c_void_p)), ("peer_flags", ctypes.POINTER(ctypes.c_void_p)),
+                ("peer_recv", ctypes.POINTER(ctypes.c_void_p)), ("peer_ret", ctypes.POINTER(ctypes.c_void_p)),
+                ("epoch", ctypes.c_void_p), ("scratch", ctypes.c_void_p),
+                ("capacity_rows", ctypes.c_int64), ("max_pairs", ctypes.c_int64),
+                ("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("experts", ctypes.c_int32)]
+
+
 class DecodeFusion(ctypes.Structure):
     """`qmm_decode_fusion` of include/qmm_decode.h."""
 
@@ -125,6 +135,10 @@ _SIGNATURES = {
                                                                    ctypes.c_int, ctypes.c_int, ctypes.POINTER(Exchange),
                                                                    ctypes.c_void_p]),
     "qmm_route": (ctypes.c_int, [ctypes.POINTER(Problem)]),
+    # include/qmm_ep.h
+    "qmm_ep_dispatch": (ctypes.c_int, [ctypes.POINTER(EpExchange), ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                       ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),
+    "qmm_ep_combine": (ctypes.c_int, [ctypes.POINTER(EpExchange), ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]),
 }
 
 

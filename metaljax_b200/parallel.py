@@ -114,9 +114,16 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, w1, w3, w2, group_size=64, bits=4, mode="affine", group=None, ops=None,
-                 local_experts=False):
-        """With `local_experts` the packs already hold only this rank's E/g experts."""
+                 local_experts=False, capacity_pairs=None):
+        """With `local_experts` the packs already hold only this rank's E/g experts. With
+        `capacity_pairs` (the most (token, expert) pairs any rank brings to a call; the same number
+        on every rank) rows travel through peer memory (`qmm_ep_dispatch` / `qmm_ep_combine`:
+        stores over NVLink into symmetric buffers, sizes kept on the devices, nothing read back by
+        the host) instead of through all-to-all collectives."""
         self.group = group
+        self.capacity_pairs = capacity_pairs
+        self._peer = None                     # the peer-memory exchange, set up at the first call
+        self._peer_error = None
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.ops = ops or _CudaOps
@@ -134,9 +141,79 @@ class ExpertParallelMoE:
 
         self.w1, self.w3, self.w2 = take(w1), take(w3), take(w2)
 
+    def _peer_setup(self, x):
+        """Symmetric buffers of the peer-memory exchange for rows like x's; on any failure every
+        rank falls back to the collectives together."""
+        import ctypes
+        from . import _lib
+        d, dev = x.shape[1], x.device
+        row_bytes = d * x.element_size()
+        ok = torch.ones((), device=dev, dtype=torch.int32)
+        state = None
+        try:
+            if row_bytes % 16 or x.dtype not in (torch.bfloat16, torch.float16):
+                raise ValueError("rows must be 16-bit and a multiple of 16 bytes")
+            import torch.distributed._symmetric_memory as symm_mem
+            cap_rows = self.world * self.capacity_pairs
+            sizes = [self.world * self.e * 8, 2 * self.world * 4, cap_rows * row_bytes, self.capacity_pairs * row_bytes]
+            offs, total = [], 0
+            for sz in sizes:
+                offs.append(total)
+                total += -(-sz // 256) * 256
+            buf = symm_mem.empty((total,), dtype=torch.uint8, device=dev)
+            buf[: offs[2]].zero_()
+            hdl = symm_mem.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+            bases = [int(p) for p in hdl.buffer_ptrs]
+            arrays = [(ctypes.c_void_p * self.world)(*[b + o for b in bases]) for o in offs]
+            local = torch.zeros((64,), device=dev, dtype=torch.int32)            # [0] the call counter, [4..] CTA counters
+            ex = _lib.EpExchange()
+            ex.peer_counts, ex.peer_flags, ex.peer_recv, ex.peer_ret = (
+                ctypes.cast(a, ctypes.POINTER(ctypes.c_void_p)) for a in arrays)
+            ex.epoch, ex.scratch = local.data_ptr(), local.data_ptr() + 16
+            ex.capacity_rows, ex.max_pairs = cap_rows, self.capacity_pairs
+            ex.rank, ex.world, ex.experts = self.rank, self.world, self.e
+            state = dict(ex=ex, buf=buf, hdl=hdl, arrays=arrays, local=local, row_bytes=row_bytes, d=d, dtype=x.dtype,
+                         recv=buf[offs[2]: offs[2] + cap_rows * row_bytes].view(x.dtype).view(cap_rows, d),
+                         ret=buf[offs[3]: offs[3] + self.capacity_pairs * row_bytes].view(x.dtype).view(self.capacity_pairs, d),
+                         sizes=torch.zeros((self.el,), device=dev, dtype=torch.int32))
+        except Exception as exc:                                  # noqa: BLE001 -- any setup failure
+            self._peer_error = repr(exc)
+            ok.zero_()
+        torch.cuda.synchronize(dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        self._peer = state if int(ok.item()) == 1 else False
+
+    def _call_peer(self, x, indices, weights):
+        import ctypes
+        from . import _lib, moe
+        st = self._peer
+        t, k = indices.shape
+        pairs = t * k
+        if pairs > self.capacity_pairs:
+            raise ValueError(f"{pairs} pairs on this rank, the exchange was sized for {self.capacity_pairs}")
+        eidx = indices.reshape(-1).to(torch.int64)
+        order = torch.sort(eidx, stable=True).indices
+        tok = (order // k).contiguous()
+        counts = torch.bincount(eidx, minlength=self.e).to(torch.int32)
+        x = x.contiguous()
+        stream = _lib.stream_ptr(x)
+        lib = _lib.lib()
+        _lib.check(lib.qmm_ep_dispatch(ctypes.byref(st["ex"]), x.data_ptr(), t, st["row_bytes"], tok.data_ptr(),
+                                       counts.data_ptr(), pairs, st["sizes"].data_ptr(), stream))
+        rows, sizes = st["recv"], st["sizes"]
+        act = moe.silu_mul(moe.ragged_dot(rows, *self.w1, sizes, **self.kw), moe.ragged_dot(rows, *self.w3, sizes, **self.kw))
+        down = moe.ragged_dot(act, *self.w2, sizes, **self.kw)
+        _lib.check(lib.qmm_ep_combine(ctypes.byref(st["ex"]), down.data_ptr(), st["row_bytes"], stream))
+        return moe.routed_sum(st["ret"][:pairs], order, weights, t, k).to(x.dtype)
+
     def __call__(self, x, indices, weights, sum_dtype=torch.float32):
         """x `[T, d]` (this rank's tokens), router `indices[T, K]` (global expert ids) and
         `weights[T, K]` -> `[T, d]`."""
+        if self.capacity_pairs and self.world > 1 and x.is_cuda and self.ops is _CudaOps and sum_dtype == torch.float32:
+            if self._peer is None:
+                self._peer_setup(x)
+            if self._peer and x.shape[1] == self._peer["d"] and x.dtype == self._peer["dtype"] and x.shape[1] % 8 == 0:
+                return self._call_peer(x, indices, weights)
         t, k = indices.shape
         eidx = indices.reshape(-1).to(torch.int64)
         order = torch.sort(eidx, stable=True).indices          # pairs sorted by global expert

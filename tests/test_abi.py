@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _declared():
     names = set()
-    for header in ("qmm.h", "qmm_decode.h"):
+    for header in ("qmm.h", "qmm_decode.h", "qmm_ep.h"):
         text = open(os.path.join(ROOT, "include", header)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         names |= set(re.findall(r"\b(qmm_[a-z_0-9]+)\s*\(", text))

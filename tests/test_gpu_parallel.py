@@ -65,6 +65,15 @@ def _worker(rank, world, port, ret):
         err = O.rel_err(to_numpy(y).astype(np.float32), want)
         assert err <= 2e-2, err                           # two bf16 hand-offs inside the block
         stage = "expert-parallel done"
+        # the same block with the rows exchanged through peer memory: the same bits, call after call
+        peer = parallel.ExpertParallelMoE(*[tuple(to_torch(a, dev) for a in p) for p in packs], capacity_pairs=128)
+        for call in range(3):
+            y2 = peer(to_torch(x, dev), torch.from_numpy(idx).to(dev), torch.from_numpy(wts).to(dev))
+            assert peer._peer, peer._peer_error
+            assert torch.equal(y2, y), (call, (y2.float() - y.float()).abs().max().item())
+        torch.cuda.synchronize(dev)
+        assert _lib.poll_status() == 0
+        stage = "expert-parallel over peer memory done"
         # the Llama-shaped decode step sharded over the ranks: same logits as the float reference
         from metaljax_b200 import llama
         shape = llama.Shape(layers=2, d_model=256, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1000, ctx=48)
