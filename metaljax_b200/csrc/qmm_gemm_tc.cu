@@ -453,7 +453,15 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
   const int64_t ftiles = (p.N + kBF - 1) / kBF;
   const int num_kb = static_cast<int>((p.K + kBK - 1) / kBK);
 
+  // Programmatic dependent launch: the grid that follows may be scheduled as soon as every CTA
+  // of this one has got here (it touches memory only after its own griddepcontrol.wait). This
+  // grid sets itself up, and requests its first weight boxes, while the grid it depends on is
+  // still running; what that grid produces -- the activations, the group sizes of a ragged
+  // product -- is read only after thread 0's griddepcontrol.wait, and everything this grid
+  // writes is downstream of those reads.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
+    if (p.group_sizes) asm volatile("griddepcontrol.wait;" ::: "memory");
     int64_t tiles = 0, rows = 0;
     for (int s = 0; s < nseg; ++s) {
       seg_tile0[s] = tiles;
@@ -506,17 +514,32 @@ qmm_gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, early = 0;
       TileInfo ti;
       bool ok = true;
-      for (int64_t t = p.item0 + blockIdx.x; ok && t < p.item_end && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
+      // The weight boxes of the first tile's first ring (the stages start out free) go out before
+      // the wait for the preceding grid; their activation boxes follow it.
+      const int64_t first = p.item0 + blockIdx.x;
+      if (first < p.item_end && tile_at<BT>(first, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti)) {
+        const int64_t wrow = ti.seg * p.w_seg_rows + ti.f0;
+        for (int kb = ti.kb_lo; kb < ti.kb_hi && early < static_cast<uint32_t>(P::kStages); ++kb, ++early) {
+          mbar_expect_tx(&full[early], P::kStageBytes);
+          tma_load_2d(&w_map, smem + early * P::kStageBytes + P::kXBytes, &full[early], kb * P::kWRowBytes, static_cast<int>(wrow));
+        }
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      for (int64_t t = first; ok && t < p.item_end && tile_at<BT>(t, seg_tile0, seg_row0, nseg, ftiles, p.N, SPLIT ? p.splits : 1, num_kb, &ti);
            t += gridDim.x) {
         const int64_t wrow = ti.seg * p.w_seg_rows + ti.f0;
         for (int kb = ti.kb_lo; kb < ti.kb_hi; ++kb, ++it) {
           const int s = it % P::kStages;
+          uint8_t* stage = smem + s * P::kStageBytes;
+          if (it < early) {              // armed above, its weight box is on the way
+            tma_load_2d(&x_map, stage, &full[s], kb * kBK, static_cast<int>(ti.row0));
+            continue;
+          }
           const uint32_t ph = (it / P::kStages) & 1;
           if (!(ok = twait(&empty[s], ph ^ 1, abort_flag, 1))) break;
-          uint8_t* stage = smem + s * P::kStageBytes;
           mbar_expect_tx(&full[s], P::kStageBytes);
           tma_load_2d(&x_map, stage, &full[s], kb * kBK, static_cast<int>(ti.row0));
           tma_load_2d(&w_map, stage + P::kXBytes, &full[s], kb * P::kWRowBytes, static_cast<int>(wrow));
@@ -778,9 +801,37 @@ int* status_word() {
 
 int sm_count() { return device_sm_count(); }
 
+// Launches with programmatic stream serialization (QMM_TC_PDL=0: plain stream order): the
+// kernels of this file wait for the grid before them themselves, as late as they can.
+bool tc_pdl() {
+  static const bool on = [] {
+    const char* e = getenv("QMM_TC_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... Params, typename... Args>
+void launch_dependent(void (*kernel)(Params...), unsigned grid, unsigned threads, size_t smem, cudaStream_t stream,
+                      Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tc_pdl() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);      // a failure stays as the last error: check_launch reports it
+}
+
 // Sums the float32 partial tiles of a split product in split order and casts to y's type.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ y, int y_dtype,
                                      int64_t total, int splits) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // the partial tiles come from the grid before
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * 4;
   for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < total; i += stride) {
     float4 acc = *reinterpret_cast<const float4*>(partial + i);
@@ -807,6 +858,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
 __global__ void splitk_tail_reduce_kernel(const float* __restrict__ partial, void* __restrict__ y, int y_dtype,
                                           int64_t M, int64_t N, int64_t ftiles, int64_t tile0, int64_t tiles,
                                           int bt, int splits) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t per_tile = static_cast<int64_t>(bt) * kBF, total = tiles * per_tile;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -959,7 +1012,7 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
       if (part) {
         TcParams head = tp, tail = tp;
         head.item_end = max_tiles - rem;
-        qmm_gemm_tc_kernel<QK, XT, BT, false><<<grid, P::kThreads, P::kSmem, stream>>>(xm, wm, head);
+        launch_dependent(qmm_gemm_tc_kernel<QK, XT, BT, false>, grid, P::kThreads, P::kSmem, stream, xm, wm, head);
         tail.splits = static_cast<int>(s);
         tail.partial = part;
         tail.tail_tile0 = max_tiles - rem;
@@ -967,26 +1020,26 @@ int launch_cfg(const qmm_problem& p, cudaStream_t stream) {
         tail.item0 = (max_tiles - rem) * s;
         tail.item_end = max_tiles * s;
         const int64_t tail_grid = rem * s < grid ? rem * s : grid;
-        qmm_gemm_tc_kernel<QK, XT, BT, true><<<static_cast<unsigned>(tail_grid), P::kThreads, P::kSmem, stream>>>(xm, wm, tail);
+        launch_dependent(qmm_gemm_tc_kernel<QK, XT, BT, true>, static_cast<unsigned>(tail_grid), P::kThreads, P::kSmem, stream, xm, wm, tail);
         const int64_t total = rem * BT * kBF;
         int64_t blocks = (total + 255) / 256;
         if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
-        splitk_tail_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(part, p.y, p.y_dtype, p.M, p.N, ftiles,
-                                                                                    max_tiles - rem, rem, BT, static_cast<int>(s));
+        launch_dependent(splitk_tail_reduce_kernel, static_cast<unsigned>(blocks), 256, 0, stream, part, p.y, p.y_dtype, p.M, p.N,
+                         ftiles, max_tiles - rem, rem, BT, static_cast<int>(s));
         count_launch(3);
         if (part_async) cudaFreeAsync(part, stream);
         return check_launch("qmm_gemm_tc_kernel");
       }
     }
   }
-  if (splits > 1) qmm_gemm_tc_kernel<QK, XT, BT, true><<<grid, P::kThreads, P::kSmem, stream>>>(xm, wm, tp);
-  else qmm_gemm_tc_kernel<QK, XT, BT, false><<<grid, P::kThreads, P::kSmem, stream>>>(xm, wm, tp);
+  if (splits > 1) launch_dependent(qmm_gemm_tc_kernel<QK, XT, BT, true>, grid, P::kThreads, P::kSmem, stream, xm, wm, tp);
+  else launch_dependent(qmm_gemm_tc_kernel<QK, XT, BT, false>, grid, P::kThreads, P::kSmem, stream, xm, wm, tp);
   count_launch();
   if (splits > 1) {
     const int64_t total = p.M * p.N;
     int64_t blocks = (total / 4 + 255) / 256;
     if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
-    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(tp.partial, p.y, p.y_dtype, total, splits);
+    launch_dependent(splitk_reduce_kernel, static_cast<unsigned>(blocks), 256, 0, stream, tp.partial, p.y, p.y_dtype, total, splits);
     count_launch();
     if (scratch_async) cudaFreeAsync(tp.partial, stream);
   }
