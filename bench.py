@@ -53,8 +53,10 @@ WORKLOADS = {
 L2_BYTES = 126 * 1024 * 1024
 # Whole decode steps of the Llama-3-8B-shaped model: name -> batch. The weights are sharded on N
 # over the ranks, so these scale strongly.
-DECODE_STEPS = {"decode_llama3_8b_b1": 1, "decode_llama3_8b_b16": 16, "decode_llama3_8b_b64": 64}
+DECODE_STEPS = {"decode_llama3_8b_b1": 1, "decode_llama3_8b_b8": 8, "decode_llama3_8b_b16": 16, "decode_llama3_8b_b32": 32,
+                "decode_llama3_8b_b64": 64}
 DEFAULT = "decode_llama3_8b_b64"
+ALSO_STEPS = ["decode_llama3_8b_b1", "decode_llama3_8b_b16", "decode_llama3_8b_b64"]     # the batches the configs name
 # The expert block of a Mixtral-8x7B-shaped mixture-of-experts layer: 4096 tokens, top-2 of 8
 # experts, d 4096, ffn 14336, int4 group-64 expert weights; three grouped ragged products over
 # 8192 (token, expert) pairs plus the routed weighted sum. Over N ranks: experts split, tokens
@@ -97,14 +99,35 @@ def work_of(name):
     return flops, weight_bytes, total_bytes
 
 
-def config_of(name, world):
+DECODE_SHARDING = "auto"      # --decode-sharding
+
+
+def decode_sharding(batch, world):
+    """How a decode step of `batch` sequences is split over `world` ranks: "rows" (every rank steps
+    batch / N sequences with the whole weights, nothing exchanged) where the batch divides, else
+    "weights" (every linear split on its output rows, every rank steps every sequence). Above a few
+    rows a step is bound by per-sequence work -- the KV cache and the tensor-core kernel's cost per
+    weight block -- not by the weight bytes, which is why the sequences are what to split."""
+    if world == 1:
+        return "weights"
+    if DECODE_SHARDING != "auto":
+        return DECODE_SHARDING
+    return "rows" if batch % world == 0 else "weights"
+
+
+def config_of(name, world, sharding=None):
     """What the workload is; both arms print exactly this."""
     if name in DECODE_STEPS:
+        sharding = sharding or decode_sharding(DECODE_STEPS[name], world)
         return {"workload": name, "batch": DECODE_STEPS[name], "layers": 32, "d_model": 4096, "heads": 32, "kv_heads": 8,
                 "ffn": 14336, "vocab": 128256, "context": 2048, "group_size": 64, "bits": 4,
                 "weights": "N(0, 0.02) quantized per group of 64: scale = (max - min)/15, zero = round(-min/scale)",
-                "parallelism": f"tp{world}: every linear sharded on its output rows, slices exchanged after it",
-                "l2": "one step streams this rank's packed weights (4.2 GB / N) and KV cache: far more than L2"}
+                "parallelism": (f"dp{world}: the sequences split over the ranks (batch / N each), whole weights on every rank, "
+                                "nothing exchanged" if sharding == "rows" else
+                                f"tp{world}: every linear sharded on its output rows, slices exchanged after it"),
+                "l2": ("one step streams the packed weights (4.2 GB) and this rank's sequences' KV cache: far more than L2"
+                       if sharding == "rows" else
+                       "one step streams this rank's packed weights (4.2 GB / N) and KV cache: far more than L2")}
     if name in MOE_BLOCKS:
         t, k, e, d, f = MOE_BLOCKS[name]
         return {"workload": name, "tokens": t, "top_k": k, "experts": e, "d_model": d, "ffn": f, "group_size": 64, "bits": 4,
@@ -478,26 +501,29 @@ def qmm_line(name, args, torch, dist, device, world, pk):
 # ---- the decode step ------------------------------------------------------------------------------
 
 
-def decode_step_bytes(batch, world):
+def decode_step_bytes(batch, world, sharding="weights"):
     """Algorithmic HBM bytes one rank touches per decode step: its shard of the packed weights
-    and tables, and its heads' KV cache of `batch` sequences."""
+    and tables (all of them when the sequences are what is split) and its share of the KV cache
+    of `batch` sequences."""
     from metaljax_b200 import llama
     sh = llama.LLAMA3_8B
     kv = 2 * sh.layers * batch * sh.kv_heads * sh.ctx * sh.head_dim * 2
-    return sh.weight_bytes() / world, kv / world
+    return sh.weight_bytes() / (1 if sharding == "rows" else world), kv / world
 
 
-def measure_decode_step(batch, steps, warmup, torch, dist, device):
+def measure_decode_step(batch, steps, warmup, torch, dist, device, sharding="weights"):
     """One Llama-3-8B-shaped decode step per timed step, replayed from a CUDA graph: device
-    time (tokens resident) and end to end (token ids from pinned host memory, next ids back)."""
+    time (tokens resident) and end to end (token ids from pinned host memory, next ids back;
+    with the sequences split over the ranks every rank copies its own)."""
     from metaljax_b200 import _lib, llama
-    step = llama.DecodeStep(llama.LLAMA3_8B, batch, device, seed=7, weights="normal")
+    step = llama.DecodeStep(llama.LLAMA3_8B, batch, device, seed=7, weights="normal", shard=sharding)
+    batch_here = step.batch
     n1 = _lib.launch_count()
     step.capture(warmup=max(warmup, 3))
     per_step = (_lib.launch_count() - n1) // (max(warmup, 3) + 1)
     ms = time_device(lambda i: step.replay(), steps, 3, torch, dist)
-    host_in = torch.zeros((batch,), dtype=torch.int64).pin_memory()
-    host_out = torch.zeros((batch,), dtype=torch.int64).pin_memory()
+    host_in = torch.zeros((batch_here,), dtype=torch.int64).pin_memory()
+    host_out = torch.zeros((batch_here,), dtype=torch.int64).pin_memory()
 
     def e2e_step(i):
         host_in.fill_(i % 1000)
@@ -515,21 +541,24 @@ def measure_decode_step(batch, steps, warmup, torch, dist, device):
     return res
 
 
-def decode_step_line(name, args, torch, dist, device, world, pk):
+def decode_step_line(name, args, torch, dist, device, world, pk, sharding=None):
     batch = DECODE_STEPS[name]
-    res = measure_decode_step(batch, args.steps, args.warmup, torch, dist, device)
+    sharding = sharding or decode_sharding(batch, world)
+    res = measure_decode_step(batch, args.steps, args.warmup, torch, dist, device, sharding)
     ms_step, e2e_ms = max_over_ranks([res["ms_per_step"], res["e2e_ms_per_step"]], torch, dist, device)
-    wb, kvb = decode_step_bytes(batch, world)
+    wb, kvb = decode_step_bytes(batch, world, sharding)
     achieved = (wb + kvb) / (res["ms_per_step"] * 1e-3) / 1e9
     return {
         "metric": "decode_tok_s", "value": batch / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": res["steps"], "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": config_of(name, world),
+        "config": config_of(name, world, sharding),
         "how": {"timed": "cuda graph replay of the whole step", "exchange": res["exchange"]},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                     "bytes": "this rank's packed weights + tables and its KV cache, read once per step"},
+                     "bytes": ("the packed weights + tables and this rank's sequences' KV cache, read once per step"
+                               if sharding == "rows" else
+                               "this rank's packed weights + tables and its KV cache, read once per step")},
         "e2e": {"value": batch / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": res["h2d"],
                 "d2h_bytes_per_step": res["d2h"], "ms_per_step": e2e_ms},
         "gpu_launches": int(res["launches_per_step"] * res["steps"]),
@@ -635,6 +664,20 @@ def parity_check(torch, dist, device, world, rank):
             if not torch.equal(step.step(), first):
                 errs.append(float("inf"))
         del step
+    # the same step with the sequences split over the ranks (two and seventeen per rank: the fused
+    # single-row path does not apply, the multi-row and the tensor-core kernels both do)
+    for per_rank in (2, 17):
+        batch = per_rank * world
+        fw = llama.random_full_weights(shape, batch, device, seed=5)
+        step = llama.DecodeStep(shape, batch, device, full_weights=fw, shard="rows")
+        tokens = torch.arange(batch, device=device) * 13 % shape.vocab
+        mine = slice(step.rows_rank * step.batch, (step.rows_rank + 1) * step.batch)
+        step.tokens.copy_(tokens[mine])
+        step.step()
+        got = step.logits()
+        want = llama.reference_logits(fw, shape, tokens, batch)[mine]
+        errs.append((got - want).abs().max().item() / want.abs().max().item())
+        del step
     rng = np.random.default_rng(0)
     e, kk, d, f, t = 8, 2, 256, 512, 64 + 8 * rank
     packs = [affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:], affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:],
@@ -653,8 +696,9 @@ def parity_check(torch, dist, device, world, rank):
     moe_err = O.rel_err(to_numpy(y).astype(np.float32), O.moe_combine_exact(down, wts))
     step_err, moe_err = max_over_ranks([max(errs), moe_err], torch, dist, device)
     return {"decode_step": step_err, "ep_moe": moe_err, "bounds": {"decode_step": 3e-2, "ep_moe": 2e-2},
-            "what": "sharded decode step (2 layers, d 1024, batch 1 and 5) vs the float32 step on the dequantized "
-                    "weights; expert-parallel SwiGLU block (8 experts, top-2) vs the oracle's pair-space product"}
+            "what": "decode step (2 layers, d 1024) with the weights sharded (batch 1 and 5) and with the sequences "
+                    "sharded (2 and 17 per rank) vs the float32 step on the dequantized weights; expert-parallel "
+                    "SwiGLU block (8 experts, top-2) vs the oracle's pair-space product"}
 
 
 def line_of(name, args, torch, dist, device, world, pk):
@@ -676,13 +720,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS) + sorted(DECODE_STEPS) + sorted(MOE_BLOCKS))
+    ap.add_argument("--decode-sharding", default="auto", choices=["auto", "rows", "weights"],
+                    help="decode steps at N > 1: split the sequences, or the weights (auto: sequences where the batch divides)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-also", action="store_true", help="only the headline workload")
     ap.add_argument("--profile-window", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
-    global PROFILE_WINDOW
+    global PROFILE_WINDOW, DECODE_SHARDING
     PROFILE_WINDOW = args.profile_window
+    DECODE_SHARDING = args.decode_sharding
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -716,12 +763,17 @@ def main():
 
     if not args.no_also and name == DEFAULT:
         if world == 1:
-            sides = [w for w in ALSO_AT_ONE] + [w for w in sorted(DECODE_STEPS, key=DECODE_STEPS.get) if w != name]
+            sides = [w for w in ALSO_AT_ONE] + [w for w in ALSO_STEPS if w != name]
         else:
-            sides = [w for w in sorted(DECODE_STEPS, key=DECODE_STEPS.get) if w != name] + sorted(MOE_BLOCKS)
+            sides = [w for w in ALSO_STEPS if w != name] + sorted(MOE_BLOCKS)
         for side_name in sides:
             side = line_of(side_name, args, torch, dist, device, world, pk)
             line.setdefault("also", []).append({key: side[key] for key in ALSO_KEYS})
+        if world > 1 and DECODE_SHARDING == "auto":
+            # the other way to split the headline and the batch-16 step: the weights instead of the sequences
+            for side_name in (w for w in reversed(ALSO_STEPS) if decode_sharding(DECODE_STEPS[w], world) == "rows"):
+                side = decode_step_line(side_name, args, torch, dist, device, world, pk, sharding="weights")
+                line["also"].append({key: side[key] for key in ALSO_KEYS})
         _lib.poll_status()
 
     if rank == 0 and not args.no_cpu:

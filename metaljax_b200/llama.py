@@ -159,10 +159,25 @@ class DecodeStep:
     """Weights, KV cache and buffers of one rank, and the step itself."""
 
     def __init__(self, shape: Shape, batch: int, device, group=None, seed: int = 0, weights: str = "codes",
-                 full_weights=None, gather: str = "peer"):
-        self.shape, self.batch, self.device, self.group = shape, batch, torch.device(device), group
+                 full_weights=None, gather: str = "peer", shard: str = "weights"):
+        """`shard="weights"`: every linear is split on its output rows over the ranks and every rank
+        steps all `batch` sequences. `shard="rows"`: the sequences are split instead -- rank r steps
+        rows `[r * batch / N, (r + 1) * batch / N)` with the whole weights and its own sequences' KV
+        cache, and nothing is exchanged; `self.batch` is then this rank's share."""
+        self.shape, self.device, self.group = shape, torch.device(device), group
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.shard, self.global_batch = shard, batch
+        self.rows_world, self.rows_rank = 1, 0
+        if shard == "rows" and self.world > 1:
+            if batch % self.world:
+                raise ValueError(f"{batch} sequences do not split over {self.world} ranks")
+            self.rows_world, self.rows_rank = self.world, self.rank
+            batch //= self.world
+            self.world, self.rank = 1, 0                     # as far as the weights are concerned
+        elif shard not in ("weights", "rows"):
+            raise ValueError("shard is 'weights' or 'rows'")
+        self.batch = batch
         sh, g, r = shape, self.world, self.rank
         if sh.heads % g or sh.kv_heads % g or sh.ffn % (16 * g) or sh.d_model % (16 * g):
             raise ValueError(f"shape does not split over {g} ranks")
@@ -201,10 +216,13 @@ class DecodeStep:
             self.embedding = fw["embedding"].to(torch.bfloat16)
         # KV cache of this rank's heads, filled up to (not including) the decode position
         kv_shape = (sh.layers, batch, self.kv_l, sh.ctx, hd)
+        rows = slice(self.rows_rank * batch, (self.rows_rank + 1) * batch)           # of a full cache's sequences
+        if self.rows_world > 1:
+            gen = torch.Generator(device=self.device).manual_seed(seed * 1000 + 500 + self.rows_rank)   # its own sequences
         self.k_cache = (torch.randn(kv_shape, generator=gen, device=dev, dtype=torch.float32) * 0.5).to(torch.bfloat16) \
-            if fw is None else fw["k_cache"][:, :, r * self.kv_l:(r + 1) * self.kv_l].contiguous()
+            if fw is None else fw["k_cache"][:, rows, r * self.kv_l:(r + 1) * self.kv_l].contiguous()
         self.v_cache = (torch.randn(kv_shape, generator=gen, device=dev, dtype=torch.float32) * 0.5).to(torch.bfloat16) \
-            if fw is None else fw["v_cache"][:, :, r * self.kv_l:(r + 1) * self.kv_l].contiguous()
+            if fw is None else fw["v_cache"][:, rows, r * self.kv_l:(r + 1) * self.kv_l].contiguous()
         bf = dict(device=dev, dtype=torch.bfloat16)
         b = batch
         self.res = torch.empty((b, sh.d_model), **bf)
@@ -285,6 +303,14 @@ class DecodeStep:
                 dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
                 if int(ok.item()) == 0:
                     self.fused = False
+        # Above one row: the rotary kernel followed by torch's scaled_dot_product_attention, which reads the
+        # cache at the HBM roofline there; QMM_DECODE_ATTENTION=own runs the single-row path's one-kernel
+        # rotary + append + attention instead (built for latency: at 64 rows it reaches about a third of that).
+        self.own_attention = not self.fused and os.environ.get("QMM_DECODE_ATTENTION", "sdpa") == "own"
+        if self.own_attention:
+            self.attn_l = torch.empty((b, self.h_l * hd), **bf)
+            nbytes = _lib.lib().qmm_decode_attention_scratch_bytes(b, self.h_l, self.kv_l, hd, sh.ctx)
+            self.attn_scratch = torch.zeros((nbytes,), device=dev, dtype=torch.uint8)
         if self.fused:
             # the fused gate/up kernel applies SwiGLU in its epilogue: its rows alternate gate_j, up_j
             idx = torch.stack([torch.arange(self.ffn_l, device=dev), torch.arange(self.ffn_l, device=dev) + self.ffn_l],
@@ -417,8 +443,12 @@ class DecodeStep:
         add_rmsnorm(self.res, self.layers[0]["ln1"], self.normed, eps=sh.eps)
         for li, layer in enumerate(self.layers):
             layer["qkv"](self.normed, self.qkv)
-            rope_kv(self.qkv, self.q, self.k_cache[li], self.v_cache[li], self.h_l, self.kv_l, hd, pos, sh.theta)
-            attn = F.scaled_dot_product_attention(self.q, self.k_cache[li], self.v_cache[li], enable_gqa=True)
+            if self.own_attention:
+                attn = decode_attention(self.qkv, self.k_cache[li], self.v_cache[li], self.attn_l, self.attn_scratch,
+                                        self.h_l, self.kv_l, hd, pos, sh.theta)
+            else:
+                rope_kv(self.qkv, self.q, self.k_cache[li], self.v_cache[li], self.h_l, self.kv_l, hd, pos, sh.theta)
+                attn = F.scaled_dot_product_attention(self.q, self.k_cache[li], self.v_cache[li], enable_gqa=True)
             attn_full = self._gather(attn.reshape(b, self.h_l * hd), self.attn_full)
             layer["o"](attn_full, self.o_l)
             o_full = self._gather(self.o_l, self.o_full)
@@ -470,6 +500,8 @@ class DecodeStep:
 
     def exchange_description(self) -> str:
         """How the slices of a sharded linear reach the other ranks (for benchmark records)."""
+        if self.rows_world > 1:
+            return "none: the sequences are split over the ranks, every rank holds the whole weights"
         if self.fused and self.world > 1:
             return ("stamped peer stores from the epilogue of each sharded kernel (attention, o, gate/up, down), read "
                     "as they arrive by the kernel that consumes the row")

@@ -93,6 +93,19 @@ def _worker(rank, world, port, ret):
             for _ in range(3):                                                # slots and flags cycle correctly
                 assert torch.equal(step.step(), nxt)
             stage = f"decode step batch {batch} ({gather}) done"
+        # the same step with the sequences split over the ranks instead of the weights
+        batch = 6
+        fw = llama.random_full_weights(shape, batch, dev, seed=4)
+        step = llama.DecodeStep(shape, batch, dev, full_weights=fw, shard="rows")
+        assert step.batch == batch // world and step.world == 1
+        tokens = torch.arange(batch, device=dev) * 7 % shape.vocab
+        mine = slice(rank * step.batch, (rank + 1) * step.batch)
+        step.tokens.copy_(tokens[mine])
+        step.step()
+        want = llama.reference_logits(fw, shape, tokens, batch)[mine]
+        err = (step.logits() - want).abs().max().item() / want.abs().max().item()
+        assert err <= 3e-2, ("decode step, sequences split", err)
+        stage = "decode step with the sequences split done"
         assert _lib.poll_status() == 0
         ret[rank] = "ok"
     except Exception as exc:                              # surfaced by the parent
