@@ -133,7 +133,16 @@ const char* qmm_last_error(void);
  *           kernel's epilogue
  *   transpose   must be 1 (the only form the reference emits)
  *   group_size  32 | 64 | 128 (affine), 32 (mxfp4);  bits 4 | 8 (affine), 4 (mxfp4)
- * Accumulation is float32. */
+ * Accumulation is float32.
+ *
+ * Stream order: the kernels are launched with programmatic stream serialization. x (and the
+ * index / size arrays of the gathered and ragged forms) are read, and y is written, only after
+ * everything queued before the call on `stream` has completed and is visible. The packed
+ * weight and its tables are requested earlier -- once the grid queued directly before has
+ * finished its thread blocks -- because in the reference's protocol they are constants made
+ * once by the pack prologue (src/metaljax/qmm.py:2305-2387), long before the first fused op. A
+ * caller that rewrites a weight on the same stream immediately before using it puts an event
+ * or any other kernel in between. */
 int qmm_quantized_matmul(const qmm_tensor* x, const qmm_tensor* w, const qmm_tensor* scales,
                          const qmm_tensor* biases, qmm_tensor* y, int transpose, int group_size,
                          int bits, int mode, void* stream);
