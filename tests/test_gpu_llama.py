@@ -109,6 +109,30 @@ def test_single_row_step_fused_against_unfused(monkeypatch):
     assert _lib.poll_status() == 0
 
 
+def test_multi_row_step_with_the_one_kernel_attention(monkeypatch):
+    """Above one row the step's attention is torch's; QMM_DECODE_ATTENTION=own swaps in the
+    library's rotary + append + attention kernel. Same logits as the float reference, the same rows appended to the cache."""
+    from metaljax_b200 import _lib, llama
+    shape, batch = _small(), 5
+    fw = llama.random_full_weights(shape, batch, DEV, seed=21)
+    tokens = torch.arange(batch, device=DEV) * 5 % shape.vocab
+    want = llama.reference_logits(fw, shape, tokens, batch)
+    caches = {}
+    for which in ("sdpa", "own"):
+        monkeypatch.setenv("QMM_DECODE_ATTENTION", which)
+        step = llama.DecodeStep(shape, batch, DEV, full_weights=fw)
+        assert step.own_attention == (which == "own")
+        step.tokens.copy_(tokens)
+        step.step()
+        err = (step.logits() - want).abs().max().item() / want.abs().max().item()
+        assert err <= 3e-2, (which, err)
+        caches[which] = (step.k_cache.clone(), step.v_cache.clone())
+    for own, ref in zip(caches["own"], caches["sdpa"]):
+        assert torch.equal(own[0], ref[0])                       # the first layer appends the same bits
+        assert (own.float() - ref.float()).abs().max().item() <= 3e-2 * ref.float().abs().max().item()   # deeper ones follow the logits
+    assert _lib.poll_status() == 0
+
+
 def test_decode_linear_prologues_and_self_exchange():
     """`qmm_decode_linear` against the unfused sequence: SwiGLU prologue bit for bit (the same
     bf16 row reaches the same kernel), add + RMS-norm within a bf16 rounding of the row; and the
