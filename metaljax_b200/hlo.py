@@ -558,6 +558,7 @@ EVAL = {
     "stablehlo.multiply": _binary(torch.mul),
     "stablehlo.divide": lambda op, x, y: x / y if x.dtype.is_floating_point else torch.div(x, y, rounding_mode="trunc"),
     "stablehlo.maximum": _binary(torch.maximum), "stablehlo.minimum": _binary(torch.minimum),
+    "stablehlo.clamp": lambda op, lo, x, hi: torch.minimum(torch.maximum(x, lo), hi),
     "stablehlo.and": _binary(torch.bitwise_and), "stablehlo.or": _binary(torch.bitwise_or),
     "stablehlo.xor": _binary(torch.bitwise_xor),
     "stablehlo.shift_left": _shift(lambda x, y: x << y),

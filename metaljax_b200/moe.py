@@ -197,6 +197,9 @@ class Match:
 
 
 def emit_reads(m):
+    reads = getattr(m, "reads", None)           # a planned region lists what it gathers
+    if reads is not None:
+        return tuple(reads)
     return (m.lhs, m.router_indices, m.router_weights)
 
 

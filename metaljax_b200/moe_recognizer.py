@@ -167,6 +167,21 @@ class ExpertBlock(moe.Match):
         super().__init__()
         self.verified = False
 
+    def matches(self):
+        """The quantized / float matches the block runs on (no longer roots of their own)."""
+        return (self.gate, self.up, self.down)
+
+
+class ExpertRegion(ExpertBlock):
+    """A dense expert region planned node by node in pair space (`pair_plan`): any element-wise
+    work between any number of per-expert dots. `y` is the node of the weighted value, `dots` the
+    matches its dots run on."""
+
+    __slots__ = ("planner", "y", "dots", "e_axis", "t_axis", "reads")
+
+    def matches(self):
+        return tuple(self.dots)
+
 
 def _float_match(st, dot):
     """A dot whose weight operand is a FLOAT array computed from `@main`'s arguments alone (an
@@ -257,6 +272,30 @@ def _plan_swiglu(st, Y, r: Router) -> ExpertBlock:
     raise _Reject("no silu(gate) * up under the last expert dot")
 
 
+def _plan_region(st, Y, r: Router, e_axis, t_axis) -> ExpertRegion:
+    """The general plan: whatever element-wise region and per-expert dots produce Y
+    (src/metaljax/moe.py:450-810)."""
+    from . import pair_plan
+
+    def find(dot):
+        return _float_match(st, dot)
+
+    planner = pair_plan.Planner(st, r.E, r.T, find)
+    y = planner.plan(Y, e_axis, t_axis)
+    if not planner.matches:
+        raise _Reject("no per-expert dot in the region")
+    modes = {m.mode == "float" for m in planner.matches}
+    b = ExpertRegion()
+    b.router, b.planner, b.y, b.dots = r, planner, y, list(dict.fromkeys(planner.matches))
+    b.e_axis, b.t_axis = e_axis, t_axis
+    b.x = b.gate = b.up = b.down = None
+    b.reads = tuple(dict.fromkeys(planner.reads))
+    b.T, b.K, b.E, b.P = r.T, r.K, r.E, r.T * r.K
+    b.bytes = planner.bytes(b.P)
+    del modes
+    return b
+
+
 def analyze(interp, st) -> None:
     """Find dense expert blocks on top of the quantized matches in `st` (the reference chains
     its recognizers the same way, src/metaljax/qmm.py:1085-1091). Never raises."""
@@ -279,7 +318,11 @@ def analyze(interp, st) -> None:
                     r = match_router(S)
                     if s_dims[r.e_axis] != e_axis:
                         raise _Reject("the outer sum is not over the expert axis")
-                    block = _plan_swiglu(st, mul.operands[1 - s_side], r)
+                    Y = mul.operands[1 - s_side]
+                    try:
+                        block = _plan_swiglu(st, Y, r)             # the one-launch-per-projection block
+                    except _Reject:
+                        block = _plan_region(st, Y, r, e_axis, s_dims[r.t_axis])
                     break
                 if block is None:
                     continue
@@ -301,17 +344,20 @@ def analyze(interp, st) -> None:
                     needed.add(id(v.op))
                     stack.extend(v.op.operands)
                 skip = {id(mul): mul}
-                roots = {id(m.root) for m in (block.gate, block.up, block.down)}
-                for m in (block.gate, block.up, block.down):
+                roots = {id(m.root) for m in block.matches()}
+                for m in block.matches():
                     skip.update(m.ops)
                     skip[id(m.root)] = m.root
-                stack = [mul.operands[1 - s_side]]                 # Y back to the projections
-                while stack:
-                    v = stack.pop()
-                    if v is block.x or v.op is None or id(v.op) in skip:
-                        continue
-                    skip[id(v.op)] = v.op
-                    stack.extend(v.op.operands)
+                if isinstance(block, ExpertRegion):
+                    skip.update(block.planner.region)              # exactly the ops the plan replaces
+                else:
+                    stack = [mul.operands[1 - s_side]]             # Y back to the projections
+                    while stack:
+                        v = stack.pop()
+                        if v is block.x or v.op is None or id(v.op) in skip:
+                            continue
+                        skip[id(v.op)] = v.op
+                        stack.extend(v.op.operands)
                 grew = True
                 while grew:                                         # dead sweep
                     grew = False
@@ -334,7 +380,7 @@ def analyze(interp, st) -> None:
                     raise _Reject("a value of the expert region is also read outside it")
                 block.ops = skip
                 block.skip_keys = tuple(skip)
-                for m in (block.gate, block.up, block.down):
+                for m in block.matches():
                     m.absorbed = True
                 st.moe.append(block)
                 STATS["recognized"] += 1
@@ -355,7 +401,7 @@ def prologue(interp, st, device=None) -> bool:
             b.verified = True
             continue
         b.disabled = True
-        for m in (b.gate, b.up, b.down):
+        for m in b.matches():
             m.absorbed = False
         changed = True
     return changed
@@ -398,6 +444,8 @@ def emit(interp, b: ExpertBlock, env):
     r = b.router
     idx = hlo.evaluate_value(r.indices, env).to(torch.int64)
     wts = hlo.evaluate_value(r.weights, env)
+    if isinstance(b, ExpertRegion):
+        return [_emit_region(interp, b, env, idx, wts)]
     x = env[b.x]
     if list(b.gate.lperm) != list(range(x.dim())):
         x = x.permute(*b.gate.lperm)
@@ -414,3 +462,27 @@ def emit(interp, b: ExpertBlock, env):
                         _expert_pack(interp, b.gate, b.E), _expert_pack(interp, b.up, b.E),
                         _expert_pack(interp, b.down, b.E), **kw)
     return [y.reshape(b.out_shape).to(b.out_dtype)]
+
+
+def _emit_region(interp, b: ExpertRegion, env, idx, wts, ragged=None):
+    """A planned region over the routed pairs: sort the pairs by expert, evaluate the plan's nodes
+    on `[P, ...]` arrays, weight and add every token's K results."""
+    from . import pair_plan
+    order, tok, sizes = moe.sort_pairs(idx, b.E)
+    eor = torch.repeat_interleave(torch.arange(b.E, device=idx.device), sizes.to(torch.int64), output_size=b.P)
+
+    def weight_of(m):
+        return _float_weight(interp, m, env, b.E) if m.mode == "float" else _expert_pack(interp, m, b.E)
+
+    vals = pair_plan.evaluate(b.planner.order, env, (tok, eor, sizes), b.E, weight_of, ragged)
+    y = vals[id(b.y)]
+    if not b.y.paired or y.shape[0] != b.P:
+        raise _Reject("the weighted value has no pair axis")
+    trailing = b.y.trailing
+    out = pair_plan.weighted_sum(y.reshape([b.P] + trailing), order, wts, b.T, b.K, b.out_dtype)
+    out = out.reshape([b.T] + trailing)
+    # the root's result is Y's shape without the expert axis: put the token axis where it belongs
+    t_out = b.t_axis - (1 if b.e_axis < b.t_axis else 0)
+    if t_out:
+        out = out.movedim(0, t_out)
+    return out.reshape(b.out_shape).to(b.out_dtype)

@@ -349,3 +349,132 @@ def moe_inputs(t=6, d=64, e=4, f=64, gs=32, seed=0, device="cpu"):
     cu, su = pack(f, d)
     cd, sd = pack(d, f)
     return [a.to(device) for a in (x, logits, cg, sg, cu, su, cd, sd)]
+
+
+_ROUTER = """    %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %cst_0 = stablehlo.constant dense<0.000000e+00> : tensor<bf16>
+    %0:2 = chlo.top_k(%arg1, k = {k}) : tensor<{t}x{e}xf32> -> (tensor<{t}x{k}xf32>, tensor<{t}x{k}xi32>)
+    %1 = stablehlo.exponential %0#0 : tensor<{t}x{k}xf32>
+    %2 = stablehlo.reduce(%1 init: %cst) applies stablehlo.add across dimensions = [1] : (tensor<{t}x{k}xf32>, tensor<f32>) -> tensor<{t}xf32>
+    %3 = stablehlo.broadcast_in_dim %2, dims = [0] : (tensor<{t}xf32>) -> tensor<{t}x{k}xf32>
+    %4 = stablehlo.divide %1, %3 : tensor<{t}x{k}xf32>
+    %5 = stablehlo.iota dim = 2 : tensor<{t}x{k}x{e}xi32>
+    %6 = stablehlo.broadcast_in_dim %0#1, dims = [0, 1] : (tensor<{t}x{k}xi32>) -> tensor<{t}x{k}x{e}xi32>
+    %7 = stablehlo.compare EQ, %6, %5, SIGNED : (tensor<{t}x{k}x{e}xi32>, tensor<{t}x{k}x{e}xi32>) -> tensor<{t}x{k}x{e}xi1>
+    %8 = stablehlo.convert %7 : (tensor<{t}x{k}x{e}xi1>) -> tensor<{t}x{k}x{e}xf32>
+    %9 = stablehlo.broadcast_in_dim %4, dims = [0, 1] : (tensor<{t}x{k}xf32>) -> tensor<{t}x{k}x{e}xf32>
+    %10 = stablehlo.multiply %8, %9 : tensor<{t}x{k}x{e}xf32>
+    %11 = stablehlo.reduce(%10 init: %cst) applies stablehlo.add across dimensions = [1] : (tensor<{t}x{k}x{e}xf32>, tensor<f32>) -> tensor<{t}x{e}xf32>
+"""
+
+
+def moe_program_glu_bias(t=6, d=64, e=4, f=64, k=2):
+    """A dense expert layer of the gpt-oss kind, float (bf16) weights: ONE gate/up projection with
+    interleaved output features and a per-expert bias, `gate` clamped from above and `up` clamped
+    both ways, `(up + 1) * gate * logistic(1.702 * gate)`, a down projection with a per-expert
+    bias. Nothing of the SwiGLU shape: strided slices, clamps, scalar constants and biases that
+    have the expert axis but no token axis sit between the two dots."""
+    f2 = 2 * f
+    return f"""
+module @jit_moe_glu {{
+  func.func public @main(%arg0: tensor<{t}x{d}xbf16>, %arg1: tensor<{t}x{e}xf32>, %arg2: tensor<{e}x{f2}x{d}xbf16>, %arg3: tensor<{e}x{f2}xbf16>, %arg4: tensor<{e}x{d}x{f}xbf16>, %arg5: tensor<{e}x{d}xbf16>) -> (tensor<{t}x{d}xbf16>) {{
+{_ROUTER.format(t=t, e=e, k=k)}    %lim = stablehlo.constant dense<7.000000e+00> : tensor<bf16>
+    %nlim = stablehlo.constant dense<-7.000000e+00> : tensor<bf16>
+    %alpha = stablehlo.constant dense<1.703130e+00> : tensor<{t}x{e}x{f}xbf16>
+    %one = stablehlo.constant dense<1.000000e+00> : tensor<bf16>
+    %16 = stablehlo.dot_general %arg0, %arg2, contracting_dims = [1] x [2] : (tensor<{t}x{d}xbf16>, tensor<{e}x{f2}x{d}xbf16>) -> tensor<{t}x{e}x{f2}xbf16>
+    %17 = stablehlo.broadcast_in_dim %arg3, dims = [1, 2] : (tensor<{e}x{f2}xbf16>) -> tensor<{t}x{e}x{f2}xbf16>
+    %18 = stablehlo.add %16, %17 : tensor<{t}x{e}x{f2}xbf16>
+    %19 = stablehlo.slice %18 [0:{t}, 0:{e}, 0:{f2}:2] : (tensor<{t}x{e}x{f2}xbf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %20 = stablehlo.slice %18 [0:{t}, 0:{e}, 1:{f2}:2] : (tensor<{t}x{e}x{f2}xbf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %21 = stablehlo.broadcast_in_dim %lim, dims = [] : (tensor<bf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %22 = stablehlo.minimum %19, %21 : tensor<{t}x{e}x{f}xbf16>
+    %23 = stablehlo.clamp %nlim, %20, %lim : (tensor<bf16>, tensor<{t}x{e}x{f}xbf16>, tensor<bf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %24 = stablehlo.multiply %22, %alpha : tensor<{t}x{e}x{f}xbf16>
+    %25 = stablehlo.logistic %24 : tensor<{t}x{e}x{f}xbf16>
+    %26 = stablehlo.multiply %22, %25 : tensor<{t}x{e}x{f}xbf16>
+    %27 = stablehlo.broadcast_in_dim %one, dims = [] : (tensor<bf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %28 = stablehlo.add %23, %27 : tensor<{t}x{e}x{f}xbf16>
+    %29 = stablehlo.multiply %28, %26 : tensor<{t}x{e}x{f}xbf16>
+    %30 = stablehlo.transpose %29, dims = [1, 0, 2] : (tensor<{t}x{e}x{f}xbf16>) -> tensor<{e}x{t}x{f}xbf16>
+    %31 = stablehlo.dot_general %30, %arg4, batching_dims = [0] x [0], contracting_dims = [2] x [2] : (tensor<{e}x{t}x{f}xbf16>, tensor<{e}x{d}x{f}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %32 = stablehlo.broadcast_in_dim %arg5, dims = [0, 2] : (tensor<{e}x{d}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %33 = stablehlo.add %31, %32 : tensor<{e}x{t}x{d}xbf16>
+    %34 = stablehlo.convert %11 : (tensor<{t}x{e}xf32>) -> tensor<{t}x{e}xbf16>
+    %35 = stablehlo.broadcast_in_dim %34, dims = [1, 0] : (tensor<{t}x{e}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %36 = stablehlo.multiply %33, %35 : tensor<{e}x{t}x{d}xbf16>
+    %37 = stablehlo.reduce(%36 init: %cst_0) applies stablehlo.add across dimensions = [0] : (tensor<{e}x{t}x{d}xbf16>, tensor<bf16>) -> tensor<{t}x{d}xbf16>
+    return %37 : tensor<{t}x{d}xbf16>
+  }}
+}}
+"""
+
+
+def moe_glu_bias_inputs(t=6, d=64, e=4, f=64, seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn((t, d), generator=g) * 0.5).to(torch.bfloat16)
+    logits = torch.randn((t, e), generator=g)
+    w1 = (torch.randn((e, 2 * f, d), generator=g) * 0.1).to(torch.bfloat16)
+    b1 = (torch.randn((e, 2 * f), generator=g) * 0.1).to(torch.bfloat16)
+    w2 = (torch.randn((e, d, f), generator=g) * 0.1).to(torch.bfloat16)
+    b2 = (torch.randn((e, d), generator=g) * 0.1).to(torch.bfloat16)
+    return [a.to(device) for a in (x, logits, w1, b1, w2, b2)]
+
+
+def moe_program_gelu_quant(t=6, d=64, e=4, f=64, gs=32, k=2):
+    """Quantized experts (int8 codes, group scales) with a two-dot tanh-GELU feed-forward per
+    expert and a per-expert output scale: `down(gelu(up(x))) * gain[e]`. Not the SwiGLU shape."""
+    dg, fg = d // gs, f // gs
+    return f"""
+module @jit_moe_gelu {{
+  func.func public @main(%arg0: tensor<{t}x{d}xbf16>, %arg1: tensor<{t}x{e}xf32>, %arg2: tensor<{e}x{f}x{d}xi8>, %arg3: tensor<{e}x{f}x{dg}xbf16>, %arg4: tensor<{e}x{d}x{f}xi8>, %arg5: tensor<{e}x{d}x{fg}xbf16>, %arg6: tensor<{e}xbf16>) -> (tensor<{t}x{d}xbf16>) {{
+{_ROUTER.format(t=t, e=e, k=k)}    %half = stablehlo.constant dense<5.000000e-01> : tensor<bf16>
+    %c1 = stablehlo.constant dense<4.467770e-02> : tensor<bf16>
+    %c2 = stablehlo.constant dense<7.968750e-01> : tensor<bf16>
+    %one = stablehlo.constant dense<1.000000e+00> : tensor<bf16>
+    %12 = stablehlo.convert %arg2 : (tensor<{e}x{f}x{d}xi8>) -> tensor<{e}x{f}x{d}xbf16>
+    %13 = stablehlo.broadcast_in_dim %arg3, dims = [0, 1, 2] : (tensor<{e}x{f}x{dg}xbf16>) -> tensor<{e}x{f}x{dg}x{gs}xbf16>
+    %14 = stablehlo.reshape %13 : (tensor<{e}x{f}x{dg}x{gs}xbf16>) -> tensor<{e}x{f}x{d}xbf16>
+    %15 = stablehlo.multiply %12, %14 : tensor<{e}x{f}x{d}xbf16>
+    %16 = stablehlo.dot_general %arg0, %15, contracting_dims = [1] x [2] : (tensor<{t}x{d}xbf16>, tensor<{e}x{f}x{d}xbf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %h = stablehlo.broadcast_in_dim %half, dims = [] : (tensor<bf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %k1 = stablehlo.broadcast_in_dim %c1, dims = [] : (tensor<bf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %k2 = stablehlo.broadcast_in_dim %c2, dims = [] : (tensor<bf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %o = stablehlo.broadcast_in_dim %one, dims = [] : (tensor<bf16>) -> tensor<{t}x{e}x{f}xbf16>
+    %17 = stablehlo.multiply %16, %16 : tensor<{t}x{e}x{f}xbf16>
+    %18 = stablehlo.multiply %17, %16 : tensor<{t}x{e}x{f}xbf16>
+    %19 = stablehlo.multiply %18, %k1 : tensor<{t}x{e}x{f}xbf16>
+    %20 = stablehlo.add %16, %19 : tensor<{t}x{e}x{f}xbf16>
+    %21 = stablehlo.multiply %20, %k2 : tensor<{t}x{e}x{f}xbf16>
+    %22 = stablehlo.tanh %21 : tensor<{t}x{e}x{f}xbf16>
+    %23 = stablehlo.add %22, %o : tensor<{t}x{e}x{f}xbf16>
+    %24 = stablehlo.multiply %16, %h : tensor<{t}x{e}x{f}xbf16>
+    %25 = stablehlo.multiply %24, %23 : tensor<{t}x{e}x{f}xbf16>
+    %26 = stablehlo.transpose %25, dims = [1, 0, 2] : (tensor<{t}x{e}x{f}xbf16>) -> tensor<{e}x{t}x{f}xbf16>
+    %27 = stablehlo.convert %arg4 : (tensor<{e}x{d}x{f}xi8>) -> tensor<{e}x{d}x{f}xbf16>
+    %28 = stablehlo.broadcast_in_dim %arg5, dims = [0, 1, 2] : (tensor<{e}x{d}x{fg}xbf16>) -> tensor<{e}x{d}x{fg}x{gs}xbf16>
+    %29 = stablehlo.reshape %28 : (tensor<{e}x{d}x{fg}x{gs}xbf16>) -> tensor<{e}x{d}x{f}xbf16>
+    %30 = stablehlo.multiply %27, %29 : tensor<{e}x{d}x{f}xbf16>
+    %31 = stablehlo.dot_general %26, %30, batching_dims = [0] x [0], contracting_dims = [2] x [2] : (tensor<{e}x{t}x{f}xbf16>, tensor<{e}x{d}x{f}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %32 = stablehlo.broadcast_in_dim %arg6, dims = [0] : (tensor<{e}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %33 = stablehlo.multiply %31, %32 : tensor<{e}x{t}x{d}xbf16>
+    %34 = stablehlo.convert %11 : (tensor<{t}x{e}xf32>) -> tensor<{t}x{e}xbf16>
+    %35 = stablehlo.broadcast_in_dim %34, dims = [1, 0] : (tensor<{t}x{e}xbf16>) -> tensor<{e}x{t}x{d}xbf16>
+    %36 = stablehlo.multiply %33, %35 : tensor<{e}x{t}x{d}xbf16>
+    %37 = stablehlo.reduce(%36 init: %cst_0) applies stablehlo.add across dimensions = [0] : (tensor<{e}x{t}x{d}xbf16>, tensor<bf16>) -> tensor<{t}x{d}xbf16>
+    return %37 : tensor<{t}x{d}xbf16>
+  }}
+}}
+"""
+
+
+def moe_gelu_quant_inputs(t=6, d=64, e=4, f=64, gs=32, seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn((t, d), generator=g) * 0.5).to(torch.bfloat16)
+    logits = torch.randn((t, e), generator=g)
+    cu = torch.randint(-8, 8, (e, f, d), generator=g, dtype=torch.int8)
+    su = (torch.rand((e, f, d // gs), generator=g) * 0.02 + 0.01).to(torch.bfloat16)
+    cd = torch.randint(-8, 8, (e, d, f), generator=g, dtype=torch.int8)
+    sd = (torch.rand((e, d, f // gs), generator=g) * 0.02 + 0.01).to(torch.bfloat16)
+    gain = (torch.rand((e,), generator=g) + 0.5).to(torch.bfloat16)
+    return [a.to(device) for a in (x, logits, cu, su, cd, sd, gain)]

@@ -107,6 +107,26 @@ def test_dense_float_moe_layer_becomes_the_gathered_block():
         assert st.moe[0].gate.packs[0].w is first                  # not rebuilt for the same buffers
 
 
+def test_general_expert_regions_run_over_the_routed_pairs():
+    """Expert regions that are not the SwiGLU shape, planned node by node in pair space
+    (`pair_plan`): a gpt-oss-like float block (one interleaved gate/up projection, per-expert
+    biases, clamps, strided slices) on `qmm_ragged_mm`, and quantized experts with a tanh-GELU and
+    a per-expert gain on `qmm_ragged_dot`. Same gate as every fused program."""
+    from metaljax_b200 import moe, moe_recognizer
+    from programs import moe_glu_bias_inputs, moe_gelu_quant_inputs, moe_program_glu_bias, moe_program_gelu_quant
+    for t, d, e, f in ((6, 64, 4, 64), (48, 128, 8, 192)):
+        moe.reset_stats()
+        it = _gate(moe_program_glu_bias(t, d, e, f), moe_glu_bias_inputs(t, d, e, f, seed=t, device=DEV))
+        st = it._qmm
+        assert isinstance(st.moe[0], moe_recognizer.ExpertRegion) and st.moe[0].verified
+        assert moe.stats()["ragged_dot"] == 2                       # one grouped product per dot of the region
+        moe.reset_stats()
+        it = _gate(moe_program_gelu_quant(t, d, e, f), moe_gelu_quant_inputs(t, d, e, f, seed=t + 1, device=DEV))
+        st = it._qmm
+        assert isinstance(st.moe[0], moe_recognizer.ExpertRegion) and len(st.matches) == 2
+        assert moe.stats()["ragged_dot"] == 2
+
+
 def test_expert_stack_packs_in_row_blocks_within_a_memory_bound():
     """A [32, 5760, 2880] MXFP4 expert weight (the shape the reference's pack-transient notes
     measure, notes/qmm-pack-transient-2026-08.md:100-109): its reconstruction chain evaluated
