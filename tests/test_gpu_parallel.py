@@ -71,6 +71,10 @@ def _worker(rank, world, port, ret):
             y2 = peer(to_torch(x, dev), torch.from_numpy(idx).to(dev), torch.from_numpy(wts).to(dev))
             assert peer._peer, peer._peer_error
             assert torch.equal(y2, y), (call, (y2.float() - y.float()).abs().max().item())
+        # every pair of every rank to the experts of rank 0: the other rank receives nothing
+        idx0 = np.tile(np.array([[0, 1]], dtype=idx.dtype), (t, 1))
+        args0 = (to_torch(x, dev), torch.from_numpy(idx0).to(dev), torch.from_numpy(wts).to(dev))
+        assert torch.equal(peer(*args0), moe(*args0))
         torch.cuda.synchronize(dev)
         assert _lib.poll_status() == 0
         stage = "expert-parallel over peer memory done"
