@@ -125,8 +125,7 @@ decode_attention_kernel(const AttnParams p) {
   const int piece = tid % kPieces, sub = tid / kPieces;
   const int spos = tid / kTPP, part = tid % kTPP;    // score phase: position within the chunk, share of its row
   uint4 kr[kMine], vr[kVals];
-  auto request = [&](int64_t c0) {
-    const int64_t pp = c0 + spos;
+  auto request_v = [&](int64_t c0) {
     const int chunk_len = static_cast<int>((hi - c0 < kChunk) ? hi - c0 : kChunk);
 #pragma unroll
     for (int u = 0; u < kVals; ++u) {
@@ -134,13 +133,19 @@ decode_attention_kernel(const AttnParams p) {
       vr[u] = make_uint4(0u, 0u, 0u, 0u);
       if (i < chunk_len && c0 + i != p.pos) vr[u] = __ldg(reinterpret_cast<const uint4*>(vc + (c0 + i) * HD) + piece);
     }
+  };
+  auto request_k = [&](int64_t c0) {
+    const int64_t pp = c0 + spos;
 #pragma unroll
     for (int u = 0; u < kMine; ++u) {
       kr[u] = make_uint4(0u, 0u, 0u, 0u);
       if (pp < hi && pp != p.pos) kr[u] = __ldg(reinterpret_cast<const uint4*>(kc + pp * HD) + u * kTPP + part);
     }
   };
-  if (lo < hi) request(lo);
+  if (lo < hi) {
+    request_v(lo);
+    request_k(lo);
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   QMM_TRACE(trace, 1);
 
@@ -184,11 +189,10 @@ decode_attention_kernel(const AttnParams p) {
   }
   for (int64_t c0 = lo; c0 < hi; c0 += kChunk) {
     // scores: kTPP threads <-> position. This thread's share of its key row and its value rows of
-    // the chunk were requested together (one round trip to memory serves both; the first chunk's
-    // before the wait)
+    // the chunk are already on their way (the first chunk's since before the wait, a later one's
+    // since the registers that hold them were last read)
     const int64_t pp = c0 + spos;
     const int chunk_len = static_cast<int>((hi - c0 < kChunk) ? hi - c0 : kChunk);
-    if (c0 != lo) request(c0);
     float s[REP];
 #pragma unroll
     for (int h = 0; h < REP; ++h) s[h] = 0.0f;
@@ -215,6 +219,8 @@ decode_attention_kernel(const AttnParams p) {
         }
       }
     }
+    // the key registers are free: the next chunk's keys travel under the rest of this one
+    if (c0 + kChunk < hi) request_k(c0 + kChunk);
     // the position's kTPP shares (adjacent lanes)
 #pragma unroll
     for (int h = 0; h < REP; ++h)
@@ -265,6 +271,7 @@ decode_attention_kernel(const AttnParams p) {
         }
       }
     }
+    if (c0 + kChunk < hi) request_v(c0 + kChunk);  // ... and its values under its score phase
     __syncthreads();                               // prob may be overwritten
   }
 

@@ -620,6 +620,8 @@ def test_gather_mm_float_experts_in_router_order():
     (64, 14336, 512, 128, "f16", "f16", None),           # long K
     (48, 2048, 40000, 64, "bf16", "f32", None),          # more tiles than SMs (persistent walk), wide tables
     (20, 64, 256, 64, "bf16", "bf16", None),             # a single K block
+    (64, 1024, 28672, 64, "bf16", "bf16", None),         # 224 tiles on 148 SMs: the last wave's K blocks as one flat range
+    (32, 4096, 28672 + 128 * 30, 64, "bf16", "bf16", "f32"),   # ... a fuller last wave, ranges across tile boundaries
 ])
 def test_few_dozen_rows_take_the_tensor_core_kernel(m, k, n, gs, xdt, tdt, ydt):
     """17..64 rows (the decode step at a batch of a few dozen): the tensor-core kernel with narrow
