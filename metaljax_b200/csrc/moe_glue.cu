@@ -97,8 +97,9 @@ __global__ void routed_sum_kernel(const uint4* __restrict__ rows, const int64_t*
 using namespace qmm;
 
 extern "C" int qmm_moe_silu_mul(const void* gate, const void* up, void* out, int64_t elements, int dtype, void* stream) {
-  if (!gate || !up || !out) return fail(QMM_ERR_NULL, "moe_silu_mul: null pointer");
   if (elements < 0 || elements % 8) return fail(QMM_ERR_SHAPE, "moe_silu_mul: element count must be a multiple of 8");
+  if (elements == 0) return QMM_OK;                     // (an expert-parallel rank that was sent no rows: empty arrays have no address)
+  if (!gate || !up || !out) return fail(QMM_ERR_NULL, "moe_silu_mul: null pointer");
   if (dtype != QMM_BF16 && dtype != QMM_F16) return fail(QMM_ERR_DTYPE, "moe_silu_mul: bf16 or f16");
   if ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) & 15)
     return fail(QMM_ERR_LAYOUT, "moe_silu_mul: pointers must be 16-byte aligned");
@@ -120,9 +121,10 @@ extern "C" int qmm_moe_silu_mul(const void* gate, const void* up, void* out, int
 
 extern "C" int qmm_moe_routed_sum(const void* rows, const int64_t* row_of_pair, const float* weights, void* out,
                                   int64_t tokens, int k, int64_t width, int64_t total_rows, int dtype, void* stream) {
-  if (!rows || !row_of_pair || !weights || !out) return fail(QMM_ERR_NULL, "moe_routed_sum: null pointer");
-  if (tokens < 0 || k < 1 || width < 8 || width % 8 || total_rows < 1)
+  if (tokens < 0 || k < 1 || width < 8 || width % 8 || total_rows < (tokens ? 1 : 0))
     return fail(QMM_ERR_SHAPE, "moe_routed_sum: width must be a positive multiple of 8, k >= 1");
+  if (tokens == 0) return QMM_OK;
+  if (!rows || !row_of_pair || !weights || !out) return fail(QMM_ERR_NULL, "moe_routed_sum: null pointer");
   if (dtype != QMM_BF16 && dtype != QMM_F16) return fail(QMM_ERR_DTYPE, "moe_routed_sum: bf16 or f16");
   if ((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(out)) & 15)
     return fail(QMM_ERR_LAYOUT, "moe_routed_sum: pointers must be 16-byte aligned");

@@ -155,7 +155,7 @@ _GLUE_DTYPES = (torch.bfloat16, torch.float16)
 
 def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """`silu(gate) * up` in one pass (the SwiGLU between the grouped products)."""
-    if gate.dtype not in _GLUE_DTYPES or gate.numel() % 8 or gate.shape != up.shape:
+    if gate.dtype not in _GLUE_DTYPES or gate.numel() % 8 or gate.shape != up.shape or gate.numel() == 0:
         return torch.nn.functional.silu(gate) * up
     gate, up = gate.contiguous(), up.contiguous()
     out = torch.empty_like(gate)

@@ -124,3 +124,25 @@ def test_counts_that_never_arrive_time_out_and_the_library_recovers():
     _lib.check(lib.qmm_ep_dispatch(ctypes.byref(one.ex), x.data_ptr(), tokens, width * 2, tok.contiguous().data_ptr(),
                                    sizes.data_ptr(), pairs, full.data_ptr(), _lib.stream_ptr(x)))
     assert torch.equal(one.recv[0].view(torch.bfloat16).view(pairs, width), x.index_select(0, tok))
+
+
+def test_a_rank_that_is_sent_no_rows():
+    """The collective form of the block on a rank whose experts nobody chose: empty arrays (no
+    address) through the grouped products and the glue kernels."""
+    import numpy as np
+    from helpers import affine_case, to_torch
+    rng = np.random.default_rng(0)
+    e, d, f = 2, 128, 256
+    w1 = tuple(to_torch(a, DEV) for a in affine_case(rng, f, d, 64, 4, "bf16", lead=(e,))[1:])
+    w2 = tuple(to_torch(a, DEV) for a in affine_case(rng, d, f, 64, 4, "bf16", lead=(e,))[1:])
+    rows = torch.empty((0, d), device=DEV, dtype=torch.bfloat16)
+    sizes = torch.zeros((e,), device=DEV, dtype=torch.int32)
+    gate = moe.ragged_dot(rows, *w1, sizes)
+    up = moe.ragged_dot(rows, *w1, sizes)
+    act = moe.silu_mul(gate, up)
+    down = moe.ragged_dot(act, *w2, sizes)
+    assert tuple(gate.shape) == (0, f) and tuple(act.shape) == (0, f) and tuple(down.shape) == (0, d)
+    out = moe.routed_sum(torch.zeros((8, d), device=DEV, dtype=torch.bfloat16), torch.arange(0, device=DEV),
+                         torch.zeros((0, 2), device=DEV), 0, 2)
+    assert tuple(out.shape) == (0, d)
+    assert _lib.poll_status() == 0

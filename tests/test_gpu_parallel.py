@@ -32,7 +32,7 @@ def _worker(rank, world, port, ret):
     dev = torch.device("cuda", rank)
     # a rank that fails leaves the others in a collective: a short timeout ends those with an error
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
-                            timeout=datetime.timedelta(seconds=90))
+                            timeout=datetime.timedelta(seconds=45))
     stage = "start"
     try:
         rng = np.random.default_rng(0)                   # identical draws on every rank
@@ -129,7 +129,7 @@ def test_two_gpu_ranks():
     procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
     for p in procs:
         p.start()
-    deadline = time.time() + 300
+    deadline = time.time() + 180
     for p in procs:
         p.join(max(1.0, deadline - time.time()))
     stuck = [p for p in procs if p.is_alive()]

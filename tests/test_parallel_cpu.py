@@ -85,6 +85,15 @@ def _worker(rank, world, port, what, ret):
             down = O.gather_qmm_exact(act[:, None, :], *packs[2], np.arange(len(tidx)), eidx)[:, 0]
             want = O.moe_combine_exact(down, wts)
             np.testing.assert_allclose(y.numpy(), want, rtol=2e-4, atol=2e-4)
+            # every pair of every rank to the experts of rank 0: rank 1 is sent nothing
+            idx0 = np.tile(np.array([[0, 1]], dtype=idx.dtype), (len(x), 1))
+            y0 = moe(to_torch(x), torch.from_numpy(idx0), torch.from_numpy(wts))
+            eidx0 = idx0.reshape(-1)
+            gate = O.gather_qmm_exact(x3, *packs[0], tidx, eidx0)[:, 0]
+            up = O.gather_qmm_exact(x3, *packs[1], tidx, eidx0)[:, 0]
+            act = ((gate / (1 + np.exp(-gate))) * up).astype(np.float32)
+            down = O.gather_qmm_exact(act[:, None, :], *packs[2], np.arange(len(tidx)), eidx0)[:, 0]
+            np.testing.assert_allclose(y0.numpy(), O.moe_combine_exact(down, wts), rtol=2e-4, atol=2e-4)
         ret[rank] = "ok"
     except Exception as exc:                             # surfaced by the parent
         ret[rank] = repr(exc)
