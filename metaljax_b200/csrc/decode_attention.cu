@@ -18,6 +18,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "../../include/qmm_decode.h"
 #include "qmm_internal.h"
 
@@ -408,6 +410,355 @@ int launch_rep(const AttnParams& p, int rep, int64_t batch, cudaStream_t stream)
   return fail(QMM_ERR_UNSUPPORTED, "decode_attention: %d query heads per key/value head (1, 2, 4 or 8)", rep);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for longer slices (several sequences at once: batch x key/value heads fill
+// the machine, so a CTA walks hundreds of positions): bandwidth instead of latency. Key and
+// value rows stream through a three-stage ring of 64-position chunks (`cp.async`, 16-byte pieces,
+// XOR-swizzled so that `ldmatrix` reads are conflict free); scores and the value sum run on
+// `mma.sync.m16n8k16` with the query heads of the group as the A rows (at most 8 of 16 used --
+// the tensor work is tiny, the point is that a chunk costs a few dozen instructions per warp
+// instead of thousands of FMAs). Four warps take 16 positions of a chunk each and keep their own
+// running (max, sum, weighted values); they are merged once at the end, together with the decode
+// position's own term, which comes from shared memory and never from the cache. Slices publish
+// and combine exactly as in the kernel above.
+constexpr int kMmaChunk = 64, kMmaThreads = 128, kMmaStages = 3;
+
+__device__ __forceinline__ uint32_t attn_smem_u32(const void* q) { return static_cast<uint32_t>(__cvta_generic_to_shared(q)); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;                     // 0: the 16 bytes are written as zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldsm4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+// d += a (16 x 16, rows 8..15 zero) * b (16 x 8)
+__device__ __forceinline__ void mma_rows8(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  const uint32_t zero = 0u;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(zero), "r"(a2), "r"(zero), "r"(b0), "r"(b1));
+}
+
+template <int HD, int REP>
+__global__ void __launch_bounds__(kMmaThreads)
+decode_attention_mma_kernel(const AttnParams p) {
+  static_assert(REP <= 8, "the query heads of a group are the first eight A rows");
+  constexpr int kRowBytes = HD * 2, kPieces = HD / 8;
+  constexpr int kTensorBytes = kMmaChunk * kRowBytes;           // one chunk of keys (or of values)
+  constexpr int kStageBytes = 2 * kTensorBytes;
+  constexpr int kStat = HD + 4;
+  constexpr int kWarps = kMmaThreads / 32;
+  extern __shared__ __align__(128) uint8_t attn_smem[];
+  uint8_t* stages = attn_smem;                                       // [kMmaStages][K chunk | V chunk]
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(attn_smem + kMmaStages * kStageBytes);   // [8][HD], rotated
+  float* knew = reinterpret_cast<float*>(q_s + 8 * HD);              // [HD] the decode position's key (rotated) ...
+  float* vnew = knew + HD;                                           // ... and value
+  float* s_self = vnew + HD;                                         // [8]
+  float* pm = s_self + 8;                                            // [kWarps][8] the warps' maxima, sums
+  float* pl = pm + kWarps * 8;
+  float* wsplit = pl + kWarps * 8;                                   // [REP][64] (combine)
+  float* denom = wsplit + REP * 64;                                  // [REP]
+  float* pO = reinterpret_cast<float*>(stages);                      // [kWarps][REP][HD]: reuses the ring after the walk
+  __shared__ int is_last;
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int total_heads = p.heads + 2 * p.kv_heads;
+  const __nv_bfloat16* row = p.qkv + static_cast<int64_t>(b) * total_heads * HD;
+  const int64_t len = p.pos + 1;
+  const int64_t per = (len + p.splits - 1) / p.splits;
+  const int64_t lo = split * per, hi = (lo + per < len) ? lo + per : len;
+  __nv_bfloat16* kc = p.k_cache + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.ctx * HD;
+  __nv_bfloat16* vc = p.v_cache + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.ctx * HD;
+  const int nchunks = lo < hi ? static_cast<int>((hi - lo + kMmaChunk - 1) / kMmaChunk) : 0;
+
+  // chunk `ci` into its ring slot: every thread copies its share of the 16-byte pieces; rows past
+  // the slice and the decode position's own row (not in the cache yet) arrive as zeros
+  auto load_chunk = [&](int ci) {
+    if (ci < nchunks) {
+      uint8_t* st = stages + (ci % kMmaStages) * kStageBytes;
+      const int64_t pos0 = lo + static_cast<int64_t>(ci) * kMmaChunk;
+#pragma unroll
+      for (int i = 0; i < kMmaChunk * kPieces / kMmaThreads; ++i) {
+        const int q = tid + kMmaThreads * i, r = q / kPieces, c = q % kPieces;
+        const int64_t pos = pos0 + r;
+        const bool valid = pos < hi && pos != p.pos;
+        const int64_t from = (valid ? pos : lo) * HD + c * 8;
+        const uint32_t off = r * kRowBytes + ((c ^ (r & 7)) << 4);
+        cp_async16(attn_smem_u32(st + off), kc + from, valid);
+        cp_async16(attn_smem_u32(st + kTensorBytes + off), vc + from, valid);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // the cache holds earlier positions only: the first chunks travel under the predecessor's tail
+  load_chunk(0);
+  load_chunk(1);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- rotary embedding of the group's queries and of the key; the value ----
+  constexpr int kHalf = HD / 2;
+  const float inv_sqrt = rsqrtf(static_cast<float>(HD));
+  for (int i = tid; i < (REP + 1) * kHalf; i += kMmaThreads) {
+    const int h = i / kHalf, j = i - h * kHalf;
+    const __nv_bfloat16* src = h < REP ? row + (kvh * REP + h) * HD : row + (p.heads + kvh) * HD;
+    const float a = __bfloat162float(src[j]), c = __bfloat162float(src[j + kHalf]);
+    float sn, cs;
+    const float freq = exp2f(-2.0f * static_cast<float>(j) / static_cast<float>(HD) * log2f(p.theta));
+    sincosf(static_cast<float>(p.pos) * freq, &sn, &cs);
+    const __nv_bfloat16 rlo = __float2bfloat16_rn(a * cs - c * sn), rhi = __float2bfloat16_rn(c * cs + a * sn);
+    if (h < REP) {
+      q_s[h * HD + j] = rlo;
+      q_s[h * HD + j + kHalf] = rhi;
+    } else {
+      knew[j] = __bfloat162float(rlo);
+      knew[j + kHalf] = __bfloat162float(rhi);
+    }
+  }
+  for (int i = tid; i < (8 - REP) * HD; i += kMmaThreads) q_s[REP * HD + i] = __float2bfloat16_rn(0.0f);
+  for (int i = tid; i < HD; i += kMmaThreads) vnew[i] = __bfloat162float(row[(p.heads + p.kv_heads + kvh) * HD + i]);
+  __syncthreads();
+  const bool owns = p.pos >= lo && p.pos < hi;
+  if (owns) {
+    for (int i = tid; i < HD; i += kMmaThreads) {
+      kc[p.pos * HD + i] = __float2bfloat16_rn(knew[i]);
+      vc[p.pos * HD + i] = __float2bfloat16_rn(vnew[i]);
+    }
+    // the decode position's own score per head (one warp per head, heads w, w + 4)
+    for (int h = warp; h < REP; h += kWarps) {
+      float acc = 0.0f;
+      for (int d = lane; d < HD; d += 32) acc = fmaf(__bfloat162float(q_s[h * HD + d]), knew[d], acc);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) s_self[h] = acc * inv_sqrt;
+    }
+  }
+  // this lane's query fragments: A rows g (a0: dims 2t, 2t+1 of a 16-wide step; a2: the same + 8)
+  uint32_t qa[HD / 16][2];
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+    qa[ks][0] = *reinterpret_cast<const uint32_t*>(q_s + g * HD + ks * 16 + t * 2);
+    qa[ks][1] = *reinterpret_cast<const uint32_t*>(q_s + g * HD + ks * 16 + 8 + t * 2);
+  }
+
+  float m_run = -INFINITY, l_run = 0.0f;            // of query head g (the four lanes of a row agree)
+  float o[HD / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < HD / 8; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nt][e] = 0.0f;
+  const int lm = lane >> 3, lr = lane & 7;          // ldmatrix: this lane addresses row lr of matrix lm
+
+  for (int ci = 0; ci < nchunks; ++ci) {
+    asm volatile("cp.async.wait_group 1;" ::: "memory");      // chunk ci has landed (this thread's pieces)
+    __syncthreads();                                           // everybody's pieces; and chunk ci - 1 is consumed
+    load_chunk(ci + 2);                                        // into the slot chunk ci - 1 used
+    const uint32_t ks_base = attn_smem_u32(stages + (ci % kMmaStages) * kStageBytes);
+    const uint32_t vs_base = ks_base + kTensorBytes;
+    // scores of this warp's 16 positions: two 8-position tiles
+    float sc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+    {
+      const int r = warp * 16 + (lm >> 1) * 8 + lr;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        uint32_t kb[4];
+        ldsm4(kb, ks_base + r * kRowBytes + ((((ks * 2 + (lm & 1)) ^ (r & 7))) << 4));
+        mma_rows8(sc[0], qa[ks][0], qa[ks][1], kb[0], kb[1]);
+        mma_rows8(sc[1], qa[ks][0], qa[ks][1], kb[2], kb[3]);
+      }
+    }
+    const int64_t pos0 = lo + static_cast<int64_t>(ci) * kMmaChunk + warp * 16 + t * 2;
+    float cmax = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int64_t pos = pos0 + j * 8 + e;
+        sc[j][e] = (pos < hi && pos != p.pos) ? sc[j][e] * inv_sqrt : -INFINITY;
+        cmax = fmaxf(cmax, sc[j][e]);
+      }
+    cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 1));
+    cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, 2));
+    const float m_new = fmaxf(m_run, cmax);
+    const float alpha = (m_run == -INFINITY) ? 0.0f : __expf(m_run - m_new);
+    float pr[2][2], csum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pr[j][e] = (sc[j][e] == -INFINITY) ? 0.0f : __expf(sc[j][e] - m_new);
+        csum += pr[j][e];
+      }
+    csum += __shfl_xor_sync(0xffffffffu, csum, 1);
+    csum += __shfl_xor_sync(0xffffffffu, csum, 2);
+    l_run = l_run * alpha + csum;
+    m_run = m_new;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+      o[nt][0] *= alpha;
+      o[nt][1] *= alpha;
+    }
+    // weighted values: the probabilities are the A rows now (k = this warp's 16 positions)
+    const __nv_bfloat162 p0 = __floats2bfloat162_rn(pr[0][0], pr[0][1]), p1 = __floats2bfloat162_rn(pr[1][0], pr[1][1]);
+    const uint32_t pa0 = *reinterpret_cast<const uint32_t*>(&p0), pa2 = *reinterpret_cast<const uint32_t*>(&p1);
+    {
+      const int r = warp * 16 + (lm & 1) * 8 + lr;
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t vb[4];
+        ldsm4_trans(vb, vs_base + r * kRowBytes + ((((dp * 2 + (lm >> 1)) ^ (r & 7))) << 4));
+        mma_rows8(o[2 * dp], pa0, pa2, vb[0], vb[1]);
+        mma_rows8(o[2 * dp + 1], pa0, pa2, vb[2], vb[3]);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();                                   // the ring is free: it holds the warps' results from here on
+
+  // ---- the four warps' results and the decode position's own term into one (max, sum, values) ----
+  if (g < REP) {
+    if (t == 0) {
+      pm[warp * 8 + g] = m_run;
+      pl[warp * 8 + g] = l_run;
+    }
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt)
+      *reinterpret_cast<float2*>(pO + (warp * REP + g) * HD + nt * 8 + t * 2) = make_float2(o[nt][0], o[nt][1]);
+  }
+  __syncthreads();
+  float* mine = p.part + ((static_cast<int64_t>(b) * p.kv_heads + kvh) * p.splits + split) * REP * kStat;
+  for (int i = tid; i < REP * HD; i += kMmaThreads) {
+    const int h = i / HD, d = i - h * HD;
+    float mx = owns ? s_self[h] : -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, pm[w * 8 + h]);
+    float num = 0.0f, den = 0.0f;
+    if (mx != -INFINITY) {
+      if (owns) {
+        const float ws = __expf(s_self[h] - mx);
+        num = ws * vnew[d];
+        den = ws;
+      }
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float mw = pm[w * 8 + h];
+        const float ww = (mw == -INFINITY) ? 0.0f : __expf(mw - mx);
+        num = fmaf(ww, pO[(w * REP + h) * HD + d], num);
+        den = fmaf(ww, pl[w * 8 + h], den);
+      }
+    }
+    mine[h * kStat + d] = num;
+    if (d == 0) {
+      mine[h * kStat + HD] = mx;
+      mine[h * kStat + HD + 1] = den;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  uint32_t* counter = p.counters + b * p.kv_heads + kvh;
+  if (tid == 0) {
+    const bool last = atomicAdd(counter, 1u) == static_cast<uint32_t>(p.splits - 1);
+    if (last) *counter = 0;
+    is_last = last;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+
+  // ---- the last slice of this (row, head) to finish combines them all ----
+  const float* all = p.part + (static_cast<int64_t>(b) * p.kv_heads + kvh) * p.splits * REP * kStat;
+  for (int h = warp; h < REP; h += kWarps) {
+    float ms[2], ls[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int sp = lane + 32 * u;
+      ms[u] = sp < p.splits ? __ldcg(all + (sp * REP + h) * kStat + HD) : -INFINITY;
+      ls[u] = sp < p.splits ? __ldcg(all + (sp * REP + h) * kStat + HD + 1) : 0.0f;
+    }
+    float mx = fmaxf(ms[0], ms[1]);
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
+    float den = 0.0f;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const float w = (ms[u] == -INFINITY) ? 0.0f : __expf(ms[u] - mx);
+      wsplit[h * 64 + lane + 32 * u] = w;
+      den = fmaf(w, ls[u], den);
+    }
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o2);
+    if (lane == 0) denom[h] = den;
+  }
+  __syncthreads();
+  const uint32_t stamp = p.push_world > 0
+      ? (*reinterpret_cast<const volatile uint32_t*>(p.epoch) << 10) | static_cast<uint32_t>(p.push_site + 1) : 0u;
+  for (int i = tid; i < REP * HD / 4; i += kMmaThreads) {
+    const int h = i / (HD / 4), d0 = (i - h * (HD / 4)) * 4;
+    float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int sp = 0; sp < p.splits; ++sp) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(all + (sp * REP + h) * kStat + d0));
+      const float w = wsplit[h * 64 + sp];
+      num.x = fmaf(w, v.x, num.x); num.y = fmaf(w, v.y, num.y);
+      num.z = fmaf(w, v.z, num.z); num.w = fmaf(w, v.w, num.w);
+    }
+    const float inv = 1.0f / denom[h];
+    const __nv_bfloat162 v0 = __floats2bfloat162_rn(num.x * inv, num.y * inv);
+    const __nv_bfloat162 v1 = __floats2bfloat162_rn(num.z * inv, num.w * inv);
+    const uint2 ov = make_uint2(*reinterpret_cast<const uint32_t*>(&v0), *reinterpret_cast<const uint32_t*>(&v1));
+    const int64_t col = static_cast<int64_t>(kvh * REP + h) * HD + d0;
+    if (p.out) *reinterpret_cast<uint2*>(p.out + static_cast<int64_t>(b) * p.heads * HD + col) = ov;
+    if (p.push_world > 0) {
+      const uint4 unit = make_uint4(ov.x, stamp, ov.y, stamp);
+      for (int r = 0; r < p.push_world; ++r)
+        *reinterpret_cast<uint4*>(p.push_dst[r] + b * p.push_row_bytes + col * 4) = unit;
+    }
+  }
+}
+
+template <int HD, int REP>
+int launch_attention_mma(const AttnParams& p, int64_t batch, cudaStream_t stream) {
+  constexpr size_t smem = kMmaStages * 2 * kMmaChunk * HD * 2 + 8 * HD * 2 + 2 * HD * 4 + (8 + 2 * 4 * 8 + REP * 64 + REP) * 4 + 64;
+  static bool configured[kMaxDevices] = {};
+  const int dev = current_device();
+  if (dev < 0) return QMM_ERR_DEVICE;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<HD, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.splits), static_cast<unsigned>(p.kv_heads), static_cast<unsigned>(batch));
+  cfg.blockDim = dim3(kMmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attention_mma_kernel<HD, REP>, p);
+  if (e != cudaSuccess) return fail(QMM_ERR_CUDA, "decode_attention_mma_kernel launch: %s", cudaGetErrorString(e));
+  count_launch();
+  return check_launch("decode_attention_mma_kernel");
+}
+
+template <int HD>
+int launch_rep_mma(const AttnParams& p, int rep, int64_t batch, cudaStream_t stream) {
+  switch (rep) {
+    case 1: return launch_attention_mma<HD, 1>(p, batch, stream);
+    case 2: return launch_attention_mma<HD, 2>(p, batch, stream);
+    case 4: return launch_attention_mma<HD, 4>(p, batch, stream);
+    case 8: return launch_attention_mma<HD, 8>(p, batch, stream);
+  }
+  return fail(QMM_ERR_UNSUPPORTED, "decode_attention: %d query heads per key/value head (1, 2, 4 or 8)", rep);
+}
+
 }  // namespace
 }  // namespace qmm
 
@@ -449,6 +800,15 @@ extern "C" int qmm_decode_attention(const void* qkv, void* k_cache, void* v_cach
   if (splits > (len + 127) / 128) splits = (len + 127) / 128;
   if (splits > 64) splits = 64;
   if (splits < 1) splits = 1;
+  // Slices of a few hundred positions and more (several sequences at once) take the streaming
+  // kernel, two CTAs per SM; QMM_ATTN_KERNEL=simt / mma forces one.
+  int64_t wide = 2 * device_sm_count() / (batch * kv_heads);      // (rounded down: one wave of CTAs)
+  if (wide > (len + 255) / 256) wide = (len + 255) / 256;
+  if (wide > 64) wide = 64;
+  if (wide < 1) wide = 1;
+  const char* force = getenv("QMM_ATTN_KERNEL");
+  const bool mma = force ? force[0] == 'm' : (len + splits - 1) / splits >= 256;
+  if (mma) splits = wide;
   p.splits = static_cast<int>(splits);
   const int rep = heads / kv_heads;
   const int64_t part_bytes = batch * kv_heads * 64 * rep * (head_dim + 4) * 4;
@@ -467,5 +827,6 @@ extern "C" int qmm_decode_attention(const void* qkv, void* k_cache, void* v_cach
     }
   }
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (mma) return head_dim == 128 ? launch_rep_mma<128>(p, rep, batch, st) : launch_rep_mma<64>(p, rep, batch, st);
   return head_dim == 128 ? launch_rep<128>(p, rep, batch, st) : launch_rep<64>(p, rep, batch, st);
 }

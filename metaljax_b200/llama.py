@@ -6,7 +6,8 @@ embedding -> per layer [RMSNorm, fused q/k/v linear, rotary + KV append, GQA att
 the cache, output linear, residual + RMSNorm, fused gate/up linear, SwiGLU, down linear] ->
 final norm -> lm_head -> argmax. Every linear is an int4 group-64 `quantized_matmul`; the
 element-wise glue is this package's three small CUDA kernels (include/qmm_decode.h);
-attention over the cache is torch's scaled_dot_product_attention. Nothing here runs on the CPU.
+attention over the cache is the library's own kernel (`QMM_DECODE_ATTENTION=sdpa`: torch's
+scaled_dot_product_attention). Nothing here runs on the CPU.
 
 Weights are synthetic: either packed random codes with U(0.002, 0.02) scales and
 bias = -8*scale (`weights="codes"`, what the benchmark uses), or N(0, 0.02) values quantized
@@ -303,10 +304,10 @@ class DecodeStep:
                 dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
                 if int(ok.item()) == 0:
                     self.fused = False
-        # Above one row: the rotary kernel followed by torch's scaled_dot_product_attention, which reads the
-        # cache at the HBM roofline there; QMM_DECODE_ATTENTION=own runs the single-row path's one-kernel
-        # rotary + append + attention instead (built for latency: at 64 rows it reaches about a third of that).
-        self.own_attention = not self.fused and os.environ.get("QMM_DECODE_ATTENTION", "sdpa") == "own"
+        # Above one row too, rotary + append + attention are one kernel of the library (its streaming
+        # tensor-core form once a slice of the context is a few hundred positions long);
+        # QMM_DECODE_ATTENTION=sdpa runs the rotary kernel followed by torch's scaled_dot_product_attention.
+        self.own_attention = not self.fused and os.environ.get("QMM_DECODE_ATTENTION", "own") != "sdpa"
         if self.own_attention:
             self.attn_l = torch.empty((b, self.h_l * hd), **bf)
             nbytes = _lib.lib().qmm_decode_attention_scratch_bytes(b, self.h_l, self.kv_l, hd, sh.ctx)

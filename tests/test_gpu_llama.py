@@ -110,8 +110,9 @@ def test_single_row_step_fused_against_unfused(monkeypatch):
 
 
 def test_multi_row_step_with_the_one_kernel_attention(monkeypatch):
-    """Above one row the step's attention is torch's; QMM_DECODE_ATTENTION=own swaps in the
-    library's rotary + append + attention kernel. Same logits as the float reference, the same rows appended to the cache."""
+    """Above one row the step's attention is the library's rotary + append + attention kernel;
+    QMM_DECODE_ATTENTION=sdpa swaps in the rotary kernel and torch's attention. Same logits as
+    the float reference, the same rows appended to the cache."""
     from metaljax_b200 import _lib, llama
     shape, batch = _small(), 5
     fw = llama.random_full_weights(shape, batch, DEV, seed=21)
@@ -212,12 +213,16 @@ def test_decode_linear_prologues_and_self_exchange():
 @pytest.mark.parametrize("batch,heads,kvh,hd,ctx,pos", [
     (1, 8, 2, 128, 2048, 2047), (1, 4, 4, 64, 48, 47), (3, 4, 2, 64, 300, 150), (2, 8, 1, 128, 1000, 0),
     (64, 4, 1, 128, 2048, 2047), (5, 16, 2, 64, 513, 512), (1, 32, 8, 128, 2048, 1000),
+    (7, 8, 8, 128, 700, 640), (2, 2, 1, 64, 130, 64),
 ])
-def test_decode_attention_against_rope_and_sdpa(batch, heads, kvh, hd, ctx, pos):
+@pytest.mark.parametrize("kernel", ["simt", "mma"])
+def test_decode_attention_against_rope_and_sdpa(batch, heads, kvh, hd, ctx, pos, kernel, monkeypatch):
     """The one-kernel rotary + append + attention against the rotary kernel followed by torch's
-    scaled_dot_product_attention over positions 0..pos, cache contents included."""
+    scaled_dot_product_attention over positions 0..pos, cache contents included -- both of its
+    forms: the latency kernel of short slices and the streaming tensor-core kernel of long ones."""
     import torch.nn.functional as F
     from metaljax_b200 import _lib, llama
+    monkeypatch.setenv("QMM_ATTN_KERNEL", kernel)
     g = torch.Generator(device=DEV).manual_seed(batch * 100 + heads)
     qkv = torch.randn((batch, (heads + 2 * kvh) * hd), generator=g, device=DEV).to(torch.bfloat16)
     kc = (torch.randn((batch, kvh, ctx, hd), generator=g, device=DEV) * 0.5).to(torch.bfloat16)
