@@ -214,6 +214,7 @@ def test_decode_linear_prologues_and_self_exchange():
     (1, 8, 2, 128, 2048, 2047), (1, 4, 4, 64, 48, 47), (3, 4, 2, 64, 300, 150), (2, 8, 1, 128, 1000, 0),
     (64, 4, 1, 128, 2048, 2047), (5, 16, 2, 64, 513, 512), (1, 32, 8, 128, 2048, 1000),
     (7, 8, 8, 128, 700, 640), (2, 2, 1, 64, 130, 64),
+    (64, 32, 8, 128, 2048, 2047),                         # one layer of the batch-64 step: 537 MB of cache
 ])
 @pytest.mark.parametrize("kernel", ["simt", "mma"])
 def test_decode_attention_against_rope_and_sdpa(batch, heads, kvh, hd, ctx, pos, kernel, monkeypatch):
