@@ -130,7 +130,9 @@ int qmm_decode_linear(const qmm_problem* problem, const qmm_decode_fusion* fusio
  * computes. qkv as for qmm_decode_rope_kv; out [batch, heads * head_dim] bf16 (query head i
  * attends through key/value head i / (heads / kv_heads)), or NULL when the row is only pushed.
  * head_dim 64 or 128; heads / kv_heads 1, 2, 4 or 8. The context is cut into slices that run as
- * separate CTAs; their partial results meet in `scratch`, device memory the caller provides:
+ * separate CTAs (slices of a few hundred positions and more -- many sequences at once -- take a
+ * streaming tensor-core form of the kernel, short ones a latency form; same results within
+ * rounding); their partial results meet in `scratch`, device memory the caller provides:
  * qmm_decode_attention_scratch_bytes(...) bytes, zeroed once before the first call, not shared
  * by calls that can overlap. With push_slot >= 0 the row also goes to every rank's gather slot
  * (this rank's heads are a column block of the gathered row) as exchange `push_site` of `ex`. */
