@@ -200,7 +200,8 @@ def test_real_jax_lowering_recognizes_nothing():
     checkout where that exists; the file is not redistributed."""
     import os
     import pytest
-    path = os.path.join(os.environ.get("METALJAX_REFERENCE", "/root/reference"), "tests", "data", "qwen3_prefill_shrunk.mlir")
+    beside = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+    path = os.path.join(os.environ.get("METALJAX_REFERENCE", beside), "tests", "data", "qwen3_prefill_shrunk.mlir")
     if not os.path.exists(path):
         pytest.skip("no reference checkout on this machine")
     it = recognizer.Interpreter(open(path).read())
