@@ -601,6 +601,20 @@ def moe_line(name, args, torch, dist, device, world, pk):
         exchange = os.environ.get("QMM_EP_EXCHANGE", "peer")               # "nccl": all-to-all collectives
         block = parallel.ExpertParallelMoE(w1, w3, w2, group=None, local_experts=True,
                                            capacity_pairs=tl * k if exchange == "peer" else None)
+        if exchange == "peer":
+            # one call before anything is timed: if the exchange over peer memory does not come up on
+            # every rank (no symmetric memory, a wait that ran out), every rank uses the collectives
+            good = torch.ones((), device=device, dtype=torch.int32)
+            try:
+                block(xs[0], idx, wts)
+                _lib.poll_status()
+                if not block._peer:
+                    good.zero_()
+            except Exception:                                               # noqa: BLE001 -- decided together below
+                good.zero_()
+            dist.all_reduce(good, op=dist.ReduceOp.MIN)
+            if int(good.item()) == 0:
+                block = parallel.ExpertParallelMoE(w1, w3, w2, group=None, local_experts=True)
         run = lambda x: block(x, idx, wts)                                  # noqa: E731
     else:
         run = lambda x: moe.moe_experts(x, idx, wts, w1, w3, w2)            # noqa: E731
