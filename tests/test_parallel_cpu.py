@@ -114,3 +114,57 @@ def test_two_cpu_ranks(what):
         p.join(180)
         assert not p.is_alive(), "rank did not finish"
     assert dict(ret) == {0: "ok", 1: "ok"}, dict(ret)
+
+
+def _failing_worker(rank, world, port, ret):
+    """Rank 1 fails on the host between two calls (it raises instead of joining the second one);
+    rank 0 must come back from its collective with an error, not wait for ever."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    try:
+        rng = np.random.default_rng(0)
+        e, kk, d, f, t = 4, 2, 64, 128, 6
+        packs = [affine_case(rng, f, d, 64, 4, "f32", lead=(e,))[1:], affine_case(rng, f, d, 64, 4, "f32", lead=(e,))[1:],
+                 affine_case(rng, d, f, 64, 4, "f32", lead=(e,))[1:]]
+        moe = parallel.ExpertParallelMoE(*[tuple(to_torch(a) for a in p) for p in packs], ops=OracleOps)
+        x = activations(np.random.default_rng(rank), (t, d), "f32", 0.5)
+        idx, wts = O.topk_router(np.random.default_rng(rank).standard_normal((t, e)).astype(np.float32), kk)
+        args = (to_torch(x), torch.from_numpy(idx), torch.from_numpy(wts))
+        moe(*args)                                        # a healthy first call on both ranks
+        if rank == 1:
+            ret[rank] = "left between calls"
+            return                                        # (no collective in flight: the rank just never joins again)
+        t0 = time.time()
+        try:
+            moe(*args)
+            ret[rank] = "the second call returned without its peer"
+        except Exception as exc:                          # noqa: BLE001 -- whatever the backend raises
+            ret[rank] = f"error after {time.time() - t0:.0f} s: {type(exc).__name__}"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:                                 # noqa: BLE001 -- the group is already broken on rank 0
+            pass
+
+
+def test_a_rank_that_leaves_ends_the_others_collective_with_an_error():
+    """Failure detection without touching a GPU: the failure is made on the host (a rank that
+    never joins), and the survivor's next collective ends with an error inside the process
+    group's timeout instead of hanging."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:                                       # exactly the processes started above
+        p.terminate()
+    assert not stuck, dict(ret)
+    assert ret.get(1) == "left between calls"
+    assert str(ret.get(0, "")).startswith("error after"), dict(ret)
