@@ -1,12 +1,17 @@
 """Benchmark of the fused quantized matmul and its decode-step caller on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+                    [--decode-sharding auto|rows|weights]
 
 One JSON line on stdout (rank 0). The default workload is the path that shards over GPUs: one
 decode step of a Llama-3-8B-shaped model (32 layers, d 4096, 32/8 heads, ffn 14336, vocabulary
 128256, every linear an int4 group-64 quantized matmul, bf16 KV cache of 2048 positions) at
-batch 64, the linears sharded on their output rows over the N ranks (q/k/v by head, so the KV
-cache and attention stay local) with the slices exchanged over NVLink. `value` is tokens/s of
+batch 64. Over N ranks the step is split by its sequences where the batch divides by N (every
+rank steps batch / N sequences with the whole weights and their KV cache, nothing exchanged:
+above a few rows the step is bound by per-sequence work, not by the weight bytes), else by its
+weights (the linears sharded on their output rows, q/k/v by head so that the KV cache and
+attention stay local, the slices exchanged over NVLink); `--decode-sharding` forces one, and
+`also` carries the weight-sharded step beside the sequence-sharded one. `value` is tokens/s of
 the whole job with everything resident in HBM, the step replayed from one CUDA graph; `e2e` is
 the same through the public call with token ids copied in from pinned host memory and the next
 ids copied back inside the timed region; `roofline` is this rank's packed weights + tables + KV
@@ -17,8 +22,9 @@ reference's fused dequantize-and-dot loop timed on the host cores on a bounded s
 at M = 1 (GB/s of weight bytes) and M = 2048 (TFLOP/s) in int4 / int8 at both Llama MLP shapes,
 MXFP4 at M = 1 / 512 / 4096, the Mixtral-shaped expert block, the decode step at batch 1 and 16
 -- each with its own roofline; at N > 1 the decode step at the other batches, the
-expert-parallel expert block (rows exchanged through peer memory), and `parity`: the sharded decode step and the
-expert-parallel block checked at small shapes against their references before anything is timed.
+expert-parallel expert block (rows exchanged through peer memory), and `parity`: the decode step
+in both splits and the expert-parallel block checked at small shapes against their references
+before anything is timed.
 """
 
 from __future__ import annotations
