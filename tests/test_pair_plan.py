@@ -110,3 +110,18 @@ def test_weighted_sum_matches_the_dense_form():
         p = int(order[r])
         want[p // K] += wts[p // K, p % K] * y[r]
     assert torch.allclose(got, want, atol=1e-6)
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("t,d,e,f,k", [(1, 64, 4, 64, 2), (1, 64, 8, 128, 4), (3, 128, 4, 64, 1), (7, 64, 8, 64, 3), (2, 64, 4, 192, 2)])
+def test_regions_at_other_sizes_one_token_and_one_choice_included(t, d, e, f, k):
+    """A single token (every decode step: the token axis is a unit axis, which a broadcast must
+    not be mistaken for), a single choice per token, more experts than tokens."""
+    for text, args in ((moe_program_glu_bias(t, d, e, f, k), moe_glu_bias_inputs(t, d, e, f, seed=t)),
+                       (moe_program_gelu_quant(t, d, e, f, 32, k), moe_gelu_quant_inputs(t, d, e, f, 32, seed=t))):
+        it, st, b, got, want = _run_region(text, args)
+        assert (b.T, b.K, b.E) == (t, k, e)
+        err = (got.float() - want.float()).abs().max().item()
+        assert err <= 2e-2 * max(want.float().abs().max().item(), 1e-6), (t, d, e, f, k, err)
