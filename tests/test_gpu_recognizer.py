@@ -114,7 +114,7 @@ def test_general_expert_regions_run_over_the_routed_pairs():
     a per-expert gain on `qmm_ragged_dot`. Same gate as every fused program."""
     from metaljax_b200 import moe, moe_recognizer
     from programs import moe_glu_bias_inputs, moe_gelu_quant_inputs, moe_program_glu_bias, moe_program_gelu_quant
-    for t, d, e, f in ((6, 64, 4, 64), (48, 128, 8, 192)):
+    for t, d, e, f in ((6, 64, 4, 64), (48, 128, 8, 192), (1, 64, 4, 64)):
         moe.reset_stats()
         it = _gate(moe_program_glu_bias(t, d, e, f), moe_glu_bias_inputs(t, d, e, f, seed=t, device=DEV))
         st = it._qmm
