@@ -54,9 +54,11 @@ WORKLOADS = {
     "decode_int4_g64_m1_4096x4096": (1, 4096, 4096, 64, 4, "affine"),
     "decode_int4_g64_m1_28672x4096": (1, 4096, 28672, 64, 4, "affine"),
     "decode_int4_g64_m1_65536x4096": (1, 4096, 65536, 64, 4, "affine"),
+    "decode_int4_g64_m8_28672x4096": (8, 4096, 28672, 64, 4, "affine"),     # what a rank runs with 64 sequences on 8 GPUs
     "decode_mxfp4_m1_5760x2880": (1, 2880, 5760, 32, 4, "mxfp4"),
 }
 L2_BYTES = 126 * 1024 * 1024
+STREAM_ROWS = 16      # up to this many rows a product is a weight stream (GB/s against HBM), above it a GEMM (TFLOP/s)
 # Whole decode steps of the Llama-3-8B-shaped model: name -> batch. The weights are sharded on N
 # over the ranks, so these scale strongly.
 DECODE_STEPS = {"decode_llama3_8b_b1": 1, "decode_llama3_8b_b8": 8, "decode_llama3_8b_b16": 16, "decode_llama3_8b_b32": 32,
@@ -307,8 +309,8 @@ def cpu_baseline_of(name):
     m = WORKLOADS[name][0]
     _, weight_bytes, _ = work_of(name)
     cb = cpu_qmm_sample(name)
-    val = cb["flops"] / cb["seconds_per_sample"] / 1e12 if m > 1 else weight_bytes / cb["seconds_per_sample"] / 1e9
-    return {"value": val, "unit": "TFLOP/s" if m > 1 else "GB/s", "cores": cb["cores"], "kind": "port",
+    val = cb["flops"] / cb["seconds_per_sample"] / 1e12 if m > STREAM_ROWS else weight_bytes / cb["seconds_per_sample"] / 1e9
+    return {"value": val, "unit": "TFLOP/s" if m > STREAM_ROWS else "GB/s", "cores": cb["cores"], "kind": "port",
             "sample": f"first {cb['rows']} of {m} rows of x against the whole weight, "
                       f"{cb['reps']} calls in {cb['seconds_per_sample'] * cb['reps']:.1f} s"}
 
@@ -369,7 +371,7 @@ def metric_of(name):
     if name in MOE_BLOCKS:
         return "moe_block_tflops", "TFLOP/s"
     m = WORKLOADS[name][0]
-    return ("qmm_tflops_m%d" % m, "TFLOP/s") if m > 1 else ("qmm_weight_gbs_m1", "GB/s")
+    return ("qmm_tflops_m%d" % m, "TFLOP/s") if m > STREAM_ROWS else ("qmm_weight_gbs_m%d" % m, "GB/s")
 
 
 def run_reference(args, rank):
@@ -395,7 +397,7 @@ def run_reference(args, rank):
         ms = 2.0 * t * k * 3 * d * f / (value * 1e12) * 1e3
     else:
         flops, wb, _ = work_of(name)
-        ms = (flops / (value * 1e12) if WORKLOADS[name][0] > 1 else wb / (value * 1e9)) * 1e3
+        ms = (flops / (value * 1e12) if WORKLOADS[name][0] > STREAM_ROWS else wb / (value * 1e9)) * 1e3
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -421,7 +423,7 @@ def measure_qmm(name, args, torch, qmm, _lib, dist, device):
         x, w, s, b, y = data[i % sets]
         qmm.quantized_matmul(x, w, s, b, out=y, **kw)
 
-    steps = args.steps if m > 1 else args.steps * 50
+    steps = args.steps if m > STREAM_ROWS else args.steps * 50
     warm = max(args.warmup, 3)
     n0 = _lib.launch_count()
     ms = time_device(step, steps, warm, torch, dist)
@@ -429,7 +431,7 @@ def measure_qmm(name, args, torch, qmm, _lib, dist, device):
     # The same calls replayed from one CUDA graph (every node on a different weight set): a
     # decode call is launch-latency sized, and with several ranks on one host the per-call
     # Python time of eight processes can exceed a 0.26 ms step. The smaller time is reported.
-    gsteps = steps if m > 1 else sets
+    gsteps = steps if m > STREAM_ROWS else sets
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -438,7 +440,7 @@ def measure_qmm(name, args, torch, qmm, _lib, dist, device):
             for i in range(gsteps):
                 step(warm + i)
     torch.cuda.current_stream().wait_stream(side)
-    reps = 1 if m > 1 else max(5, steps // gsteps)
+    reps = 1 if m > STREAM_ROWS else max(5, steps // gsteps)
     gms = time_device(lambda i: graph.replay(), reps, 3, torch, dist) / (reps * gsteps)
     timed = "stream launches"
     ms_step = ms / steps
@@ -476,7 +478,7 @@ def qmm_line(name, args, torch, dist, device, world, pk):
     ms_step, e2e_ms = max_over_ranks([res["ms_per_step"], res["e2e_ms_per_step"]], torch, dist, device)
     flops, weight_bytes, total_bytes = res["flops"], res["weight_bytes"], res["total_bytes"]
     metric, unit = metric_of(name)
-    if m > 1:
+    if m > STREAM_ROWS:
         value = world * flops / (ms_step * 1e-3) / 1e12
         e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
         achieved = flops / (res["ms_per_step"] * 1e-3) / 1e12
