@@ -843,7 +843,7 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   const int nt = p.M <= 8 ? 1 : 2;
   // Tables are staged in passes of 64 or 128 groups (one or two batches of table loads).
   // Preference order: (1) the activations of all of K stay in shared memory, two CTAs per SM,
-  // ring of 4 then of 2 boxes per warp, passes of 128 then of 64 groups; (2) the activations are restaged pass by pass, a pass
+  // ring of 4, then 2, then 1 box per warp, passes of 128 then of 64 groups; (2) the activations are restaged pass by pass, a pass
   // being a multiple of 8 boxes (one per warp), two CTAs per SM; (3) the same with one CTA
   // per SM and its larger shared memory; (4) whatever pass fits.
   const int kround = static_cast<int>((p.K + boxk - 1) / boxk * boxk);
@@ -860,7 +860,12 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
     return smem_bytes(gp, nt, group_k, mx, 1 << ring_shift);
   };
   bool done = false;
-  for (int ring_shift = 2; !done && ring_shift >= 1; --ring_shift)
+  // (down to a single box per warp: at 8 rows and K = 4096 that keeps the activations resident at
+  // two CTAs per SM -- one pass over K instead of two restaged ones, 1301 -> ~940 instructions per
+  // warp-tile -- and sixteen warps per SM still cover the box round trip; QMM_GEMV_RING_MIN=1
+  // restores the two-box floor)
+  static const int ring_min = [] { const char* e = getenv("QMM_GEMV_RING_MIN"); return e ? atoi(e) : 0; }();
+  for (int ring_shift = 2; !done && ring_shift >= ring_min; --ring_shift)
     for (int mult = 2; !done && mult >= 1; --mult) {       // passes of 128, then of 64 groups
       const int want = mult * pass_k;
       done = configure(kround, kround < want ? kround : want, ring_shift, 2) <= kSmemBudget;

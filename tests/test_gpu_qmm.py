@@ -421,6 +421,28 @@ def test_decode_kernel_long_k_and_wide_batch():
         assert O.rel_err(to_numpy(y), O.qmm_exact(x, w, s, b, 64, 4)) <= 2e-5
 
 
+@pytest.mark.parametrize("m,k,n,gs,bits,mode", [(8, 4096, 1000, 64, 4, "affine"), (7, 4096, 272, 64, 4, "affine"),
+                                                (8, 4096, 48, 128, 8, "affine"), (8, 4096, 80, 32, 4, "mxfp4"),
+                                                (4, 8192, 64, 64, 4, "affine"), (8, 3584, 160, 32, 4, "affine")])
+def test_decode_kernel_with_a_single_box_ring(m, k, n, gs, bits, mode):
+    """Rows and K at which the activations only stay resident (two CTAs per SM) with ONE box per
+    warp in flight: the ring's slot and parity arithmetic at depth one, several tiles per CTA."""
+    rng = np.random.default_rng(m * 31 + n)
+    x = activations(rng, (m, k))
+    if mode == "mxfp4":
+        codes = rng.integers(0, 16, size=(n, k), dtype=np.uint8)
+        w = O.pack_codes(codes, 4)
+        s = rng.integers(119, 128, size=(n, k // 32), dtype=np.uint8)
+        b = None
+    else:
+        _, w, s, b = affine_case(rng, n, k, gs, bits, "bf16")
+    with _lib.force_route("gemv"):
+        y = qmm.quantized_matmul(to_torch(x, DEV), to_torch(w, DEV), to_torch(s, DEV), None if b is None else to_torch(b, DEV),
+                                 group_size=gs, bits=bits, mode=mode, out_dtype=torch.float32)
+    assert O.rel_err(to_numpy(y), O.qmm_exact(x, w, s, b, gs, bits, mode)) <= (2e-5 if mode == "affine" and bits == 4 else 2e-3)
+    assert _lib.poll_status() == 0
+
+
 # ---- benchmark configurations at full size ---------------------------------------------------
 
 
