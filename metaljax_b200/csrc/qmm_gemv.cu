@@ -874,7 +874,8 @@ int launch_gemv(const qmm_problem& p, cudaStream_t stream) {
   for (int ctas = 2; !done && ctas >= 1; --ctas) {
     const size_t budget = ctas == 2 ? kSmemBudget : kSmemBudgetOne;
     for (int kc = kc_res / (8 * boxk) * (8 * boxk); !done && kc >= 8 * boxk; kc -= 8 * boxk)
-      done = configure(kc, kc, 2, ctas) <= budget || configure(kc, kc, 1, ctas) <= budget;
+      done = configure(kc, kc, 2, ctas) <= budget || configure(kc, kc, 1, ctas) <= budget ||
+             (ring_min == 0 && nt == 1 && configure(kc, kc, 0, ctas) <= budget);     // (up to 8 rows: fewer, longer passes win)
   }
   for (int kc = kc_res; !done && kc >= boxk; kc -= boxk) done = configure(kc, kc, 1, 1) <= kSmemBudgetOne;
   if (!done) return fail(QMM_ERR_UNSUPPORTED, "decode kernel: no staging plan fits shared memory");

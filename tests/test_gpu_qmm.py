@@ -423,7 +423,8 @@ def test_decode_kernel_long_k_and_wide_batch():
 
 @pytest.mark.parametrize("m,k,n,gs,bits,mode", [(8, 4096, 1000, 64, 4, "affine"), (7, 4096, 272, 64, 4, "affine"),
                                                 (8, 4096, 48, 128, 8, "affine"), (8, 4096, 80, 32, 4, "mxfp4"),
-                                                (4, 8192, 64, 64, 4, "affine"), (8, 3584, 160, 32, 4, "affine")])
+                                                (4, 8192, 64, 64, 4, "affine"), (8, 3584, 160, 32, 4, "affine"),
+                                                (8, 14336, 336, 64, 4, "affine")])        # restaged passes with one box
 def test_decode_kernel_with_a_single_box_ring(m, k, n, gs, bits, mode):
     """Rows and K at which the activations only stay resident (two CTAs per SM) with ONE box per
     warp in flight: the ring's slot and parity arithmetic at depth one, several tiles per CTA."""
